@@ -1,0 +1,228 @@
+/*
+ * llmopt_cuda.h — C ABI of libllmopt_cuda.so, the B200 (sm_100a) replacement
+ * for the native layer behind llmopt's `Metal_native` module.
+ *
+ * Every entry point below stands in for one `caml_llmopt_metal_*` /
+ * `caml_llmopt_ring_*` / `caml_llmopt_prebaked_*` primitive of the reference
+ * (native/ocaml_metal_stubs.m, bound in lib/metal_native.ml:8-124).  The
+ * calling convention of a kernel is the reference's: a kernel NAME, the buffers
+ * in binding order, the packed little-endian parameter bytes of
+ * lib/metal_parameters.ml, and a Metal-style grid in threads plus threadgroup
+ * size.  The CUDA launchers size their own grids; the Metal grid is accepted
+ * and ignored.
+ *
+ * Conventions
+ *   - plain C types only: opaque handles, pointers, sizes;
+ *   - every function that can fail returns an int: 0 success,
+ *     LLMOPT_CUDA_FAILURE (reference: `Failure msg`) or
+ *     LLMOPT_CUDA_INVALID_ARGUMENT (reference: `Invalid_argument msg`); the
+ *     message is kept per thread and read with llmopt_cuda_last_error();
+ *   - nothing here aborts or exits the process;
+ *   - handles are reference counted; *_release drops one reference, views keep
+ *     their parent alive (native/ocaml_metal_stubs.m:945-970);
+ *   - one context = one device + one stream; calls on one context must come
+ *     from one thread at a time (the OCaml runtime lock gives that), the ring
+ *     worker is the only internal thread.
+ */
+#ifndef LLMOPT_CUDA_H
+#define LLMOPT_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Only the entry points declared here are exported by the shared library. */
+#pragma GCC visibility push(default)
+
+#define LLMOPT_CUDA_OK 0
+#define LLMOPT_CUDA_FAILURE 1
+#define LLMOPT_CUDA_INVALID_ARGUMENT 2
+
+typedef struct llmopt_cuda_context llmopt_cuda_context;
+typedef struct llmopt_cuda_library llmopt_cuda_library;
+typedef struct llmopt_cuda_buffer llmopt_cuda_buffer;
+typedef struct llmopt_cuda_batch llmopt_cuda_batch;
+typedef struct llmopt_cuda_prebaked llmopt_cuda_prebaked;
+typedef struct llmopt_cuda_ring llmopt_cuda_ring;
+
+/* One recorded dispatch: the tuple (name, buffers, parameters, grid, group,
+ * barrier_before) of Metal_native.Batch.dispatch_item (lib/metal_native.mli:40-51). */
+typedef struct llmopt_cuda_dispatch_record {
+  const char* name;
+  llmopt_cuda_buffer* const* buffers;
+  int buffer_count;          /* <= 16 */
+  const void* parameters;
+  size_t parameter_bytes;    /* <= 256 */
+  int grid[3];
+  int group[3];
+  int barrier_before;
+} llmopt_cuda_dispatch_record;
+
+/* Message of the last failed call on this thread ("" if none). */
+const char* llmopt_cuda_last_error(void);
+
+/* ---- context, library ------------------------------------------------------ */
+
+/* caml_llmopt_metal_create_context (native/ocaml_metal_stubs.m:410-475).
+ * `device` < 0 selects the current CUDA device. */
+int llmopt_cuda_create_context(int device, llmopt_cuda_context** out);
+void llmopt_cuda_release_context(llmopt_cuda_context* context);
+/* caml_llmopt_metal_device_name */
+const char* llmopt_cuda_device_name(llmopt_cuda_context* context);
+/* caml_llmopt_metal_load_library (:614-700): opens the built-in kernel registry;
+ * `path` is accepted for signature compatibility and not read. */
+int llmopt_cuda_load_library(llmopt_cuda_context* context, const char* path, llmopt_cuda_library** out);
+void llmopt_cuda_release_library(llmopt_cuda_library* library);
+/* caml_llmopt_metal_has_function: 1 if `name` resolves to a launcher, else 0. */
+int llmopt_cuda_has_function(llmopt_cuda_library* library, const char* name);
+/* caml_llmopt_metal_preload_pipeline: fails if the name does not resolve. */
+int llmopt_cuda_preload_pipeline(llmopt_cuda_library* library, const char* name);
+/* Number of kernel names in the registry and the i-th name (for package validation). */
+int llmopt_cuda_function_count(llmopt_cuda_library* library);
+const char* llmopt_cuda_function_name(llmopt_cuda_library* library, int index);
+/* Registers `alias` (for example a digest-named epilogue kernel,
+ * lib/epilogue.ml:217-229) as another name of the existing kernel `target`. */
+int llmopt_cuda_register_alias(llmopt_cuda_library* library, const char* alias, const char* target);
+
+/* ---- buffers ---------------------------------------------------------------- */
+
+/* caml_llmopt_metal_buffer_of_bytes (:702-724) */
+int llmopt_cuda_buffer_of_bytes(llmopt_cuda_context* context, const void* bytes, size_t length,
+                                llmopt_cuda_buffer** out);
+/* caml_llmopt_metal_create_buffer (:726-745): zero filled; length <= 0 gives 16 bytes. */
+int llmopt_cuda_create_buffer(llmopt_cuda_context* context, int64_t length, llmopt_cuda_buffer** out);
+/* caml_llmopt_metal_map_file (:747-785): the whole file as one device buffer. */
+int llmopt_cuda_map_file(llmopt_cuda_context* context, const char* path, llmopt_cuda_buffer** out);
+/* caml_llmopt_metal_buffer_view (:945-970): bounds checked, shares storage. */
+int llmopt_cuda_buffer_view(llmopt_cuda_buffer* parent, int64_t offset, int64_t length, llmopt_cuda_buffer** out);
+void llmopt_cuda_release_buffer(llmopt_cuda_buffer* buffer);
+/* caml_llmopt_metal_buffer_length */
+size_t llmopt_cuda_buffer_length(llmopt_cuda_buffer* buffer);
+/* caml_llmopt_metal_buffer_contents: copies the whole buffer to `destination`
+ * (`capacity` >= buffer length) after all queued work on the context finished. */
+int llmopt_cuda_buffer_contents(llmopt_cuda_buffer* buffer, void* destination, size_t capacity);
+/* caml_llmopt_metal_buffer_argmax_f16 (:787-810): argmax of the LAST row of
+ * `vocabulary` halves, first maximum wins. */
+int llmopt_cuda_buffer_argmax_f16(llmopt_cuda_buffer* buffer, int64_t vocabulary, int64_t* out);
+/* caml_llmopt_metal_buffer_copy: equal lengths required. */
+int llmopt_cuda_buffer_copy(llmopt_cuda_buffer* source, llmopt_cuda_buffer* destination);
+/* caml_llmopt_metal_buffer_set_int64 / _set_u32_array: host writes, ordered
+ * after the work already queued on the context's stream. */
+int llmopt_cuda_buffer_set_int64(llmopt_cuda_buffer* buffer, int64_t offset, int64_t value);
+int llmopt_cuda_buffer_set_u32_array(llmopt_cuda_buffer* buffer, int64_t offset, const uint32_t* values,
+                                     size_t count);
+/* Host write of arbitrary bytes (Metal buffers are host-visible; CUDA needs a copy). */
+int llmopt_cuda_buffer_write(llmopt_cuda_buffer* buffer, int64_t offset, const void* bytes, size_t length);
+/* Raw device address of the buffer (for callers that own other CUDA code). */
+void* llmopt_cuda_buffer_device_pointer(llmopt_cuda_buffer* buffer);
+
+/* ---- dispatch ---------------------------------------------------------------- */
+
+/* caml_llmopt_metal_dispatch (:1384-1454): runs one kernel and waits for it. */
+int llmopt_cuda_dispatch(llmopt_cuda_library* library, const llmopt_cuda_dispatch_record* record);
+
+/* caml_llmopt_metal_begin_batch .. abort_batch (:1132-1382). A batch defers its
+ * dispatches until commit, as a Metal command buffer does; abort drops them. */
+int llmopt_cuda_begin_batch(llmopt_cuda_library* library, llmopt_cuda_batch** out);
+int llmopt_cuda_batch_dispatch(llmopt_cuda_batch* batch, llmopt_cuda_library* library,
+                               const llmopt_cuda_dispatch_record* record);
+int llmopt_cuda_batch_dispatch_all(llmopt_cuda_batch* batch, llmopt_cuda_library* library,
+                                   const llmopt_cuda_dispatch_record* records, size_t count);
+/* rejects overlapping ranges of one allocation and unequal lengths */
+int llmopt_cuda_batch_copy(llmopt_cuda_batch* batch, llmopt_cuda_buffer* source, llmopt_cuda_buffer* destination);
+int llmopt_cuda_batch_barrier(llmopt_cuda_batch* batch); /* no-op: one in-order stream */
+int llmopt_cuda_commit_batch(llmopt_cuda_batch* batch);       /* runs everything, blocks */
+int llmopt_cuda_commit_batch_async(llmopt_cuda_batch* batch); /* runs everything, returns */
+int llmopt_cuda_abort_batch(llmopt_cuda_batch* batch);
+void llmopt_cuda_release_batch(llmopt_cuda_batch* batch);
+/* Waits for all work queued on the context. */
+int llmopt_cuda_synchronize(llmopt_cuda_context* context);
+
+/* ---- prebaked per-token plan -------------------------------------------------- */
+
+/* A row binding: before every replay, row `past_tokens` of `table` (rows of
+ * `row_bytes`) is copied on the device into `destination`. It replaces the host
+ * writes the reference engine does between tokens (RoPE row, cache slot). */
+typedef struct llmopt_cuda_row_binding {
+  llmopt_cuda_buffer* destination;
+  llmopt_cuda_buffer* table;
+  size_t row_bytes;
+} llmopt_cuda_row_binding;
+
+/* caml_llmopt_prebaked_create (:1879-2135): records are captured once into a CUDA
+ * graph. Records whose name starts with "llmopt_attention_q8_paged_" read
+ * past_tokens from a device cell instead of parameter byte 12; the record named
+ * "llmopt_cache_pack_checkpoint_q8_simd" reads `checkpoint` instead of byte 0. */
+int llmopt_cuda_prebaked_create(llmopt_cuda_library* library, const llmopt_cuda_dispatch_record* records,
+                                size_t count, llmopt_cuda_buffer* token_buffer, llmopt_cuda_buffer* output_buffer,
+                                llmopt_cuda_prebaked** out);
+int llmopt_cuda_prebaked_create_bound(llmopt_cuda_library* library, const llmopt_cuda_dispatch_record* records,
+                                      size_t count, llmopt_cuda_buffer* token_buffer,
+                                      llmopt_cuda_buffer* output_buffer, const llmopt_cuda_row_binding* bindings,
+                                      size_t binding_count, llmopt_cuda_prebaked** out);
+/* caml_llmopt_prebaked_execute (:2167-2563): writes the token id (int64) into the
+ * token buffer, publishes past_tokens / checkpoint, replays, waits, returns the
+ * int32 at the start of the output buffer. */
+int llmopt_cuda_prebaked_execute(llmopt_cuda_prebaked* plan, int64_t token, int32_t past_tokens,
+                                 int32_t checkpoint, int32_t* next_token);
+/* Device-chained decode (the ring worker's llmopt_chain_token_id path,
+ * native/ocaml_metal_stubs.m:1568-1577): `steps` replays back to back, each
+ * feeding its output token to the next and advancing past_tokens by one, with no
+ * host round trip in between. `tokens_out` receives `steps` ids; `elapsed_ms`
+ * (may be NULL) the device time of the replays measured with CUDA events. */
+int llmopt_cuda_prebaked_execute_chained(llmopt_cuda_prebaked* plan, int64_t first_token, int32_t past_tokens,
+                                         int32_t checkpoint, int32_t steps, int32_t* tokens_out,
+                                         float* elapsed_ms);
+/* Number of kernel nodes in the captured graph. */
+int llmopt_cuda_prebaked_kernel_count(llmopt_cuda_prebaked* plan);
+void llmopt_cuda_release_prebaked(llmopt_cuda_prebaked* plan);
+
+/* ---- ring queue ------------------------------------------------------------------ */
+
+/* caml_llmopt_ring_* (:1465-1877): submission / completion queues of 256 entries
+ * served by one worker thread that replays a prebaked plan per request. */
+int llmopt_cuda_ring_create(llmopt_cuda_ring** out);
+int llmopt_cuda_ring_start_worker(llmopt_cuda_ring* ring, llmopt_cuda_library* library,
+                                  const llmopt_cuda_dispatch_record* records, size_t count,
+                                  llmopt_cuda_buffer* token_buffer, llmopt_cuda_buffer* output_buffer);
+/* `accepted` = 0 when the submission queue is full. flags == 2 stops the worker. */
+int llmopt_cuda_ring_submit(llmopt_cuda_ring* ring, int64_t request_id, int64_t token, int32_t past_tokens,
+                            int32_t flags, int* accepted);
+int llmopt_cuda_ring_wait_completion(llmopt_cuda_ring* ring, int64_t* request_id, int32_t* token, int32_t* status);
+int llmopt_cuda_ring_poll_completion(llmopt_cuda_ring* ring, int* available, int64_t* request_id, int32_t* token,
+                                     int32_t* status);
+int llmopt_cuda_ring_destroy(llmopt_cuda_ring* ring);
+
+/* ---- host-side helpers ------------------------------------------------------------ */
+
+/* caml_llmopt_f16_argmax (:2565-2579): argmax over `count` halves in host memory. */
+int64_t llmopt_cuda_f16_argmax(const void* halves, size_t count);
+
+/* ---- second boundary: the Python single-op entry ------------------------------------ */
+
+/* native/metal_runtime.cpp:58-136 `w4a16_linear(input, packed_weight, scale, bias)`
+ * on raw device pointers: input [m,k] f16, packed [n,k/2] u8, scale [n,k/64] f16,
+ * bias [n] f16 or NULL, output [m,n] f16; runs on `stream` (a cudaStream_t, may
+ * be NULL for the default stream) and does not synchronise. */
+int llmopt_cuda_w4a16_linear(llmopt_cuda_context* context, const void* input, const void* packed_weight,
+                             const void* scale, const void* bias, void* output, int64_t m, int64_t n, int64_t k,
+                             void* stream);
+
+/* ---- measurement ---------------------------------------------------------------------- */
+
+/* Average device time in milliseconds of one dispatch, measured with CUDA
+ * events on the context's stream over `iterations` launches after `warmup`;
+ * with flush_l2 != 0 a buffer larger than L2 is rewritten before every timed
+ * launch (outside the timed interval). */
+int llmopt_cuda_time_dispatch(llmopt_cuda_library* library, const llmopt_cuda_dispatch_record* record, int warmup,
+                              int iterations, int flush_l2, float* average_ms);
+
+#pragma GCC visibility pop
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLMOPT_CUDA_H */

@@ -1,0 +1,227 @@
+// Grouped-Q8 cache codec for sm_100a: attention K/V pack / unpack and recurrent
+// checkpoint pack / unpack.  Bit-exact restatement of
+//   llmopt_cache_pack_attention_q8{,_simd,_pair_simd}   lib/metal_cache_source.ml:46-182
+//   llmopt_cache_unpack_attention_q8{,_vec4}            lib/metal_cache_source.ml:184-243
+//   llmopt_cache_{pack,unpack}_checkpoint_q8{,_simd,_vec4}  lib/metal_cache_source.ml:245-347
+// Integer results and stored scales must equal the reference byte for byte:
+// scale = half(max == 0 ? 1 : max / 127) (fp32 division), q = clamp(rint(x /
+// float(scale)), -127, 127) with IEEE division and round-half-even.
+//
+// One warp owns one quantisation group (the reference's *_simd mapping); lanes
+// stride the group so any group size works.  HBM-bound and tiny: 2 bytes read,
+// 1 + 2/G written per element.
+#include "common.cuh"
+
+namespace llmopt {
+namespace {
+
+struct AttentionCacheParams {  // lib/metal_cache_source.ml:9-20
+  uint32_t items, segment_offset, heads, head_dim, group_size, token_elements, token_groups,
+      token_stride, source_items, source_offset;
+};
+struct AttentionCachePairParams {  // lib/metal_cache_source.ml:22-34
+  uint32_t items, key_segment_offset, value_segment_offset, heads, head_dim, group_size,
+      token_elements, token_groups, token_stride, source_items, source_offset;
+};
+struct CheckpointCacheParams {  // lib/metal_cache_source.ml:36-44
+  uint32_t checkpoint, layer, layer_elements, group_size, checkpoint_elements, checkpoint_groups,
+      checkpoint_stride;
+};
+
+__device__ __forceinline__ void quantize_group(const __half* __restrict__ source, uint32_t group_size,
+                                               int8_t* __restrict__ values, __half* __restrict__ scale_out,
+                                               uint32_t lane) {
+  float maximum = 0.0f;
+  for (uint32_t index = lane; index < group_size; index += 32)
+    maximum = fmaxf(maximum, fabsf(__half2float(source[index])));
+  maximum = warp_max(maximum);
+  const __half stored = __float2half_rn(maximum == 0.0f ? 1.0f : __fdiv_rn(maximum, 127.0f));
+  const float scale = __half2float(stored);
+  for (uint32_t index = lane; index < group_size; index += 32) {
+    int quantized = (int)rintf(__fdiv_rn(__half2float(source[index]), scale));
+    quantized = max(-127, min(127, quantized));
+    values[index] = (int8_t)quantized;
+  }
+  if (lane == 0) *scale_out = stored;
+}
+
+__global__ void pack_attention_kernel(const __half* __restrict__ source, const uint32_t* __restrict__ slots,
+                                      uint8_t* __restrict__ pool, AttentionCacheParams p) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t logical_group = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t groups_per_head = p.head_dim / p.group_size;
+  const uint32_t segment_groups = p.heads * groups_per_head;
+  if (logical_group >= p.items * segment_groups) return;
+  const uint32_t item = logical_group / segment_groups;
+  const uint32_t local_group = logical_group - item * segment_groups;
+  const uint32_t head = local_group / groups_per_head;
+  const uint32_t group_in_head = local_group - head * groups_per_head;
+  const size_t source_base = ((size_t)head * p.source_items + p.source_offset + item) * p.head_dim +
+                             (size_t)group_in_head * p.group_size;
+  const size_t slot_base = (size_t)slots[item] * p.token_stride;
+  int8_t* values = reinterpret_cast<int8_t*>(pool + slot_base);
+  __half* scales = reinterpret_cast<__half*>(pool + slot_base + p.token_elements);
+  const uint32_t value_base = p.segment_offset + head * p.head_dim + group_in_head * p.group_size;
+  quantize_group(source + source_base, p.group_size, values + value_base,
+                 scales + p.segment_offset / p.group_size + local_group, lane);
+}
+
+__global__ void pack_attention_pair_kernel(const __half* __restrict__ key_source,
+                                           const __half* __restrict__ value_source,
+                                           const uint32_t* __restrict__ slots, uint8_t* __restrict__ pool,
+                                           AttentionCachePairParams p) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t logical_group = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t groups_per_head = p.head_dim / p.group_size;
+  const uint32_t segment_groups = p.heads * groups_per_head;
+  if (logical_group >= p.items * segment_groups) return;
+  const uint32_t item = logical_group / segment_groups;
+  const uint32_t local_group = logical_group - item * segment_groups;
+  const uint32_t head = local_group / groups_per_head;
+  const uint32_t group_in_head = local_group - head * groups_per_head;
+  const size_t source_base = ((size_t)head * p.source_items + p.source_offset + item) * p.head_dim +
+                             (size_t)group_in_head * p.group_size;
+  const size_t slot_base = (size_t)slots[item] * p.token_stride;
+  int8_t* values = reinterpret_cast<int8_t*>(pool + slot_base);
+  __half* scales = reinterpret_cast<__half*>(pool + slot_base + p.token_elements);
+  const uint32_t local_offset = head * p.head_dim + group_in_head * p.group_size;
+  quantize_group(key_source + source_base, p.group_size, values + p.key_segment_offset + local_offset,
+                 scales + p.key_segment_offset / p.group_size + local_group, lane);
+  quantize_group(value_source + source_base, p.group_size, values + p.value_segment_offset + local_offset,
+                 scales + p.value_segment_offset / p.group_size + local_group, lane);
+}
+
+__global__ void unpack_attention_kernel(const uint8_t* __restrict__ pool, const uint32_t* __restrict__ slots,
+                                        __half* __restrict__ destination, AttentionCacheParams p) {
+  const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+  const uint32_t segment_elements = p.heads * p.head_dim;
+  if (gid >= p.items * segment_elements) return;
+  const uint32_t item = gid / segment_elements;
+  const uint32_t local = gid - item * segment_elements;
+  const uint32_t head = local / p.head_dim;
+  const uint32_t within_head = local - head * p.head_dim;
+  const uint32_t groups_per_head = p.head_dim / p.group_size;
+  const uint32_t local_group = head * groups_per_head + within_head / p.group_size;
+  const size_t slot_base = (size_t)slots[item] * p.token_stride;
+  const int8_t* values = reinterpret_cast<const int8_t*>(pool + slot_base);
+  const __half* scales = reinterpret_cast<const __half*>(pool + slot_base + p.token_elements);
+  const size_t destination_index = ((size_t)head * p.items + item) * p.head_dim + within_head;
+  destination[destination_index] = __float2half_rn(
+      (float)values[p.segment_offset + local] *
+      __half2float(scales[p.segment_offset / p.group_size + local_group]));
+}
+
+__global__ void pack_checkpoint_kernel(const __half* __restrict__ source, uint8_t* __restrict__ pool,
+                                       CheckpointCacheParams p, const uint32_t* __restrict__ checkpoint_cell) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t logical_group = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t layer_groups = p.layer_elements / p.group_size;
+  if (logical_group >= layer_groups) return;
+  const uint32_t checkpoint = checkpoint_cell ? *checkpoint_cell : p.checkpoint;
+  const size_t base = (size_t)checkpoint * p.checkpoint_stride;
+  int8_t* values = reinterpret_cast<int8_t*>(pool + base);
+  __half* scales = reinterpret_cast<__half*>(pool + base + p.checkpoint_elements);
+  quantize_group(source + (size_t)logical_group * p.group_size, p.group_size,
+                 values + (size_t)p.layer * p.layer_elements + (size_t)logical_group * p.group_size,
+                 scales + (size_t)p.layer * layer_groups + logical_group, lane);
+}
+
+__global__ void unpack_checkpoint_kernel(const uint8_t* __restrict__ pool, __half* __restrict__ destination,
+                                         CheckpointCacheParams p) {
+  const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= p.layer_elements) return;
+  const size_t base = (size_t)p.checkpoint * p.checkpoint_stride;
+  const int8_t* values = reinterpret_cast<const int8_t*>(pool + base);
+  const __half* scales = reinterpret_cast<const __half*>(pool + base + p.checkpoint_elements);
+  const uint32_t layer_groups = p.layer_elements / p.group_size;
+  destination[gid] = __float2half_rn((float)values[(size_t)p.layer * p.layer_elements + gid] *
+                                     __half2float(scales[(size_t)p.layer * layer_groups + gid / p.group_size]));
+}
+
+template <typename P>
+bool read_params(const KernelArgs& args, P* out) {
+  if (args.param_bytes != sizeof(P)) return false;
+  memcpy(out, args.params, sizeof(P));
+  return true;
+}
+
+bool valid_geometry(uint32_t head_dim, uint32_t group_size) {
+  return group_size > 0 && head_dim > 0 && head_dim % group_size == 0;
+}
+
+}  // namespace
+
+// Buffers: [source f16, slots u32, pool u8]; params 40 bytes (lib/metal_cache.ml:315-318).
+int launch_cache_pack_attention_q8(const KernelArgs& args) {
+  AttentionCacheParams p;
+  LLMOPT_REQUIRE(args.buffer_count == 3, "expects buffers [source, slots, pool]");
+  LLMOPT_REQUIRE(read_params(args, &p), "expects 40 parameter bytes");
+  LLMOPT_REQUIRE(valid_geometry(p.head_dim, p.group_size), "head_dim must be a multiple of group_size");
+  LLMOPT_REQUIRE(args.lengths[1] >= (size_t)p.items * 4, "slots buffer is shorter than items");
+  LLMOPT_REQUIRE(args.lengths[0] >= ((size_t)(p.heads - 1) * p.source_items + p.source_offset + p.items) * p.head_dim * 2,
+                 "source buffer is shorter than the packed range");
+  const uint32_t groups = p.items * p.heads * (p.head_dim / p.group_size);
+  if (groups == 0) return 0;
+  pack_attention_kernel<<<(groups + 7) / 8, 256, 0, args.stream>>>(
+      (const __half*)args.buffers[0], (const uint32_t*)args.buffers[1], (uint8_t*)args.buffers[2], p);
+  return check_launch(args);
+}
+
+// Buffers: [key source, value source, slots, pool]; params 44 bytes (lib/metal_cache.ml:344-347).
+int launch_cache_pack_attention_q8_pair(const KernelArgs& args) {
+  AttentionCachePairParams p;
+  LLMOPT_REQUIRE(args.buffer_count == 4, "expects buffers [key, value, slots, pool]");
+  LLMOPT_REQUIRE(read_params(args, &p), "expects 44 parameter bytes");
+  LLMOPT_REQUIRE(valid_geometry(p.head_dim, p.group_size), "head_dim must be a multiple of group_size");
+  LLMOPT_REQUIRE(args.lengths[2] >= (size_t)p.items * 4, "slots buffer is shorter than items");
+  const uint32_t groups = p.items * p.heads * (p.head_dim / p.group_size);
+  if (groups == 0) return 0;
+  pack_attention_pair_kernel<<<(groups + 7) / 8, 256, 0, args.stream>>>(
+      (const __half*)args.buffers[0], (const __half*)args.buffers[1], (const uint32_t*)args.buffers[2],
+      (uint8_t*)args.buffers[3], p);
+  return check_launch(args);
+}
+
+// Buffers: [pool, slots, destination]; params 40 bytes.
+int launch_cache_unpack_attention_q8(const KernelArgs& args) {
+  AttentionCacheParams p;
+  LLMOPT_REQUIRE(args.buffer_count == 3, "expects buffers [pool, slots, destination]");
+  LLMOPT_REQUIRE(read_params(args, &p), "expects 40 parameter bytes");
+  LLMOPT_REQUIRE(valid_geometry(p.head_dim, p.group_size), "head_dim must be a multiple of group_size");
+  LLMOPT_REQUIRE(args.lengths[1] >= (size_t)p.items * 4, "slots buffer is shorter than items");
+  const size_t elements = (size_t)p.items * p.heads * p.head_dim;
+  LLMOPT_REQUIRE(args.lengths[2] >= elements * 2, "destination buffer is too short");
+  if (elements == 0) return 0;
+  unpack_attention_kernel<<<(uint32_t)((elements + 255) / 256), 256, 0, args.stream>>>(
+      (const uint8_t*)args.buffers[0], (const uint32_t*)args.buffers[1], (__half*)args.buffers[2], p);
+  return check_launch(args);
+}
+
+// Buffers: [source, pool]; params 28 bytes (lib/metal_cache.ml:544-547).
+int launch_cache_pack_checkpoint_q8(const KernelArgs& args) {
+  CheckpointCacheParams p;
+  LLMOPT_REQUIRE(args.buffer_count == 2, "expects buffers [source, pool]");
+  LLMOPT_REQUIRE(read_params(args, &p), "expects 28 parameter bytes");
+  LLMOPT_REQUIRE(p.group_size > 0 && p.layer_elements % p.group_size == 0, "layer_elements must be a multiple of group_size");
+  LLMOPT_REQUIRE(args.lengths[0] >= (size_t)p.layer_elements * 2, "source buffer is too short");
+  const uint32_t groups = p.layer_elements / p.group_size;
+  if (groups == 0) return 0;
+  pack_checkpoint_kernel<<<(groups + 7) / 8, 256, 0, args.stream>>>(
+      (const __half*)args.buffers[0], (uint8_t*)args.buffers[1], p, args.checkpoint_cell);
+  return check_launch(args);
+}
+
+// Buffers: [pool, destination]; params 28 bytes.
+int launch_cache_unpack_checkpoint_q8(const KernelArgs& args) {
+  CheckpointCacheParams p;
+  LLMOPT_REQUIRE(args.buffer_count == 2, "expects buffers [pool, destination]");
+  LLMOPT_REQUIRE(read_params(args, &p), "expects 28 parameter bytes");
+  LLMOPT_REQUIRE(p.group_size > 0 && p.layer_elements % p.group_size == 0, "layer_elements must be a multiple of group_size");
+  LLMOPT_REQUIRE(args.lengths[1] >= (size_t)p.layer_elements * 2, "destination buffer is too short");
+  if (p.layer_elements == 0) return 0;
+  unpack_checkpoint_kernel<<<(p.layer_elements + 255) / 256, 256, 0, args.stream>>>(
+      (const uint8_t*)args.buffers[0], (__half*)args.buffers[1], p);
+  return check_launch(args);
+}
+
+}  // namespace llmopt
