@@ -62,9 +62,10 @@ __global__ void rotary_qk_kernel(const __half* __restrict__ q_input, const __hal
     const uint32_t rotated_col = col < p.half_dimension ? col + p.half_dimension : col - p.half_dimension;
     __half rotated = input[input_base + rotated_col];
     if (col < p.half_dimension) rotated = __hneg(rotated);
-    const __half direct = __hmul(input[input_base + col], cosine[trig_base + col]);
-    const __half turned = __hmul(rotated, sine[trig_base + col]);
-    output[output_base + col] = __hadd(direct, turned);
+    // *_rn: each operation rounds on its own, never contracted into an fma
+    const __half direct = __hmul_rn(input[input_base + col], cosine[trig_base + col]);
+    const __half turned = __hmul_rn(rotated, sine[trig_base + col]);
+    output[output_base + col] = __hadd_rn(direct, turned);
   }
 }
 
@@ -96,11 +97,9 @@ __global__ void argmax_f16_kernel(const __half* __restrict__ values, uint32_t co
   uint32_t best_index = 0xffffffffu;
   for (uint32_t i = tid; i < count; i += 256) {
     const float value = __half2float(values[i]);
-    if (value > best || (value == best && i < best_index) || best_index == 0xffffffffu) {
-      if (value > best || best_index == 0xffffffffu || (value == best && i < best_index)) {
-        best = value;
-        best_index = i;
-      }
+    if (best_index == 0xffffffffu || value > best) {
+      best = value;
+      best_index = i;
     }
   }
   best_values[tid] = best;

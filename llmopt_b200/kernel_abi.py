@@ -1,0 +1,117 @@
+"""Mirror of the reference's ``Kernel_abi`` surface for the hot path
+(lib/kernel_abi.ml:1-151): operation wire names and the kernel ``Entry`` record,
+plus the entry table of the kernels libllmopt_cuda.so provides.  The wire
+strings and entry names are the reference's; packages refer to kernels by them."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+# Kernel_abi.Operation.to_string, lib/kernel_abi.ml:36-70 (hot-path subset)
+W4A16_LINEAR = "w4a16-linear-g64"
+W4A16_QKV_LINEAR = "w4a16-qkv-linear-g64"
+W4A16_SWIGLU_FFN = "w4a16-swiglu-ffn-g64"
+W4A16_LM_HEAD_ARGMAX = "w4a16-lm-head-argmax"
+RMS_NORM = "rms-norm"
+ROTARY_QK = "rotary-qk"
+SHORT_CONV = "short-conv"
+SHORT_CONV_STEP = "short-conv-step"
+SHORT_CONV_PREFILL = "short-conv-prefill"
+ATTENTION = "attention"
+EMBEDDING = "embedding"
+CACHE = "cache"
+
+OPERATIONS = (
+    W4A16_LINEAR, W4A16_QKV_LINEAR, W4A16_SWIGLU_FFN, W4A16_LM_HEAD_ARGMAX, RMS_NORM, ROTARY_QK, SHORT_CONV,
+    SHORT_CONV_STEP, SHORT_CONV_PREFILL, ATTENTION, EMBEDDING, CACHE,
+)
+
+
+@dataclass(frozen=True)
+class Entry:
+    """``Kernel_abi.Entry.t`` (lib/kernel_abi.ml:110-118)."""
+
+    name: str
+    operation: str
+    input_dtype: str
+    output_dtype: str
+    threadgroup: tuple = (256, 1, 1)
+    tile: Optional[tuple] = None
+
+    def __post_init__(self):
+        # Entry.make, lib/kernel_abi.ml:120-133
+        if not self.name.strip():
+            raise ValueError("kernel entry-point name cannot be empty")
+        if any(v <= 0 for v in self.threadgroup):
+            raise ValueError("kernel threadgroup dimensions must be positive")
+        if self.tile is not None and (any(v <= 0 for v in self.tile) or self.tile[2] % 4 != 0):
+            raise ValueError("kernel tile dimensions must be positive and tile_k must be divisible by four")
+
+
+def _entries() -> list[Entry]:
+    f16, f32, u8, i64 = "float16", "float32", "uint8", "int64"
+    table = []
+
+    def add(name, operation, input_dtype=f16, output_dtype=f16, threadgroup=(256, 1, 1)):
+        table.append(Entry(name, operation, input_dtype, output_dtype, threadgroup))
+
+    for suffix in ("", "_m4", "_m8"):  # lib/metal_w4a16_source.ml:196-208
+        add("llmopt_w4a16_linear_f16_g64" + suffix, W4A16_LINEAR)
+        add("llmopt_w4a16_qkv_linear_f16_g64" + suffix, W4A16_QKV_LINEAR)
+        add("llmopt_w4a16_dual_swiglu_f16_g64" + suffix, W4A16_SWIGLU_FFN)
+        add("llmopt_w4a16_down_add_f16_g64" + suffix, W4A16_SWIGLU_FFN)
+    add("llmopt_w4a16_linear_f16_g64_affine", W4A16_LINEAR)
+    add("llmopt_w4a16_swiglu_rms_f16_g64", W4A16_SWIGLU_FFN)
+    add("llmopt_w4a16_swiglu_rms_f32_g64", W4A16_SWIGLU_FFN, f32, f16)
+    for stem in ("llmopt_w4a16_lm_head_argmax", "llmopt_w4a16_lm_head_argmax_extra",
+                 "llmopt_w4a16_lm_head_argmax_stage1", "llmopt_w4a16_lm_head_argmax_stage1_extra"):
+        add(stem + "_f16", W4A16_LM_HEAD_ARGMAX, f16, "int32")
+        add(stem + "_f32", W4A16_LM_HEAD_ARGMAX, f32, "int32")
+    add("llmopt_w4a16_lm_head_reduce", W4A16_LM_HEAD_ARGMAX, "int32", "int32")
+    for name in ("llmopt_cache_pack_attention_q8", "llmopt_cache_pack_attention_q8_simd",
+                 "llmopt_cache_pack_attention_q8_pair_simd", "llmopt_cache_pack_checkpoint_q8",
+                 "llmopt_cache_pack_checkpoint_q8_simd"):
+        add(name, CACHE, f16, u8)
+    for name in ("llmopt_cache_unpack_attention_q8", "llmopt_cache_unpack_attention_q8_vec4",
+                 "llmopt_cache_unpack_checkpoint_q8", "llmopt_cache_unpack_checkpoint_q8_vec4"):
+        add(name, CACHE, u8, f16)
+    for name in ("llmopt_attention_q8_paged_simd_h64", "llmopt_attention_q8_paged_simd_generic",
+                 "llmopt_attention_q8_paged_simd_h64_gqa3", "llmopt_attention_q8_paged_simd_h64_split8",
+                 "llmopt_attention_q8_paged_simd_h64_gqa3_split8", "llmopt_attention_q8_paged_batched"):
+        add(name, ATTENTION)
+    add("llmopt_attention_q8_paged_simd_h256", ATTENTION, threadgroup=(32, 1, 1))
+    add("llmopt_attention_q8_paged_simd_h512", ATTENTION, threadgroup=(32, 1, 1))
+    add("llmopt_short_conv_f16", SHORT_CONV)
+    add("llmopt_short_conv_f16_f32", SHORT_CONV, f32, f16)
+    add("llmopt_short_conv_silu_tm_f16", SHORT_CONV)
+    add("llmopt_short_conv_silu_tm_f32", SHORT_CONV, f32, f16)
+    add("llmopt_short_conv_step_f16", SHORT_CONV_STEP)
+    add("llmopt_short_conv_step_fused_f16", SHORT_CONV_STEP)
+    add("llmopt_short_conv_prefill_f16", SHORT_CONV_PREFILL)
+    add("llmopt_short_conv_prefill_init_f16", SHORT_CONV_PREFILL)
+    add("llmopt_rms_norm_f16", RMS_NORM)
+    add("llmopt_rms_norm_f16_simd", RMS_NORM)
+    add("llmopt_rms_norm_f32_f16", RMS_NORM, f32, f16)
+    add("llmopt_rms_norm_f32_f16_simd", RMS_NORM, f32, f16)
+    add("llmopt_rotary_qk_f16_simd_h64", ROTARY_QK)
+    add("llmopt_embedding_f16", EMBEDDING, i64, f16)
+    add("llmopt_chain_token_id", EMBEDDING, i64, i64, (32, 1, 1))
+    return table
+
+
+ENTRIES: tuple = tuple(_entries())
+
+
+def find_entry(*, operation: str, input_dtype: str, output_dtype: str, name: Optional[str] = None) -> Entry:
+    """``Metal_native.kernel_entry`` lookup rule (lib/metal_native.ml:461-487):
+    exactly one entry must match the operation, both dtypes and, if given, the name."""
+    if operation not in OPERATIONS:
+        raise ValueError(f"unsupported kernel operation: {operation}")
+    matches = [e for e in ENTRIES if e.operation == operation and e.input_dtype == input_dtype
+               and e.output_dtype == output_dtype and (name is None or e.name == name)]
+    if not matches:
+        raise LookupError(f"package declares no kernel for operation {operation}" + (f" named {name}" if name else ""))
+    if len(matches) > 1:
+        raise LookupError(f"package declares multiple kernels for operation {operation}")
+    return matches[0]
