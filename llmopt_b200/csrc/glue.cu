@@ -88,6 +88,12 @@ __global__ void chain_token_kernel(const uint32_t* __restrict__ argmax_in, long 
   if (blockIdx.x == 0 && threadIdx.x == 0) token_out[0] = (long long)argmax_in[0];
 }
 
+__global__ void chain_tokens_kernel(const uint32_t* __restrict__ argmax_in, long long* __restrict__ token_out,
+                                    uint32_t count) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) token_out[i] = (long long)argmax_in[i];
+}
+
 __global__ void argmax_f16_kernel(const __half* __restrict__ values, uint32_t count, int* __restrict__ result) {
   // strict '>' keeps the first maximum (native/ocaml_metal_stubs.m:787-794)
   __shared__ float best_values[256];
@@ -187,6 +193,19 @@ int launch_chain_token_id(const KernelArgs& args) {
   LLMOPT_REQUIRE(args.buffer_count == 2, "expects 2 buffers");
   LLMOPT_REQUIRE(args.lengths[0] >= 4 && args.lengths[1] >= 8, "buffer is too short");
   chain_token_kernel<<<1, 32, 0, args.stream>>>((const uint32_t*)args.buffers[0], (long long*)args.buffers[1]);
+  return check_launch(args);
+}
+
+// Batched form of the token chain (one id per sequence): buffers [argmax u32[n],
+// token i64[n]], params {count}. No counterpart in the reference, whose decode
+// steps carry one sequence.
+int launch_chain_token_ids(const KernelArgs& args) {
+  LLMOPT_REQUIRE(args.buffer_count == 2 && args.param_bytes == 4, "expects 2 buffers and 4 parameter bytes");
+  const uint32_t count = param_u32(args, 0);
+  LLMOPT_REQUIRE(args.lengths[0] >= (size_t)count * 4 && args.lengths[1] >= (size_t)count * 8, "buffer is too short");
+  if (count == 0) return 0;
+  chain_tokens_kernel<<<(count + 127) / 128, 128, 0, args.stream>>>((const uint32_t*)args.buffers[0],
+                                                                     (long long*)args.buffers[1], count);
   return check_launch(args);
 }
 

@@ -49,6 +49,7 @@ template <bool INPUT_F32> int launch_rms_norm(const KernelArgs&);
 int launch_rotary_qk(const KernelArgs&);
 int launch_embedding_f16(const KernelArgs&);
 int launch_chain_token_id(const KernelArgs&);
+int launch_chain_token_ids(const KernelArgs&);
 void launch_argmax_f16(const __half* values, uint32_t count, int* result, cudaStream_t stream);
 
 // ---- objects -----------------------------------------------------------------------
@@ -222,6 +223,7 @@ static void register_kernels(llmopt_cuda_library* library) {
   add("llmopt_rotary_qk_f16_simd_h64", launch_rotary_qk);
   add("llmopt_embedding_f16", launch_embedding_f16);
   add("llmopt_chain_token_id", launch_chain_token_id);
+  add("llmopt_chain_token_ids", launch_chain_token_ids);
 }
 
 static bool is_paged_attention_name(const char* name) {

@@ -1,0 +1,235 @@
+"""Whole-token decode over the hot-path kernels: builds, for one model and batch
+size, the per-token dispatch list the reference's schedule executor would
+record (embedding, per block: RMSNorm, fused W4A16 QKV, rotary, paged Q8
+attention, Q8 cache pack, W4A16 o-proj + residual, W4A16 SwiGLU FFN; or the gated
+short-conv block; then the W4A16 LM-head argmax) and hands it to a prebaked plan
+— the role of ``Metal_runtime.bind_decode_plan`` + ``Prebaked``
+(lib/metal_schedule_executor.ml:495-547, lib/serving_engine.ml:699-790).
+
+The per-token host work of the reference engine (RoPE row, cache slot of the new
+token) is done on the device by the plan's row bindings.  Batch > 1 (one token
+per sequence per step, per-sequence slot tables) is an extension: the reference
+decodes sequences one at a time (lib/serving_engine.ml:1542-1548).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import dispatch, kernel_abi, parameters
+from .cuda_native import Batch, Buffer, Prebaked, Runtime
+from .kv_cache import AttentionLayer, Layout
+from .model import ModelConfig
+from .quantize import rope_tables
+
+
+class DecodeEngine:
+    def __init__(self, runtime: Runtime, config: ModelConfig, weights: dict, *, batch: int = 1, capacity: int = 1024,
+                 kv_heads_local: Optional[int] = None):
+        self.runtime, self.config, self.batch, self.capacity = runtime, config, batch, capacity
+        self.layout = Layout([AttentionLayer(config.kv_heads, config.head_dim)] * config.attention_layers,
+                             group_size=config.kv_group_size)
+        self.cache = dispatch.Cache(runtime, self.layout, token_capacity=batch * capacity)
+        self._keep = []
+        self._upload(weights)
+        self._workspace()
+        self.plan = None
+        self.records = None
+
+    # ---- device state ---------------------------------------------------------------------
+    def _tensor(self, array, dtype=None) -> dispatch.Tensor:
+        array = np.ascontiguousarray(array)
+        names = {np.dtype(np.float16): "float16", np.dtype(np.uint8): "uint8", np.dtype(np.uint32): "uint32"}
+        return dispatch.Tensor(Buffer.of_array(self.runtime, array), tuple(array.shape), dtype or names[array.dtype])
+
+    def _empty(self, shape, dtype="float16", itemsize=2) -> dispatch.Tensor:
+        return dispatch.Tensor(Buffer.create(self.runtime, math.prod(shape) * itemsize), tuple(shape), dtype)
+
+    def _upload(self, weights: dict) -> None:
+        config = self.config
+        self.embedding = self._tensor(weights["embedding"])
+        self.lm_head = tuple(self._tensor(a) for a in weights["lm_head"])
+        self.final_norm = self._tensor(weights["final_norm"])
+        self.layers = []
+        for index in range(len(config.layers)):
+            source = weights[f"layer{index}"]
+            layer = {}
+            for key, value in source.items():
+                layer[key] = tuple(self._tensor(a) for a in value) if isinstance(value, tuple) else self._tensor(value)
+            self.layers.append(layer)
+        cosine, sine = rope_tables(self.capacity + 1, config.head_dim, config.rope_theta)
+        self.cos_table, self.sin_table = self._tensor(cosine), self._tensor(sine)
+
+    def _workspace(self) -> None:
+        config, batch = self.config, self.batch
+        hidden, dim = config.hidden, config.head_dim
+        self.token_ids = self._empty((batch,), "int64", 8)
+        self.out_tokens = self._empty((batch,), "int32", 4)
+        self.hidden_a = self._empty((batch, hidden))
+        self.hidden_b = self._empty((batch, hidden))
+        self.normed = self._empty((batch, hidden))
+        self.q = self._empty((batch, config.query_heads * dim))
+        self.k = self._empty((batch, config.kv_heads * dim))
+        self.v = self._empty((batch, config.kv_heads * dim))
+        self.q_rot = self._empty((batch, config.query_heads, 1, dim))
+        self.k_rot = self._empty((batch, config.kv_heads, 1, dim))
+        self.attended = self._empty((batch, config.query_heads * dim))
+        self.cos_row = self._empty((1, 1, dim))
+        self.sin_row = self._empty((1, 1, dim))
+        self.new_slots = self._empty((batch,), "uint32", 4)
+        if config.conv_layers:
+            self.in_proj = self._empty((batch, 3 * hidden))
+            self.conv_out = self._empty((batch, hidden))
+            self.conv_states = [self._empty((batch, hidden, 3)) for _ in range(config.conv_layers)]
+        # slot(b, position) = b * capacity + position: [batch, capacity] for reads,
+        # its transpose [capacity, batch] so one row holds the new slot of every sequence
+        table = (np.arange(batch, dtype=np.uint32)[:, None] * self.capacity
+                 + np.arange(self.capacity, dtype=np.uint32)[None, :])
+        self.slot_table = self._tensor(table, "uint32")
+        self.slot_table_by_position = self._tensor(np.ascontiguousarray(table.T), "uint32")
+
+    # ---- the per-token record list ----------------------------------------------------------
+    def build(self, past_tokens: int = 0) -> None:
+        config, batch, runtime = self.config, self.batch, self.runtime
+        hidden, dim = config.hidden, config.head_dim
+        commands = Batch(runtime)
+        context = dispatch.Context(runtime, batch=commands, decode_uniforms_past_tokens=past_tokens)
+        run = lambda name, buffers, params, grid=(256, 1, 1): commands.dispatch(
+            name=name, buffers=buffers, parameters=params, grid=grid, group=(256, 1, 1))
+        run("llmopt_embedding_f16", [self.token_ids.buffer, self.embedding.buffer, self.hidden_a.buffer],
+            parameters.embedding(tokens=batch, vocabulary=config.vocabulary, width=hidden), (batch * hidden, 1, 1))
+        current, other = self.hidden_a, self.hidden_b
+        attention_index = conv_index = 0
+        for kind, layer in zip(config.layers, self.layers):
+            run("llmopt_rms_norm_f16_simd", [current.buffer, layer["input_norm"].buffer, self.normed.buffer],
+                parameters.rms_norm(rows=batch, width=hidden, epsilon=config.epsilon),
+                (dispatch.simd_rows_grid(batch), 1, 1))
+            if kind == "attention":
+                dispatch.dispatch_w4a16_qkv_linear_command(
+                    context, input=self.normed, q_weight=layer["q"][0], q_scale=layer["q"][1], k_weight=layer["k"][0],
+                    k_scale=layer["k"][1], v_weight=layer["v"][0], v_scale=layer["v"][1], q_output=self.q,
+                    k_output=self.k, v_output=self.v)
+                run("llmopt_rotary_qk_f16_simd_h64",
+                    [self.q.buffer, self.k.buffer, self.cos_row.buffer, self.sin_row.buffer, self.q_rot.buffer,
+                     self.k_rot.buffer],
+                    parameters.rotary_qk(batches=batch, tokens=1, q_heads=config.query_heads, k_heads=config.kv_heads,
+                                         width=dim, half_dimension=dim // 2, trig_batches=1),
+                    (dispatch.simd_rows_grid(batch * (config.query_heads + config.kv_heads)), 1, 1))
+                region = self.layout.attentions[attention_index]
+                paged = dispatch.PagedAttentionConfig(
+                    token_elements=self.layout.token_elements, key_offset=region.key_offset,
+                    value_offset=region.value_offset, group_size=self.layout.group_size,
+                    token_stride=self.layout.bytes_per_token, scale=float(np.float32(1.0 / math.sqrt(dim))))
+                value_now = dispatch.Tensor(self.v.buffer, (batch, config.kv_heads, 1, dim))
+                attended = dispatch.Tensor(self.attended.buffer, (batch, 1, config.query_heads, dim))
+                if batch == 1:
+                    slots = dispatch.Tensor(self.slot_table.buffer, (self.capacity,), "uint32")
+                    dispatch.dispatch_paged_attention_q8(
+                        context, config=paged, query=self.q_rot, current_key=self.k_rot, current_value=value_now,
+                        pool=dispatch.Tensor(self.cache.token_pool, (0,), "uint8"), slots=slots, output=attended)
+                else:
+                    dispatch.dispatch_paged_attention_q8(
+                        context, config=paged, query=self.q_rot, current_key=self.k_rot, current_value=value_now,
+                        pool=dispatch.Tensor(self.cache.token_pool, (0,), "uint8"), slots=self.slot_table,
+                        output=attended, slot_batch_stride=self.capacity)
+                # Q8 pack of the new token: one item per sequence; a sequence's K (or V)
+                # row is kv_heads * D contiguous halves, packed as one "head" of that width
+                pack = parameters.cache_attention_pair(
+                    items=batch, key_segment_offset=region.key_offset, value_segment_offset=region.value_offset,
+                    heads=1, head_dim=config.kv_heads * dim, group_size=self.layout.group_size,
+                    token_elements=self.layout.token_elements, token_groups=self.layout.token_groups,
+                    token_stride=self.layout.bytes_per_token, source_items=batch, source_offset=0)
+                groups = batch * config.kv_heads * dim // self.layout.group_size
+                run("llmopt_cache_pack_attention_q8_pair_simd",
+                    [self.k_rot.buffer, self.v.buffer, self.new_slots.buffer, self.cache.token_pool], pack,
+                    (dispatch.round_up(groups, 8) * 32, 1, 1))
+                dispatch.dispatch_w4a16_linear(context, input=self.attended, weight=layer["o"][0], scale=layer["o"][1],
+                                               output=other, bias=current, bias_row_stride=hidden)
+                attention_index += 1
+            else:
+                dispatch.dispatch_w4a16_linear(context, input=self.normed, weight=layer["in_proj"][0],
+                                               scale=layer["in_proj"][1], output=self.in_proj)
+                state = self.conv_states[conv_index]
+                for b in range(batch):  # the step kernel carries one sequence (lib/metal_recurrent_source.ml:151)
+                    dispatch.dispatch_short_conv_step(
+                        context,
+                        in_proj=dispatch.Tensor(self.in_proj.buffer.view(b * 6 * hidden, 6 * hidden), (1, 1, 3 * hidden)),
+                        conv_state=dispatch.Tensor(state.buffer.view(b * 6 * hidden, 6 * hidden), (1, hidden, 3)),
+                        conv_weight=layer["conv"],
+                        output=dispatch.Tensor(self.conv_out.buffer.view(b * 2 * hidden, 2 * hidden), (1, 1, hidden)))
+                dispatch.dispatch_w4a16_linear(context, input=self.conv_out, weight=layer["out_proj"][0],
+                                               scale=layer["out_proj"][1], output=other, bias=current,
+                                               bias_row_stride=hidden)
+                conv_index += 1
+            current, other = other, current
+            dispatch.dispatch_w4a16_swiglu_ffn_command(
+                context, m=batch, n=config.intermediate, k=hidden, epsilon=config.epsilon, activation=current,
+                residual=current, gate_weight=layer["gate"][0], gate_scale=layer["gate"][1], up_weight=layer["up"][0],
+                up_scale=layer["up"][1], down_weight=layer["down"][0], down_scale=layer["down"][1],
+                norm_weight=layer["ffn_norm"], output=other, reference_guards=False)
+            current, other = other, current
+        for row0 in range(0, batch, 32):  # the LM head takes at most 32 rows per dispatch
+            rows = min(32, batch - row0)
+            dispatch.dispatch_w4a16_lm_head_argmax_command(
+                context, m=rows, n=config.vocabulary, k=hidden, epsilon=config.epsilon,
+                input=dispatch.Tensor(current.buffer.view(row0 * hidden * 2, rows * hidden * 2), (rows, hidden)),
+                norm_weight=self.final_norm, weight=self.lm_head[0], scale=self.lm_head[1],
+                output=dispatch.Tensor(self.out_tokens.buffer.view(row0 * 4, rows * 4), (rows,), "int32"),
+                reference_guards=False, two_stage=False)
+        if batch == 1:
+            run("llmopt_chain_token_id", [self.out_tokens.buffer, self.token_ids.buffer], b"", (32, 1, 1))
+        else:
+            run("llmopt_chain_token_ids", [self.out_tokens.buffer, self.token_ids.buffer], parameters.u32s([batch]),
+                (batch, 1, 1))
+        self.records = list(commands.pending)
+        self._context = context
+        commands.abort()
+        row = self.config.head_dim * 2
+        self.plan = Prebaked(runtime, self.records, self.token_ids.buffer, self.out_tokens.buffer, row_bindings=[
+            (self.cos_row.buffer, self.cos_table.buffer, row), (self.sin_row.buffer, self.sin_table.buffer, row),
+            (self.new_slots.buffer, self.slot_table_by_position.buffer, 4 * self.batch)])
+
+    # ---- stepping ------------------------------------------------------------------------------
+    def step(self, tokens: Sequence[int], past_tokens: int) -> list:
+        """One host-driven decode step: token ids in, next token ids out (the
+        ``Prebaked.execute`` round trip, one per token)."""
+        if self.plan is None:
+            self.build(past_tokens)
+        if len(tokens) != self.batch:
+            raise ValueError("one token per sequence is required")
+        if past_tokens >= self.capacity:
+            raise ValueError("the cache capacity is exhausted")
+        if self.batch > 1:
+            self.token_ids.buffer.write(0, np.asarray(tokens, np.int64))
+        first = self.plan.execute(token=int(tokens[0]), past_tokens=past_tokens)
+        if self.batch == 1:
+            return [first]
+        return self.out_tokens.buffer.to_numpy(np.int32).tolist()
+
+    def generate_chained(self, tokens: Sequence[int], past_tokens: int, steps: int):
+        """``steps`` device-chained greedy steps; returns (ids of sequence 0, device ms)."""
+        if self.plan is None:
+            self.build(past_tokens)
+        if past_tokens + steps > self.capacity:
+            raise ValueError("the cache capacity is exhausted")
+        if self.batch > 1:
+            self.token_ids.buffer.write(0, np.asarray(tokens, np.int64))
+        return self.plan.execute_chained(token=int(tokens[0]), past_tokens=past_tokens, steps=steps)
+
+    def fill_cache_random(self, past_tokens: int, seed: int = 0) -> None:
+        """Pre-fills every sequence's first ``past_tokens`` slots with random int8
+        payload and valid fp16 scales (a context that was never computed)."""
+        rng = np.random.default_rng(seed)
+        stride, elements = self.layout.bytes_per_token, self.layout.token_elements
+        block = np.zeros((past_tokens, stride), np.uint8)
+        block[:, :elements] = rng.integers(-127, 128, size=(past_tokens, elements), dtype=np.int8).view(np.uint8)
+        scales = rng.uniform(0.004, 0.02, size=(past_tokens, (stride - elements) // 2)).astype(np.float16)
+        block[:, elements:] = scales.view(np.uint8).reshape(past_tokens, -1)
+        first = self.cache.token_pool.view(0, past_tokens * stride)
+        first.write(0, block)
+        for b in range(1, self.batch):
+            first.copy_to(self.cache.token_pool.view(b * self.capacity * stride, past_tokens * stride))
+        self.runtime.synchronize()

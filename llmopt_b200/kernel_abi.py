@@ -97,6 +97,7 @@ def _entries() -> list[Entry]:
     add("llmopt_rotary_qk_f16_simd_h64", ROTARY_QK)
     add("llmopt_embedding_f16", EMBEDDING, i64, f16)
     add("llmopt_chain_token_id", EMBEDDING, i64, i64, (32, 1, 1))
+    add("llmopt_chain_token_ids", EMBEDDING, "int32", i64, (128, 1, 1))
     return table
 
 
