@@ -1,0 +1,138 @@
+"""Single-kernel probe: one dispatch of the hot path at a given shape on synthetic
+data, timed with CUDA events with the L2 flushed before every launch, reported
+as achieved GB/s over the algorithmic bytes.  The counterpart of the reference's
+stand-alone Metal tile probes (bench/metal_q4_tile_probe.swift); also the small,
+self-terminating command used for profiler captures.
+
+  python -m llmopt_b200.kernel_bench --op linear|qkv|gate_up|down|lm_head|attention \\
+         --m 1 --k 4096 --n 14336 [--heads 32 --kv-heads 8 --dim 128 --past 8192] [--iters 20]
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import numpy as np
+
+from . import cuda_native, dispatch, parameters
+from .cuda_native import Batch, Buffer
+from .kv_cache import AttentionLayer, Layout
+
+
+def _w4(runtime, rng, n, k):
+    packed = rng.integers(0, 256, size=(n, k // 2), dtype=np.uint8)
+    scale = rng.uniform(0.005, 0.02, size=(n, k // 64)).astype(np.float16)
+    return (dispatch.Tensor(Buffer.of_array(runtime, packed), (n, k // 2), "uint8"),
+            dispatch.Tensor(Buffer.of_array(runtime, scale), (n, k // 64), "float16"))
+
+
+def _f16(runtime, rng, shape):
+    return dispatch.Tensor(Buffer.of_array(runtime, rng.standard_normal(shape).astype(np.float16)), tuple(shape))
+
+
+def build_item(runtime, args):
+    """Returns (DispatchItem, algorithmic bytes)."""
+    rng = np.random.default_rng(0)
+    m, k, n = args.m, args.k, args.n
+    commands = Batch(runtime)
+    context = dispatch.Context(runtime, batch=commands)
+    weight_bytes = lambda rows, cols: rows * cols // 2 + rows * (cols // 64) * 2
+    if args.op == "linear":
+        w, s = _w4(runtime, rng, n, k)
+        dispatch.dispatch_w4a16_linear(context, input=_f16(runtime, rng, (m, k)), weight=w, scale=s,
+                                       output=_f16(runtime, rng, (m, n)))
+        nbytes = weight_bytes(n, k) + m * k * 2 + m * n * 2
+    elif args.op == "qkv":
+        nq, nkv = args.heads * args.dim, args.kv_heads * args.dim
+        (qw, qs), (kw, ks), (vw, vs) = _w4(runtime, rng, nq, k), _w4(runtime, rng, nkv, k), _w4(runtime, rng, nkv, k)
+        dispatch.dispatch_w4a16_qkv_linear_command(
+            context, input=_f16(runtime, rng, (m, k)), q_weight=qw, q_scale=qs, k_weight=kw, k_scale=ks, v_weight=vw,
+            v_scale=vs, q_output=_f16(runtime, rng, (m, nq)), k_output=_f16(runtime, rng, (m, nkv)),
+            v_output=_f16(runtime, rng, (m, nkv)))
+        nbytes = weight_bytes(nq + 2 * nkv, k) + m * k * 2 + m * (nq + 2 * nkv) * 2
+    elif args.op in ("gate_up", "down"):
+        gw, gs = _w4(runtime, rng, n, k)
+        uw, us = _w4(runtime, rng, n, k)
+        dw, ds = _w4(runtime, rng, k, n)
+        dispatch.dispatch_w4a16_swiglu_ffn_command(
+            context, m=m, n=n, k=k, epsilon=1e-5, activation=_f16(runtime, rng, (m, k)),
+            residual=_f16(runtime, rng, (m, k)), gate_weight=gw, gate_scale=gs, up_weight=uw, up_scale=us,
+            down_weight=dw, down_scale=ds,
+            norm_weight=dispatch.Tensor(Buffer.of_array(runtime, np.ones(k, np.float16)), (k,)),
+            output=_f16(runtime, rng, (m, k)), reference_guards=False)
+        if args.op == "gate_up":
+            index, nbytes = 1, 2 * weight_bytes(n, k) + m * k * 2 + m * n * 2
+        else:
+            index, nbytes = 2, weight_bytes(k, n) + m * n * 2 + 2 * m * k * 2
+        item = commands.pending[index]
+        commands.abort()
+        return item, nbytes, context
+    elif args.op == "lm_head":
+        w, s = _w4(runtime, rng, n, k)
+        dispatch.dispatch_w4a16_lm_head_argmax_command(
+            context, m=m, n=n, k=k, epsilon=1e-5, input=_f16(runtime, rng, (m, k)),
+            norm_weight=dispatch.Tensor(Buffer.of_array(runtime, np.ones(k, np.float16)), (k,)), weight=w, scale=s,
+            output=dispatch.Tensor(Buffer.create(runtime, 4 * m), (m,), "int32"), reference_guards=False,
+            two_stage=False)
+        nbytes = weight_bytes(n, k) + m * k * 2 + m * 4
+    elif args.op == "attention":
+        layout = Layout([AttentionLayer(args.kv_heads, args.dim)] * args.layers, group_size=args.group)
+        capacity = args.past + 1
+        block = np.zeros((capacity, layout.bytes_per_token), np.uint8)
+        block[:, :layout.token_elements] = rng.integers(-127, 128, size=(capacity, layout.token_elements),
+                                                        dtype=np.int8).view(np.uint8)
+        scales = rng.uniform(0.004, 0.02, size=(capacity, layout.token_groups)).astype(np.float16)
+        block[:, layout.token_elements:] = scales.view(np.uint8).reshape(capacity, -1)
+        pool = Buffer.create(runtime, m * capacity * layout.bytes_per_token)
+        first = pool.view(0, block.nbytes)
+        first.write(0, block)
+        for b in range(1, m):
+            first.copy_to(pool.view(b * block.nbytes, block.nbytes))
+        slots = (np.arange(m, dtype=np.uint32)[:, None] * capacity + np.arange(args.past, dtype=np.uint32)[None, :])
+        region = layout.attentions[args.layers // 2]
+        config = dispatch.PagedAttentionConfig(
+            token_elements=layout.token_elements, key_offset=region.key_offset, value_offset=region.value_offset,
+            group_size=args.group, token_stride=layout.bytes_per_token, scale=float(np.float32(1 / math.sqrt(args.dim))))
+        dispatch.dispatch_paged_attention_q8(
+            context, config=config, query=_f16(runtime, rng, (m, args.heads, 1, args.dim)),
+            current_key=_f16(runtime, rng, (m, args.kv_heads, 1, args.dim)),
+            current_value=_f16(runtime, rng, (m, args.kv_heads, 1, args.dim)),
+            pool=dispatch.Tensor(pool, (0,), "uint8"),
+            slots=dispatch.Tensor(Buffer.of_array(runtime, np.ascontiguousarray(slots)), tuple(slots.shape), "uint32"),
+            output=_f16(runtime, rng, (m, 1, args.heads, args.dim)), slot_batch_stride=args.past)
+        per_key = 2 * args.kv_heads * args.dim + 4 * args.kv_heads * args.dim // args.group + 4
+        nbytes = m * (args.past * per_key + 2 * args.heads * args.dim * 2 + 2 * args.kv_heads * args.dim * 2)
+    else:
+        raise SystemExit(f"unknown op {args.op}")
+    item = commands.pending[0]
+    commands.abort()
+    return item, nbytes, context
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--op", required=True)
+    parser.add_argument("--m", type=int, default=1)
+    parser.add_argument("--k", type=int, default=4096)
+    parser.add_argument("--n", type=int, default=14336)
+    parser.add_argument("--heads", type=int, default=32)
+    parser.add_argument("--kv-heads", type=int, default=8)
+    parser.add_argument("--dim", type=int, default=128)
+    parser.add_argument("--group", type=int, default=64)
+    parser.add_argument("--layers", type=int, default=2)
+    parser.add_argument("--past", type=int, default=8192)
+    parser.add_argument("--iters", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--no-flush", action="store_true")
+    args = parser.parse_args()
+    runtime = cuda_native.Runtime()
+    item, nbytes, _keep = build_item(runtime, args)
+    milliseconds = runtime.time_dispatch(item, warmup=args.warmup, iterations=args.iters, flush_l2=not args.no_flush)
+    print(json.dumps({"op": args.op, "kernel": item.name, "m": args.m, "k": args.k, "n": args.n, "ms": milliseconds,
+                      "algorithmic_bytes": nbytes, "gbs": nbytes / milliseconds / 1e6}))
+
+
+if __name__ == "__main__":
+    main()
