@@ -211,6 +211,33 @@ int llmopt_cuda_w4a16_linear(llmopt_cuda_context* context, const void* input, co
                              const void* scale, const void* bias, void* output, int64_t m, int64_t n, int64_t k,
                              void* stream);
 
+/* ---- entry point that allocates nothing ---------------------------------------------- */
+
+/* No counterpart in the reference. For hosts that cannot let the library allocate
+ * device memory (all HBM already owned by the host's own pools, a fixed memory
+ * budget, or a path where an allocation's implicit device synchronisation is not
+ * acceptable): the split-K paged Q8 decode attention of
+ * llmopt_attention_q8_paged_* with its split scratch in an 8 MiB array that is
+ * part of the library image (held on every GPU that loads the library until the
+ * process exits). No context is needed; the CURRENT device is used and all
+ * pointers are raw device pointers on it:
+ *   query [b, hq, 1, D] f16, current_key / current_value [b, hkv, 1, D] f16,
+ *   pool u8, slots u32 ([past] shared, or [b, slot_batch_stride] with a nonzero
+ *   stride), output [b, 1, hq, D] f16, parameters = the 64-byte paged-attention
+ *   block (lib/metal_parameters.ml:119-140).
+ * Decode shape only (one query token, no mask, no window, D 64 or 128, group 32 or
+ * 64, <= 8 query heads per KV head); batches x kv_heads may not exceed 2016
+ * (D = 128) or 3954 (D = 64) — larger problems are rejected with
+ * LLMOPT_CUDA_INVALID_ARGUMENT. Runs on `stream` (a cudaStream_t; NULL = default
+ * stream) without synchronising. The first call on each device resolves the
+ * array's device address; make it before any stream capture begins. Calls share
+ * the array, which keeps the previous call's contents; nothing needs clearing,
+ * but calls that overlap on the GPU race on it and must be serialised. */
+int llmopt_cuda_attention_q8_paged_static(const void* query, const void* current_key, const void* current_value,
+                                          const void* pool, const void* slots, void* output,
+                                          const void* parameters, size_t parameter_bytes,
+                                          uint32_t slot_batch_stride, void* stream);
+
 /* ---- measurement ---------------------------------------------------------------------- */
 
 /* Average device time in milliseconds of one dispatch, measured with CUDA

@@ -107,6 +107,7 @@ SIGNATURES = {
     "llmopt_cuda_ring_destroy": (_I, [_P]),
     "llmopt_cuda_f16_argmax": (_I64, [_P, _SZ]),
     "llmopt_cuda_w4a16_linear": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P]),
+    "llmopt_cuda_attention_q8_paged_static": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, ctypes.c_uint32, _P]),
     "llmopt_cuda_time_dispatch": (_I, [_P, _REC, _I, _I, _I, ctypes.POINTER(ctypes.c_float)]),
 }
 
