@@ -247,6 +247,14 @@ int llmopt_cuda_attention_q8_paged_static(const void* query, const void* current
 int llmopt_cuda_time_dispatch(llmopt_cuda_library* library, const llmopt_cuda_dispatch_record* record, int warmup,
                               int iterations, int flush_l2, float* average_ms);
 
+/* The same for a LIST of dispatches run back to back between one pair of events
+ * (for example one kernel over the distinct weights of every layer): returns the
+ * average milliseconds per dispatch. With a list whose operands exceed the L2
+ * many times over no flush is needed, and the launch-to-launch overhead is the
+ * one a replayed plan sees rather than that of an isolated launch. */
+int llmopt_cuda_time_dispatches(llmopt_cuda_library* library, const llmopt_cuda_dispatch_record* records,
+                                size_t count, int warmup, int iterations, float* average_ms_per_dispatch);
+
 #pragma GCC visibility pop
 
 #ifdef __cplusplus

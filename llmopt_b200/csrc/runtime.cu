@@ -67,6 +67,9 @@ struct Context {
   void* flush_buffer = nullptr;  // L2 flush target for timing
   size_t flush_bytes = 0;
   int* argmax_result = nullptr;  // device int
+  // Pinned, device-visible word: kernels whose bounded waits ran out set it; the host
+  // reads it after every stream wait.
+  uint32_t* device_error = nullptr;
 };
 
 struct Allocation {
@@ -120,6 +123,7 @@ static void release(Context* context) {
   for (void* block : context->scratch_blocks) cudaFree(block);
   if (context->flush_buffer) cudaFree(context->flush_buffer);
   if (context->argmax_result) cudaFree(context->argmax_result);
+  if (context->device_error) cudaFreeHost(context->device_error);
   if (context->stream) cudaStreamDestroy(context->stream);
   delete static_cast<llmopt_cuda_context*>(context);
 }
@@ -147,6 +151,7 @@ void* context_scratch(Context* context, size_t bytes, std::string* error) {
   return block;
 }
 int context_sm_count(Context* context) { return context->sm_count; }
+uint32_t* context_device_error(Context* context) { return context->device_error; }
 
 static void register_kernels(llmopt_cuda_library* library) {
   auto add = [&](const char* name, Launcher launcher) {
@@ -321,6 +326,10 @@ static int run_record(Context* context, const OwnedRecord& record, const uint32_
 static int wait_stream(Context* context, const char* what) {
   cudaError_t status = cudaStreamSynchronize(context->stream);
   if (status != cudaSuccess) return cuda_failure(what, status);
+  if (context->device_error && *(volatile uint32_t*)context->device_error != 0) {
+    *(volatile uint32_t*)context->device_error = 0;
+    return set_error(LLMOPT_CUDA_FAILURE, std::string(what) + ": a bounded device-side wait ran out (results are invalid)");
+  }
   return LLMOPT_CUDA_OK;
 }
 
@@ -440,6 +449,8 @@ int llmopt_cuda_create_context(int device, llmopt_cuda_context** out) {
     return cuda_failure("cudaStreamCreate failed", status);
   }
   status = cudaMalloc((void**)&context->argmax_result, sizeof(int));
+  if (status == cudaSuccess) status = cudaHostAlloc((void**)&context->device_error, sizeof(uint32_t), cudaHostAllocMapped);
+  if (status == cudaSuccess) *context->device_error = 0;
   if (status != cudaSuccess) {
     release(context);
     return cuda_failure("context allocation failed", status);
@@ -1172,6 +1183,40 @@ int llmopt_cuda_time_dispatch(llmopt_cuda_library* library, const llmopt_cuda_di
   cudaEventDestroy(end);
   release_record(owned);
   if (status == LLMOPT_CUDA_OK) *average_ms = (float)(total / iterations);
+  return status;
+}
+
+int llmopt_cuda_time_dispatches(llmopt_cuda_library* library, const llmopt_cuda_dispatch_record* records,
+                                size_t count, int warmup, int iterations, float* average_ms_per_dispatch) {
+  if (average_ms_per_dispatch == nullptr || iterations <= 0 || count == 0 || records == nullptr)
+    return set_error(LLMOPT_CUDA_INVALID_ARGUMENT, "bad timing request");
+  std::vector<OwnedRecord> owned(count);
+  for (size_t i = 0; i < count; ++i)
+    if (int status = own_record(library, &records[i], &owned[i])) {
+      for (size_t j = 0; j < i; ++j) release_record(owned[j]);
+      return status;
+    }
+  Context* context = library->context;
+  cudaEvent_t begin, end;
+  cudaEventCreate(&begin);
+  cudaEventCreate(&end);
+  int status = LLMOPT_CUDA_OK;
+  double total = 0.0;
+  for (int i = 0; i < warmup + iterations && status == LLMOPT_CUDA_OK; ++i) {
+    cudaEventRecord(begin, context->stream);
+    for (size_t j = 0; j < count && status == LLMOPT_CUDA_OK; ++j) status = run_record(context, owned[j], nullptr, nullptr);
+    cudaEventRecord(end, context->stream);
+    if (status == LLMOPT_CUDA_OK) status = wait_stream(context, "timed dispatches failed");
+    if (status == LLMOPT_CUDA_OK && i >= warmup) {
+      float elapsed = 0.0f;
+      cudaEventElapsedTime(&elapsed, begin, end);
+      total += elapsed;
+    }
+  }
+  cudaEventDestroy(begin);
+  cudaEventDestroy(end);
+  for (OwnedRecord& record : owned) release_record(record);
+  if (status == LLMOPT_CUDA_OK) *average_ms_per_dispatch = (float)(total / iterations / (double)count);
   return status;
 }
 

@@ -40,4 +40,7 @@ struct GemvProblem {
 // Rows beyond 64 are processed in passes of 64.
 int launch_w4a16_gemv(const KernelArgs& args, GemvProblem problem, int epilogue, bool affine);
 
+// Pipelined fast path (K % 512 == 0, <= 32 rows); returns -1 if the shape is outside its domain.
+int launch_w4a16_gemv_pipe(const KernelArgs& args, const GemvProblem& problem, int epilogue);
+
 }  // namespace llmopt

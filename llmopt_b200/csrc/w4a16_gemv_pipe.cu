@@ -1,0 +1,470 @@
+// Pipelined W4A16 group-64 decode product: the HBM-bound fast path of
+// w4a16_gemv.cu for K a multiple of 512 (same storage contract, same outputs).
+//
+// Why a second kernel: the direct-load kernel keeps only a few 8-byte loads per
+// lane in flight and pays address arithmetic and a nibble-bias subtraction per
+// weight; at the Llama FFN shapes it is latency- and issue-bound at a quarter of
+// the HBM roofline (the memory system here needs on the order of 100 KB per SM in
+// flight to stream at its rate).  This kernel separates the two jobs:
+//   * a PRODUCER warp streams the packed weights and scales of 16-column tiles
+//     into a deep shared-memory ring with 16-byte asynchronous copies (cp.async,
+//     two 256-byte row pieces per warp instruction) whose completion arrives on
+//     one mbarrier per ring stage (cp.async.mbarrier.arrive); bytes in flight are bounded by shared memory
+//     only, not by registers or by the consumers' progress;
+//   * eight CONSUMER warps wait on a stage's "full" barrier, each takes one group
+//     of 64 of the stage's 512 k, and release the stage on its "empty" barrier —
+//     no CTA-wide barrier and no copy instructions on the math path;
+//   * shared rows are padded by 32 bytes, so the 8-byte fragment reads of a
+//     half-warp (4 rows x 32 bytes) fall in distinct banks;
+//   * for small activation blocks (M*K <= 16 Ki elements) the activations sit in
+//     shared memory already in MMA fragment order, and the nibble bias is not
+//     subtracted per weight: even nibbles enter the MMA as 1032 + q, odd ones as
+//     72 + q (one LOP3 each, exact fp16 integers), and the per-group term
+//     1032*sum(x_even) + 72*sum(x_odd), computed once per CTA in fp32, is removed
+//     from the group sum before it is scaled — products stay exact, the fp32
+//     group sums differ from the unbiased form by fp32 rounding (~1e-5 of the
+//     group magnitude);
+//   * tiles are dealt round-robin to a grid sized so every CTA gets the same
+//     number of tiles; the consumers' partial sums are added in fixed order.
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the warp records
+// an error word the host checks and goes on without waiting, still taking part in
+// every later barrier, so the kernel always terminates.
+#include "w4a16_gemv_device.cuh"
+
+namespace llmopt {
+using namespace gemv;
+
+uint32_t* context_device_error(Context* ctx);
+
+namespace {
+
+constexpr int kChunkK = 512;                 // k per ring stage: 8 groups, one per consumer warp
+constexpr int kRowBytes = kChunkK / 2 + 32;  // 256 data bytes + 32 of padding
+constexpr int kStageWeights = 16 * kRowBytes;
+constexpr int kStageScales = 16 * 16;        // 8 fp16 scales per row
+constexpr int kStageBytes = kStageWeights + kStageScales;
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr uint32_t kSpinLimit = 1u << 18;    // polls of ~0.1 us: tens of milliseconds at most
+
+__device__ __forceinline__ uint32_t shared_address(const void* pointer) {
+  return (uint32_t)__cvta_generic_to_shared(pointer);
+}
+__device__ __forceinline__ void mbarrier_init(uint32_t barrier, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(barrier), "r"(count));
+}
+__device__ __forceinline__ void mbarrier_arrive(uint32_t barrier) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(barrier) : "memory");
+}
+__device__ __forceinline__ bool mbarrier_test(uint32_t barrier, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(barrier), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait: false (and an error word) if the phase never completed.
+__device__ __forceinline__ bool mbarrier_wait(uint32_t barrier, uint32_t parity, uint32_t* error_word) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    if (mbarrier_test(barrier, parity)) return true;
+  atomicExch(error_word, 1u);
+  return false;
+}
+// 16-byte asynchronous copy global -> shared (bypassing L1), and the arrival on an
+// mbarrier that fires once all earlier copies of this thread have landed.
+__device__ __forceinline__ void copy_16(uint32_t destination, const void* source) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(destination), "l"(source) : "memory");
+}
+__device__ __forceinline__ void arrive_when_copied(uint32_t barrier) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(barrier) : "memory");
+}
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// (word & mask) ^ constant with the exponent of 1024 (even nibbles) or 64 (odd
+// nibbles) and bit 3 of the nibble flipped: the halves read 1032 + q and 72 + q.
+__device__ __forceinline__ void nibbles_biased(uint32_t word, uint32_t& even_pair, uint32_t& odd_pair) {
+  even_pair = lop3_and_xor(word, 0x000F000Fu, 0x64086408u);
+  odd_pair = lop3_and_xor(word, 0x00F000F0u, 0x54805480u);
+}
+
+template <int NT, int NMAT, int EPI, bool SMALLX>
+__global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvProblem p, const uint32_t stage_count,
+                                                                   uint32_t* error_word) {
+  extern __shared__ __align__(16) unsigned char shared[];
+  constexpr int kAcc = NMAT * NT * 4;
+  const uint32_t groups = p.k >> 6;
+  // [full barriers | empty barriers] [ring] [reduce] [x fragments] [x bias]
+  uint64_t* barriers = reinterpret_cast<uint64_t*>(shared);
+  unsigned char* stages = shared + ((stage_count * 16u + 15u) & ~15u);
+  float* reduce = reinterpret_cast<float*>(stages + stage_count * (NMAT * kStageBytes));  // [8][kAcc][32]
+  uint4* x_fragments = reinterpret_cast<uint4*>(reduce + kConsumerWarps * kAcc * 32);     // [groups][2][x_rows][4]
+  float* x_bias = reinterpret_cast<float*>(x_fragments + (SMALLX ? groups * 2 * p.x_rows * 4 + 1 : 0));
+  const uint32_t full_base = shared_address(barriers);
+  const uint32_t empty_base = full_base + stage_count * 8u;
+
+  const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+  const uint32_t chunks_per_tile = p.k / kChunkK;
+  const uint32_t half_k = p.k >> 1;
+
+  uint32_t tiles[3] = {0, 0, 0}, total_tiles = 0;
+  if (EPI == kEpiQkv) {
+    for (uint32_t i = 0; i < p.matrices; ++i) {
+      tiles[i] = (p.mat[i].n + 15u) >> 4;
+      total_tiles += tiles[i];
+    }
+  } else {
+    tiles[0] = (p.mat[0].n + 15u) >> 4;
+    total_tiles = tiles[0];
+  }
+  const uint32_t my_tiles = blockIdx.x < total_tiles ? (total_tiles - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
+
+  auto locate = [&](uint32_t tile, uint32_t& matrix, uint32_t& local_tile) {
+    matrix = 0;
+    local_tile = tile;
+    if (EPI == kEpiQkv) {
+      if (local_tile >= tiles[0]) { local_tile -= tiles[0]; matrix = 1; }
+      if (matrix == 1 && local_tile >= tiles[1]) { local_tile -= tiles[1]; matrix = 2; }
+    }
+  };
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < stage_count; ++s) {
+      mbarrier_init(full_base + s * 8u, 32);                // one arrival per producer lane, when its copies land
+      mbarrier_init(empty_base + s * 8u, kConsumerWarps);   // one arrival per consumer warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------ producer ------------------------------
+    uint32_t stage = 0, parity = 1;  // a fresh "empty" barrier reads as released
+    bool aborted = false;
+    // per instruction the warp copies two 256-byte row pieces: lane -> (row pair member, 16-byte piece)
+    const uint32_t piece = (lane & 15u) * 16u, row_in_pair = lane >> 4;
+    for (uint32_t slot = 0; slot < my_tiles; ++slot) {
+      uint32_t matrix, local_tile;
+      locate(blockIdx.x + slot * gridDim.x, matrix, local_tile);
+      for (uint32_t chunk = 0; chunk < chunks_per_tile; ++chunk) {
+        if (!aborted) aborted = !mbarrier_wait(empty_base + stage * 8u, parity, error_word);
+        const uint32_t full = full_base + stage * 8u;
+        if (!aborted) {
+          const uint32_t target = shared_address(stages + stage * (NMAT * kStageBytes));
+#pragma unroll
+          for (int a = 0; a < NMAT; ++a) {
+            const GemvMatrix& mat = p.mat[EPI == kEpiQkv ? matrix : a];
+            const unsigned char* chunk_base = mat.packed + (size_t)chunk * (kChunkK / 2) + piece;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t row_in_tile = 2 * i + row_in_pair;
+              const uint32_t row = min(local_tile * 16u + row_in_tile, mat.n - 1u);
+              copy_16(target + a * kStageBytes + row_in_tile * kRowBytes + piece, chunk_base + (size_t)row * half_k);
+            }
+            if (lane < 16) {
+              const uint32_t row = min(local_tile * 16u + lane, mat.n - 1u);
+              copy_16(target + a * kStageBytes + kStageWeights + lane * 16,
+                      reinterpret_cast<const unsigned char*>(mat.scale + (size_t)row * groups) + chunk * 16);
+            }
+          }
+        }
+        arrive_when_copied(full);
+        if (++stage == stage_count) {
+          stage = 0;
+          parity ^= 1u;
+        }
+      }
+    }
+    // the copies must have landed before this warp's shared memory can go away
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    return;
+  }
+
+  // ------------------------------ consumers ------------------------------
+  const uint32_t r = lane >> 2, c = lane & 3u;
+  if (SMALLX) {
+    // activations -> shared in MMA fragment order: unit ((g*2 + h)*x_rows + row)*4 + c holds
+    // x[row][64g + 16c + 8h + {0,4,1,5,2,6,3,7}]
+    const uint32_t units = groups * 2 * p.x_rows * 4;
+    for (uint32_t unit = threadIdx.x; unit < units; unit += kConsumerWarps * 32) {
+      const uint32_t cc = unit & 3u, row = (unit >> 2) % p.x_rows, gh = (unit >> 2) / p.x_rows;
+      const uint4 source =
+          *reinterpret_cast<const uint4*>(p.x + (size_t)row * p.k + (gh >> 1) * 64 + cc * 16 + (gh & 1u) * 8);
+      uint4 permuted;
+      permuted.x = prmt(source.x, source.z, 0x5410u);
+      permuted.y = prmt(source.x, source.z, 0x7632u);
+      permuted.z = prmt(source.y, source.w, 0x5410u);
+      permuted.w = prmt(source.y, source.w, 0x7632u);
+      x_fragments[unit] = permuted;
+    }
+    for (uint32_t index = threadIdx.x; index < p.x_rows * groups; index += kConsumerWarps * 32) {
+      const uint32_t row = index / groups, g = index - row * groups;
+      const __half2* source = reinterpret_cast<const __half2*>(p.x + (size_t)row * p.k + (g << 6));
+      float even = 0.0f, odd = 0.0f;
+      for (int i = 0; i < 32; ++i) {
+        const float2 pair = __half22float2(source[i]);
+        even += pair.x;
+        odd += pair.y;
+      }
+      x_bias[index] = 1032.0f * even + 72.0f * odd;
+    }
+    if (threadIdx.x == 0) {
+      x_fragments[units] = make_uint4(0u, 0u, 0u, 0u);
+      x_bias[p.x_rows * groups] = 0.0f;
+    }
+    consumer_barrier();
+  }
+
+  float acc[NMAT][NT][4];
+#pragma unroll
+  for (int a = 0; a < NMAT; ++a)
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[a][t][j] = 0.0f;
+
+  uint32_t stage_index = 0, parity = 0;
+  bool aborted = false;
+  // this lane's fragment words inside a stage: rows r and r+8, bytes [warp*32 + c*8, +8)
+  const uint32_t word_offset = r * kRowBytes + warp * 32 + c * 8;
+  const uint32_t scale_offset = kStageWeights + r * 16 + warp * 2;
+  // SMALLX addressing: fragment unit of (group g, half h, row r, c) is ((g*2 + h)*x_rows + r)*4 + c
+  const uint32_t fragment_stride = 2 * p.x_rows * 4, fragment_lane = r * 4 + c;
+  const uint32_t zero_unit = groups * fragment_stride, zero_bias = p.x_rows * groups;
+  const bool has_row = r < p.x_rows, has_bias0 = 2 * c < p.x_rows, has_bias1 = 2 * c + 1 < p.x_rows;
+  const uint32_t bias_index0 = (2 * c) * groups, bias_index1 = (2 * c + 1) * groups;
+
+  for (uint32_t slot = 0; slot < my_tiles; ++slot) {
+    for (uint32_t chunk = 0; chunk < chunks_per_tile; ++chunk) {
+      if (!aborted) aborted = !mbarrier_wait(full_base + stage_index * 8u, parity, error_word);
+      const uint32_t g = chunk * 8 + warp;  // this warp's group
+      const unsigned char* stage = stages + stage_index * (NMAT * kStageBytes);
+
+      if (SMALLX) {
+        // lanes whose batch row does not exist read the zero unit / zero bias instead
+        const uint32_t unit = g * fragment_stride + fragment_lane;
+        const uint4 first = x_fragments[has_row ? unit : zero_unit];
+        const uint4 second = x_fragments[has_row ? unit + p.x_rows * 4 : zero_unit];
+        const uint32_t frag[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
+        const float bias0 = x_bias[has_bias0 ? bias_index0 + g : zero_bias];
+        const float bias1 = x_bias[has_bias1 ? bias_index1 + g : zero_bias];
+#pragma unroll
+        for (int a = 0; a < NMAT; ++a) {
+          const unsigned char* base = stage + a * kStageBytes;
+          const uint2 word_a = *reinterpret_cast<const uint2*>(base + word_offset);
+          const uint2 word_b = *reinterpret_cast<const uint2*>(base + word_offset + 8 * kRowBytes);
+          const float scale_a = __half2float(*reinterpret_cast<const __half*>(base + scale_offset));
+          const float scale_b = __half2float(*reinterpret_cast<const __half*>(base + scale_offset + 8 * 16));
+          // the group's bias term rides in as the accumulator's start value
+          float sum[4] = {-bias0, -bias1, -bias0, -bias1};
+          uint32_t a_even, a_odd, b_even, b_odd;
+          nibbles_biased(word_a.x, a_even, a_odd);
+          nibbles_biased(word_b.x, b_even, b_odd);
+          mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[0], frag[1]);
+          nibbles_biased(word_a.x >> 8, a_even, a_odd);
+          nibbles_biased(word_b.x >> 8, b_even, b_odd);
+          mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[2], frag[3]);
+          nibbles_biased(word_a.y, a_even, a_odd);
+          nibbles_biased(word_b.y, b_even, b_odd);
+          mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[4], frag[5]);
+          nibbles_biased(word_a.y >> 8, a_even, a_odd);
+          nibbles_biased(word_b.y >> 8, b_even, b_odd);
+          mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[6], frag[7]);
+          acc[a][0][0] = fmaf(scale_a, sum[0], acc[a][0][0]);
+          acc[a][0][1] = fmaf(scale_a, sum[1], acc[a][0][1]);
+          acc[a][0][2] = fmaf(scale_b, sum[2], acc[a][0][2]);
+          acc[a][0][3] = fmaf(scale_b, sum[3], acc[a][0][3]);
+        }
+      } else {
+        uint32_t a_frag[NMAT][4][4];
+        float scale_a[NMAT], scale_b[NMAT];
+#pragma unroll
+        for (int a = 0; a < NMAT; ++a) {
+          const unsigned char* base = stage + a * kStageBytes;
+          const uint2 word_a = *reinterpret_cast<const uint2*>(base + word_offset);
+          const uint2 word_b = *reinterpret_cast<const uint2*>(base + word_offset + 8 * kRowBytes);
+          scale_a[a] = __half2float(*reinterpret_cast<const __half*>(base + scale_offset));
+          scale_b[a] = __half2float(*reinterpret_cast<const __half*>(base + scale_offset + 8 * 16));
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+            uint32_t bits_a = w == 0 ? word_a.x : word_a.y;
+            uint32_t bits_b = w == 0 ? word_b.x : word_b.y;
+#pragma unroll
+            for (int step = 0; step < 2; ++step) {
+              nibbles_to_half2<true>(bits_a, a_frag[a][w * 2 + step][0], a_frag[a][w * 2 + step][2]);
+              nibbles_to_half2<true>(bits_b, a_frag[a][w * 2 + step][1], a_frag[a][w * 2 + step][3]);
+              bits_a >>= 8;
+              bits_b >>= 8;
+            }
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          const uint32_t batch_row = t * 8 + r;
+          uint4 first = make_uint4(0u, 0u, 0u, 0u), second = first;
+          if (batch_row < p.x_rows) {
+            const uint4* source = reinterpret_cast<const uint4*>(p.x + (size_t)batch_row * p.k + (g << 6) + (c << 4));
+            first = __ldg(source);
+            second = __ldg(source + 1);
+          }
+          uint32_t frag[8];
+          frag[0] = prmt(first.x, first.z, 0x5410u);
+          frag[1] = prmt(first.x, first.z, 0x7632u);
+          frag[2] = prmt(first.y, first.w, 0x5410u);
+          frag[3] = prmt(first.y, first.w, 0x7632u);
+          frag[4] = prmt(second.x, second.z, 0x5410u);
+          frag[5] = prmt(second.x, second.z, 0x7632u);
+          frag[6] = prmt(second.y, second.w, 0x5410u);
+          frag[7] = prmt(second.y, second.w, 0x7632u);
+#pragma unroll
+          for (int a = 0; a < NMAT; ++a) {
+            float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              mma_16816(sum, a_frag[a][i][0], a_frag[a][i][1], a_frag[a][i][2], a_frag[a][i][3], frag[2 * i],
+                        frag[2 * i + 1]);
+            acc[a][t][0] = fmaf(scale_a[a], sum[0], acc[a][t][0]);
+            acc[a][t][1] = fmaf(scale_a[a], sum[1], acc[a][t][1]);
+            acc[a][t][2] = fmaf(scale_b[a], sum[2], acc[a][t][2]);
+            acc[a][t][3] = fmaf(scale_b[a], sum[3], acc[a][t][3]);
+          }
+        }
+      }
+
+      // the stage's words are in registers: hand it back to the producer
+      __syncwarp();
+      if (lane == 0) mbarrier_arrive(empty_base + stage_index * 8u);
+      if (++stage_index == stage_count) {
+        stage_index = 0;
+        parity ^= 1u;
+      }
+    }
+
+    // tile finished: fixed-order sum of the eight warps' partials, then the writeback
+    consumer_barrier();  // the previous tile's reader is done with the buffer
+#pragma unroll
+    for (int a = 0; a < NMAT; ++a)
+#pragma unroll
+      for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          reduce[(warp * kAcc + (a * NT + t) * 4 + j) * 32 + lane] = acc[a][t][j];
+          acc[a][t][j] = 0.0f;
+        }
+    consumer_barrier();
+    // the reducing warp rotates with the tile so no warp is always the late one
+    if (warp == (slot & 7u)) {
+      float total[NMAT][NT][4];
+#pragma unroll
+      for (int a = 0; a < NMAT; ++a)
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) sum += reduce[(w * kAcc + (a * NT + t) * 4 + j) * 32 + lane];
+            total[a][t][j] = sum;
+          }
+      uint32_t matrix, local_tile;
+      locate(blockIdx.x + slot * gridDim.x, matrix, local_tile);
+      write_tile<NT, NMAT, EPI>(p, total, matrix, local_tile, p.mat[EPI == kEpiQkv ? matrix : 0].n, lane);
+    }
+  }
+}
+
+struct PipePlan {
+  size_t shared_bytes;
+  uint32_t ctas;
+  uint32_t stages;
+};
+
+// Ring depth and grid: the CTA count that gives every CTA the same number of
+// tiles, and the deepest ring that (a) fits beside the other resident CTAs and
+// (b) is not longer than the chunks one CTA streams.
+template <int NT, int NMAT, int EPI, bool SMALLX>
+bool plan_pipe(const KernelArgs& args, const GemvProblem& p, PipePlan* plan) {
+  uint32_t total_tiles = 0;
+  const uint32_t matrices = EPI == kEpiQkv ? p.matrices : 1u;
+  for (uint32_t i = 0; i < matrices; ++i) total_tiles += (p.mat[i].n + 15u) / 16u;
+  const uint32_t groups = p.k / 64;
+  size_t fixed_bytes = (size_t)kConsumerWarps * NMAT * NT * 4 * 32 * sizeof(float) + 64;
+  if (SMALLX) fixed_bytes += (size_t)groups * 2 * p.x_rows * 4 * 16 + 16 + (size_t)(p.x_rows * groups + 4) * sizeof(float);
+  const size_t stage_bytes = (size_t)NMAT * kStageBytes + 16;
+  const uint32_t sms = (uint32_t)context_sm_count(args.ctx);
+  constexpr size_t kSharedPerSm = 220 * 1024;  // usable shared memory of one SM
+  const uint32_t chunks_per_tile = p.k / kChunkK;
+  // Consumer warps are the scarce resource (the math is issue-bound), bytes in flight the
+  // second: take the most resident CTAs per SM (up to 3) whose ring still holds at least
+  // four stages, and launch one CTA per slot so no slot idles in the first rounds.
+  PipePlan best = {0, 0, 0};
+  for (uint32_t resident = 3; resident >= 1; --resident) {
+    const size_t per_cta = kSharedPerSm / resident - 1024;
+    if (per_cta <= fixed_bytes + 2 * stage_bytes) continue;
+    uint32_t stages = (uint32_t)((per_cta - fixed_bytes) / stage_bytes);
+    if (stages < 4 && resident > 1) continue;
+    const uint32_t slots = sms * resident;
+    const uint32_t ctas = total_tiles < slots ? total_tiles : slots;
+    const uint32_t chunks = ((total_tiles + ctas - 1u) / ctas) * chunks_per_tile;
+    if (stages > chunks) stages = chunks < 2 ? 2 : chunks;
+    if (stages > 32) stages = 32;
+    best.shared_bytes = fixed_bytes + stages * stage_bytes;
+    best.ctas = ctas == 0 ? 1 : ctas;
+    best.stages = stages;
+    break;
+  }
+  if (best.stages < 2) return false;
+  *plan = best;
+  return true;
+}
+
+template <int NT, int NMAT, int EPI, bool SMALLX>
+int launch_pipe(const KernelArgs& args, const GemvProblem& p) {
+  PipePlan plan;
+  if (!plan_pipe<NT, NMAT, EPI, SMALLX>(args, p, &plan)) return -1;
+  auto kernel = w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.shared_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  kernel<<<plan.ctas, kThreads, plan.shared_bytes, args.stream>>>(p, plan.stages, context_device_error(args.ctx));
+  return check_launch(args);
+}
+
+template <int EPI, int NMAT>
+int launch_pipe_by_rows(const KernelArgs& args, const GemvProblem& p) {
+  const uint32_t rows = p.x_rows;
+  const bool small = (size_t)rows * p.k <= 16384 && rows <= 8 && EPI != kEpiSplitF32;
+  if (rows <= 8) {
+    if (small) return launch_pipe<1, NMAT, EPI, true>(args, p);
+    return launch_pipe<1, NMAT, EPI, false>(args, p);
+  }
+  if (rows <= 16) return launch_pipe<2, NMAT, EPI, false>(args, p);
+  if (rows <= 32) return launch_pipe<4, NMAT, EPI, false>(args, p);
+  return -1;  // 33..64 rows stay on the direct-load kernel
+}
+
+}  // namespace
+
+// Returns -1 when the shape is outside this kernel's domain (the caller then
+// uses the direct-load kernel), 0 on success, 1 on a launch failure.
+int launch_w4a16_gemv_pipe(const KernelArgs& args, const GemvProblem& problem, int epilogue) {
+  if (args.ctx == nullptr || problem.k % kChunkK != 0) return -1;
+  const uint32_t matrices = epilogue == kEpiQkv ? problem.matrices : (epilogue == kEpiDualSwiglu ? 2u : 1u);
+  for (uint32_t i = 0; i < matrices; ++i) {
+    if (((uintptr_t)problem.mat[i].packed & 15u) != 0 || ((uintptr_t)problem.mat[i].scale & 15u) != 0) return -1;
+    if (problem.mat[i].n == 0) return -1;
+  }
+  if (((uintptr_t)problem.x & 15u) != 0) return -1;
+  switch (epilogue) {
+    case kEpiLinear: return launch_pipe_by_rows<kEpiLinear, 1>(args, problem);
+    case kEpiQkv: return launch_pipe_by_rows<kEpiQkv, 1>(args, problem);
+    case kEpiDualSwiglu: return launch_pipe_by_rows<kEpiDualSwiglu, 2>(args, problem);
+    case kEpiTagged: return launch_pipe_by_rows<kEpiTagged, 1>(args, problem);
+    case kEpiSplitF32: return launch_pipe_by_rows<kEpiSplitF32, 1>(args, problem);
+    default: return -1;
+  }
+}
+
+}  // namespace llmopt

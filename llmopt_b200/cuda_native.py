@@ -109,6 +109,7 @@ SIGNATURES = {
     "llmopt_cuda_w4a16_linear": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P]),
     "llmopt_cuda_attention_q8_paged_static": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, ctypes.c_uint32, _P]),
     "llmopt_cuda_time_dispatch": (_I, [_P, _REC, _I, _I, _I, ctypes.POINTER(ctypes.c_float)]),
+    "llmopt_cuda_time_dispatches": (_I, [_P, _REC, _SZ, _I, _I, ctypes.POINTER(ctypes.c_float)]),
 }
 
 
@@ -331,6 +332,15 @@ class Runtime:
         out = ctypes.c_float()
         _check(load_library().llmopt_cuda_time_dispatch(
             self._library, records.array, warmup, iterations, int(flush_l2), ctypes.byref(out)))
+        return float(out.value)
+
+    def time_dispatches(self, items: Sequence[DispatchItem], *, warmup: int = 2, iterations: int = 5) -> float:
+        """Average device milliseconds per dispatch of a list run back to back (one
+        pair of CUDA events around the list)."""
+        records = _RecordArray(items)
+        out = ctypes.c_float()
+        _check(load_library().llmopt_cuda_time_dispatches(
+            self._library, records.array, len(records), warmup, iterations, ctypes.byref(out)))
         return float(out.value)
 
     def w4a16_linear_pointers(self, x_ptr: int, packed_ptr: int, scale_ptr: int, bias_ptr: Optional[int],

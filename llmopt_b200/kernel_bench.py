@@ -126,12 +126,29 @@ def main() -> None:
     parser.add_argument("--iters", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--no-flush", action="store_true")
+    parser.add_argument("--copies", type=int, default=1,
+                        help="distinct operand sets launched back to back (total should exceed the L2 several times)")
     args = parser.parse_args()
     runtime = cuda_native.Runtime()
     item, nbytes, _keep = build_item(runtime, args)
-    milliseconds = runtime.time_dispatch(item, warmup=args.warmup, iterations=args.iters, flush_l2=not args.no_flush)
-    print(json.dumps({"op": args.op, "kernel": item.name, "m": args.m, "k": args.k, "n": args.n, "ms": milliseconds,
-                      "algorithmic_bytes": nbytes, "gbs": nbytes / milliseconds / 1e6}))
+    result = {"op": args.op, "kernel": item.name, "m": args.m, "k": args.k, "n": args.n, "algorithmic_bytes": nbytes}
+    if args.copies > 1:
+        # distinct operands per launch, launched back to back: in-plan conditions (cold
+        # operands because the set exceeds the L2, launch gaps as in a replayed plan)
+        keep, items = [_keep], [item]
+        for _ in range(args.copies - 1):
+            other, _, context = build_item(runtime, args)
+            keep.append(context)
+            items.append(other)
+        milliseconds = runtime.time_dispatches(items, warmup=args.warmup, iterations=args.iters)
+        result.update({"mode": f"{args.copies} distinct operand sets back to back", "ms": milliseconds,
+                       "gbs": nbytes / milliseconds / 1e6})
+    else:
+        milliseconds = runtime.time_dispatch(item, warmup=args.warmup, iterations=args.iters,
+                                             flush_l2=not args.no_flush)
+        result.update({"mode": "isolated launch, L2 flushed before each", "ms": milliseconds,
+                       "gbs": nbytes / milliseconds / 1e6})
+    print(json.dumps(result))
 
 
 if __name__ == "__main__":
