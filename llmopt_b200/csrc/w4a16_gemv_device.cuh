@@ -108,5 +108,38 @@ __device__ __forceinline__ void write_tile(const GemvProblem& p, float (&acc)[NM
     }
 }
 
+// The same writeback for ONE accumulator position (batch tile t, register j, lane):
+// `value[a]` are the finished sums of the NMAT matrices at that position and
+// `partner` the sum at lane ^ 2 (only read by the split-fp32 form).
+template <int NT, int NMAT, int EPI>
+__device__ __forceinline__ void write_position(const GemvProblem& p, const float (&value)[NMAT], float partner,
+                                               uint32_t matrix, uint32_t local_tile, uint32_t n, uint32_t t,
+                                               uint32_t j, uint32_t lane) {
+  const uint32_t r = lane >> 2, c = lane & 3u;
+  const uint32_t column = local_tile * 16u + r + ((j & 2) ? 8u : 0u);
+  if (EPI == kEpiSplitF32) {
+    const uint32_t row = t * 4 + 2 * c + (j & 1);
+    if (c < 2 && row < p.m && column < n) p.out_f32[(size_t)row * n + column] = value[0] + partner;
+    return;
+  }
+  const uint32_t row = t * 8 + 2 * c + (j & 1);
+  if (row >= p.m || column >= n) return;
+  if (EPI == kEpiLinear) {
+    float result = value[0];
+    if (p.has_aux) result += __half2float(p.aux0[(size_t)row * p.aux_row_stride + column]);
+    p.out[0][(size_t)row * n + column] = __float2half_rn(result);
+  } else if (EPI == kEpiQkv) {
+    p.out[matrix][(size_t)row * n + column] = __float2half_rn(value[0]);
+  } else if (EPI == kEpiDualSwiglu) {
+    const float gate = value[0], up = value[NMAT - 1];
+    const float silu = gate / (1.0f + expf(-gate));
+    p.out[0][(size_t)row * n + column] = __float2half_rn(silu * up);
+  } else if (EPI == kEpiTagged) {
+    const float first = p.aux0 ? __half2float(p.aux0[column]) : 0.0f;
+    const float second = p.aux1 ? __half2float(p.aux1[column]) : 0.0f;
+    p.out[0][(size_t)row * n + column] = __float2half_rn(epilogue_tagged(p.tag, value[0], first, second));
+  }
+}
+
 }  // namespace gemv
 }  // namespace llmopt

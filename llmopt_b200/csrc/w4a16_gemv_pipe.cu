@@ -38,11 +38,17 @@ uint32_t* context_device_error(Context* ctx);
 
 namespace {
 
-constexpr int kChunkK = 512;                 // k per ring stage: 8 groups, one per consumer warp
-constexpr int kRowBytes = kChunkK / 2 + 32;  // 256 data bytes + 32 of padding
-constexpr int kStageWeights = 16 * kRowBytes;
-constexpr int kStageScales = 16 * 16;        // 8 fp16 scales per row
-constexpr int kStageBytes = kStageWeights + kStageScales;
+// A ring stage holds GPW groups of 64 k for each of the 8 consumer warps:
+// 512*GPW k of 16 weight rows (+32 bytes of padding per row) and their scales.
+// More groups per warp and stage = more independent work per wait (the math of
+// one group is a dependent chain) and less per-stage overhead.
+template <int GPW> struct Stage {
+  static constexpr int kChunkK = 512 * GPW;
+  static constexpr int kRowBytes = kChunkK / 2 + 32;
+  static constexpr int kWeights = 16 * kRowBytes;
+  static constexpr int kScaleRow = 16 * GPW;  // 8*GPW fp16 scales per row
+  static constexpr int kBytes = kWeights + 16 * kScaleRow;
+};
 constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr uint32_t kSpinLimit = 1u << 18;    // polls of ~0.1 us: tens of milliseconds at most
@@ -89,11 +95,14 @@ __device__ __forceinline__ void nibbles_biased(uint32_t word, uint32_t& even_pai
   odd_pair = lop3_and_xor(word, 0x00F000F0u, 0x54805480u);
 }
 
-template <int NT, int NMAT, int EPI, bool SMALLX>
+template <int NT, int NMAT, int EPI, bool SMALLX, int GPW>
 __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvProblem p, const uint32_t stage_count,
                                                                    uint32_t* error_word) {
   extern __shared__ __align__(16) unsigned char shared[];
   constexpr int kAcc = NMAT * NT * 4;
+  constexpr int kChunkK = Stage<GPW>::kChunkK, kRowBytes = Stage<GPW>::kRowBytes;
+  constexpr int kStageWeights = Stage<GPW>::kWeights, kScaleRow = Stage<GPW>::kScaleRow;
+  constexpr int kStageBytes = Stage<GPW>::kBytes;
   const uint32_t groups = p.k >> 6;
   // [full barriers | empty barriers] [ring] [reduce] [x fragments] [x bias]
   uint64_t* barriers = reinterpret_cast<uint64_t*>(shared);
@@ -142,8 +151,6 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
     // ------------------------------ producer ------------------------------
     uint32_t stage = 0, parity = 1;  // a fresh "empty" barrier reads as released
     bool aborted = false;
-    // per instruction the warp copies two 256-byte row pieces: lane -> (row pair member, 16-byte piece)
-    const uint32_t piece = (lane & 15u) * 16u, row_in_pair = lane >> 4;
     for (uint32_t slot = 0; slot < my_tiles; ++slot) {
       uint32_t matrix, local_tile;
       locate(blockIdx.x + slot * gridDim.x, matrix, local_tile);
@@ -155,17 +162,38 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
 #pragma unroll
           for (int a = 0; a < NMAT; ++a) {
             const GemvMatrix& mat = p.mat[EPI == kEpiQkv ? matrix : a];
-            const unsigned char* chunk_base = mat.packed + (size_t)chunk * (kChunkK / 2) + piece;
+            // one warp instruction copies 512 contiguous bytes of one row
+            constexpr int kPerRow = kChunkK / 2 / 512;  // instructions per row piece (GPW/2, at least... see below)
+            if (kPerRow >= 1) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const uint32_t row_in_tile = 2 * i + row_in_pair;
-              const uint32_t row = min(local_tile * 16u + row_in_tile, mat.n - 1u);
-              copy_16(target + a * kStageBytes + row_in_tile * kRowBytes + piece, chunk_base + (size_t)row * half_k);
+              for (int row_in_tile = 0; row_in_tile < 16; ++row_in_tile) {
+                const uint32_t row = min(local_tile * 16u + row_in_tile, mat.n - 1u);
+                const unsigned char* source = mat.packed + (size_t)row * half_k + (size_t)chunk * (kChunkK / 2) + lane * 16;
+#pragma unroll
+                for (int part = 0; part < (kPerRow >= 1 ? kPerRow : 1); ++part)
+                  copy_16(target + a * kStageBytes + row_in_tile * kRowBytes + part * 512 + lane * 16, source + part * 512);
+              }
+            } else {
+              // 256-byte row pieces: two rows per instruction
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const uint32_t row_in_tile = 2 * i + (lane >> 4);
+                const uint32_t row = min(local_tile * 16u + row_in_tile, mat.n - 1u);
+                copy_16(target + a * kStageBytes + row_in_tile * kRowBytes + (lane & 15u) * 16,
+                        mat.packed + (size_t)row * half_k + (size_t)chunk * (kChunkK / 2) + (lane & 15u) * 16);
+              }
             }
-            if (lane < 16) {
-              const uint32_t row = min(local_tile * 16u + lane, mat.n - 1u);
-              copy_16(target + a * kStageBytes + kStageWeights + lane * 16,
-                      reinterpret_cast<const unsigned char*>(mat.scale + (size_t)row * groups) + chunk * 16);
+            // scales: 16 rows x kScaleRow bytes = 16*GPW sixteen-byte pieces
+#pragma unroll
+            for (int i = 0; i < (16 * GPW + 31) / 32; ++i) {
+              const uint32_t piece = i * 32 + lane;
+              if (piece < 16u * GPW) {
+                const uint32_t row_in_tile = piece / GPW, part = piece % GPW;
+                const uint32_t row = min(local_tile * 16u + row_in_tile, mat.n - 1u);
+                copy_16(target + a * kStageBytes + kStageWeights + row_in_tile * kScaleRow + part * 16,
+                        reinterpret_cast<const unsigned char*>(mat.scale + (size_t)row * groups) +
+                            (size_t)chunk * kScaleRow + part * 16);
+              }
             }
           }
         }
@@ -198,15 +226,24 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
       permuted.w = prmt(source.y, source.w, 0x7632u);
       x_fragments[unit] = permuted;
     }
+    consumer_barrier();
+    // per (row, group): 1032 * sum of the even-k activations + 72 * sum of the odd-k ones, read
+    // back from the fragment units (words x, z hold even k, words y, w odd k), fixed order
     for (uint32_t index = threadIdx.x; index < p.x_rows * groups; index += kConsumerWarps * 32) {
       const uint32_t row = index / groups, g = index - row * groups;
-      const __half2* source = reinterpret_cast<const __half2*>(p.x + (size_t)row * p.k + (g << 6));
       float even = 0.0f, odd = 0.0f;
-      for (int i = 0; i < 32; ++i) {
-        const float2 pair = __half22float2(source[i]);
-        even += pair.x;
-        odd += pair.y;
-      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const uint4 unit_words = x_fragments[((g * 2 + h) * p.x_rows + row) * 4 + cc];
+          const float2 e0 = __half22float2(*reinterpret_cast<const __half2*>(&unit_words.x));
+          const float2 o0 = __half22float2(*reinterpret_cast<const __half2*>(&unit_words.y));
+          const float2 e1 = __half22float2(*reinterpret_cast<const __half2*>(&unit_words.z));
+          const float2 o1 = __half22float2(*reinterpret_cast<const __half2*>(&unit_words.w));
+          even += (e0.x + e0.y) + (e1.x + e1.y);
+          odd += (o0.x + o0.y) + (o1.x + o1.y);
+        }
       x_bias[index] = 1032.0f * even + 72.0f * odd;
     }
     if (threadIdx.x == 0) {
@@ -226,108 +263,118 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
 
   uint32_t stage_index = 0, parity = 0;
   bool aborted = false;
-  // this lane's fragment words inside a stage: rows r and r+8, bytes [warp*32 + c*8, +8)
-  const uint32_t word_offset = r * kRowBytes + warp * 32 + c * 8;
-  const uint32_t scale_offset = kStageWeights + r * 16 + warp * 2;
+  // this lane's fragment words inside a stage: rows r and r+8, bytes [group*32 + c*8, +8) of
+  // the warp's first group (group index in the stage = warp*GPW + j)
+  const uint32_t word_offset = r * kRowBytes + warp * GPW * 32 + c * 8;
+  const uint32_t scale_offset = kStageWeights + r * kScaleRow + warp * GPW * 2;
   // SMALLX addressing: fragment unit of (group g, half h, row r, c) is ((g*2 + h)*x_rows + r)*4 + c
   const uint32_t fragment_stride = 2 * p.x_rows * 4, fragment_lane = r * 4 + c;
+  // lanes whose batch row does not exist read the zero unit / zero bias: base + g * stride
+  // with stride 0 and the base pointing at the zero entry, so no select is needed per group
   const uint32_t zero_unit = groups * fragment_stride, zero_bias = p.x_rows * groups;
   const bool has_row = r < p.x_rows, has_bias0 = 2 * c < p.x_rows, has_bias1 = 2 * c + 1 < p.x_rows;
-  const uint32_t bias_index0 = (2 * c) * groups, bias_index1 = (2 * c + 1) * groups;
+  const uint4* first_base = x_fragments + (has_row ? fragment_lane : zero_unit);
+  const uint4* second_base = x_fragments + (has_row ? fragment_lane + p.x_rows * 4 : zero_unit);
+  const uint32_t unit_stride = has_row ? fragment_stride : 0u;
+  const float* bias_base0 = x_bias + (has_bias0 ? (2 * c) * groups : zero_bias);
+  const float* bias_base1 = x_bias + (has_bias1 ? (2 * c + 1) * groups : zero_bias);
+  const uint32_t bias_stride0 = has_bias0 ? 1u : 0u, bias_stride1 = has_bias1 ? 1u : 0u;
 
   for (uint32_t slot = 0; slot < my_tiles; ++slot) {
     for (uint32_t chunk = 0; chunk < chunks_per_tile; ++chunk) {
       if (!aborted) aborted = !mbarrier_wait(full_base + stage_index * 8u, parity, error_word);
-      const uint32_t g = chunk * 8 + warp;  // this warp's group
       const unsigned char* stage = stages + stage_index * (NMAT * kStageBytes);
-
-      if (SMALLX) {
-        // lanes whose batch row does not exist read the zero unit / zero bias instead
-        const uint32_t unit = g * fragment_stride + fragment_lane;
-        const uint4 first = x_fragments[has_row ? unit : zero_unit];
-        const uint4 second = x_fragments[has_row ? unit + p.x_rows * 4 : zero_unit];
-        const uint32_t frag[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
-        const float bias0 = x_bias[has_bias0 ? bias_index0 + g : zero_bias];
-        const float bias1 = x_bias[has_bias1 ? bias_index1 + g : zero_bias];
 #pragma unroll
-        for (int a = 0; a < NMAT; ++a) {
-          const unsigned char* base = stage + a * kStageBytes;
-          const uint2 word_a = *reinterpret_cast<const uint2*>(base + word_offset);
-          const uint2 word_b = *reinterpret_cast<const uint2*>(base + word_offset + 8 * kRowBytes);
-          const float scale_a = __half2float(*reinterpret_cast<const __half*>(base + scale_offset));
-          const float scale_b = __half2float(*reinterpret_cast<const __half*>(base + scale_offset + 8 * 16));
-          // the group's bias term rides in as the accumulator's start value
-          float sum[4] = {-bias0, -bias1, -bias0, -bias1};
-          uint32_t a_even, a_odd, b_even, b_odd;
-          nibbles_biased(word_a.x, a_even, a_odd);
-          nibbles_biased(word_b.x, b_even, b_odd);
-          mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[0], frag[1]);
-          nibbles_biased(word_a.x >> 8, a_even, a_odd);
-          nibbles_biased(word_b.x >> 8, b_even, b_odd);
-          mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[2], frag[3]);
-          nibbles_biased(word_a.y, a_even, a_odd);
-          nibbles_biased(word_b.y, b_even, b_odd);
-          mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[4], frag[5]);
-          nibbles_biased(word_a.y >> 8, a_even, a_odd);
-          nibbles_biased(word_b.y >> 8, b_even, b_odd);
-          mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[6], frag[7]);
-          acc[a][0][0] = fmaf(scale_a, sum[0], acc[a][0][0]);
-          acc[a][0][1] = fmaf(scale_a, sum[1], acc[a][0][1]);
-          acc[a][0][2] = fmaf(scale_b, sum[2], acc[a][0][2]);
-          acc[a][0][3] = fmaf(scale_b, sum[3], acc[a][0][3]);
-        }
-      } else {
-        uint32_t a_frag[NMAT][4][4];
-        float scale_a[NMAT], scale_b[NMAT];
-#pragma unroll
-        for (int a = 0; a < NMAT; ++a) {
-          const unsigned char* base = stage + a * kStageBytes;
-          const uint2 word_a = *reinterpret_cast<const uint2*>(base + word_offset);
-          const uint2 word_b = *reinterpret_cast<const uint2*>(base + word_offset + 8 * kRowBytes);
-          scale_a[a] = __half2float(*reinterpret_cast<const __half*>(base + scale_offset));
-          scale_b[a] = __half2float(*reinterpret_cast<const __half*>(base + scale_offset + 8 * 16));
-#pragma unroll
-          for (int w = 0; w < 2; ++w) {
-            uint32_t bits_a = w == 0 ? word_a.x : word_a.y;
-            uint32_t bits_b = w == 0 ? word_b.x : word_b.y;
-#pragma unroll
-            for (int step = 0; step < 2; ++step) {
-              nibbles_to_half2<true>(bits_a, a_frag[a][w * 2 + step][0], a_frag[a][w * 2 + step][2]);
-              nibbles_to_half2<true>(bits_b, a_frag[a][w * 2 + step][1], a_frag[a][w * 2 + step][3]);
-              bits_a >>= 8;
-              bits_b >>= 8;
-            }
-          }
-        }
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          const uint32_t batch_row = t * 8 + r;
-          uint4 first = make_uint4(0u, 0u, 0u, 0u), second = first;
-          if (batch_row < p.x_rows) {
-            const uint4* source = reinterpret_cast<const uint4*>(p.x + (size_t)batch_row * p.k + (g << 6) + (c << 4));
-            first = __ldg(source);
-            second = __ldg(source + 1);
-          }
-          uint32_t frag[8];
-          frag[0] = prmt(first.x, first.z, 0x5410u);
-          frag[1] = prmt(first.x, first.z, 0x7632u);
-          frag[2] = prmt(first.y, first.w, 0x5410u);
-          frag[3] = prmt(first.y, first.w, 0x7632u);
-          frag[4] = prmt(second.x, second.z, 0x5410u);
-          frag[5] = prmt(second.x, second.z, 0x7632u);
-          frag[6] = prmt(second.y, second.w, 0x5410u);
-          frag[7] = prmt(second.y, second.w, 0x7632u);
+      for (int jg = 0; jg < GPW; ++jg) {
+        const uint32_t g = (chunk * 8 + warp) * GPW + jg;  // one of this warp's groups
+        if (SMALLX) {
+          const uint4 first = first_base[g * unit_stride];
+          const uint4 second = second_base[g * unit_stride];
+          const uint32_t frag[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
+          const float bias0 = bias_base0[g * bias_stride0];
+          const float bias1 = bias_base1[g * bias_stride1];
 #pragma unroll
           for (int a = 0; a < NMAT; ++a) {
-            float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const unsigned char* base = stage + a * kStageBytes;
+            const uint2 word_a = *reinterpret_cast<const uint2*>(base + word_offset + jg * 32);
+            const uint2 word_b = *reinterpret_cast<const uint2*>(base + word_offset + jg * 32 + 8 * kRowBytes);
+            const float scale_a = __half2float(*reinterpret_cast<const __half*>(base + scale_offset + jg * 2));
+            const float scale_b =
+                __half2float(*reinterpret_cast<const __half*>(base + scale_offset + jg * 2 + 8 * kScaleRow));
+            // the group's bias term rides in as the accumulator's start value
+            float sum[4] = {-bias0, -bias1, -bias0, -bias1};
+            uint32_t a_even, a_odd, b_even, b_odd;
+            nibbles_biased(word_a.x, a_even, a_odd);
+            nibbles_biased(word_b.x, b_even, b_odd);
+            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[0], frag[1]);
+            nibbles_biased(word_a.x >> 8, a_even, a_odd);
+            nibbles_biased(word_b.x >> 8, b_even, b_odd);
+            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[2], frag[3]);
+            nibbles_biased(word_a.y, a_even, a_odd);
+            nibbles_biased(word_b.y, b_even, b_odd);
+            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[4], frag[5]);
+            nibbles_biased(word_a.y >> 8, a_even, a_odd);
+            nibbles_biased(word_b.y >> 8, b_even, b_odd);
+            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[6], frag[7]);
+            acc[a][0][0] = fmaf(scale_a, sum[0], acc[a][0][0]);
+            acc[a][0][1] = fmaf(scale_a, sum[1], acc[a][0][1]);
+            acc[a][0][2] = fmaf(scale_b, sum[2], acc[a][0][2]);
+            acc[a][0][3] = fmaf(scale_b, sum[3], acc[a][0][3]);
+          }
+        } else {
+          uint32_t a_frag[NMAT][4][4];
+          float scale_a[NMAT], scale_b[NMAT];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              mma_16816(sum, a_frag[a][i][0], a_frag[a][i][1], a_frag[a][i][2], a_frag[a][i][3], frag[2 * i],
-                        frag[2 * i + 1]);
-            acc[a][t][0] = fmaf(scale_a[a], sum[0], acc[a][t][0]);
-            acc[a][t][1] = fmaf(scale_a[a], sum[1], acc[a][t][1]);
-            acc[a][t][2] = fmaf(scale_b[a], sum[2], acc[a][t][2]);
-            acc[a][t][3] = fmaf(scale_b[a], sum[3], acc[a][t][3]);
+          for (int a = 0; a < NMAT; ++a) {
+            const unsigned char* base = stage + a * kStageBytes;
+            const uint2 word_a = *reinterpret_cast<const uint2*>(base + word_offset + jg * 32);
+            const uint2 word_b = *reinterpret_cast<const uint2*>(base + word_offset + jg * 32 + 8 * kRowBytes);
+            scale_a[a] = __half2float(*reinterpret_cast<const __half*>(base + scale_offset + jg * 2));
+            scale_b[a] = __half2float(*reinterpret_cast<const __half*>(base + scale_offset + jg * 2 + 8 * kScaleRow));
+#pragma unroll
+            for (int w = 0; w < 2; ++w) {
+              uint32_t bits_a = w == 0 ? word_a.x : word_a.y;
+              uint32_t bits_b = w == 0 ? word_b.x : word_b.y;
+#pragma unroll
+              for (int step = 0; step < 2; ++step) {
+                nibbles_to_half2<true>(bits_a, a_frag[a][w * 2 + step][0], a_frag[a][w * 2 + step][2]);
+                nibbles_to_half2<true>(bits_b, a_frag[a][w * 2 + step][1], a_frag[a][w * 2 + step][3]);
+                bits_a >>= 8;
+                bits_b >>= 8;
+              }
+            }
+          }
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            const uint32_t batch_row = t * 8 + r;
+            uint4 first = make_uint4(0u, 0u, 0u, 0u), second = first;
+            if (batch_row < p.x_rows) {
+              const uint4* source =
+                  reinterpret_cast<const uint4*>(p.x + (size_t)batch_row * p.k + (g << 6) + (c << 4));
+              first = __ldg(source);
+              second = __ldg(source + 1);
+            }
+            uint32_t frag[8];
+            frag[0] = prmt(first.x, first.z, 0x5410u);
+            frag[1] = prmt(first.x, first.z, 0x7632u);
+            frag[2] = prmt(first.y, first.w, 0x5410u);
+            frag[3] = prmt(first.y, first.w, 0x7632u);
+            frag[4] = prmt(second.x, second.z, 0x5410u);
+            frag[5] = prmt(second.x, second.z, 0x7632u);
+            frag[6] = prmt(second.y, second.w, 0x5410u);
+            frag[7] = prmt(second.y, second.w, 0x7632u);
+#pragma unroll
+            for (int a = 0; a < NMAT; ++a) {
+              float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                mma_16816(sum, a_frag[a][i][0], a_frag[a][i][1], a_frag[a][i][2], a_frag[a][i][3], frag[2 * i],
+                          frag[2 * i + 1]);
+              acc[a][t][0] = fmaf(scale_a[a], sum[0], acc[a][t][0]);
+              acc[a][t][1] = fmaf(scale_a[a], sum[1], acc[a][t][1]);
+              acc[a][t][2] = fmaf(scale_b[a], sum[2], acc[a][t][2]);
+              acc[a][t][3] = fmaf(scale_b[a], sum[3], acc[a][t][3]);
+            }
           }
         }
       }
@@ -353,23 +400,29 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
           acc[a][t][j] = 0.0f;
         }
     consumer_barrier();
-    // the reducing warp rotates with the tile so no warp is always the late one
-    if (warp == (slot & 7u)) {
-      float total[NMAT][NT][4];
-#pragma unroll
-      for (int a = 0; a < NMAT; ++a)
-#pragma unroll
-        for (int t = 0; t < NT; ++t)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float sum = 0.0f;
-#pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) sum += reduce[(w * kAcc + (a * NT + t) * 4 + j) * 32 + lane];
-            total[a][t][j] = sum;
-          }
+    // every consumer thread finishes some accumulator positions: fixed-order sum over the
+    // eight warps' partials, then the writeback of that position
+    {
       uint32_t matrix, local_tile;
       locate(blockIdx.x + slot * gridDim.x, matrix, local_tile);
-      write_tile<NT, NMAT, EPI>(p, total, matrix, local_tile, p.mat[EPI == kEpiQkv ? matrix : 0].n, lane);
+      const uint32_t n = p.mat[EPI == kEpiQkv ? matrix : 0].n;
+      for (uint32_t position = threadIdx.x; position < NT * 4 * 32; position += kConsumerWarps * 32) {
+        const uint32_t tj = position >> 5, position_lane = position & 31u;
+        float value[NMAT];
+#pragma unroll
+        for (int a = 0; a < NMAT; ++a) {
+          float sum = 0.0f;
+#pragma unroll
+          for (int w = 0; w < kConsumerWarps; ++w) sum += reduce[(w * kAcc + a * NT * 4 + tj) * 32 + position_lane];
+          value[a] = sum;
+        }
+        float partner = 0.0f;
+        if (EPI == kEpiSplitF32) {
+#pragma unroll
+          for (int w = 0; w < kConsumerWarps; ++w) partner += reduce[(w * kAcc + tj) * 32 + (position_lane ^ 2u)];
+        }
+        write_position<NT, NMAT, EPI>(p, value, partner, matrix, local_tile, n, tj >> 2, tj & 3u, position_lane);
+      }
     }
   }
 }
@@ -378,12 +431,14 @@ struct PipePlan {
   size_t shared_bytes;
   uint32_t ctas;
   uint32_t stages;
+  uint32_t resident;  // CTAs per SM the plan was sized for
 };
 
-// Ring depth and grid: the CTA count that gives every CTA the same number of
-// tiles, and the deepest ring that (a) fits beside the other resident CTAs and
-// (b) is not longer than the chunks one CTA streams.
-template <int NT, int NMAT, int EPI, bool SMALLX>
+// Ring depth and grid: consumer warps are the scarce resource (the math is a chain of
+// dependent instructions per group), bytes in flight the second: take the most
+// resident CTAs per SM (up to 3) whose ring still holds at least three stages, and one
+// CTA per slot.
+template <int NT, int NMAT, int EPI, bool SMALLX, int GPW>
 bool plan_pipe(const KernelArgs& args, const GemvProblem& p, PipePlan* plan) {
   uint32_t total_tiles = 0;
   const uint32_t matrices = EPI == kEpiQkv ? p.matrices : 1u;
@@ -391,45 +446,56 @@ bool plan_pipe(const KernelArgs& args, const GemvProblem& p, PipePlan* plan) {
   const uint32_t groups = p.k / 64;
   size_t fixed_bytes = (size_t)kConsumerWarps * NMAT * NT * 4 * 32 * sizeof(float) + 64;
   if (SMALLX) fixed_bytes += (size_t)groups * 2 * p.x_rows * 4 * 16 + 16 + (size_t)(p.x_rows * groups + 4) * sizeof(float);
-  const size_t stage_bytes = (size_t)NMAT * kStageBytes + 16;
+  const size_t stage_bytes = (size_t)NMAT * Stage<GPW>::kBytes + 16;
   const uint32_t sms = (uint32_t)context_sm_count(args.ctx);
   constexpr size_t kSharedPerSm = 220 * 1024;  // usable shared memory of one SM
-  const uint32_t chunks_per_tile = p.k / kChunkK;
-  // Consumer warps are the scarce resource (the math is issue-bound), bytes in flight the
-  // second: take the most resident CTAs per SM (up to 3) whose ring still holds at least
-  // four stages, and launch one CTA per slot so no slot idles in the first rounds.
-  PipePlan best = {0, 0, 0};
+  const uint32_t chunks_per_tile = p.k / Stage<GPW>::kChunkK;
   for (uint32_t resident = 3; resident >= 1; --resident) {
     const size_t per_cta = kSharedPerSm / resident - 1024;
     if (per_cta <= fixed_bytes + 2 * stage_bytes) continue;
     uint32_t stages = (uint32_t)((per_cta - fixed_bytes) / stage_bytes);
-    if (stages < 4 && resident > 1) continue;
+    if (stages < 3 && resident > 1) continue;
     const uint32_t slots = sms * resident;
     const uint32_t ctas = total_tiles < slots ? total_tiles : slots;
     const uint32_t chunks = ((total_tiles + ctas - 1u) / ctas) * chunks_per_tile;
     if (stages > chunks) stages = chunks < 2 ? 2 : chunks;
     if (stages > 32) stages = 32;
-    best.shared_bytes = fixed_bytes + stages * stage_bytes;
-    best.ctas = ctas == 0 ? 1 : ctas;
-    best.stages = stages;
-    break;
+    plan->shared_bytes = fixed_bytes + stages * stage_bytes;
+    plan->ctas = ctas == 0 ? 1 : ctas;
+    plan->stages = stages;
+    plan->resident = resident;
+    return true;
   }
-  if (best.stages < 2) return false;
-  *plan = best;
-  return true;
+  return false;
 }
 
-template <int NT, int NMAT, int EPI, bool SMALLX>
-int launch_pipe(const KernelArgs& args, const GemvProblem& p) {
-  PipePlan plan;
-  if (!plan_pipe<NT, NMAT, EPI, SMALLX>(args, p, &plan)) return -1;
-  auto kernel = w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX>;
+template <int NT, int NMAT, int EPI, bool SMALLX, int GPW>
+int run_pipe(const KernelArgs& args, const GemvProblem& p, const PipePlan& plan) {
+  auto kernel = w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX, GPW>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.shared_bytes) != cudaSuccess) {
     cudaGetLastError();
     return -1;
   }
   kernel<<<plan.ctas, kThreads, plan.shared_bytes, args.stream>>>(p, plan.stages, context_device_error(args.ctx));
   return check_launch(args);
+}
+
+// Groups per warp and stage: the most (4, 2, 1) that K allows and that still leaves at
+// least two CTAs (18 warps) resident per SM; a fat stage that forces one CTA per SM
+// loses more to idle issue slots than it gains from amortised waits.
+template <int NT, int NMAT, int EPI, bool SMALLX>
+int launch_pipe(const KernelArgs& args, const GemvProblem& p) {
+  PipePlan plan4 = {}, plan2 = {}, plan1 = {};
+  const bool ok4 = NT == 1 && NMAT == 1 && p.k % 2048 == 0 && plan_pipe<NT, NMAT, EPI, SMALLX, 4>(args, p, &plan4);
+  if (ok4 && plan4.resident >= 2) return run_pipe<NT, NMAT, EPI, SMALLX, 4>(args, p, plan4);
+  const bool ok2 = NT <= 2 && p.k % 1024 == 0 && plan_pipe<NT, NMAT, EPI, SMALLX, 2>(args, p, &plan2);
+  if (ok2 && plan2.resident >= 2) return run_pipe<NT, NMAT, EPI, SMALLX, 2>(args, p, plan2);
+  const bool ok1 = plan_pipe<NT, NMAT, EPI, SMALLX, 1>(args, p, &plan1);
+  if (ok1 && plan1.resident >= 2) return run_pipe<NT, NMAT, EPI, SMALLX, 1>(args, p, plan1);
+  if (ok2) return run_pipe<NT, NMAT, EPI, SMALLX, 2>(args, p, plan2);
+  if (ok1) return run_pipe<NT, NMAT, EPI, SMALLX, 1>(args, p, plan1);
+  if (ok4) return run_pipe<NT, NMAT, EPI, SMALLX, 4>(args, p, plan4);
+  return -1;
 }
 
 template <int EPI, int NMAT>
@@ -450,7 +516,7 @@ int launch_pipe_by_rows(const KernelArgs& args, const GemvProblem& p) {
 // Returns -1 when the shape is outside this kernel's domain (the caller then
 // uses the direct-load kernel), 0 on success, 1 on a launch failure.
 int launch_w4a16_gemv_pipe(const KernelArgs& args, const GemvProblem& problem, int epilogue) {
-  if (args.ctx == nullptr || problem.k % kChunkK != 0) return -1;
+  if (args.ctx == nullptr || problem.k % 512 != 0) return -1;
   const uint32_t matrices = epilogue == kEpiQkv ? problem.matrices : (epilogue == kEpiDualSwiglu ? 2u : 1u);
   for (uint32_t i = 0; i < matrices; ++i) {
     if (((uintptr_t)problem.mat[i].packed & 15u) != 0 || ((uintptr_t)problem.mat[i].scale & 15u) != 0) return -1;
