@@ -5,14 +5,23 @@
 // (max, denominator, weighted accumulators), applied across CTAs.
 //
 // Data flow of one warp and one tile of 16 keys:
-//   pool (int8, HBM) --16-byte loads, one key row per 4 or 8 lanes--> registers
-//   registers --PRMT + half2 subtract: exact int8 -> fp16 integers--> shared
-//   S^T[key, head]   = K[key, :] . Q^T       mma.sync m16n8k16, A = K tile (ldmatrix),
+//   pool (int8, HBM) --cp.async, 16 bytes per lane--> the warp's ring of raw tiles in
+//                                            shared memory (several tiles in flight)
+//   raw int8 words --PRMT + half2 subtract: exact int8 -> fp16 integers--> MMA fragments
+//                                            (no fp16 copy of the tile is ever stored)
+//   S^T[key, head]   = K[key, :] . Q^T       mma.sync m16n8k16, A = K tile,
 //                                            B = query heads of the KV group
 //   scores scaled by the fp16 group scales in fp32, online softmax per head
-//   O^T[dim, head]  += V^T[dim, key] . P^T    A = V tile (ldmatrix.trans),
-//                                            B = P^T (movmatrix of the score tile,
-//                                            V group scales folded into P)
+//   O^T[dim, head]  += V^T[dim, key] . P^T    A = V tile (bytes of two keys interleaved
+//                                            by PRMT), B = P^T (movmatrix of the score
+//                                            tile, V group scales folded into P)
+// The contraction index of an MMA may be permuted freely as long as both operands agree,
+// and so may the row index of the PV product as long as the writeback agrees.  Both
+// are chosen so that each lane reads whole 32-bit words of int8 and the reads of a
+// warp fall into 32 different banks (rows are padded by 16 bytes):
+//   QK^T, k-step s: lane (r, c) holds dims 16 s + 4 c .. + 3 of keys r and r + 8;
+//   PV, word w = r + 8 j: dims 4 w .. 4 w + 3 of keys 2c, 2c+1, 2c+8, 2c+9 feed rows
+//   r and r + 8 of the two m-tiles 2 j and 2 j + 1.
 // All query heads that share a KV head ride in the MMA n dimension, so K and V
 // are read and converted once per KV head.  The bound is HBM: per key and KV
 // head 2 D bytes of int8 plus 4 D / group bytes of scales.
@@ -28,6 +37,9 @@ namespace {
 
 constexpr int kTileKeys = 16;
 constexpr int kWarps = 4;
+constexpr int kResidentCtas = 4;  // per SM, by shared memory and registers (128 per thread)
+constexpr uint32_t kNoSlot = 0xffffffffu;
+constexpr float kLowest = -1.0e30f;  // "no key yet" maximum; keeps the softmax free of inf - inf
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
   uint32_t d;
@@ -39,10 +51,9 @@ __device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
   asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
-// Four int8 -> two half2 of exact integers: byte ^ 0x80 is the value + 128; placed
-// under the exponent of 1024.0 it reads 1024 + 128 + value; subtract 1152.
-__device__ __forceinline__ void int8x4_to_half2x2(uint32_t word, uint32_t& first, uint32_t& second) {
-  const uint32_t biased = word ^ 0x80808080u;
+// Four bytes already XORed with 0x80 (value + 128) -> two half2 of exact integers:
+// a byte placed under the exponent of 1024.0 reads 1024 + 128 + value; subtract 1152.
+__device__ __forceinline__ void biased_bytes_to_half2x2(uint32_t biased, uint32_t& first, uint32_t& second) {
   first = hsub2_u32(prmt(biased, 0x64646464u, 0x4140u), 0x64806480u);
   second = hsub2_u32(prmt(biased, 0x64646464u, 0x4342u), 0x64806480u);
 }
@@ -51,18 +62,6 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
       "{%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* shared_address) {
-  const uint32_t address = (uint32_t)__cvta_generic_to_shared(shared_address);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(address));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* shared_address) {
-  const uint32_t address = (uint32_t)__cvta_generic_to_shared(shared_address);
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(address));
 }
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t value) {
   uint32_t d;
@@ -73,56 +72,100 @@ __device__ __forceinline__ uint32_t pack_half2(float low, float high) {
   const __half2 pair = __floats2half2_rn(low, high);
   return *reinterpret_cast<const uint32_t*>(&pair);
 }
-
-template <int D, bool ALIGN16>
-struct RawTile {
-  // One warp-wide load instruction covers 32 * 16 bytes = 32 / (D / 16) key rows.
-  static constexpr int kLanesPerKey = D / 16;
-  static constexpr int kKeysPerLoad = 32 / kLanesPerKey;
-  static constexpr int kLoads = kTileKeys / kKeysPerLoad;
-  uint4 key[kLoads];
-  uint4 value[kLoads];
-};
-
-template <bool ALIGN16>
-__device__ __forceinline__ uint4 load_16_bytes(const uint8_t* address) {
-  if (ALIGN16) return __ldg(reinterpret_cast<const uint4*>(address));
-  const uint2 low = __ldg(reinterpret_cast<const uint2*>(address));
-  const uint2 high = __ldg(reinterpret_cast<const uint2*>(address + 8));
-  return make_uint4(low.x, low.y, high.x, high.y);
+__device__ __forceinline__ uint32_t lds32(uint32_t address) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ float exp2_fast(float x) {  // 2^x; -inf and very negative x give 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// Asynchronous copy of CP bytes; source_bytes == 0 writes zeros and reads nothing.
+template <int CP>
+__device__ __forceinline__ void copy_async(uint32_t shared_address, const void* source, uint32_t source_bytes) {
+  if (CP == 16)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(shared_address), "l"(source),
+                 "r"(source_bytes)
+                 : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(shared_address), "l"(source),
+                 "r"(source_bytes)
+                 : "memory");
+}
+// Small asynchronous copy (4 or 8 bytes) for the group scales.
+template <int BYTES>
+__device__ __forceinline__ void copy_async_small(uint32_t shared_address, const void* source, uint32_t source_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;" ::"r"(shared_address), "l"(source), "n"(BYTES),
+               "r"(source_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void copy_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
 }
 
-template <int D, int GROUP, bool ALIGN16>
-__global__ void __launch_bounds__(kWarps * 32)
+// Shared-memory shape of one warp's ring.  CP is the copy size: 16 bytes, or 8 for
+// pools whose rows are only 8-byte aligned.
+template <int D, int CP>
+struct SplitShape {
+  static constexpr int kRowBytes = D + 16;  // the padding spreads the fragment reads over all banks
+  static constexpr int kTileBytes = kTileKeys * kRowBytes;
+  static constexpr int kScaleBytes = 2 * kTileKeys * 8;  // [K | V][key][up to 4 halves]
+  static constexpr int kStageBytes = 2 * kTileBytes + kScaleBytes;
+  // Sixteen warps per SM hide the latencies of the conversion and MMA chain better than
+  // a deeper ring under fewer warps does (measured: 2 stages x 4 CTAs beats 3 x 3 and 5 x 2).
+  static constexpr int kStages = D == 128 ? 2 : 4;
+  static constexpr int kLanesPerKey = D / CP;
+  static constexpr int kKeysPerPass = 32 / kLanesPerKey;
+  static constexpr int kPasses = kTileKeys / kKeysPerPass;
+  static constexpr int kRingBytes = kWarps * kStages * kStageBytes;
+};
+
+template <int D, int GROUP, int CP>
+__global__ void __launch_bounds__(kWarps * 32, kResidentCtas)
 paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__ pool,
                    const uint32_t* __restrict__ slots, float* __restrict__ scratch, PagedParams p,
                    uint32_t slot_batch_stride, uint32_t splits, const uint32_t* __restrict__ past_cell) {
-  using Raw = RawTile<D, ALIGN16>;
-  constexpr int kStride = D + 8;          // halves per shared row; 16 bytes of padding
-  constexpr int kSteps = D / 16;          // k-steps of QK^T, m-tiles of PV
-  __shared__ __align__(16) __half tiles[kWarps][2][kTileKeys][kStride];
+  using Shape = SplitShape<D, CP>;
+  constexpr int kSteps = D / 16;  // k-steps of QK^T, m-tiles of PV
+  constexpr int kStages = Shape::kStages;
+  constexpr int groups_per_head = D / GROUP;  // 1, 2 or 4
+  constexpr int steps_per_group = GROUP / 16;
+  extern __shared__ __align__(16) uint8_t ring[];
 
   const uint32_t past = past_cell ? *past_cell : p.past_length;
   const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
   const uint32_t r = lane >> 2, c = lane & 3u;
   const uint32_t split = blockIdx.x, kv_head = blockIdx.y, batch = blockIdx.z;
   const uint32_t heads_per_kv = p.query_heads / p.kv_heads;
-  constexpr int groups_per_head = D / GROUP;  // 1, 2 or 4
-  constexpr int steps_per_group = GROUP / 16;
 
   uint32_t chunk = (past + splits - 1u) / splits;
   chunk = (chunk + kTileKeys - 1u) / kTileKeys * kTileKeys;
   const uint32_t range_begin = min(split * chunk, past);
   const uint32_t range_end = min(range_begin + chunk, past);
   const uint32_t tile_count = (range_end - range_begin + kTileKeys - 1u) / kTileKeys;
+  // this warp's tiles: warp, warp + kWarps, ...
+  const uint32_t my_tiles = tile_count > warp ? (tile_count - warp + kWarps - 1u) / kWarps : 0u;
 
   const uint32_t* batch_slots = slots + (size_t)batch * slot_batch_stride;
-  const uint32_t scale_index_key = p.key_offset / GROUP + kv_head * groups_per_head;
-  const uint32_t scale_index_value = p.value_offset / GROUP + kv_head * groups_per_head;
-  const uint32_t key_byte = p.key_offset + kv_head * D + (lane % Raw::kLanesPerKey) * 16;
-  const uint32_t value_byte = p.value_offset + kv_head * D + (lane % Raw::kLanesPerKey) * 16;
+  const uint32_t copy_lane = lane % Shape::kLanesPerKey;
+  const uint32_t key_byte = p.key_offset + kv_head * D + copy_lane * CP;
+  const uint32_t value_byte = p.value_offset + kv_head * D + copy_lane * CP;
+  // lanes 0..15 fetch the K scales of key `lane`, lanes 16..31 the V scales of key `lane - 16`
+  // The scales of one head are 2, 4 or 8 bytes; they travel as one 4- or 8-byte copy (a single
+  // half rides in the aligned word that holds it and is picked out by scale_pick).
+  constexpr int kScaleCopy = groups_per_head == 4 ? 8 : 4;
+  const uint32_t scale_byte =
+      p.token_elements + 2u * ((lane < 16 ? p.key_offset : p.value_offset) / GROUP + kv_head * groups_per_head);
+  const uint32_t scale_pick_key = ((p.token_elements + 2u * (p.key_offset / GROUP + kv_head)) >> 1) & 1u;
+  const uint32_t scale_pick_value = ((p.token_elements + 2u * (p.value_offset / GROUP + kv_head)) >> 1) & 1u;
+  const uint8_t* const pool_scale = pool + (groups_per_head == 1 ? (scale_byte & ~3u) : scale_byte);
+  const uint32_t ring_base = (uint32_t)__cvta_generic_to_shared(ring) + warp * kStages * Shape::kStageBytes;
 
-  // Query fragments: B operand, n = head r of this KV group, k = dims 16 s + 2c (+8).
+  // Query fragments: B operand, n = head r of this KV group, k = dims 16 s + 4 c .. + 3.
   uint32_t q_frag[kSteps][2];
   {
     const uint32_t head = kv_head * heads_per_kv + r;
@@ -132,92 +175,105 @@ paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__
       q_frag[s][0] = 0u;
       q_frag[s][1] = 0u;
       if (r < heads_per_kv) {
-        q_frag[s][0] = *reinterpret_cast<const uint32_t*>(source + 16 * s + 2 * c);
-        q_frag[s][1] = *reinterpret_cast<const uint32_t*>(source + 16 * s + 2 * c + 8);
+        q_frag[s][0] = *reinterpret_cast<const uint32_t*>(source + 16 * s + 4 * c);
+        q_frag[s][1] = *reinterpret_cast<const uint32_t*>(source + 16 * s + 4 * c + 2);
       }
     }
   }
 
-  float running_max[2] = {-INFINITY, -INFINITY};
+  // Scores are kept in units of log2(e), so that every exponential is one ex2.
+  const float score_scale = p.scale * 1.4426950408889634f;
+  float running_max[2] = {kLowest, kLowest};
   float running_sum[2] = {0.0f, 0.0f};  // lane-local part of the denominator
+  // out[2 j + e][i]: dim 4 (r + 8 j) + 2 e + (i >> 1), head 2 c + (i & 1)
   float out[kSteps][4];
 #pragma unroll
   for (int s = 0; s < kSteps; ++s)
 #pragma unroll
     for (int j = 0; j < 4; ++j) out[s][j] = 0.0f;
 
-  // Slot of key (lane % 16) of a tile, or the invalid marker.
-  auto load_slot = [&](uint32_t tile) -> uint32_t {
-    const uint32_t position = range_begin + tile * kTileKeys + (lane & 15u);
-    return (tile < tile_count && position < range_end) ? __ldg(batch_slots + position) : 0xffffffffu;
+  // Slot of key (lane % 16) of this warp's tile `index`, or kNoSlot.
+  auto load_slot = [&](uint32_t index) -> uint32_t {
+    const uint32_t position = range_begin + (warp + index * kWarps) * kTileKeys + (lane & 15u);
+    return (index < my_tiles && position < range_end) ? __ldg(batch_slots + position) : kNoSlot;
   };
-  // Raw int8 rows + group scales of one tile.  Lanes 0..15 also fetch the scales
-  // of key `lane`: [K scales..., V scales...] as floats.
-  auto load_raw = [&](uint32_t tile_slot, Raw& raw, float (&scales)[8]) {
+  // A tile's row addresses depend on its slots, so the slots run four tiles ahead of
+  // the copies.
+  uint32_t slot_0 = load_slot(0), slot_1 = load_slot(1), slot_2 = load_slot(2), slot_3 = load_slot(3);
+  const uint8_t* const pool_key = pool + key_byte;
+  const uint8_t* const pool_value = pool + value_byte;
+  const uint32_t copy_target = (lane / Shape::kLanesPerKey) * Shape::kRowBytes + copy_lane * CP;
+
+  // Starts the copies of tile `index` into ring stage `stage` and rotates the slot registers.
+  auto issue = [&](uint32_t index, uint32_t stage) {
+    if (index < my_tiles) {
+      const uint32_t stage_base = ring_base + stage * Shape::kStageBytes;
+      const uint32_t target = stage_base + copy_target;
+      const bool whole = range_begin + (warp + index * kWarps + 1u) * kTileKeys <= range_end;
+      if (whole) {
 #pragma unroll
-    for (int i = 0; i < Raw::kLoads; ++i) {
-      const uint32_t key_in_tile = i * Raw::kKeysPerLoad + lane / Raw::kLanesPerKey;
-      const uint32_t slot = __shfl_sync(0xffffffffu, tile_slot, key_in_tile);
-      raw.key[i] = make_uint4(0u, 0u, 0u, 0u);  // absent keys read as zeros
-      raw.value[i] = raw.key[i];
-      if (slot != 0xffffffffu) {
-        const uint8_t* row = pool + (size_t)slot * p.token_stride;
-        raw.key[i] = load_16_bytes<ALIGN16>(row + key_byte);
-        raw.value[i] = load_16_bytes<ALIGN16>(row + value_byte);
+        for (int i = 0; i < Shape::kPasses; ++i) {
+          const uint32_t slot = __shfl_sync(0xffffffffu, slot_0, i * Shape::kKeysPerPass + lane / Shape::kLanesPerKey);
+          const size_t row = (size_t)slot * p.token_stride;
+          copy_async<CP>(target + i * Shape::kKeysPerPass * Shape::kRowBytes, pool_key + row, CP);
+          copy_async<CP>(target + i * Shape::kKeysPerPass * Shape::kRowBytes + Shape::kTileBytes, pool_value + row, CP);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < Shape::kPasses; ++i) {
+          const uint32_t slot = __shfl_sync(0xffffffffu, slot_0, i * Shape::kKeysPerPass + lane / Shape::kLanesPerKey);
+          const bool present = slot != kNoSlot;  // absent keys read as zeros
+          const size_t row = (size_t)(present ? slot : 0u) * p.token_stride;
+          copy_async<CP>(target + i * Shape::kKeysPerPass * Shape::kRowBytes, pool_key + row, present ? CP : 0);
+          copy_async<CP>(target + i * Shape::kKeysPerPass * Shape::kRowBytes + Shape::kTileBytes, pool_value + row,
+                         present ? CP : 0);
+        }
+      }
+      {
+        const bool present = slot_0 != kNoSlot;
+        copy_async_small<kScaleCopy>(stage_base + 2 * Shape::kTileBytes + lane * 8u,
+                                     pool_scale + (size_t)(present ? slot_0 : 0u) * p.token_stride,
+                                     present ? kScaleCopy : 0);
       }
     }
-#pragma unroll
-    for (int g = 0; g < 8; ++g) scales[g] = 0.0f;
-    if (lane < 16 && tile_slot != 0xffffffffu) {
-      const __half* scale_row =
-          reinterpret_cast<const __half*>(pool + (size_t)tile_slot * p.token_stride + p.token_elements);
-#pragma unroll
-      for (int g = 0; g < groups_per_head; ++g) {
-        scales[g] = __half2float(__ldg(scale_row + scale_index_key + g));
-        scales[4 + g] = __half2float(__ldg(scale_row + scale_index_value + g));
-      }
-    }
+    copy_async_commit();
+    slot_0 = slot_1;
+    slot_1 = slot_2;
+    slot_2 = slot_3;
+    slot_3 = load_slot(index + 4u);
   };
 
-  Raw raw;
-  float raw_scales[8];
-  uint32_t slot_now = load_slot(warp);
-  uint32_t slot_next = load_slot(warp + kWarps);
-  load_raw(slot_now, raw, raw_scales);
-
-  for (uint32_t tile = warp; tile < tile_count; tile += kWarps) {
-    __half(*key_tile)[kStride] = tiles[warp][0];
-    __half(*value_tile)[kStride] = tiles[warp][1];
-    // registers -> shared as exact fp16 integers
-    __syncwarp();
-#pragma unroll
-    for (int i = 0; i < Raw::kLoads; ++i) {
-      const uint32_t key_in_tile = i * Raw::kKeysPerLoad + lane / Raw::kLanesPerKey;
-      const uint32_t dim = (lane % Raw::kLanesPerKey) * 16;
-      uint4 low, high;
-      int8x4_to_half2x2(raw.key[i].x, low.x, low.y);
-      int8x4_to_half2x2(raw.key[i].y, low.z, low.w);
-      int8x4_to_half2x2(raw.key[i].z, high.x, high.y);
-      int8x4_to_half2x2(raw.key[i].w, high.z, high.w);
-      *reinterpret_cast<uint4*>(&key_tile[key_in_tile][dim]) = low;
-      *reinterpret_cast<uint4*>(&key_tile[key_in_tile][dim + 8]) = high;
-      int8x4_to_half2x2(raw.value[i].x, low.x, low.y);
-      int8x4_to_half2x2(raw.value[i].y, low.z, low.w);
-      int8x4_to_half2x2(raw.value[i].z, high.x, high.y);
-      int8x4_to_half2x2(raw.value[i].w, high.z, high.w);
-      *reinterpret_cast<uint4*>(&value_tile[key_in_tile][dim]) = low;
-      *reinterpret_cast<uint4*>(&value_tile[key_in_tile][dim + 8]) = high;
-    }
-    float scales[8];
-#pragma unroll
-    for (int g = 0; g < 8; ++g) scales[g] = raw_scales[g];
-    const bool valid_low = __shfl_sync(0xffffffffu, slot_now, r) != 0xffffffffu;
-    const bool valid_high = __shfl_sync(0xffffffffu, slot_now, r + 8) != 0xffffffffu;
-    // prefetch the next tile of this warp while this one is consumed
-    slot_now = slot_next;
-    slot_next = load_slot(tile + 2 * kWarps);
-    load_raw(slot_now, raw, raw_scales);
-    __syncwarp();
+  auto consume = [&](uint32_t index, uint32_t stage) {
+    const uint32_t key_tile = ring_base + stage * Shape::kStageBytes;
+    const uint32_t value_tile = key_tile + Shape::kTileBytes;
+    const uint32_t scale_tile = value_tile + Shape::kTileBytes;
+    const uint32_t first_position = range_begin + (warp + index * kWarps) * kTileKeys;
+    const bool valid_low = first_position + r < range_end;
+    const bool valid_high = first_position + r + 8u < range_end;
+    // group scales of keys r and r + 8: halves [g] of K, then of V
+    float key_scale_low[4], key_scale_high[4], value_scale_low[4], value_scale_high[4];
+    auto read_scales = [&](uint32_t address, uint32_t pick, float (&scales)[4]) {
+      if (groups_per_head == 4) {
+        uint2 raw;
+        asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(raw.x), "=r"(raw.y) : "r"(address));
+        const float2 first = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        const float2 second = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+        scales[0] = first.x;
+        scales[1] = first.y;
+        scales[2] = second.x;
+        scales[3] = second.y;
+      } else {
+        const uint32_t raw = lds32(address);
+        const float2 pair = __half22float2(*reinterpret_cast<const __half2*>(&raw));
+        scales[0] = groups_per_head == 1 && pick ? pair.y : pair.x;
+        scales[1] = pair.y;
+        scales[2] = scales[3] = 0.0f;
+      }
+    };
+    read_scales(scale_tile + r * 8u, scale_pick_key, key_scale_low);
+    read_scales(scale_tile + (r + 8u) * 8u, scale_pick_key, key_scale_high);
+    read_scales(scale_tile + 128u + r * 8u, scale_pick_value, value_scale_low);
+    read_scales(scale_tile + 128u + (r + 8u) * 8u, scale_pick_value, value_scale_high);
 
     // S^T[key, head]: rows r / r+8 are keys, columns 2c / 2c+1 are heads.
     float score[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -226,61 +282,93 @@ paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__
       float partial[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int s = g * steps_per_group; s < (g + 1) * steps_per_group; ++s) {
+        const uint32_t word_low = lds32(key_tile + r * Shape::kRowBytes + 16 * s + 4 * c) ^ 0x80808080u;
+        const uint32_t word_high = lds32(key_tile + (r + 8u) * Shape::kRowBytes + 16 * s + 4 * c) ^ 0x80808080u;
         uint32_t a[4];
-        // matrices: (keys 0-7, dims +0), (keys 8-15, dims +0), (keys 0-7, dims +8), (keys 8-15, dims +8)
-        ldmatrix_x4(a, &key_tile[(lane & 7u) + ((lane >> 3) & 1u) * 8u][16 * s + (lane >> 4) * 8u]);
+        biased_bytes_to_half2x2(word_low, a[0], a[2]);
+        biased_bytes_to_half2x2(word_high, a[1], a[3]);
         mma_16816(partial, a, q_frag[s][0], q_frag[s][1]);
       }
-      const float scale_low = __shfl_sync(0xffffffffu, scales[g], r);
-      const float scale_high = __shfl_sync(0xffffffffu, scales[g], r + 8);
-      score[0] = fmaf(partial[0], scale_low, score[0]);
-      score[1] = fmaf(partial[1], scale_low, score[1]);
-      score[2] = fmaf(partial[2], scale_high, score[2]);
-      score[3] = fmaf(partial[3], scale_high, score[3]);
+      score[0] = fmaf(partial[0], key_scale_low[g], score[0]);
+      score[1] = fmaf(partial[1], key_scale_low[g], score[1]);
+      score[2] = fmaf(partial[2], key_scale_high[g], score[2]);
+      score[3] = fmaf(partial[3], key_scale_high[g], score[3]);
     }
-    score[0] = valid_low ? score[0] * p.scale : -INFINITY;
-    score[1] = valid_low ? score[1] * p.scale : -INFINITY;
-    score[2] = valid_high ? score[2] * p.scale : -INFINITY;
-    score[3] = valid_high ? score[3] * p.scale : -INFINITY;
+    score[0] = valid_low ? score[0] * score_scale : -INFINITY;
+    score[1] = valid_low ? score[1] * score_scale : -INFINITY;
+    score[2] = valid_high ? score[2] * score_scale : -INFINITY;
+    score[3] = valid_high ? score[3] * score_scale : -INFINITY;
 
     // online softmax per head (columns 2c, 2c+1); the maximum is shared by the
     // eight lanes that hold the same c
-    float probability[4];
+    float probability[4], rescale[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       float tile_max = fmaxf(score[h], score[h + 2]);
       tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 4));
       tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 8));
       tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 16));
-      const float next_max = fmaxf(running_max[h], tile_max);
-      const float rescale = next_max == -INFINITY ? 1.0f : expf(running_max[h] - next_max);
-      probability[h] = next_max == -INFINITY ? 0.0f : expf(score[h] - next_max);
-      probability[h + 2] = next_max == -INFINITY ? 0.0f : expf(score[h + 2] - next_max);
-      running_sum[h] = running_sum[h] * rescale + probability[h] + probability[h + 2];
+      const float next_max = fmaxf(running_max[h], tile_max);  // finite: at least kLowest
+      rescale[h] = exp2_fast(running_max[h] - next_max);
+      probability[h] = exp2_fast(score[h] - next_max);
+      probability[h + 2] = exp2_fast(score[h + 2] - next_max);
+      running_sum[h] = running_sum[h] * rescale[h] + probability[h] + probability[h + 2];
       running_max[h] = next_max;
+    }
+    // the maxima settle after a few tiles; skip the rescaling sweep when no lane needs it
+    if (__any_sync(0xffffffffu, rescale[0] != 1.0f || rescale[1] != 1.0f)) {
 #pragma unroll
       for (int s = 0; s < kSteps; ++s) {
-        out[s][h] *= rescale;
-        out[s][h + 2] *= rescale;
+        out[s][0] *= rescale[0];
+        out[s][1] *= rescale[1];
+        out[s][2] *= rescale[0];
+        out[s][3] *= rescale[1];
       }
     }
 
     // O^T[dim, head] += V^T[dim, key] P^T[key, head], V group scales folded into P
 #pragma unroll
     for (int g = 0; g < groups_per_head; ++g) {
-      const float scale_low = __shfl_sync(0xffffffffu, scales[4 + g], r);
-      const float scale_high = __shfl_sync(0xffffffffu, scales[4 + g], r + 8);
-      const uint32_t p_low = movmatrix_trans(pack_half2(probability[0] * scale_low, probability[1] * scale_low));
-      const uint32_t p_high = movmatrix_trans(pack_half2(probability[2] * scale_high, probability[3] * scale_high));
+      const uint32_t p_low = movmatrix_trans(
+          pack_half2(probability[0] * value_scale_low[g], probability[1] * value_scale_low[g]));
+      const uint32_t p_high = movmatrix_trans(
+          pack_half2(probability[2] * value_scale_high[g], probability[3] * value_scale_high[g]));
 #pragma unroll
-      for (int s = g * steps_per_group; s < (g + 1) * steps_per_group; ++s) {
-        uint32_t a[4];
-        // matrices: (keys 0-7, dims +0), (keys 0-7, dims +8), (keys 8-15, dims +0), (keys 8-15, dims +8)
-        ldmatrix_x4_trans(a, &value_tile[(lane & 7u) + (lane >> 4) * 8u][16 * s + ((lane >> 3) & 1u) * 8u]);
-        mma_16816(out[s], a, p_low, p_high);
+      for (int j = g * (GROUP / 32); j < (g + 1) * (GROUP / 32); ++j) {
+        const uint32_t word = value_tile + (2u * c) * Shape::kRowBytes + 4u * (r + 8u * j);
+        const uint32_t key_0 = lds32(word), key_1 = lds32(word + Shape::kRowBytes);
+        const uint32_t key_8 = lds32(word + 8 * Shape::kRowBytes), key_9 = lds32(word + 9 * Shape::kRowBytes);
+        // bytes (dim, key): [d0 k0, d0 k1, d1 k0, d1 k1] and [d2 k0, d2 k1, d3 k0, d3 k1]
+        const uint32_t near_01 = prmt(key_0, key_1, 0x5140u) ^ 0x80808080u;
+        const uint32_t near_23 = prmt(key_0, key_1, 0x7362u) ^ 0x80808080u;
+        const uint32_t far_01 = prmt(key_8, key_9, 0x5140u) ^ 0x80808080u;
+        const uint32_t far_23 = prmt(key_8, key_9, 0x7362u) ^ 0x80808080u;
+        uint32_t a[4], b[4];
+        biased_bytes_to_half2x2(near_01, a[0], a[1]);
+        biased_bytes_to_half2x2(far_01, a[2], a[3]);
+        biased_bytes_to_half2x2(near_23, b[0], b[1]);
+        biased_bytes_to_half2x2(far_23, b[2], b[3]);
+        mma_16816(out[2 * j], a, p_low, p_high);
+        mma_16816(out[2 * j + 1], b, p_low, p_high);
       }
     }
+  };
+
+  // prologue: kStages - 1 tiles in flight
+#pragma unroll 1
+  for (uint32_t index = 0; index < (uint32_t)(kStages - 1); ++index) issue(index, index);
+  uint32_t consume_stage = 0, issue_stage = kStages - 1;
+#pragma unroll 1
+  for (uint32_t index = 0; index < my_tiles; ++index) {
+    issue(index + kStages - 1, issue_stage);
+    copy_async_wait<kStages - 1>();  // all but the newest kStages - 1 groups have landed: tile `index` is here
+    __syncwarp();
+    consume(index, consume_stage);
+    __syncwarp();  // the next issue overwrites this stage
+    issue_stage = consume_stage;
+    consume_stage = consume_stage + 1 == kStages ? 0 : consume_stage + 1;
   }
+  copy_async_wait<0>();
 
   // ---- merge the four warps, write the split record ---------------------------
 #pragma unroll
@@ -290,9 +378,9 @@ paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__
     running_sum[h] += __shfl_xor_sync(0xffffffffu, running_sum[h], 16);
   }
   __syncthreads();
-  float* stage = reinterpret_cast<float*>(&tiles[0][0][0][0]);  // [warp][16 + 8 * D]
+  float* stage = reinterpret_cast<float*>(ring);  // [warp][16 + 8 * D]
   constexpr int kRecord = 16 + 8 * D;
-  static_assert(sizeof(tiles) >= sizeof(float) * kWarps * kRecord, "merge staging must fit the tile buffers");
+  static_assert(Shape::kRingBytes >= (int)sizeof(float) * kWarps * kRecord, "merge staging must fit the ring");
   float* mine = stage + warp * kRecord;
   if (r == 0) {
     mine[2 * c] = running_max[0];
@@ -304,7 +392,7 @@ paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__
   for (int s = 0; s < kSteps; ++s)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const uint32_t dim = 16 * s + r + ((j & 2) ? 8 : 0);
+      const uint32_t dim = 4u * (r + 8u * (s >> 1)) + 2u * (s & 1) + (j >> 1);
       const uint32_t head = 2 * c + (j & 1);
       mine[16 + head * D + dim] = out[s][j];
     }
@@ -312,20 +400,20 @@ paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__
   float* record = scratch + (((size_t)batch * p.kv_heads + kv_head) * splits + split) * kRecord;
   for (uint32_t index = threadIdx.x; index < 8u * D; index += kWarps * 32) {
     const uint32_t head = index / D;
-    float merged_max = -INFINITY;
+    float merged_max = kLowest;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) merged_max = fmaxf(merged_max, stage[w * kRecord + head]);
     float total = 0.0f, denominator = 0.0f;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) {
-      const float warp_max_value = stage[w * kRecord + head];
-      const float weight = warp_max_value == -INFINITY ? 0.0f : expf(warp_max_value - merged_max);
+      const float weight = exp2_fast(stage[w * kRecord + head] - merged_max);
       total += weight * stage[w * kRecord + 16 + index];
       denominator += weight * stage[w * kRecord + 8 + head];
     }
     record[16 + index] = total;
     if (index % D == 0) {
-      record[head] = merged_max;
+      // records carry the maximum in natural units; a split without keys says -inf
+      record[head] = merged_max <= 0.5f * kLowest ? -INFINITY : merged_max * 0.6931471805599453f;
       record[8 + head] = denominator;
     }
   }
@@ -333,59 +421,85 @@ paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__
 
 // One CTA per (batch, query head): merges the split records and the current
 // token (key position past_length, fp16, lib/metal_cache_source.ml:446-470),
-// writes half(result / denominator) token-first.
+// writes half(result / denominator) token-first.  Thread s first weighs split s
+// (maxima and denominators are read side by side, not one after the other); then
+// thread d sums dimension d over the splits with the loads of several splits in flight.
 template <int D>
 __global__ void __launch_bounds__(D)
 paged_merge_kernel(const __half* __restrict__ query, const __half* __restrict__ current_key,
                    const __half* __restrict__ current_value, const float* __restrict__ scratch,
                    __half* __restrict__ output, PagedParams p, uint32_t splits) {
   constexpr int kRecord = 16 + 8 * D;
-  __shared__ float partial[D / 32];
+  static_assert(D >= (int)kMaxAttentionSplits, "one thread per split in the weighing phase");
+  __shared__ float partial[3][D / 32];
+  __shared__ float weights[kMaxAttentionSplits];
   const uint32_t head = blockIdx.x, batch = blockIdx.y, d = threadIdx.x;
   const uint32_t heads_per_kv = p.query_heads / p.kv_heads;
   const uint32_t kv_head = head / heads_per_kv, local_head = head % heads_per_kv;
   const size_t query_base = ((size_t)batch * p.query_heads + head) * D;
   const size_t current_base = ((size_t)batch * p.kv_heads + kv_head) * D;
+  const float* records = scratch + ((size_t)batch * p.kv_heads + kv_head) * splits * kRecord;
+
+  // issue every global load of the first phase before the first reduction
+  const float split_max = d < splits ? records[d * kRecord + local_head] : -INFINITY;
+  const float split_sum = d < splits ? records[d * kRecord + 8 + local_head] : 0.0f;
+  const float current_v = __half2float(current_value[current_base + d]);
   float dot = __half2float(query[query_base + d]) * __half2float(current_key[current_base + d]);
   dot = warp_sum(dot);
-  if ((d & 31u) == 0) partial[d >> 5] = dot;
-  __syncthreads();
-  float current_score = 0.0f;
-#pragma unroll
-  for (int i = 0; i < D / 32; ++i) current_score += partial[i];
-  current_score *= p.scale;
-
-  const float* records = scratch + ((size_t)batch * p.kv_heads + kv_head) * splits * kRecord;
-  float maximum = current_score;
-  for (uint32_t s = 0; s < splits; ++s) maximum = fmaxf(maximum, records[s * kRecord + local_head]);
-  const float current_weight = expf(current_score - maximum);
-  float denominator = current_weight;
-  float result = current_weight * __half2float(current_value[current_base + d]);
-  for (uint32_t s = 0; s < splits; ++s) {
-    const float split_max = records[s * kRecord + local_head];
-    if (split_max == -INFINITY) continue;
-    const float weight = expf(split_max - maximum);
-    denominator += weight * records[s * kRecord + 8 + local_head];
-    result += weight * records[s * kRecord + 16 + local_head * D + d];
+  const float warp_maximum = warp_max(split_max);
+  if ((d & 31u) == 0) {
+    partial[0][d >> 5] = dot;
+    partial[1][d >> 5] = warp_maximum;
   }
+  __syncthreads();
+  float current_score = 0.0f, maximum = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) {
+    current_score += partial[0][i];
+    maximum = fmaxf(maximum, partial[1][i]);
+  }
+  current_score *= p.scale;
+  maximum = fmaxf(maximum, current_score);
+  const float current_weight = expf(current_score - maximum);
+  const float weight = split_max == -INFINITY ? 0.0f : expf(split_max - maximum);
+  if (d < splits) weights[d] = weight;
+  const float weighted = warp_sum(weight * split_sum);
+  if ((d & 31u) == 0) partial[2][d >> 5] = weighted;
+  __syncthreads();
+  float denominator = current_weight;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) denominator += partial[2][i];
+
+  float result = current_weight * current_v;
+  const float* column = records + 16 + local_head * D + d;
+#pragma unroll 8
+  for (uint32_t s = 0; s < splits; ++s) result = fmaf(weights[s], column[(size_t)s * kRecord], result);
   const size_t output_base = ((size_t)batch * p.query_heads + head) * D;  // [b, q = 1, hq, D]
   output[output_base + d] = __float2half_rn(denominator == 0.0f ? 0.0f : result / denominator);
+}
+
+template <int D, int GROUP, int CP>
+int launch_split_copy(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride, float* scratch,
+                      uint32_t splits) {
+  auto kernel = paged_split_kernel<D, GROUP, CP>;
+  constexpr int ring_bytes = SplitShape<D, CP>::kRingBytes;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(args, "paged attention: the device cannot give one CTA its tile ring");
+  }
+  kernel<<<dim3(splits, p.kv_heads, p.batches), kWarps * 32, ring_bytes, args.stream>>>(
+      (const __half*)args.buffers[0], (const uint8_t*)args.buffers[3], (const uint32_t*)args.buffers[4], scratch, p,
+      slot_batch_stride, splits, args.past_tokens_cell);
+  return check_launch(args);
 }
 
 template <int D, int GROUP>
 int launch_split(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride, float* scratch,
                  uint32_t splits) {
   const bool aligned = (p.token_stride % 16 == 0) && (((uintptr_t)args.buffers[3]) % 16 == 0);
-  const dim3 grid(splits, p.kv_heads, p.batches);
-  if (aligned)
-    paged_split_kernel<D, GROUP, true><<<grid, kWarps * 32, 0, args.stream>>>(
-        (const __half*)args.buffers[0], (const uint8_t*)args.buffers[3], (const uint32_t*)args.buffers[4], scratch,
-        p, slot_batch_stride, splits, args.past_tokens_cell);
-  else
-    paged_split_kernel<D, GROUP, false><<<grid, kWarps * 32, 0, args.stream>>>(
-        (const __half*)args.buffers[0], (const uint8_t*)args.buffers[3], (const uint32_t*)args.buffers[4], scratch,
-        p, slot_batch_stride, splits, args.past_tokens_cell);
-  if (int status = check_launch(args)) return status;
+  const int status = aligned ? launch_split_copy<D, GROUP, 16>(args, p, slot_batch_stride, scratch, splits)
+                             : launch_split_copy<D, GROUP, 8>(args, p, slot_batch_stride, scratch, splits);
+  if (status) return status;
   paged_merge_kernel<D><<<dim3(p.query_heads, p.batches), D, 0, args.stream>>>(
       (const __half*)args.buffers[0], (const __half*)args.buffers[1], (const __half*)args.buffers[2], scratch,
       (__half*)args.buffers[6], p, splits);
@@ -396,21 +510,36 @@ int launch_split(const KernelArgs& args, const PagedParams& p, uint32_t slot_bat
 
 bool paged_split_supported(const PagedParams& p) {
   const uint32_t heads_per_kv = p.query_heads / p.kv_heads;
-  return (p.head_dim == 64 || p.head_dim == 128) && (p.group_size == 32 || p.group_size == 64) &&
-         heads_per_kv <= 8 && p.token_stride % 8 == 0 && p.key_offset % 16 == 0 && p.value_offset % 16 == 0 &&
-         p.token_elements % 2 == 0;
+  if (!((p.head_dim == 64 || p.head_dim == 128) && (p.group_size == 32 || p.group_size == 64) &&
+        heads_per_kv <= 8 && p.token_stride % 8 == 0 && p.key_offset % 16 == 0 && p.value_offset % 16 == 0))
+    return false;
+  // the group scales of one head are fetched with a single load of that size
+  const uint32_t scale_bytes = 2u * p.head_dim / p.group_size;
+  return (p.token_elements + 2u * (p.key_offset / p.group_size)) % scale_bytes == 0 &&
+         (p.token_elements + 2u * (p.value_offset / p.group_size)) % scale_bytes == 0;
 }
 
 uint32_t paged_pick_splits(const KernelArgs& args, const PagedParams& p) {
-  // Enough CTAs for about three per SM; a split is never shorter than 64 keys
-  // at capture time (a replayed plan keeps the count while the context grows).
+  // kResidentCtas CTAs are resident per SM.  Among the admissible counts take the one whose
+  // waves fill the machine best, charging a little for every extra record the merge
+  // has to read; a split is never shorter than 64 keys at capture time (a replayed
+  // plan keeps the count while the context grows).
   const uint32_t pairs = p.batches * p.kv_heads;
-  const uint32_t target = (uint32_t)context_sm_count(args.ctx) * 3u;
-  uint32_t splits = (target + pairs - 1u) / pairs;
-  const uint32_t by_length = args.past_tokens_cell ? kMaxAttentionSplits : (p.past_length + 63u) / 64u;
-  if (splits > by_length) splits = by_length;
-  if (splits > kMaxAttentionSplits) splits = kMaxAttentionSplits;
-  return splits == 0 ? 1 : splits;
+  const uint32_t resident = (uint32_t)context_sm_count(args.ctx) * (uint32_t)kResidentCtas;
+  uint32_t limit = args.past_tokens_cell ? kMaxAttentionSplits : (p.past_length + 63u) / 64u;
+  if (limit > kMaxAttentionSplits) limit = kMaxAttentionSplits;
+  uint32_t best = 1;
+  float best_score = -1.0f;
+  for (uint32_t splits = 1; splits <= limit; ++splits) {
+    const uint32_t ctas = pairs * splits;
+    const uint32_t waves = (ctas + resident - 1u) / resident;
+    const float score = (float)ctas / (float)(waves * resident) - 0.004f * (float)splits;
+    if (score > best_score) {
+      best_score = score;
+      best = splits;
+    }
+  }
+  return best;
 }
 
 int launch_paged_attention_split_on(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride,
