@@ -61,6 +61,31 @@ inline float param_f32(const KernelArgs& args, size_t index) {
     if (!(cond)) return fail(args, msg); \
   } while (0)
 
+// Whether launches of this context may overlap the tail of their predecessor
+// (programmatic dependent launch); off with LLMOPT_CUDA_OVERLAP=0.
+bool context_overlap(Context* ctx);
+
+// Launch on the dispatch's stream.  With overlap allowed the grid may become
+// resident while its predecessor in the stream is still draining; every kernel
+// therefore calls grid_dependency_wait() before it touches anything another
+// kernel of the stream may write or still read (weights are never written by a
+// kernel, so a weight prefetch may run ahead of the wait).
+template <typename... Params, typename... Args>
+inline void launch_kernel(const KernelArgs& launch, void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared,
+                          Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared;
+  config.stream = launch.stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = context_overlap(launch.ctx) ? 1 : 0;
+  cudaLaunchKernelEx(&config, kernel, static_cast<Args&&>(args)...);
+}
+
 inline int check_launch(const KernelArgs& args) {
   cudaError_t status = cudaGetLastError();
   if (status != cudaSuccess) return fail(args, std::string("launch failed: ") + cudaGetErrorString(status));
@@ -68,6 +93,17 @@ inline int check_launch(const KernelArgs& args) {
 }
 
 // ---- device helpers ---------------------------------------------------------
+// Blocks until every kernel this grid depends on has finished and its writes are
+// visible; returns at once for a launch without a programmatic dependency.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel of the stream start its launch; it still waits (above) for
+// this grid to finish before it reads what this grid writes.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// The two together: the prologue of a kernel with nothing to do ahead of its inputs.
+__device__ __forceinline__ void grid_chain_prologue() {
+  grid_launch_dependents();
+  grid_dependency_wait();
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);

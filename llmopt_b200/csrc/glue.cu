@@ -8,27 +8,10 @@
 // Launch-latency bound (a few KB each); one warp per row, 16-byte accesses
 // where the layout allows.
 #include "common.cuh"
+#include "rms_norm.cuh"
 
 namespace llmopt {
 namespace {
-
-template <typename T>
-__global__ void rms_norm_kernel(const T* __restrict__ input, const __half* __restrict__ weight,
-                                __half* __restrict__ output, uint32_t rows, uint32_t width, float epsilon) {
-  const uint32_t lane = threadIdx.x & 31u;
-  const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (row >= rows) return;
-  const T* source = input + (size_t)row * width;
-  float square_sum = 0.0f;
-  for (uint32_t col = lane; col < width; col += 32) {
-    const float value = (float)source[col];
-    square_sum += value * value;
-  }
-  square_sum = warp_sum(square_sum);
-  const float inverse = rsqrtf(square_sum / (float)width + epsilon);
-  for (uint32_t col = lane; col < width; col += 32)
-    output[(size_t)row * width + col] = __float2half_rn((float)source[col] * inverse * __half2float(weight[col]));
-}
 
 struct RotaryQkParams {  // lib/metal_normalization_source.ml:760-763
   uint32_t batches, tokens, q_heads, k_heads, width, half_dimension, trig_batches;
@@ -40,6 +23,7 @@ struct RotaryQkParams {  // lib/metal_normalization_source.ml:760-763
 __global__ void rotary_qk_kernel(const __half* __restrict__ q_input, const __half* __restrict__ k_input,
                                  const __half* __restrict__ cosine, const __half* __restrict__ sine,
                                  __half* __restrict__ q_output, __half* __restrict__ k_output, RotaryQkParams p) {
+  grid_chain_prologue();
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t total_rows = p.batches * (p.q_heads + p.k_heads) * p.tokens;
@@ -75,6 +59,7 @@ struct EmbeddingParams {  // lib/metal_tensor_source.ml:237
 
 __global__ void embedding_kernel(const long long* __restrict__ indices, const __half* __restrict__ weight,
                                  __half* __restrict__ output, EmbeddingParams p) {
+  grid_chain_prologue();
   const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= p.tokens * p.width) return;
   const uint32_t token = gid / p.width, dimension = gid % p.width;
@@ -85,16 +70,19 @@ __global__ void embedding_kernel(const long long* __restrict__ indices, const __
 }
 
 __global__ void chain_token_kernel(const uint32_t* __restrict__ argmax_in, long long* __restrict__ token_out) {
+  grid_chain_prologue();
   if (blockIdx.x == 0 && threadIdx.x == 0) token_out[0] = (long long)argmax_in[0];
 }
 
 __global__ void chain_tokens_kernel(const uint32_t* __restrict__ argmax_in, long long* __restrict__ token_out,
                                     uint32_t count) {
+  grid_chain_prologue();
   const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < count) token_out[i] = (long long)argmax_in[i];
 }
 
 __global__ void argmax_f16_kernel(const __half* __restrict__ values, uint32_t count, int* __restrict__ result) {
+  grid_chain_prologue();
   // strict '>' keeps the first maximum (native/ocaml_metal_stubs.m:787-794)
   __shared__ float best_values[256];
   __shared__ uint32_t best_indices[256];
@@ -142,13 +130,12 @@ int launch_rms_norm(const KernelArgs& args) {
   const size_t elements = (size_t)rows * width;
   LLMOPT_REQUIRE(args.lengths[0] >= elements * (INPUT_F32 ? 4 : 2) && args.lengths[1] >= (size_t)width * 2 &&
                      args.lengths[2] >= elements * 2, "buffer is too short");
-  const uint32_t blocks = (rows + 7) / 8;
   if (INPUT_F32)
-    rms_norm_kernel<float><<<blocks, 256, 0, args.stream>>>((const float*)args.buffers[0], (const __half*)args.buffers[1],
-                                                            (__half*)args.buffers[2], rows, width, param_f32(args, 2));
+    launch_rms_norm_rows<float, false>(args, (const float*)args.buffers[0], (const __half*)args.buffers[1],
+                                       (__half*)args.buffers[2], rows, width, param_f32(args, 2));
   else
-    rms_norm_kernel<__half><<<blocks, 256, 0, args.stream>>>((const __half*)args.buffers[0], (const __half*)args.buffers[1],
-                                                             (__half*)args.buffers[2], rows, width, param_f32(args, 2));
+    launch_rms_norm_rows<__half, false>(args, (const __half*)args.buffers[0], (const __half*)args.buffers[1],
+                                        (__half*)args.buffers[2], rows, width, param_f32(args, 2));
   return check_launch(args);
 }
 template int launch_rms_norm<false>(const KernelArgs&);
@@ -168,7 +155,7 @@ int launch_rotary_qk(const KernelArgs& args) {
   LLMOPT_REQUIRE(args.lengths[2] >= trig * 2 && args.lengths[3] >= trig * 2, "cosine/sine buffer is too short");
   const uint32_t rows = p.batches * (p.q_heads + p.k_heads) * p.tokens;
   if (rows == 0) return 0;
-  rotary_qk_kernel<<<(rows + 7) / 8, 256, 0, args.stream>>>(
+  launch_kernel(args, rotary_qk_kernel, dim3((rows + 7) / 8), dim3(256), 0,
       (const __half*)args.buffers[0], (const __half*)args.buffers[1], (const __half*)args.buffers[2],
       (const __half*)args.buffers[3], (__half*)args.buffers[4], (__half*)args.buffers[5], p);
   return check_launch(args);
@@ -183,7 +170,7 @@ int launch_embedding_f16(const KernelArgs& args) {
   LLMOPT_REQUIRE(args.lengths[0] >= (size_t)p.tokens * 8 && args.lengths[1] >= (size_t)p.vocabulary * p.width * 2 &&
                      args.lengths[2] >= elements * 2, "buffer is too short");
   if (elements == 0) return 0;
-  embedding_kernel<<<(uint32_t)((elements + 255) / 256), 256, 0, args.stream>>>(
+  launch_kernel(args, embedding_kernel, dim3((uint32_t)((elements + 255) / 256)), dim3(256), 0,
       (const long long*)args.buffers[0], (const __half*)args.buffers[1], (__half*)args.buffers[2], p);
   return check_launch(args);
 }
@@ -192,7 +179,7 @@ int launch_embedding_f16(const KernelArgs& args) {
 int launch_chain_token_id(const KernelArgs& args) {
   LLMOPT_REQUIRE(args.buffer_count == 2, "expects 2 buffers");
   LLMOPT_REQUIRE(args.lengths[0] >= 4 && args.lengths[1] >= 8, "buffer is too short");
-  chain_token_kernel<<<1, 32, 0, args.stream>>>((const uint32_t*)args.buffers[0], (long long*)args.buffers[1]);
+  launch_kernel(args, chain_token_kernel, dim3(1), dim3(32), 0, (const uint32_t*)args.buffers[0], (long long*)args.buffers[1]);
   return check_launch(args);
 }
 
@@ -204,7 +191,7 @@ int launch_chain_token_ids(const KernelArgs& args) {
   const uint32_t count = param_u32(args, 0);
   LLMOPT_REQUIRE(args.lengths[0] >= (size_t)count * 4 && args.lengths[1] >= (size_t)count * 8, "buffer is too short");
   if (count == 0) return 0;
-  chain_tokens_kernel<<<(count + 127) / 128, 128, 0, args.stream>>>((const uint32_t*)args.buffers[0],
+  launch_kernel(args, chain_tokens_kernel, dim3((count + 127) / 128), dim3(128), 0, (const uint32_t*)args.buffers[0],
                                                                      (long long*)args.buffers[1], count);
   return check_launch(args);
 }

@@ -37,6 +37,7 @@ __global__ void paged_rows_kernel(const __half* __restrict__ query, const __half
                                   const uint32_t* __restrict__ slots, const uint8_t* __restrict__ mask,
                                   __half* __restrict__ output, PagedParams p, uint32_t slot_batch_stride,
                                   const uint32_t* __restrict__ past_cell) {
+  grid_chain_prologue();
   if (past_cell) p.past_length = *past_cell;
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -156,7 +157,7 @@ int launch_attention_q8_paged(const KernelArgs& args) {
   if (mask == nullptr && q_len == 1 && p.window == 0 && paged_split_supported(p))
     return launch_paged_attention_split(args, p, slot_batch_stride);
   const uint32_t blocks = (uint32_t)((rows + 7) / 8);
-  paged_rows_kernel<<<blocks, 256, 0, args.stream>>>(
+  launch_kernel(args, paged_rows_kernel, dim3(blocks), dim3(256), 0,
       (const __half*)args.buffers[0], (const __half*)args.buffers[1], (const __half*)args.buffers[2],
       (const uint8_t*)args.buffers[3], (const uint32_t*)args.buffers[4], mask, (__half*)args.buffers[6], p,
       slot_batch_stride, args.past_tokens_cell);

@@ -129,6 +129,7 @@ __global__ void __launch_bounds__(kWarps * 32, kResidentCtas)
 paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__ pool,
                    const uint32_t* __restrict__ slots, float* __restrict__ scratch, PagedParams p,
                    uint32_t slot_batch_stride, uint32_t splits, const uint32_t* __restrict__ past_cell) {
+  grid_chain_prologue();
   using Shape = SplitShape<D, CP>;
   constexpr int kSteps = D / 16;  // k-steps of QK^T, m-tiles of PV
   constexpr int kStages = Shape::kStages;
@@ -429,6 +430,7 @@ __global__ void __launch_bounds__(D)
 paged_merge_kernel(const __half* __restrict__ query, const __half* __restrict__ current_key,
                    const __half* __restrict__ current_value, const float* __restrict__ scratch,
                    __half* __restrict__ output, PagedParams p, uint32_t splits) {
+  grid_chain_prologue();
   constexpr int kRecord = 16 + 8 * D;
   static_assert(D >= (int)kMaxAttentionSplits, "one thread per split in the weighing phase");
   __shared__ float partial[3][D / 32];
@@ -487,7 +489,7 @@ int launch_split_copy(const KernelArgs& args, const PagedParams& p, uint32_t slo
     cudaGetLastError();
     return fail(args, "paged attention: the device cannot give one CTA its tile ring");
   }
-  kernel<<<dim3(splits, p.kv_heads, p.batches), kWarps * 32, ring_bytes, args.stream>>>(
+  launch_kernel(args, kernel, dim3(splits, p.kv_heads, p.batches), dim3(kWarps * 32), ring_bytes,
       (const __half*)args.buffers[0], (const uint8_t*)args.buffers[3], (const uint32_t*)args.buffers[4], scratch, p,
       slot_batch_stride, splits, args.past_tokens_cell);
   return check_launch(args);
@@ -500,7 +502,7 @@ int launch_split(const KernelArgs& args, const PagedParams& p, uint32_t slot_bat
   const int status = aligned ? launch_split_copy<D, GROUP, 16>(args, p, slot_batch_stride, scratch, splits)
                              : launch_split_copy<D, GROUP, 8>(args, p, slot_batch_stride, scratch, splits);
   if (status) return status;
-  paged_merge_kernel<D><<<dim3(p.query_heads, p.batches), D, 0, args.stream>>>(
+  launch_kernel(args, paged_merge_kernel<D>, dim3(p.query_heads, p.batches), dim3(D), 0,
       (const __half*)args.buffers[0], (const __half*)args.buffers[1], (const __half*)args.buffers[2], scratch,
       (__half*)args.buffers[6], p, splits);
   return check_launch(args);

@@ -47,6 +47,7 @@ __device__ __forceinline__ void quantize_group(const __half* __restrict__ source
 
 __global__ void pack_attention_kernel(const __half* __restrict__ source, const uint32_t* __restrict__ slots,
                                       uint8_t* __restrict__ pool, AttentionCacheParams p) {
+  grid_chain_prologue();
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t logical_group = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t groups_per_head = p.head_dim / p.group_size;
@@ -70,6 +71,7 @@ __global__ void pack_attention_pair_kernel(const __half* __restrict__ key_source
                                            const __half* __restrict__ value_source,
                                            const uint32_t* __restrict__ slots, uint8_t* __restrict__ pool,
                                            AttentionCachePairParams p) {
+  grid_chain_prologue();
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t logical_group = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t groups_per_head = p.head_dim / p.group_size;
@@ -93,6 +95,7 @@ __global__ void pack_attention_pair_kernel(const __half* __restrict__ key_source
 
 __global__ void unpack_attention_kernel(const uint8_t* __restrict__ pool, const uint32_t* __restrict__ slots,
                                         __half* __restrict__ destination, AttentionCacheParams p) {
+  grid_chain_prologue();
   const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
   const uint32_t segment_elements = p.heads * p.head_dim;
   if (gid >= p.items * segment_elements) return;
@@ -113,6 +116,7 @@ __global__ void unpack_attention_kernel(const uint8_t* __restrict__ pool, const 
 
 __global__ void pack_checkpoint_kernel(const __half* __restrict__ source, uint8_t* __restrict__ pool,
                                        CheckpointCacheParams p, const uint32_t* __restrict__ checkpoint_cell) {
+  grid_chain_prologue();
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t logical_group = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t layer_groups = p.layer_elements / p.group_size;
@@ -128,6 +132,7 @@ __global__ void pack_checkpoint_kernel(const __half* __restrict__ source, uint8_
 
 __global__ void unpack_checkpoint_kernel(const uint8_t* __restrict__ pool, __half* __restrict__ destination,
                                          CheckpointCacheParams p) {
+  grid_chain_prologue();
   const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= p.layer_elements) return;
   const size_t base = (size_t)p.checkpoint * p.checkpoint_stride;
@@ -162,7 +167,7 @@ int launch_cache_pack_attention_q8(const KernelArgs& args) {
                  "source buffer is shorter than the packed range");
   const uint32_t groups = p.items * p.heads * (p.head_dim / p.group_size);
   if (groups == 0) return 0;
-  pack_attention_kernel<<<(groups + 7) / 8, 256, 0, args.stream>>>(
+  launch_kernel(args, pack_attention_kernel, dim3((groups + 7) / 8), dim3(256), 0,
       (const __half*)args.buffers[0], (const uint32_t*)args.buffers[1], (uint8_t*)args.buffers[2], p);
   return check_launch(args);
 }
@@ -176,7 +181,7 @@ int launch_cache_pack_attention_q8_pair(const KernelArgs& args) {
   LLMOPT_REQUIRE(args.lengths[2] >= (size_t)p.items * 4, "slots buffer is shorter than items");
   const uint32_t groups = p.items * p.heads * (p.head_dim / p.group_size);
   if (groups == 0) return 0;
-  pack_attention_pair_kernel<<<(groups + 7) / 8, 256, 0, args.stream>>>(
+  launch_kernel(args, pack_attention_pair_kernel, dim3((groups + 7) / 8), dim3(256), 0,
       (const __half*)args.buffers[0], (const __half*)args.buffers[1], (const uint32_t*)args.buffers[2],
       (uint8_t*)args.buffers[3], p);
   return check_launch(args);
@@ -192,7 +197,7 @@ int launch_cache_unpack_attention_q8(const KernelArgs& args) {
   const size_t elements = (size_t)p.items * p.heads * p.head_dim;
   LLMOPT_REQUIRE(args.lengths[2] >= elements * 2, "destination buffer is too short");
   if (elements == 0) return 0;
-  unpack_attention_kernel<<<(uint32_t)((elements + 255) / 256), 256, 0, args.stream>>>(
+  launch_kernel(args, unpack_attention_kernel, dim3((uint32_t)((elements + 255) / 256)), dim3(256), 0,
       (const uint8_t*)args.buffers[0], (const uint32_t*)args.buffers[1], (__half*)args.buffers[2], p);
   return check_launch(args);
 }
@@ -206,7 +211,7 @@ int launch_cache_pack_checkpoint_q8(const KernelArgs& args) {
   LLMOPT_REQUIRE(args.lengths[0] >= (size_t)p.layer_elements * 2, "source buffer is too short");
   const uint32_t groups = p.layer_elements / p.group_size;
   if (groups == 0) return 0;
-  pack_checkpoint_kernel<<<(groups + 7) / 8, 256, 0, args.stream>>>(
+  launch_kernel(args, pack_checkpoint_kernel, dim3((groups + 7) / 8), dim3(256), 0,
       (const __half*)args.buffers[0], (uint8_t*)args.buffers[1], p, args.checkpoint_cell);
   return check_launch(args);
 }
@@ -219,7 +224,7 @@ int launch_cache_unpack_checkpoint_q8(const KernelArgs& args) {
   LLMOPT_REQUIRE(p.group_size > 0 && p.layer_elements % p.group_size == 0, "layer_elements must be a multiple of group_size");
   LLMOPT_REQUIRE(args.lengths[1] >= (size_t)p.layer_elements * 2, "destination buffer is too short");
   if (p.layer_elements == 0) return 0;
-  unpack_checkpoint_kernel<<<(p.layer_elements + 255) / 256, 256, 0, args.stream>>>(
+  launch_kernel(args, unpack_checkpoint_kernel, dim3((p.layer_elements + 255) / 256), dim3(256), 0,
       (const uint8_t*)args.buffers[0], (__half*)args.buffers[1], p);
   return check_launch(args);
 }

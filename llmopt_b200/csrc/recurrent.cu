@@ -22,6 +22,7 @@ struct ShortConvSiluTmParams {  // lib/metal_recurrent_source.ml:67-70
 template <typename W>
 __global__ void short_conv_kernel(const __half* __restrict__ input, const W* __restrict__ weight,
                                   __half* __restrict__ output, ShortConvParams p) {
+  grid_chain_prologue();
   const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= p.batches * p.channels * p.output_width) return;
   const uint32_t position = gid % p.output_width;
@@ -40,6 +41,7 @@ __global__ void short_conv_kernel(const __half* __restrict__ input, const W* __r
 template <typename W>
 __global__ void short_conv_silu_tm_kernel(const __half* __restrict__ input, const W* __restrict__ weight,
                                           __half* __restrict__ output, ShortConvSiluTmParams p) {
+  grid_chain_prologue();
   const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= p.batches * p.tokens * p.channels) return;
   const uint32_t channel = gid % p.channels;
@@ -60,6 +62,7 @@ __global__ void short_conv_silu_tm_kernel(const __half* __restrict__ input, cons
 __global__ void short_conv_step_kernel(const __half* __restrict__ in_proj, __half* __restrict__ conv_state,
                                        const __half* __restrict__ conv_weight, __half* __restrict__ output,
                                        uint32_t channels) {
+  grid_chain_prologue();
   const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= channels) return;
   const float x0 = __half2float(in_proj[c]);
@@ -83,6 +86,7 @@ __global__ void short_conv_prefill_kernel(const __half* __restrict__ in_proj, co
                                           __half* __restrict__ output, __half* __restrict__ state_out,
                                           const __half* __restrict__ state_in, uint32_t tokens, uint32_t channels,
                                           uint32_t has_initial_state) {
+  grid_chain_prologue();
   const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= channels) return;
   const float w0 = __half2float(conv_weight[c * 3 + 0]);
@@ -126,10 +130,10 @@ int launch_short_conv(const KernelArgs& args) {
   if (count == 0) return 0;
   const uint32_t blocks = (uint32_t)((count + 255) / 256);
   if (WEIGHT_F32)
-    short_conv_kernel<float><<<blocks, 256, 0, args.stream>>>((const __half*)args.buffers[0], (const float*)args.buffers[1],
+    launch_kernel(args, short_conv_kernel<float>, dim3(blocks), dim3(256), 0, (const __half*)args.buffers[0], (const float*)args.buffers[1],
                                                               (__half*)args.buffers[2], p);
   else
-    short_conv_kernel<__half><<<blocks, 256, 0, args.stream>>>((const __half*)args.buffers[0], (const __half*)args.buffers[1],
+    launch_kernel(args, short_conv_kernel<__half>, dim3(blocks), dim3(256), 0, (const __half*)args.buffers[0], (const __half*)args.buffers[1],
                                                                (__half*)args.buffers[2], p);
   return check_launch(args);
 }
@@ -148,10 +152,10 @@ int launch_short_conv_silu_tm(const KernelArgs& args) {
   if (count == 0) return 0;
   const uint32_t blocks = (uint32_t)((count + 255) / 256);
   if (WEIGHT_F32)
-    short_conv_silu_tm_kernel<float><<<blocks, 256, 0, args.stream>>>(
+    launch_kernel(args, short_conv_silu_tm_kernel<float>, dim3(blocks), dim3(256), 0,
         (const __half*)args.buffers[0], (const float*)args.buffers[1], (__half*)args.buffers[2], p);
   else
-    short_conv_silu_tm_kernel<__half><<<blocks, 256, 0, args.stream>>>(
+    launch_kernel(args, short_conv_silu_tm_kernel<__half>, dim3(blocks), dim3(256), 0,
         (const __half*)args.buffers[0], (const __half*)args.buffers[1], (__half*)args.buffers[2], p);
   return check_launch(args);
 }
@@ -167,7 +171,7 @@ int launch_short_conv_step(const KernelArgs& args) {
   LLMOPT_REQUIRE(args.lengths[0] >= (size_t)channels * 6 && args.lengths[1] >= (size_t)channels * 6 &&
                      args.lengths[2] >= (size_t)channels * 6 && args.lengths[3] >= (size_t)channels * 2,
                  "buffer is too short");
-  short_conv_step_kernel<<<(channels + 255) / 256, 256, 0, args.stream>>>(
+  launch_kernel(args, short_conv_step_kernel, dim3((channels + 255) / 256), dim3(256), 0,
       (const __half*)args.buffers[0], (__half*)args.buffers[1], (const __half*)args.buffers[2], (__half*)args.buffers[3],
       channels);
   return check_launch(args);
@@ -190,7 +194,7 @@ int launch_short_conv_prefill(const KernelArgs& args) {
     LLMOPT_REQUIRE(args.lengths[4] >= (size_t)channels * 6, "initial state buffer is too short");
     state_in = (const __half*)args.buffers[4];
   }
-  short_conv_prefill_kernel<<<(channels + 255) / 256, 256, 0, args.stream>>>(
+  launch_kernel(args, short_conv_prefill_kernel, dim3((channels + 255) / 256), dim3(256), 0,
       (const __half*)args.buffers[0], (const __half*)args.buffers[1], (__half*)args.buffers[2], (__half*)args.buffers[3],
       state_in, tokens, channels, has_initial);
   return check_launch(args);

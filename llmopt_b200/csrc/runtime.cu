@@ -10,6 +10,7 @@
 
 #include <atomic>
 #include <condition_variable>
+#include <cstdlib>
 #include <cstring>
 #include <deque>
 #include <map>
@@ -70,6 +71,8 @@ struct Context {
   // Pinned, device-visible word: kernels whose bounded waits ran out set it; the host
   // reads it after every stream wait.
   uint32_t* device_error = nullptr;
+  // Launches may overlap the tail of their predecessor (programmatic dependent launch).
+  bool overlap = true;
 };
 
 struct Allocation {
@@ -151,6 +154,7 @@ void* context_scratch(Context* context, size_t bytes, std::string* error) {
   return block;
 }
 int context_sm_count(Context* context) { return context->sm_count; }
+bool context_overlap(Context* context) { return context != nullptr && context->overlap; }
 uint32_t* context_device_error(Context* context) { return context->device_error; }
 
 static void register_kernels(llmopt_cuda_library* library) {
@@ -352,6 +356,7 @@ struct RowBindings {
 };
 
 __global__ void plan_prologue_kernel(const PlanCells* cells, long long* token_buffer, RowBindings bindings) {
+  grid_chain_prologue();
   if (blockIdx.x == 0 && threadIdx.x == 0 && token_buffer != nullptr) token_buffer[0] = cells->token;
   const uint32_t past = cells->past_tokens;
   for (int b = 0; b < bindings.count; ++b) {
@@ -364,6 +369,7 @@ __global__ void plan_prologue_kernel(const PlanCells* cells, long long* token_bu
 
 // Between chained replays: next token = previous output, one more past token.
 __global__ void plan_advance_kernel(PlanCells* cells, const int* output, int* tokens_out, int step) {
+  grid_chain_prologue();
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     const int token = output[0];
     tokens_out[step] = token;
@@ -442,6 +448,7 @@ int llmopt_cuda_create_context(int device, llmopt_cuda_context** out) {
   llmopt_cuda_context* context = new llmopt_cuda_context();
   context->device = device;
   context->sm_count = properties.multiProcessorCount;
+  if (const char* overlap = getenv("LLMOPT_CUDA_OVERLAP")) context->overlap = overlap[0] != '0';
   context->name = properties.name;
   status = cudaStreamCreateWithFlags(&context->stream, cudaStreamNonBlocking);
   if (status != cudaSuccess) {
@@ -1141,6 +1148,7 @@ int llmopt_cuda_w4a16_linear(llmopt_cuda_context* context, const void* input, co
 
 namespace llmopt {
 __global__ void flush_kernel(uint4* buffer, size_t count, uint32_t seed) {
+  grid_chain_prologue();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
     buffer[i] = make_uint4(seed, seed + 1, seed + 2, seed + 3);
 }

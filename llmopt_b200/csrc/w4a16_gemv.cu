@@ -35,6 +35,7 @@ namespace {
 
 template <int NT, int NMAT, int EPI, bool AFFINE>
 __global__ void __launch_bounds__(256, (NT * NMAT >= 8) ? 1 : 2) w4a16_gemv_kernel(const GemvProblem p) {
+  grid_chain_prologue();
   // groups whose weight loads are issued together
   constexpr int kUnroll = (NT * NMAT >= 8) ? 2 : 4;
   extern __shared__ float shared[];
@@ -258,7 +259,7 @@ int launch_one(const KernelArgs& args, const GemvProblem& p) {
   }
   const uint32_t resident = (uint32_t)context_sm_count(args.ctx) * 3u;
   const uint32_t ctas = wanted < resident ? wanted : resident;
-  kernel<<<ctas == 0 ? 1 : ctas, 256, shared_bytes, args.stream>>>(p);
+  launch_kernel(args, kernel, dim3(ctas == 0 ? 1 : ctas), dim3(256), shared_bytes, p);
   return check_launch(args);
 }
 

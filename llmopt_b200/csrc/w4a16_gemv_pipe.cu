@@ -99,6 +99,10 @@ template <int NT, int NMAT, int EPI, bool SMALLX, int GPW>
 __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvProblem p, const uint32_t stage_count,
                                                                    uint32_t* error_word) {
   extern __shared__ __align__(16) unsigned char shared[];
+  // The next kernel of the stream may start its launch now; the producer warp below
+  // streams weights (which no kernel writes) without waiting for the previous kernel,
+  // the consumer warps wait for it before they read the activations.
+  grid_launch_dependents();
   constexpr int kAcc = NMAT * NT * 4;
   constexpr int kChunkK = Stage<GPW>::kChunkK, kRowBytes = Stage<GPW>::kRowBytes;
   constexpr int kStageWeights = Stage<GPW>::kWeights, kScaleRow = Stage<GPW>::kScaleRow;
@@ -210,6 +214,7 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
   }
 
   // ------------------------------ consumers ------------------------------
+  grid_dependency_wait();
   const uint32_t r = lane >> 2, c = lane & 3u;
   if (SMALLX) {
     // activations -> shared in MMA fragment order: unit ((g*2 + h)*x_rows + row)*4 + c holds
@@ -476,7 +481,7 @@ int run_pipe(const KernelArgs& args, const GemvProblem& p, const PipePlan& plan)
     cudaGetLastError();
     return -1;
   }
-  kernel<<<plan.ctas, kThreads, plan.shared_bytes, args.stream>>>(p, plan.stages, context_device_error(args.ctx));
+  launch_kernel(args, kernel, dim3(plan.ctas), dim3(kThreads), plan.shared_bytes, p, plan.stages, context_device_error(args.ctx));
   return check_launch(args);
 }
 

@@ -10,6 +10,7 @@
 //   dispatch_w4a16_lm_head_argmax_command  lib/metal_dispatch_linear.ml:570-721
 #include <float.h>
 
+#include "rms_norm.cuh"
 #include "w4a16_gemv.cuh"
 
 namespace llmopt {
@@ -19,30 +20,6 @@ namespace {
 
 // llmopt_w4a16_swiglu_rms_{f16,f32}_g64, lib/metal_w4a16_source.ml:496-526:
 // normalized = half(x * w * rsqrt(mean(x^2) + eps)); one CTA per row.
-template <typename T>
-__global__ void __launch_bounds__(256) rms_rows_kernel(const T* __restrict__ input,
-                                                       const __half* __restrict__ weight,
-                                                       __half* __restrict__ normalized, uint32_t k,
-                                                       float epsilon) {
-  __shared__ float partial[8];
-  const uint32_t row = blockIdx.x, tid = threadIdx.x;
-  const T* source = input + (size_t)row * k;
-  float sum = 0.0f;
-  for (uint32_t i = tid; i < k; i += 256) {
-    const float value = (float)source[i];
-    sum += value * value;
-  }
-  sum = warp_sum(sum);
-  if ((tid & 31u) == 0) partial[tid >> 5] = sum;
-  __syncthreads();
-  float total = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) total += partial[i];
-  const float inverse = rsqrtf(total / (float)k + epsilon);
-  for (uint32_t i = tid; i < k; i += 256)
-    normalized[(size_t)row * k + i] = __float2half_rn((float)source[i] * __half2float(weight[i]) * inverse);
-}
-
 // LM-head prologue, lib/metal_w4a16_source.ml:1022-1043: the reference keeps the
 // normalised row in fp32.  The tensor-core product takes fp16 operands, so the
 // fp32 value is carried as an exact-to-2^-22 pair hi = half(v), lo = half(v - hi)
@@ -52,6 +29,7 @@ __global__ void __launch_bounds__(256) rms_split_rows_kernel(const T* __restrict
                                                              const __half* __restrict__ weight,
                                                              __half* __restrict__ slots, uint32_t k,
                                                              float epsilon) {
+  grid_chain_prologue();
   __shared__ float partial[8];
   const uint32_t row = blockIdx.x, tid = threadIdx.x;
   const T* source = input + (size_t)row * k;
@@ -93,6 +71,7 @@ __device__ __forceinline__ bool better(float value, uint32_t index, float best, 
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ logits,
                                                              Candidate* __restrict__ candidates,
                                                              __half* __restrict__ half_logits, uint32_t n) {
+  grid_chain_prologue();
   __shared__ float values[256];
   __shared__ uint32_t indices[256];
   const uint32_t row = blockIdx.y, part = blockIdx.x, parts = gridDim.x, tid = threadIdx.x;
@@ -126,6 +105,7 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __rest
 // candidates per row, ties to the lowest index.
 __global__ void __launch_bounds__(256) argmax_reduce_kernel(const Candidate* __restrict__ candidates,
                                                             uint32_t* __restrict__ token_ids, uint32_t parts) {
+  grid_chain_prologue();
   __shared__ float values[256];
   __shared__ uint32_t indices[256];
   const uint32_t row = blockIdx.x, tid = threadIdx.x;
@@ -168,9 +148,9 @@ int lm_head_stage(const KernelArgs& args, bool input_f32, const void* input, con
   if (tiles * 8 > m * 2 || (m % 4) != 0)  // unused slot rows must read as zeros
     cudaMemsetAsync(slots, 0, slot_bytes, args.stream);
   if (input_f32)
-    rms_split_rows_kernel<float><<<m, 256, 0, args.stream>>>((const float*)input, norm_weight, slots, k, epsilon);
+    launch_kernel(args, rms_split_rows_kernel<float>, dim3(m), dim3(256), 0, (const float*)input, norm_weight, slots, k, epsilon);
   else
-    rms_split_rows_kernel<__half><<<m, 256, 0, args.stream>>>((const __half*)input, norm_weight, slots, k, epsilon);
+    launch_kernel(args, rms_split_rows_kernel<__half>, dim3(m), dim3(256), 0, (const __half*)input, norm_weight, slots, k, epsilon);
   if (int status = check_launch(args)) return status;
   GemvProblem problem = {};
   problem.x = slots;
@@ -181,7 +161,7 @@ int lm_head_stage(const KernelArgs& args, bool input_f32, const void* input, con
   problem.matrices = 1;
   problem.out_f32 = logits_f32;
   if (int status = launch_w4a16_gemv(args, problem, kEpiSplitF32, false)) return status;
-  argmax_partial_kernel<<<dim3(kCandidateParts, m), 256, 0, args.stream>>>(logits_f32, candidates, logits, n);
+  launch_kernel(args, argmax_partial_kernel, dim3(kCandidateParts, m), dim3(256), 0, logits_f32, candidates, logits, n);
   return check_launch(args);
 }
 
@@ -280,8 +260,8 @@ int launch_w4a16_swiglu_rms_f16(const KernelArgs& args) {
   LLMOPT_REQUIRE(m > 0 && k > 0, "needs m, k > 0");
   LLMOPT_REQUIRE(args.lengths[0] >= (size_t)m * k * 2 && args.lengths[1] >= (size_t)k * 2 &&
                      args.lengths[2] >= (size_t)m * k * 2, "buffer is too short");
-  rms_rows_kernel<__half><<<m, 256, 0, args.stream>>>((const __half*)args.buffers[0], (const __half*)args.buffers[1],
-                                                      (__half*)args.buffers[2], k, param_f32(args, 3));
+  launch_rms_norm_rows<__half, true>(args, (const __half*)args.buffers[0], (const __half*)args.buffers[1],
+                                     (__half*)args.buffers[2], m, k, param_f32(args, 3));
   return check_launch(args);
 }
 int launch_w4a16_swiglu_rms_f32(const KernelArgs& args) {
@@ -290,8 +270,8 @@ int launch_w4a16_swiglu_rms_f32(const KernelArgs& args) {
   LLMOPT_REQUIRE(m > 0 && k > 0, "needs m, k > 0");
   LLMOPT_REQUIRE(args.lengths[0] >= (size_t)m * k * 4 && args.lengths[1] >= (size_t)k * 2 &&
                      args.lengths[2] >= (size_t)m * k * 2, "buffer is too short");
-  rms_rows_kernel<float><<<m, 256, 0, args.stream>>>((const float*)args.buffers[0], (const __half*)args.buffers[1],
-                                                     (__half*)args.buffers[2], k, param_f32(args, 3));
+  launch_rms_norm_rows<float, true>(args, (const float*)args.buffers[0], (const __half*)args.buffers[1],
+                                    (__half*)args.buffers[2], m, k, param_f32(args, 3));
   return check_launch(args);
 }
 
@@ -407,7 +387,7 @@ int launch_w4a16_lm_head_argmax(const KernelArgs& args) {
                                  (const uint8_t*)args.buffers[2], (const __half*)args.buffers[3], candidates,
                                  EXTRA ? (__half*)args.buffers[5] : nullptr, m, n, k, param_f32(args, 3)))
     return status;
-  argmax_reduce_kernel<<<m, 256, 0, args.stream>>>(candidates, (uint32_t*)args.buffers[4], kCandidateParts);
+  launch_kernel(args, argmax_reduce_kernel, dim3(m), dim3(256), 0, candidates, (uint32_t*)args.buffers[4], kCandidateParts);
   return check_launch(args);
 }
 template int launch_w4a16_lm_head_argmax<false, false>(const KernelArgs&);
@@ -445,7 +425,7 @@ int launch_w4a16_lm_head_reduce(const KernelArgs& args) {
   LLMOPT_REQUIRE(m > 0, "needs m > 0");
   LLMOPT_REQUIRE(args.lengths[0] >= (size_t)m * kCandidateParts * sizeof(Candidate) && args.lengths[1] >= (size_t)m * 4,
                  "buffer is too short");
-  argmax_reduce_kernel<<<m, 256, 0, args.stream>>>((const Candidate*)args.buffers[0], (uint32_t*)args.buffers[1],
+  launch_kernel(args, argmax_reduce_kernel, dim3(m), dim3(256), 0, (const Candidate*)args.buffers[0], (uint32_t*)args.buffers[1],
                                                    kCandidateParts);
   return check_launch(args);
 }
