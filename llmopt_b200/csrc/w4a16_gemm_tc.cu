@@ -1,0 +1,500 @@
+// Prefill (M >= 64) W4A16 group-64 product on the 5th-generation tensor cores:
+//   Y[M, N] = X[M, K] . dequant(W[N, K])^T, fp32 accumulate in tensor memory, one rounding to half.
+// Restates lib/metal_w4a16_source.ml:60-212 (the reference's tiled simdgroup-matrix kernels for
+// M > 1: dequantise a weight tile into threadgroup memory, multiply on the matrix units) for sm_100a.
+//
+// One CTA computes a 128 x 256 output tile (or 128 x 128 of silu(gate) * up in the dual form, the
+// 256 tile rows being 128 gate rows and 128 up rows).  Per 64-wide k-block, which is exactly one
+// quantisation group:
+//   warp 0    TMA: the X tile [128 x 64] fp16 (128-byte swizzle) and the packed weight rows
+//             [256 x 32 bytes] into a 5-deep ring, completion on an mbarrier by byte count;
+//   warps 2-9 one thread per weight row: 32 packed bytes -> 64 exact integers in fp16 (PRMT + LOP3
+//             + one subtract) -> times the group scale -> the row of the B tile in the canonical
+//             K-major 128-byte-swizzled layout (3-deep ring); generic-proxy writes are published
+//             to the tensor core with fence.proxy.async;
+//   warp 1    one thread issues four tcgen05.mma (128 x 256 x 16, kind::f16) per k-block with the
+//             accumulator in tensor memory; tcgen05.commit releases the ring stages.
+// After the last k-block the eight conversion warps read the accumulator (tcgen05.ld, each warp
+// its 32-lane quarter and one column half), apply the epilogue and store halves.
+//
+// The weight rounding differs from the decode kernels in one place: the B operand is
+// half(q * scale) (the tensor core needs fp16 operands), where the decode path scales the fp32
+// group sum; the difference is below 2^-11 per weight and averages out over K.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out raises the context's device error
+// word and the CTA drains its copies, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include <atomic>
+
+#include "w4a16_gemv.cuh"
+#include "w4a16_gemv_device.cuh"
+
+namespace llmopt {
+using namespace gemv;
+
+uint32_t* context_device_error(Context* ctx);
+
+namespace {
+
+constexpr int kBM = 128, kBN = 256, kBK = 64;
+constexpr int kLoadStages = 5, kBStages = 3;
+constexpr int kATileBytes = kBM * kBK * 2;   // 16 KiB
+constexpr int kRawTileBytes = kBN * kBK / 2;  // 8 KiB
+constexpr int kBTileBytes = kBN * kBK * 2;    // 32 KiB
+constexpr int kConvertWarps = 8;
+constexpr int kThreadsTc = (2 + kConvertWarps) * 32;
+constexpr uint32_t kTmemColumns = 256;
+constexpr uint32_t kWaitLimit = 1u << 20;
+
+constexpr int kOffsetA = 0;
+constexpr int kOffsetB = kOffsetA + kLoadStages * kATileBytes;
+constexpr int kOffsetRaw = kOffsetB + kBStages * kBTileBytes;
+constexpr int kOffsetBarriers = kOffsetRaw + kLoadStages * kRawTileBytes;
+constexpr int kBarrierCount = 2 * kLoadStages + 2 * kBStages + 1;
+constexpr int kOffsetTmemHolder = kOffsetBarriers + kBarrierCount * 8;
+constexpr int kOffsetAbort = kOffsetTmemHolder + 4;
+constexpr int kSharedBytesTc = kOffsetAbort + 4 + 1024;  // + slack to align the base to 1024 bytes
+
+enum TcEpilogue { kTcLinear = 0, kTcDualSwiglu = 1, kTcTagged = 2 };
+
+struct TcProblem {
+  uint32_t m, n, k;  // n: output columns
+  const __half* scale[2];
+  const __half* zero[2];
+  __half* out;
+  const __half* aux0;
+  const __half* aux1;
+  uint32_t aux_row_stride;
+  uint32_t has_aux;
+  uint32_t tag;
+};
+
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void barrier_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void barrier_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void barrier_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase of parity `parity`; false when the limit ran out.
+__device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t destination, const CUtensorMap* map, int32_t x, int32_t y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(destination), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 bytes, 8-row
+// groups 1024 bytes apart (stride byte offset), descriptor version 1.
+__device__ __forceinline__ uint64_t operand_descriptor(uint32_t shared_address) {
+  uint64_t descriptor = 0;
+  descriptor |= (uint64_t)((shared_address & 0x3ffffu) >> 4);  // start address, bits [0, 14)
+  descriptor |= (uint64_t)1 << 16;                             // leading byte offset (unused with swizzle)
+  descriptor |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset, bits [32, 46)
+  descriptor |= (uint64_t)1 << 46;                             // version
+  descriptor |= (uint64_t)2 << 61;                             // SWIZZLE_128B
+  return descriptor;
+}
+
+// Instruction descriptor for kind::f16: fp16 A and B, fp32 accumulator, both K-major, 128 x 256.
+constexpr uint32_t kInstruction = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) |
+                                  ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(kInstruction), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load_32(uint32_t address, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(address)
+      : "memory");
+}
+
+// Two packed bytes' worth of one row: byte b of `word` holds k = 2b (low nibble) and 2b + 1.
+// Returns half2(w[2b] , w[2b+1]) = (q * scale) for the symmetric form, ((u - zero) * scale) for
+// the affine one.  `scales` = (scale, scale / 16): the high nibble is read in place, 16 times
+// too large, and the factor is folded into its multiplier (exact: a power of two).
+template <bool AFFINE, int BYTE>
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t word, uint32_t scales, uint32_t zeros) {
+  constexpr uint32_t selector = BYTE | (BYTE << 4) | (BYTE << 8) | (BYTE << 12);
+  const uint32_t spread = prmt(word, word, selector);  // the byte in both half-words
+  if (AFFINE) {
+    // (1024 + u, 1024 + 16 u) -> (u, 16 u) -> minus (zero, 16 zero) -> times (scale, scale / 16)
+    const uint32_t biased = lop3_and_xor(spread, 0x00f0000fu, 0x64006400u);
+    const uint32_t integers = hsub2_u32(biased, 0x64006400u);
+    return hmul2_u32(hsub2_u32(integers, zeros), scales);
+  }
+  // two's complement nibble q: (q ^ 8) is q + 8 as unsigned; 1024 + 8 + q and 1024 + 128 + 16 q
+  const uint32_t biased = lop3_and_xor(spread, 0x00f0000fu, 0x64806408u);
+  return hmul2_u32(hsub2_u32(biased, 0x64806408u), scales);
+}
+
+// Launch id of the last launch in which a bounded wait ran out (0: none).
+__device__ uint32_t g_abandoned_launch = 0;
+
+template <int EPI, bool AFFINE>
+__global__ void __launch_bounds__(kThreadsTc, 1)
+w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w0,
+                     const __grid_constant__ CUtensorMap map_w1, const TcProblem p, uint32_t* error_word,
+                     uint32_t launch_id) {
+  extern __shared__ unsigned char shared_raw[];
+  grid_chain_prologue();
+  // A CTA that starts after another one of the same launch has given up does nothing, which
+  // keeps a failing grid short.  The mark lives in device memory: the error word is pinned host
+  // memory, and polling it from every CTA costs a PCIe round trip per thread.
+  if (*reinterpret_cast<volatile uint32_t*>(&g_abandoned_launch) == launch_id) return;
+  // 128-byte-swizzled tiles need 1024-byte alignment
+  const uint32_t base = (smem_u32(shared_raw) + 1023u) & ~1023u;
+  unsigned char* base_pointer = shared_raw + (base - smem_u32(shared_raw));
+  const uint32_t load_full = base + kOffsetBarriers, load_empty = load_full + kLoadStages * 8;
+  const uint32_t b_full = load_empty + kLoadStages * 8, b_empty = b_full + kBStages * 8;
+  const uint32_t accumulator_full = b_empty + kBStages * 8;
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_pointer + kOffsetTmemHolder);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(base_pointer + kOffsetAbort);
+
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+  constexpr uint32_t columns_per_tile = EPI == kTcDualSwiglu ? kBN / 2 : kBN;
+  const uint32_t n0 = blockIdx.x * columns_per_tile, m0 = blockIdx.y * kBM;
+  const uint32_t k_blocks = p.k / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kLoadStages; ++s) {
+      barrier_init(load_full + s * 8, 1);   // the producer's expect_tx arrival; completes by byte count
+      barrier_init(load_empty + s * 8, 1);  // one tcgen05.commit
+    }
+    for (int s = 0; s < kBStages; ++s) {
+      barrier_init(b_full + s * 8, kConvertWarps);  // one arrival per conversion warp
+      barrier_init(b_empty + s * 8, 1);             // one tcgen05.commit
+    }
+    barrier_init(accumulator_full, 1);
+    *abort_flag = 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(base + kOffsetTmemHolder),
+                 "r"(kTmemColumns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_holder;
+
+  auto give_up = [&]() {
+    *abort_flag = 1u;
+    g_abandoned_launch = launch_id;
+    if (error_word) atomicExch(error_word, 1u);
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t issued = 0;
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+        const uint32_t s = kb % kLoadStages, round = kb / kLoadStages;
+        if (*abort_flag || !barrier_wait(load_empty + s * 8, (round & 1u) ^ 1u)) {
+          give_up();
+          break;
+        }
+        barrier_expect_tx(load_full + s * 8, kATileBytes + kRawTileBytes);
+        tma_load_2d(base + kOffsetA + s * kATileBytes, &map_x, (int32_t)(kb * kBK), (int32_t)m0, load_full + s * 8);
+        const uint32_t raw = base + kOffsetRaw + s * kRawTileBytes;
+        if (EPI == kTcDualSwiglu) {
+          tma_load_2d(raw, &map_w0, (int32_t)(kb * (kBK / 2)), (int32_t)n0, load_full + s * 8);
+          tma_load_2d(raw + kRawTileBytes / 2, &map_w1, (int32_t)(kb * (kBK / 2)), (int32_t)n0, load_full + s * 8);
+        } else {
+          tma_load_2d(raw, &map_w0, (int32_t)(kb * (kBK / 2)), (int32_t)n0, load_full + s * 8);
+          tma_load_2d(raw + kRawTileBytes / 2, &map_w0, (int32_t)(kb * (kBK / 2)), (int32_t)(n0 + kBN / 2),
+                      load_full + s * 8);
+        }
+        issued = kb + 1;
+      }
+      if (*abort_flag) {
+        // the copies already started must land before the shared memory goes away
+        const uint32_t first = issued > kLoadStages ? issued - kLoadStages : 0u;
+        for (uint32_t kb = first; kb < issued; ++kb)
+          barrier_wait(load_full + (kb % kLoadStages) * 8, (kb / kLoadStages) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      bool ok = true;
+      for (uint32_t kb = 0; kb < k_blocks && ok; ++kb) {
+        const uint32_t s = kb % kLoadStages, t = kb % kBStages;
+        ok = !*abort_flag && barrier_wait(load_full + s * 8, (kb / kLoadStages) & 1u) &&
+             barrier_wait(b_full + t * 8, (kb / kBStages) & 1u);
+        if (!ok) {
+          give_up();
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_tile = base + kOffsetA + s * kATileBytes, b_tile = base + kOffsetB + t * kBTileBytes;
+#pragma unroll
+        for (int j = 0; j < kBK / 16; ++j)
+          mma_f16(tmem_base, operand_descriptor(a_tile + j * 32), operand_descriptor(b_tile + j * 32),
+                  (kb > 0 || j > 0) ? 1u : 0u);
+        mma_commit(load_empty + s * 8);
+        mma_commit(b_empty + t * 8);
+      }
+      if (ok) mma_commit(accumulator_full);
+    }
+  } else {
+    // ------------------------------ conversion, then epilogue ------------------------------
+    const uint32_t row = threadIdx.x - 64u;  // row of the B tile, 0..255
+    const uint32_t matrix = EPI == kTcDualSwiglu ? row / (kBN / 2) : 0u;
+    const uint32_t weight_row = EPI == kTcDualSwiglu ? n0 + row % (kBN / 2) : n0 + row;
+    const bool row_present = weight_row < p.n;
+    const uint32_t groups = p.k / 64;
+    const __half* scale_row = p.scale[matrix] + (size_t)(row_present ? weight_row : 0u) * groups;
+    const __half* zero_row = AFFINE ? p.zero[matrix] + (size_t)(row_present ? weight_row : 0u) * groups : nullptr;
+    const uint32_t swizzle = (row & 7u) * 16u;
+    bool ok = true;
+    __half next_scale = row_present ? __ldg(scale_row) : __float2half(0.0f);
+    __half next_zero = AFFINE && row_present ? __ldg(zero_row) : __float2half(0.0f);
+    for (uint32_t kb = 0; kb < k_blocks; ++kb) {
+      const uint32_t s = kb % kLoadStages, t = kb % kBStages;
+      const __half scale = next_scale, zero = next_zero;
+      if (kb + 1 < k_blocks && row_present) {
+        next_scale = __ldg(scale_row + kb + 1);
+        if (AFFINE) next_zero = __ldg(zero_row + kb + 1);
+      }
+      ok = !*abort_flag && barrier_wait(load_full + s * 8, (kb / kLoadStages) & 1u) &&
+           barrier_wait(b_empty + t * 8, ((kb / kBStages) & 1u) ^ 1u);
+      if (!ok) {
+        give_up();
+        break;
+      }
+      const unsigned char* raw = base_pointer + kOffsetRaw + s * kRawTileBytes + row * 32u;
+      const uint4 first = *reinterpret_cast<const uint4*>(raw), second = *reinterpret_cast<const uint4*>(raw + 16);
+      const uint32_t words[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
+      const __half2 scale_pair = __halves2half2(scale, __hmul(scale, __float2half(0.0625f)));
+      const __half2 zero_pair = __halves2half2(zero, __hmul(zero, __float2half(16.0f)));
+      const uint32_t scales = *reinterpret_cast<const uint32_t*>(&scale_pair);
+      const uint32_t zeros = *reinterpret_cast<const uint32_t*>(&zero_pair);
+      unsigned char* b_row = base_pointer + kOffsetB + t * kBTileBytes + row * 128u;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {  // word c = k 8c .. 8c+7 = 16-byte chunk c of the row
+        uint4 chunk;
+        chunk.x = dequant_pair<AFFINE, 0>(words[c], scales, zeros);
+        chunk.y = dequant_pair<AFFINE, 1>(words[c], scales, zeros);
+        chunk.z = dequant_pair<AFFINE, 2>(words[c], scales, zeros);
+        chunk.w = dequant_pair<AFFINE, 3>(words[c], scales, zeros);
+        *reinterpret_cast<uint4*>(b_row + ((c * 16u) ^ swizzle)) = chunk;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // publish to the tensor core's proxy
+      __syncwarp();
+      if (lane == 0) barrier_arrive(b_full + t * 8);
+    }
+
+    // epilogue: this warp reads its lane quarter and one half of the columns
+    ok = ok && !*abort_flag && barrier_wait(accumulator_full, 0u);
+    if (!ok) give_up();
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t quarter = warp & 3u, half_index = (warp - 2u) >> 2;
+      const uint32_t out_row = m0 + quarter * 32u + lane;
+      const uint32_t lane_address = tmem_base + ((quarter * 32u) << 16);
+      if (EPI == kTcDualSwiglu) {
+        // columns [0, 128) gate, [128, 256) up; this warp covers 64 output columns
+#pragma unroll 1
+        for (uint32_t piece = 0; piece < 2; ++piece) {
+          const uint32_t column = half_index * 64u + piece * 32u;
+          uint32_t gate[32], up[32];
+          tmem_load_32(lane_address + column, gate);
+          tmem_load_32(lane_address + kBN / 2 + column, up);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (out_row < p.m) {
+            __half* target = p.out + (size_t)out_row * p.n + n0 + column;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (n0 + column + i < p.n) {
+                const float g = __uint_as_float(gate[i]);
+                // silu in fp32, one rounding of the product: lib/metal_w4a16_source.ml:571-575
+                target[i] = __float2half_rn((g / (1.0f + expf(-g))) * __uint_as_float(up[i]));
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (uint32_t piece = 0; piece < 4; ++piece) {
+          const uint32_t column = half_index * 128u + piece * 32u;
+          uint32_t values[32];
+          tmem_load_32(lane_address + column, values);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (out_row < p.m) {
+            const size_t out_index = (size_t)out_row * p.n + n0 + column;
+            const bool whole = n0 + column + 32u <= p.n && (out_index & 7u) == 0;
+            if (EPI == kTcLinear && whole && !p.has_aux) {
+              uint32_t packed[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const __half2 pair = __floats2half2_rn(__uint_as_float(values[2 * i]), __uint_as_float(values[2 * i + 1]));
+                packed[i] = *reinterpret_cast<const uint32_t*>(&pair);
+              }
+              uint4* target = reinterpret_cast<uint4*>(p.out + out_index);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) target[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const uint32_t col = n0 + column + i;
+                if (col < p.n) {
+                  float value = __uint_as_float(values[i]);
+                  if (EPI == kTcTagged) {
+                    const float first = p.aux0 ? __half2float(p.aux0[col]) : 0.0f;
+                    const float second = p.aux1 ? __half2float(p.aux1[col]) : 0.0f;
+                    p.out[out_index + i] = __float2half_rn(epilogue_tagged(p.tag, value, first, second));
+                  } else {
+                    if (p.has_aux) value += __half2float(p.aux0[(size_t)out_row * p.aux_row_stride + col]);
+                    p.out[out_index + i] = __float2half_rn(value);
+                  }
+                }
+              }
+            }
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+  }
+
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
+  }
+}
+
+// cuTensorMapEncodeTiled, resolved through the runtime so that the library does not link libcuda.
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled function = []() -> EncodeTiled {
+    void* pointer = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &pointer, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiled>(pointer);
+  }();
+  return function;
+}
+
+bool make_map(CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t inner, uint64_t outer,
+              uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t element_strides[2] = {1, 1};
+  return encode(map, type, 2, const_cast<void*>(base), dims, strides, box, element_strides,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int EPI, bool AFFINE>
+int run_tc(const KernelArgs& args, const CUtensorMap& map_x, const CUtensorMap& map_w0, const CUtensorMap& map_w1,
+           const TcProblem& p) {
+  auto kernel = w4a16_gemm_tc_kernel<EPI, AFFINE>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSharedBytesTc) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  constexpr uint32_t columns_per_tile = EPI == kTcDualSwiglu ? kBN / 2 : kBN;
+  const dim3 grid((p.n + columns_per_tile - 1) / columns_per_tile, (p.m + kBM - 1) / kBM);
+  static std::atomic<uint32_t> launches{0};
+  launch_kernel(args, kernel, grid, dim3(kThreadsTc), kSharedBytesTc, map_x, map_w0, map_w1, p,
+                context_device_error(args.ctx), launches.fetch_add(1) + 1u);
+  return check_launch(args);
+}
+
+}  // namespace
+
+// Tensor-core path for M >= 64; returns -1 when the shape or the pointers are outside its domain
+// (the caller then falls back to passes of the small-M kernel).
+int launch_w4a16_gemm_tc(const KernelArgs& args, const GemvProblem& problem, int epilogue, bool affine) {
+  if (args.ctx == nullptr || problem.m < 64 || problem.k % 64 != 0) return -1;
+  if (epilogue != kEpiLinear && epilogue != kEpiDualSwiglu && epilogue != kEpiTagged) return -1;
+  if (affine && epilogue != kEpiLinear) return -1;
+  const uint32_t matrices = epilogue == kEpiDualSwiglu ? 2u : 1u;
+  if (((uintptr_t)problem.x & 15u) != 0) return -1;
+  for (uint32_t i = 0; i < matrices; ++i)
+    if (((uintptr_t)problem.mat[i].packed & 15u) != 0 || problem.mat[i].n != problem.mat[0].n) return -1;
+
+  CUtensorMap map_x, map_w[2];
+  if (!make_map(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, problem.x, problem.k, problem.m, (uint64_t)problem.k * 2, kBK,
+                kBM, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -1;
+  for (uint32_t i = 0; i < 2; ++i) {
+    const GemvMatrix& mat = problem.mat[i < matrices ? i : 0];
+    if (!make_map(&map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, mat.packed, problem.k / 2, mat.n, problem.k / 2, kBK / 2,
+                  kBN / 2, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return -1;
+  }
+  TcProblem p = {};
+  p.m = problem.m;
+  p.n = problem.mat[0].n;
+  p.k = problem.k;
+  for (uint32_t i = 0; i < 2; ++i) {
+    p.scale[i] = problem.mat[i < matrices ? i : 0].scale;
+    p.zero[i] = problem.mat[i < matrices ? i : 0].zero;
+  }
+  p.out = problem.out[0];
+  p.aux0 = problem.aux0;
+  p.aux1 = problem.aux1;
+  p.aux_row_stride = problem.aux_row_stride;
+  p.has_aux = problem.has_aux;
+  p.tag = problem.tag;
+  if (epilogue == kEpiDualSwiglu) return run_tc<kTcDualSwiglu, false>(args, map_x, map_w[0], map_w[1], p);
+  if (epilogue == kEpiTagged) return run_tc<kTcTagged, false>(args, map_x, map_w[0], map_w[1], p);
+  return affine ? run_tc<kTcLinear, true>(args, map_x, map_w[0], map_w[1], p)
+                : run_tc<kTcLinear, false>(args, map_x, map_w[0], map_w[1], p);
+}
+
+}  // namespace llmopt

@@ -299,6 +299,12 @@ int launch_w4a16_gemv(const KernelArgs& args, GemvProblem problem, int epilogue,
     if (status >= 0) return status;
   }
 
+  // 64 rows and more: the tensor-memory GEMM
+  if (problem.m >= 64 && problem.x_rows == problem.m) {
+    const int status = launch_w4a16_gemm_tc(args, problem, epilogue, affine);
+    if (status >= 0) return status;
+  }
+
   if (epilogue == kEpiSplitF32) {
     LLMOPT_REQUIRE(problem.x_rows <= 64 && problem.x_rows % 8 == 0 && problem.m * 2 <= problem.x_rows,
                    "split activations need 8-row slot tiles and at most 32 rows");

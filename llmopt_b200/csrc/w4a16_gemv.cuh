@@ -40,6 +40,9 @@ struct GemvProblem {
 // Rows beyond 64 are processed in passes of 64.
 int launch_w4a16_gemv(const KernelArgs& args, GemvProblem problem, int epilogue, bool affine);
 
+// Tensor-core GEMM for M >= 64 (tcgen05 / tensor memory); returns -1 outside its domain.
+int launch_w4a16_gemm_tc(const KernelArgs& args, const GemvProblem& problem, int epilogue, bool affine);
+
 // Pipelined fast path (K % 512 == 0, <= 32 rows); returns -1 if the shape is outside its domain.
 int launch_w4a16_gemv_pipe(const KernelArgs& args, const GemvProblem& problem, int epilogue);
 

@@ -132,6 +132,8 @@ def main() -> None:
     runtime = cuda_native.Runtime()
     item, nbytes, _keep = build_item(runtime, args)
     result = {"op": args.op, "kernel": item.name, "m": args.m, "k": args.k, "n": args.n, "algorithmic_bytes": nbytes}
+    products = {"linear": 1, "gate_up": 2, "down": 1, "lm_head": 1}.get(args.op)
+    flops = 2.0 * args.m * args.k * args.n * products if products else None
     if args.copies > 1:
         # distinct operands per launch, launched back to back: in-plan conditions (cold
         # operands because the set exceeds the L2, launch gaps as in a replayed plan)
@@ -148,6 +150,8 @@ def main() -> None:
                                              flush_l2=not args.no_flush)
         result.update({"mode": "isolated launch, L2 flushed before each", "ms": milliseconds,
                        "gbs": nbytes / milliseconds / 1e6})
+    if flops:
+        result["tflops"] = flops / result["ms"] / 1e9
     print(json.dumps(result))
 
 
