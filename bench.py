@@ -43,8 +43,9 @@ def measured_peaks() -> dict:
     if os.path.exists(path):
         with open(path) as handle:
             peaks = json.load(handle)
-        return {"hbm_gbs": float(peaks["hbm_gbs"]), "source": "measured"}
-    return {"hbm_gbs": 6650.0, "source": "fallback"}
+        return {"hbm_gbs": float(peaks["hbm_gbs"]), "bf16_tflops": float(peaks.get("bf16_tflops", 1590.0)),
+                "bf16_tflops_sustained": float(peaks.get("bf16_tflops_sustained", 1400.0)), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 class ClockSampler:
@@ -226,6 +227,46 @@ def time_kernels(engine, runtime) -> dict:
     return table
 
 
+# DRAM bytes per launch (ncu: dram__bytes_read.sum + dram__bytes_write.sum) over the algorithmic
+# bytes of the same launch, from the captures summarised under profiles/ (GEMV: batch 1 gate/up;
+# attention: batch 8, 8192 tokens; both grow in proportion to the units processed).
+TRAFFIC_RATIO = {
+    "gate_up_swiglu": (62_610_176 / 62_427_136, "profiles/w4a16_gemv_pipe_m1_llama3_8b.md"),
+    "paged_attention_q8": (147_036_160 / 138_838_016, "profiles/paged_attention_q8_split_llama3_8b.md"),
+}
+
+
+def time_prefill_gemm(engine, runtime, peaks) -> dict:
+    """The prefill side of the path: the gate/up projection of the first layers at M = 2048 rows
+    (one prefill chunk) on the tcgen05 GEMM, device-timed back to back; dense-equivalent FLOPs."""
+    from llmopt_b200 import dispatch
+    from llmopt_b200.cuda_native import Batch, Buffer
+
+    config = engine.config
+    m, k, n = 2048, config.hidden, config.intermediate
+    rng = np.random.default_rng(1)
+    x = dispatch.Tensor(Buffer.of_array(runtime, rng.standard_normal((m, k)).astype(np.float16)), (m, k))
+    residual = dispatch.Tensor(Buffer.create(runtime, m * k * 2), (m, k))
+    output = dispatch.Tensor(Buffer.create(runtime, m * k * 2), (m, k))
+    commands = Batch(runtime)
+    context = dispatch.Context(runtime, batch=commands)
+    items = []
+    for layer in engine.layers[:4]:
+        dispatch.dispatch_w4a16_swiglu_ffn_command(
+            context, m=m, n=n, k=k, epsilon=config.epsilon, activation=x, residual=residual,
+            gate_weight=layer["gate"][0], gate_scale=layer["gate"][1], up_weight=layer["up"][0],
+            up_scale=layer["up"][1], down_weight=layer["down"][0], down_scale=layer["down"][1],
+            norm_weight=layer["ffn_norm"], output=output, reference_guards=False)
+    items = [item for item in commands.pending if item.name.startswith("llmopt_w4a16_dual_swiglu")]
+    name = items[0].name
+    milliseconds = runtime.time_dispatches(items, warmup=1, iterations=3)
+    commands.abort()
+    tflops = 2.0 * 2 * m * k * n / milliseconds / 1e9
+    return {"kernel": name, "m": m, "k": k, "n": n, "products": 2, "ms": milliseconds, "bound": "tensor",
+            "achieved": tflops, "unit": "TFLOP/s", "peak": peaks["bf16_tflops"], "frac": tflops / peaks["bf16_tflops"],
+            "peak_sustained": peaks.get("bf16_tflops_sustained"), "peak_source": peaks["source"]}
+
+
 def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
     from llmopt_b200 import cuda_native
     from llmopt_b200.decode_engine import DecodeEngine
@@ -305,7 +346,10 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         "roofline": {
             "bound": "hbm", "kernel": dominant["name"], "achieved": dominant["gbs"], "peak": peaks["hbm_gbs"],
             "unit": "GB/s", "frac": dominant["gbs"] / peaks["hbm_gbs"], "peak_source": peaks["source"],
-            "frac_of_spec_8000": dominant["gbs"] / 8000.0, "traffic": None,
+            "frac_of_spec_8000": dominant["gbs"] / 8000.0,
+            "traffic": round(dominant["bytes"] * TRAFFIC_RATIO[dominant["kernel"]][0])
+            if dominant["kernel"] in TRAFFIC_RATIO else None,
+            "traffic_source": TRAFFIC_RATIO.get(dominant["kernel"], (None, None))[1],
             "bytes_per_launch": dominant["bytes"], "ms_per_launch": dominant["ms"],
         },
         "step_roofline": {
@@ -316,6 +360,8 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         "kernels": {k: {"ms": round(v["ms"], 5), "gbs": round(v["gbs"], 1), "frac": round(v["gbs"] / peaks["hbm_gbs"], 3)}
                     for k, v in kernels.items()},
     }
+    if config.hidden >= 2048:
+        result["prefill_gemm"] = time_prefill_gemm(engine, runtime, peaks)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         baseline = cpu_reference_rate(config, args.batch)
         result["cpu_baseline"] = {k: baseline[k] for k in ("value", "unit", "cores", "kind", "sample")}
