@@ -99,6 +99,17 @@ int llmopt_cuda_map_file(llmopt_cuda_context* context, const char* path, llmopt_
 /* caml_llmopt_metal_buffer_view (:945-970): bounds checked, shares storage. */
 int llmopt_cuda_buffer_view(llmopt_cuda_buffer* parent, int64_t offset, int64_t length, llmopt_cuda_buffer** out);
 void llmopt_cuda_release_buffer(llmopt_cuda_buffer* buffer);
+/* No counterpart in the reference (which is single-device): lets the other ranks of a
+ * tensor-parallel group (one process per GPU) map this buffer.  `handle` receives
+ * LLMOPT_CUDA_EXPORT_HANDLE_BYTES opaque bytes and `offset` the buffer's offset inside its
+ * allocation; a peer process passes both, with the length, to llmopt_cuda_buffer_import and gets
+ * a buffer it may bind to the llmopt_tp_exchange_* kernels.  The exporter must outlive every
+ * import.  Exchange kernels wait on peers with a bound (about two seconds) and report a
+ * time-out through the usual error path of the next stream wait. */
+#define LLMOPT_CUDA_EXPORT_HANDLE_BYTES 64
+int llmopt_cuda_buffer_export(llmopt_cuda_buffer* buffer, void* handle, uint64_t* offset);
+int llmopt_cuda_buffer_import(llmopt_cuda_context* context, const void* handle, uint64_t offset, uint64_t length,
+                              llmopt_cuda_buffer** out);
 /* caml_llmopt_metal_buffer_length */
 size_t llmopt_cuda_buffer_length(llmopt_cuda_buffer* buffer);
 /* caml_llmopt_metal_buffer_contents: copies the whole buffer to `destination`

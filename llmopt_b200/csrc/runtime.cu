@@ -36,6 +36,9 @@ template <int TAG> int launch_w4a16_linear_tagged(const KernelArgs&);
 template <bool F32, bool EXTRA> int launch_w4a16_lm_head_argmax(const KernelArgs&);
 template <bool F32, bool EXTRA> int launch_w4a16_lm_head_stage1(const KernelArgs&);
 int launch_w4a16_lm_head_reduce(const KernelArgs&);
+int launch_w4a16_linear_partial_f32(const KernelArgs&);
+int launch_tp_exchange_sum(const KernelArgs&);
+int launch_tp_exchange_argmax(const KernelArgs&);
 int launch_cache_pack_attention_q8(const KernelArgs&);
 int launch_cache_pack_attention_q8_pair(const KernelArgs&);
 int launch_cache_unpack_attention_q8(const KernelArgs&);
@@ -80,6 +83,7 @@ struct Allocation {
   Context* context = nullptr;
   void* base = nullptr;
   size_t length = 0;
+  bool imported = false;  // a peer process's allocation opened through CUDA IPC
 };
 
 }  // namespace llmopt
@@ -133,7 +137,12 @@ static void release(Context* context) {
 static void release(Allocation* allocation) {
   if (allocation->references.fetch_sub(1) != 1) return;
   cudaSetDevice(allocation->context->device);
-  cudaFree(allocation->base);  // cudaFree waits for work that may still use the memory
+  if (allocation->imported) {
+    cudaStreamSynchronize(allocation->context->stream);
+    cudaIpcCloseMemHandle(allocation->base);
+  } else {
+    cudaFree(allocation->base);  // cudaFree waits for work that may still use the memory
+  }
   release(allocation->context);
   delete allocation;
 }
@@ -167,6 +176,10 @@ static void register_kernels(llmopt_cuda_library* library) {
   add("llmopt_w4a16_linear_f16_g64_m4", launch_w4a16_linear);
   add("llmopt_w4a16_linear_f16_g64_m8", launch_w4a16_linear);
   add("llmopt_w4a16_linear_f16_g64_affine", launch_w4a16_linear_affine);
+  // tensor-parallel extensions (no reference counterpart)
+  add("llmopt_w4a16_linear_partial_f32_g64", launch_w4a16_linear_partial_f32);
+  add("llmopt_tp_exchange_sum_f16", launch_tp_exchange_sum);
+  add("llmopt_tp_exchange_argmax", launch_tp_exchange_argmax);
   add("llmopt_w4a16_qkv_linear_f16_g64", launch_w4a16_qkv_linear);
   add("llmopt_w4a16_qkv_linear_f16_g64_m4", launch_w4a16_qkv_linear);
   add("llmopt_w4a16_qkv_linear_f16_g64_m8", launch_w4a16_qkv_linear);
@@ -609,6 +622,45 @@ int llmopt_cuda_buffer_view(llmopt_cuda_buffer* parent, int64_t offset, int64_t 
   view->offset = parent->offset + (size_t)offset;
   view->length = (size_t)length;
   *out = view;
+  return LLMOPT_CUDA_OK;
+}
+
+// ---- sharing a buffer with the other ranks of a tensor-parallel group -------------------
+int llmopt_cuda_buffer_export(llmopt_cuda_buffer* buffer, void* handle, uint64_t* offset) {
+  if (buffer == nullptr) return set_error(LLMOPT_CUDA_FAILURE, "CUDA buffer has been finalized");
+  if (handle == nullptr || offset == nullptr) return set_error(LLMOPT_CUDA_INVALID_ARGUMENT, "null pointer argument");
+  if (buffer->allocation->imported)
+    return set_error(LLMOPT_CUDA_INVALID_ARGUMENT, "an imported buffer cannot be exported again");
+  static_assert(sizeof(cudaIpcMemHandle_t) == LLMOPT_CUDA_EXPORT_HANDLE_BYTES, "handle size");
+  CUDA_TRY(cudaSetDevice(buffer->allocation->context->device), "cudaSetDevice failed");
+  cudaIpcMemHandle_t ipc;
+  CUDA_TRY(cudaIpcGetMemHandle(&ipc, buffer->allocation->base), "CUDA could not export the buffer");
+  memcpy(handle, &ipc, sizeof(ipc));
+  *offset = buffer->offset;
+  return LLMOPT_CUDA_OK;
+}
+
+int llmopt_cuda_buffer_import(llmopt_cuda_context* context, const void* handle, uint64_t offset, uint64_t length,
+                              llmopt_cuda_buffer** out) {
+  if (context == nullptr) return set_error(LLMOPT_CUDA_FAILURE, "CUDA context has been finalized");
+  if (handle == nullptr || out == nullptr) return set_error(LLMOPT_CUDA_INVALID_ARGUMENT, "null pointer argument");
+  CUDA_TRY(cudaSetDevice(context->device), "cudaSetDevice failed");
+  cudaIpcMemHandle_t ipc;
+  memcpy(&ipc, handle, sizeof(ipc));
+  void* base = nullptr;
+  cudaError_t status = cudaIpcOpenMemHandle(&base, ipc, cudaIpcMemLazyEnablePeerAccess);
+  if (status != cudaSuccess) return cuda_failure("CUDA could not open a peer's buffer", status);
+  Allocation* allocation = new Allocation();
+  allocation->context = context;
+  retain(context);
+  allocation->base = base;
+  allocation->length = (size_t)(offset + length);
+  allocation->imported = true;
+  llmopt_cuda_buffer* buffer = new llmopt_cuda_buffer();
+  buffer->allocation = allocation;
+  buffer->offset = (size_t)offset;
+  buffer->length = (size_t)length;
+  *out = buffer;
   return LLMOPT_CUDA_OK;
 }
 

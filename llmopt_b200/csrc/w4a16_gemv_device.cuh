@@ -93,7 +93,10 @@ __device__ __forceinline__ void write_tile(const GemvProblem& p, float (&acc)[NM
       if (EPI == kEpiLinear) {
         float result = value;
         if (p.has_aux) result += __half2float(p.aux0[(size_t)row * p.aux_row_stride + column]);
-        p.out[0][(size_t)row * n + column] = __float2half_rn(result);
+        if (p.out_f32)  // unrounded partial sum of a K-split product (tensor-parallel row split)
+          p.out_f32[(size_t)row * n + column] = result;
+        else
+          p.out[0][(size_t)row * n + column] = __float2half_rn(result);
       } else if (EPI == kEpiQkv) {
         p.out[matrix][(size_t)row * n + column] = __float2half_rn(value);
       } else if (EPI == kEpiDualSwiglu) {
@@ -127,7 +130,10 @@ __device__ __forceinline__ void write_position(const GemvProblem& p, const float
   if (EPI == kEpiLinear) {
     float result = value[0];
     if (p.has_aux) result += __half2float(p.aux0[(size_t)row * p.aux_row_stride + column]);
-    p.out[0][(size_t)row * n + column] = __float2half_rn(result);
+    if (p.out_f32)
+      p.out_f32[(size_t)row * n + column] = result;
+    else
+      p.out[0][(size_t)row * n + column] = __float2half_rn(result);
   } else if (EPI == kEpiQkv) {
     p.out[matrix][(size_t)row * n + column] = __float2half_rn(value[0]);
   } else if (EPI == kEpiDualSwiglu) {

@@ -199,6 +199,27 @@ int launch_w4a16_linear(const KernelArgs& args) {
   return launch_w4a16_gemv(args, problem, kEpiLinear, false);
 }
 
+// Extension for tensor-parallel row splits (no reference counterpart): the same product with the
+// fp32 accumulator written unrounded, buffers [input, weight, scale, output f32], params {m, n, k}.
+// The ranks' partial sums are added and rounded once by llmopt_tp_exchange_sum_f16.
+int launch_w4a16_linear_partial_f32(const KernelArgs& args) {
+  LLMOPT_REQUIRE(args.buffer_count == 4 && args.param_bytes == 12, "expects 4 buffers and 12 parameter bytes");
+  const uint32_t m = param_u32(args, 0), n = param_u32(args, 1), k = param_u32(args, 2);
+  LLMOPT_REQUIRE(m > 0 && m <= 32 && n > 0 && k > 0 && k % 64 == 0, "needs 0 < m <= 32, n > 0 and k a multiple of 64");
+  LLMOPT_REQUIRE(args.lengths[0] >= (size_t)m * k * 2, "input buffer is too short");
+  LLMOPT_REQUIRE(weight_sizes_ok(args, 1, 2, n, k), "weight or scale buffer is too short");
+  LLMOPT_REQUIRE(args.lengths[3] >= (size_t)m * n * 4, "output buffer is too short");
+  GemvProblem problem = {};
+  problem.x = (const __half*)args.buffers[0];
+  problem.x_rows = m;
+  problem.m = m;
+  problem.k = k;
+  problem.mat[0] = {(const uint8_t*)args.buffers[1], (const __half*)args.buffers[2], nullptr, n};
+  problem.matrices = 1;
+  problem.out_f32 = (float*)args.buffers[3];
+  return launch_w4a16_gemv(args, problem, kEpiLinear, false);
+}
+
 // Affine variant (unsigned nibbles with an fp16 zero point per group,
 // w = (u - z) s): buffers [input, weight, scale, zero, bias, output], same
 // parameter block. No counterpart kernel name in the reference; the algebra is

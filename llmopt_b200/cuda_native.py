@@ -72,6 +72,8 @@ SIGNATURES = {
     "llmopt_cuda_map_file": (_I, [_P, ctypes.c_char_p, _PP]),
     "llmopt_cuda_buffer_view": (_I, [_P, _I64, _I64, _PP]),
     "llmopt_cuda_release_buffer": (None, [_P]),
+    "llmopt_cuda_buffer_export": (_I, [_P, _P, ctypes.POINTER(ctypes.c_uint64)]),
+    "llmopt_cuda_buffer_import": (_I, [_P, _P, ctypes.c_uint64, ctypes.c_uint64, _PP]),
     "llmopt_cuda_buffer_length": (_SZ, [_P]),
     "llmopt_cuda_buffer_contents": (_I, [_P, _P, _SZ]),
     "llmopt_cuda_buffer_argmax_f16": (_I, [_P, _I64, ctypes.POINTER(_I64)]),
@@ -185,6 +187,22 @@ class Buffer:
         out = ctypes.c_void_p()
         _check(load_library().llmopt_cuda_buffer_view(self._handle, int(offset), int(nbytes), ctypes.byref(out)))
         return Buffer(out.value, self._runtime)
+
+    def export_handle(self) -> tuple:
+        """(opaque 64 bytes, offset, length): what a peer process needs to map this buffer."""
+        handle = ctypes.create_string_buffer(64)
+        offset = ctypes.c_uint64()
+        _check(load_library().llmopt_cuda_buffer_export(self._handle, handle, ctypes.byref(offset)))
+        return handle.raw, int(offset.value), self.byte_length()
+
+    @classmethod
+    def import_handle(cls, runtime: "Runtime", exported: tuple) -> "Buffer":
+        """Maps a buffer another process exported with ``export_handle``."""
+        handle, offset, length = exported
+        out = ctypes.c_void_p()
+        _check(load_library().llmopt_cuda_buffer_import(
+            runtime._context, ctypes.create_string_buffer(bytes(handle), 64), int(offset), int(length), ctypes.byref(out)))
+        return cls(out.value, runtime)
 
     def byte_length(self) -> int:
         return int(load_library().llmopt_cuda_buffer_length(self._handle))

@@ -10,6 +10,11 @@ The per-token host work of the reference engine (RoPE row, cache slot of the new
 token) is done on the device by the plan's row bindings.  Batch > 1 (one token
 per sequence per step, per-sequence slot tables) is an extension: the reference
 decodes sequences one at a time (lib/serving_engine.ml:1542-1548).
+
+With an ``ExchangeGroup`` the engine builds one rank's share of a tensor-parallel
+decode (``tensor_parallel.py``): local heads and columns, fp32 partial sums of the
+row-split products exchanged and reduced over peer memory, one argmax over all
+ranks' vocabulary shards.  Every rank computes the same hidden state and token.
 """
 
 from __future__ import annotations
@@ -28,8 +33,13 @@ from .quantize import rope_tables
 
 class DecodeEngine:
     def __init__(self, runtime: Runtime, config: ModelConfig, weights: dict, *, batch: int = 1, capacity: int = 1024,
-                 kv_heads_local: Optional[int] = None):
+                 group=None):
+        """``config`` and ``weights`` are the whole model's, or, with ``group`` (an
+        ``ExchangeGroup`` of more than one rank), this rank's ``tensor_parallel.local_config`` /
+        ``shard_weights`` share; the embedding table is always whole."""
         self.runtime, self.config, self.batch, self.capacity = runtime, config, batch, capacity
+        self.group = group  # a group of one rank still takes the exchange kernels (single-GPU check of the plan)
+        self.full_vocabulary = config.vocabulary * (self.group.world if self.group else 1)
         self.layout = Layout([AttentionLayer(config.kv_heads, config.head_dim)] * config.attention_layers,
                              group_size=config.kv_group_size)
         self.cache = dispatch.Cache(runtime, self.layout, token_capacity=batch * capacity)
@@ -77,6 +87,7 @@ class DecodeEngine:
         self.q_rot = self._empty((batch, config.query_heads, 1, dim))
         self.k_rot = self._empty((batch, config.kv_heads, 1, dim))
         self.attended = self._empty((batch, config.query_heads * dim))
+        self.product = self._empty((batch, config.intermediate))
         self.cos_row = self._empty((1, 1, dim))
         self.sin_row = self._empty((1, 1, dim))
         self.new_slots = self._empty((batch,), "uint32", 4)
@@ -100,7 +111,28 @@ class DecodeEngine:
         run = lambda name, buffers, params, grid=(256, 1, 1): commands.dispatch(
             name=name, buffers=buffers, parameters=params, grid=grid, group=(256, 1, 1))
         run("llmopt_embedding_f16", [self.token_ids.buffer, self.embedding.buffer, self.hidden_a.buffer],
-            parameters.embedding(tokens=batch, vocabulary=config.vocabulary, width=hidden), (batch * hidden, 1, 1))
+            parameters.embedding(tokens=batch, vocabulary=self.full_vocabulary, width=hidden), (batch * hidden, 1, 1))
+        group = self.group
+        exchange = 0  # index of the next exchange of this step (slots are assigned round-robin)
+        if group is not None:
+            from .tensor_parallel import CANDIDATE_PARTS, plan_slots
+
+            exchanges = 2 * len(config.layers) + (batch + 31) // 32
+            slot_count, slot_of = plan_slots(exchanges)
+            if slot_count > group.slot_count or max(batch * hidden * 4, min(batch, 32) * CANDIDATE_PARTS * 8) > group.slot_bytes:
+                raise ValueError("the exchange group's slots are too few or too small for this plan")
+
+        def row_split_linear(source, weight, scale, k_local, residual, output):
+            """x[:, K slice] . W[:, K slice]^T as an fp32 partial into this rank's slot, then the
+            exchange that adds all ranks' partial sums and the residual."""
+            nonlocal exchange
+            slot = slot_of[exchange]
+            exchange += 1
+            run("llmopt_w4a16_linear_partial_f32_g64",
+                [source.buffer, weight.buffer, scale.buffer, group.slot_view(slot, batch * hidden * 4)],
+                parameters.u32s([batch, hidden, k_local]))
+            group.sum_record(commands.dispatch, slot=slot, rows=batch, width=hidden, residual=residual.buffer,
+                             output=output.buffer)
         current, other = self.hidden_a, self.hidden_b
         attention_index = conv_index = 0
         for kind, layer in zip(config.layers, self.layers):
@@ -146,8 +178,13 @@ class DecodeEngine:
                 run("llmopt_cache_pack_attention_q8_pair_simd",
                     [self.k_rot.buffer, self.v.buffer, self.new_slots.buffer, self.cache.token_pool], pack,
                     (dispatch.round_up(groups, 8) * 32, 1, 1))
-                dispatch.dispatch_w4a16_linear(context, input=self.attended, weight=layer["o"][0], scale=layer["o"][1],
-                                               output=other, bias=current, bias_row_stride=hidden)
+                if group is None:
+                    dispatch.dispatch_w4a16_linear(context, input=self.attended, weight=layer["o"][0],
+                                                   scale=layer["o"][1], output=other, bias=current,
+                                                   bias_row_stride=hidden)
+                else:
+                    row_split_linear(self.attended, layer["o"][0], layer["o"][1], config.query_heads * dim, current,
+                                     other)
                 attention_index += 1
             else:
                 dispatch.dispatch_w4a16_linear(context, input=self.normed, weight=layer["in_proj"][0],
@@ -165,14 +202,36 @@ class DecodeEngine:
                                                bias_row_stride=hidden)
                 conv_index += 1
             current, other = other, current
-            dispatch.dispatch_w4a16_swiglu_ffn_command(
-                context, m=batch, n=config.intermediate, k=hidden, epsilon=config.epsilon, activation=current,
-                residual=current, gate_weight=layer["gate"][0], gate_scale=layer["gate"][1], up_weight=layer["up"][0],
-                up_scale=layer["up"][1], down_weight=layer["down"][0], down_scale=layer["down"][1],
-                norm_weight=layer["ffn_norm"], output=other, reference_guards=False)
+            if group is None:
+                dispatch.dispatch_w4a16_swiglu_ffn_command(
+                    context, m=batch, n=config.intermediate, k=hidden, epsilon=config.epsilon, activation=current,
+                    residual=current, gate_weight=layer["gate"][0], gate_scale=layer["gate"][1],
+                    up_weight=layer["up"][0], up_scale=layer["up"][1], down_weight=layer["down"][0],
+                    down_scale=layer["down"][1], norm_weight=layer["ffn_norm"], output=other, reference_guards=False)
+            else:
+                # the same three kernels on this rank's intermediate columns; the down projection is
+                # the row-split product
+                ffn = parameters.w4a16_swiglu_ffn(m=batch, n=config.intermediate, k=hidden, epsilon=config.epsilon)
+                run("llmopt_w4a16_swiglu_rms_f16_g64", [current.buffer, layer["ffn_norm"].buffer, self.normed.buffer],
+                    ffn, (batch * 256, 1, 1))
+                run("llmopt_w4a16_dual_swiglu_f16_g64" + ("" if batch == 1 else "_m4"),
+                    [self.normed.buffer, layer["gate"][0].buffer, layer["gate"][1].buffer, layer["up"][0].buffer,
+                     layer["up"][1].buffer, self.product.buffer], ffn)
+                row_split_linear(self.product, layer["down"][0], layer["down"][1], config.intermediate, current, other)
             current, other = other, current
         for row0 in range(0, batch, 32):  # the LM head takes at most 32 rows per dispatch
             rows = min(32, batch - row0)
+            if group is not None:
+                slot = slot_of[exchange]
+                exchange += 1
+                run("llmopt_w4a16_lm_head_argmax_stage1_f16",
+                    [current.buffer.view(row0 * hidden * 2, rows * hidden * 2), self.final_norm.buffer,
+                     self.lm_head[0].buffer, self.lm_head[1].buffer, group.slot_view(slot, rows * CANDIDATE_PARTS * 8)],
+                    parameters.w4a16_lm_head_argmax(m=rows, n=config.vocabulary, k=hidden, epsilon=config.epsilon),
+                    (256 * 256, rows, 1))
+                group.argmax_record(commands.dispatch, slot=slot, rows=rows, shard_columns=config.vocabulary,
+                                    output=self.out_tokens.buffer.view(row0 * 4, rows * 4))
+                continue
             dispatch.dispatch_w4a16_lm_head_argmax_command(
                 context, m=rows, n=config.vocabulary, k=hidden, epsilon=config.epsilon,
                 input=dispatch.Tensor(current.buffer.view(row0 * hidden * 2, rows * hidden * 2), (rows, hidden)),
