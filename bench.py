@@ -171,10 +171,25 @@ def workload_config(args, config) -> dict:
         "workload": f"{config.name} greedy decode, batch {args.batch}, context {args.context} tokens of Q8 KV "
                     f"(group {config.kv_group_size}), W4A16 group-64 linears",
         "batch": args.batch, "context": args.context,
-        "parallelism": f"{args.gpus} independent replicas (one per GPU)" if args.gpus > 1 else "single",
+        "parallelism": parallelism_label(args, config),
         "l2": "every step streams its weights and KV once; the working set per step is far larger than the "
               "126 MB L2, so nothing is flushed between steps",
     }
+
+
+def tensor_parallel_run(args, config) -> bool:
+    from llmopt_b200 import tensor_parallel
+
+    return args.gpus > 1 and args.parallel == "tp" and tensor_parallel.shards(config, args.gpus)
+
+
+def parallelism_label(args, config) -> str:
+    if args.gpus <= 1:
+        return "single"
+    if tensor_parallel_run(args, config):
+        return (f"tp{args.gpus}: column-split QKV / gate / up / LM head, row-split o_proj / down with fp32 partial sums "
+                f"reduced over peer memory (NVLink), attention split by KV head; one sequence set for all GPUs")
+    return f"{args.gpus} independent replicas (one per GPU, no exchange)"
 
 
 def time_kernels(engine, runtime) -> dict:
@@ -200,6 +215,11 @@ def time_kernels(engine, runtime) -> dict:
             label = "gate_up_swiglu"
         elif name.startswith("llmopt_w4a16_down_add"):
             nbytes, label = linear_bytes(hidden, config.intermediate, extra=batch * hidden * 2), "down_add"
+        elif name.startswith("llmopt_w4a16_linear_partial_f32"):  # row-split product of a tensor-parallel rank
+            params = np.frombuffer(bytes(item.parameters), np.uint32)
+            n, k = int(params[1]), int(params[2])
+            nbytes = n * k // 2 + n * (k // 64) * 2 + batch * k * 2 + batch * n * 4
+            label = f"linear_partial_n{n}_k{k}"
         elif name.startswith("llmopt_w4a16_linear"):
             params = np.frombuffer(bytes(item.parameters), np.uint32)
             nbytes = linear_bytes(int(params[1]), int(params[2]), extra=batch * int(params[1]) * 2 if params[3] else 0)
@@ -272,14 +292,28 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
     from llmopt_b200.decode_engine import DecodeEngine
     from llmopt_b200.model import decode_bytes_per_token, random_weights
 
-    # N > 1: one independent replica of the whole model per GPU (data parallel over
-    # sequences, no collective on the data path); tensor-parallel sharding of the
-    # linears is not built yet.
+    # N > 1: tensor parallel when the model splits over N ranks (every rank decodes the same
+    # sequences with its share of every layer), else one independent replica of the whole model
+    # per GPU (no exchange on the data path).
     runtime = cuda_native.Runtime(local)
+    whole_config = config
     fast = config.hidden >= 2048
     weights = random_weights(config, seed=0, fast=fast)
     capacity = args.context + args.steps * 2 + args.warmup * 2 + 16
-    engine = DecodeEngine(runtime, config, weights, batch=args.batch, capacity=capacity)
+    tensor_parallel_mode = tensor_parallel_run(args, config)
+    if tensor_parallel_mode:
+        from llmopt_b200 import tensor_parallel
+
+        exchange_group = tensor_parallel.ExchangeGroup.create(
+            runtime, rank, world, max(args.batch * config.hidden * 4, min(args.batch, 32) * 256 * 8), 7,
+            tensor_parallel.torch_all_gather())
+        shard = tensor_parallel.shard_weights(config, weights, rank, world)
+        del weights
+        weights = shard
+        config = tensor_parallel.local_config(config, world)
+        engine = DecodeEngine(runtime, config, weights, batch=args.batch, capacity=capacity, group=exchange_group)
+    else:
+        engine = DecodeEngine(runtime, config, weights, batch=args.batch, capacity=capacity)
     del weights
     engine.fill_cache_random(args.context, seed=0)
     engine.build(args.context)
@@ -303,7 +337,8 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         group.barrier()
     clocks = sampler.stop()
     ms_per_step = elapsed_ms / args.steps
-    value = world * args.batch * 1000.0 / ms_per_step
+    jobs = 1 if tensor_parallel_mode else world  # tensor parallel: all GPUs decode the same sequences
+    value = jobs * args.batch * 1000.0 / ms_per_step
 
     # end to end: the host drives every token (token id in, H2D; next id out, D2H)
     tokens = first
@@ -321,7 +356,7 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         slowest = torch.tensor([e2e_seconds], dtype=torch.float64)
         group.all_reduce(slowest, op=group.ReduceOp.MAX)
         e2e_seconds = float(slowest.item())
-    e2e_value = world * args.batch * args.steps / e2e_seconds
+    e2e_value = jobs * args.batch * args.steps / e2e_seconds
     h2d = 16 + (8 * args.batch if args.batch > 1 else 0)
     d2h = 4 + (4 * args.batch if args.batch > 1 else 0)
 
@@ -336,9 +371,9 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
     result = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak" if world > 1 else "strong",
+        "scaling": "weak" if world > 1 and not tensor_parallel_mode else "strong",
         "vs_baseline": None, "dtype": "w4a16 (int4 weights, f16 activations, f32 accumulate); q8 KV",
-        "data": "synthetic", "config": workload_config(args, config),
+        "data": "synthetic", "config": workload_config(args, whole_config),
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": (engine.plan.kernel_count() + 1) * args.steps,
         "kernels_per_step": engine.plan.kernel_count(),
@@ -360,8 +395,10 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         "kernels": {k: {"ms": round(v["ms"], 5), "gbs": round(v["gbs"], 1), "frac": round(v["gbs"] / peaks["hbm_gbs"], 3)}
                     for k, v in kernels.items()},
     }
-    if config.hidden >= 2048:
+    if config.hidden >= 2048 and world == 1:
         result["prefill_gemm"] = time_prefill_gemm(engine, runtime, peaks)
+    if group is not None:
+        group.barrier()  # no rank leaves (and unmaps its exchange region) while a peer still runs
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         baseline = cpu_reference_rate(config, args.batch)
         result["cpu_baseline"] = {k: baseline[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -378,6 +415,8 @@ def main() -> None:
     parser.add_argument("--batch", type=int, default=1)
     parser.add_argument("--context", type=int, default=None)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
+                        help="with --gpus N > 1: tensor parallel (when the model splits over N) or N replicas")
     args = parser.parse_args()
     from llmopt_b200 import model
 
