@@ -522,20 +522,28 @@ bool paged_split_supported(const PagedParams& p) {
 }
 
 uint32_t paged_pick_splits(const KernelArgs& args, const PagedParams& p) {
-  // kResidentCtas CTAs are resident per SM.  Among the admissible counts take the one whose
-  // waves fill the machine best, charging a little for every extra record the merge
-  // has to read; a split is never shorter than 64 keys at capture time (a replayed
-  // plan keeps the count while the context grows).
+  // kResidentCtas CTAs are resident per SM.  Few (batch, KV head) pairs: as many splits as
+  // allowed, the machine cannot be filled anyway and a short split is a short dependent chain.
+  // Otherwise: from the smallest count that fills 85% of the CTA slots up to four times that,
+  // the one whose waves fill the machine best, charging a little for every extra record the merge
+  // has to read.  A split is never shorter than 64 keys at capture time (a replayed plan keeps the
+  // count while the context grows).
   const uint32_t pairs = p.batches * p.kv_heads;
   const uint32_t resident = (uint32_t)context_sm_count(args.ctx) * (uint32_t)kResidentCtas;
   uint32_t limit = args.past_tokens_cell ? kMaxAttentionSplits : (p.past_length + 63u) / 64u;
   if (limit > kMaxAttentionSplits) limit = kMaxAttentionSplits;
-  uint32_t best = 1;
+  if (limit == 0) return 1;
+  const uint32_t fill_target = (resident * 85u + 99u) / 100u;
+  const uint32_t first = (fill_target + pairs - 1u) / pairs;
+  if (first >= limit) return limit;
+  uint32_t last = first * 4u > first + 8u ? first * 4u : first + 8u;
+  if (last > limit) last = limit;
+  uint32_t best = first;
   float best_score = -1.0f;
-  for (uint32_t splits = 1; splits <= limit; ++splits) {
+  for (uint32_t splits = first; splits <= last; ++splits) {
     const uint32_t ctas = pairs * splits;
     const uint32_t waves = (ctas + resident - 1u) / resident;
-    const float score = (float)ctas / (float)(waves * resident) - 0.004f * (float)splits;
+    const float score = (float)ctas / (float)(waves * resident) - 0.002f * (float)splits;
     if (score > best_score) {
       best_score = score;
       best = splits;

@@ -107,14 +107,21 @@ __global__ void __launch_bounds__(256) exchange_sum_kernel(Regions regions, cons
   if (epoch != 0u) {
     const uint32_t elements = p.rows * p.width;
     for (uint32_t index = (blockIdx.x * 256u + threadIdx.x) * 4u; index < elements; index += gridDim.x * 1024u) {
+      // all peers' loads are issued before the first one is used: one NVLink round trip, not one per rank
+      float4 parts[kMaxRanks];
+#pragma unroll
+      for (uint32_t r = 0; r < kMaxRanks; ++r)
+        if (r < p.ranks)
+          parts[r] = *reinterpret_cast<const float4*>(regions.base[r] + p.slot_offset + (size_t)index * 4u);
       float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      for (uint32_t r = 0; r < p.ranks; ++r) {
-        const float4 part = *reinterpret_cast<const float4*>(regions.base[r] + p.slot_offset + (size_t)index * 4u);
-        sum.x += part.x;
-        sum.y += part.y;
-        sum.z += part.z;
-        sum.w += part.w;
-      }
+#pragma unroll
+      for (uint32_t r = 0; r < kMaxRanks; ++r)
+        if (r < p.ranks) {  // rank order: every rank adds the same numbers in the same order
+          sum.x += parts[r].x;
+          sum.y += parts[r].y;
+          sum.z += parts[r].z;
+          sum.w += parts[r].w;
+        }
       if (p.has_residual) {
         const __half2* add = reinterpret_cast<const __half2*>(residual + index);
         const float2 low = __half22float2(add[0]), high = __half22float2(add[1]);
