@@ -39,6 +39,7 @@ int launch_w4a16_lm_head_reduce(const KernelArgs&);
 int launch_w4a16_linear_partial_f32(const KernelArgs&);
 int launch_tp_exchange_sum(const KernelArgs&);
 int launch_tp_exchange_argmax(const KernelArgs&);
+int launch_attention_dense(const KernelArgs&);
 int launch_cache_pack_attention_q8(const KernelArgs&);
 int launch_cache_pack_attention_q8_pair(const KernelArgs&);
 int launch_cache_unpack_attention_q8(const KernelArgs&);
@@ -176,6 +177,11 @@ static void register_kernels(llmopt_cuda_library* library) {
   add("llmopt_w4a16_linear_f16_g64_m4", launch_w4a16_linear);
   add("llmopt_w4a16_linear_f16_g64_m8", launch_w4a16_linear);
   add("llmopt_w4a16_linear_f16_g64_affine", launch_w4a16_linear_affine);
+  // dense prefill attention: lib/metal_attention_source.ml (specialised per head size, and generic)
+  for (const char* name : {"llmopt_attention_f16", "llmopt_attention_f16_simd_h32", "llmopt_attention_f16_simd_h64",
+                           "llmopt_attention_f16_simd_h80", "llmopt_attention_f16_simd_h96",
+                           "llmopt_attention_f16_simd_h128", "llmopt_attention_f16_simd_h256"})
+    add(name, launch_attention_dense);
   // tensor-parallel extensions (no reference counterpart)
   add("llmopt_w4a16_linear_partial_f32_g64", launch_w4a16_linear_partial_f32);
   add("llmopt_tp_exchange_sum_f16", launch_tp_exchange_sum);

@@ -276,6 +276,60 @@ def paged_attention_kernel_name(*, split8: bool, experimental_gqa3_split8: bool,
     return "llmopt_attention_q8_paged_simd_generic"
 
 
+def dispatch_attention(context: Context, *, causal: bool, scale: float, query: Tensor, key: Tensor, value: Tensor,
+                       output: Tensor, mask: Optional[Tensor] = None) -> list:
+    """dispatch_attention, lib/metal_dispatch_attention.ml:6-102: dense fp16 attention (prefill).
+    query [b,h,q,d]; key [b,kvh,k,d]; value [b,kvh,k,d] or token-first [b,k,kvh,d]; output
+    [b,h,q,d], or token-first when its shape is [b,q,h*d] or [b,q,h,d]."""
+    if len(query.shape) != 4:
+        raise DispatchError("attention query must have rank four")
+    batches, heads, query_length, head_dimension = query.shape
+    if len(key.shape) != 4:
+        raise DispatchError("attention key must have rank four")
+    kv_heads, key_length = key.shape[1], key.shape[2]
+    if tuple(value.shape) == (batches, kv_heads, key_length, head_dimension):
+        token_first_value = 0
+    elif tuple(value.shape) == (batches, key_length, kv_heads, head_dimension):
+        token_first_value = 1
+    else:
+        raise DispatchError("attention value must match key in head-major or token-major layout")
+    if mask is not None:
+        if len(mask.shape) != 4:
+            raise DispatchError("attention mask must have rank four")
+        if mask.dtype == "bool":
+            mask_dtype = 1
+        elif mask.dtype == "float16":
+            mask_dtype = 2
+        else:
+            raise DispatchError(f"attention mask dtype {mask.dtype} is unsupported")
+        mask_batches, mask_heads, mask_buffer = mask.shape[0], mask.shape[1], mask.buffer
+    else:
+        mask_batches, mask_heads, mask_dtype, mask_buffer = 0, 0, 0, query.buffer
+    token_first_output = 1 if tuple(output.shape) in ((batches, query_length, heads * head_dimension),
+                                                      (batches, query_length, heads, head_dimension)) else 0
+    params = parameters.attention(
+        batches=batches, heads=heads, query_length=query_length, key_length=key_length,
+        head_dimension=head_dimension, mask_batches=mask_batches, mask_heads=mask_heads, causal=causal, scale=scale,
+        kv_heads=kv_heads, token_first_output=token_first_output, past_length=max(0, key_length - query_length),
+        token_first_value=token_first_value, mask_dtype=mask_dtype)
+    entry, simd = None, False
+    candidates = [(f"llmopt_attention_f16_simd_h{head_dimension}", True)] if head_dimension % 8 == 0 else []
+    for name, is_simd in candidates + [("llmopt_attention_f16", False)]:
+        try:
+            entry = context.runtime.kernel_entry(name=name, operation=kernel_abi.ATTENTION, input_dtype=query.dtype,
+                                                 output_dtype=output.dtype)
+            simd = is_simd
+            break
+        except (LookupError, RuntimeError):  # no such entry, or the library lacks the function
+            continue
+    if entry is None:
+        raise DispatchError(f"serving package has no attention kernel for {query.dtype} -> {output.dtype}")
+    rows = batches * heads * query_length
+    grid_x = batches * heads * ((query_length + 31) // 32) * 128 if simd else rows
+    return [_run(context, entry, [query.buffer, key.buffer, value.buffer, mask_buffer, output.buffer], params,
+                 (grid_x, 1, 1))]
+
+
 def dispatch_paged_attention_q8(context: Context, *, config: PagedAttentionConfig, query: Tensor,
                                 current_key: Tensor, current_value: Tensor, pool: Tensor, slots: Tensor,
                                 output: Tensor, mask: Optional[Tensor] = None,

@@ -80,6 +80,10 @@ def _entries() -> list[Entry]:
                  "llmopt_attention_q8_paged_simd_h64_gqa3", "llmopt_attention_q8_paged_simd_h64_split8",
                  "llmopt_attention_q8_paged_simd_h64_gqa3_split8", "llmopt_attention_q8_paged_batched"):
         add(name, ATTENTION)
+    for name in ("llmopt_attention_f16", "llmopt_attention_f16_simd_h32", "llmopt_attention_f16_simd_h64",
+                 "llmopt_attention_f16_simd_h80", "llmopt_attention_f16_simd_h96", "llmopt_attention_f16_simd_h128",
+                 "llmopt_attention_f16_simd_h256"):
+        add(name, ATTENTION, threadgroup=(128, 1, 1) if "simd" in name else (1, 1, 1))
     add("llmopt_attention_q8_paged_simd_h256", ATTENTION, threadgroup=(32, 1, 1))
     add("llmopt_attention_q8_paged_simd_h512", ATTENTION, threadgroup=(32, 1, 1))
     add("llmopt_short_conv_f16", SHORT_CONV)
