@@ -40,6 +40,10 @@ int launch_w4a16_linear_partial_f32(const KernelArgs&);
 int launch_tp_exchange_sum(const KernelArgs&);
 int launch_tp_exchange_argmax(const KernelArgs&);
 int launch_attention_dense(const KernelArgs&);
+int launch_q4_0_linear(const KernelArgs&);
+int launch_q4_0_gated_linear(const KernelArgs&);
+int launch_q4_0_qkv_linear(const KernelArgs&);
+int launch_q4_0_dequant(const KernelArgs&);
 int launch_cache_pack_attention_q8(const KernelArgs&);
 int launch_cache_pack_attention_q8_pair(const KernelArgs&);
 int launch_cache_unpack_attention_q8(const KernelArgs&);
@@ -178,10 +182,43 @@ static void register_kernels(llmopt_cuda_library* library) {
   add("llmopt_w4a16_linear_f16_g64_m8", launch_w4a16_linear);
   add("llmopt_w4a16_linear_f16_g64_affine", launch_w4a16_linear_affine);
   // dense prefill attention: lib/metal_attention_source.ml (specialised per head size, and generic)
-  for (const char* name : {"llmopt_attention_f16", "llmopt_attention_f16_simd_h32", "llmopt_attention_f16_simd_h64",
-                           "llmopt_attention_f16_simd_h80", "llmopt_attention_f16_simd_h96",
-                           "llmopt_attention_f16_simd_h128", "llmopt_attention_f16_simd_h256"})
-    add(name, launch_attention_dense);
+  add("llmopt_attention_f16", launch_attention_dense);
+  add("llmopt_attention_f16_simd_h32", launch_attention_dense);
+  add("llmopt_attention_f16_simd_h64", launch_attention_dense);
+  add("llmopt_attention_f16_simd_h80", launch_attention_dense);
+  add("llmopt_attention_f16_simd_h96", launch_attention_dense);
+  add("llmopt_attention_f16_simd_h128", launch_attention_dense);
+  add("llmopt_attention_f16_simd_h256", launch_attention_dense);
+  // Q4_0-block family: every tiling tactic of the reference maps to the same arithmetic
+  add("llmopt_dequant_q4_0", launch_q4_0_dequant);
+  add("llmopt_q4_0_linear_f16", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_add", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_x4", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_x4_add", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_x8", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_x8_add", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_x16", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_x16_add", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_m2", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_m2_add", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_m4", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_m4_add", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_m16", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_m16_add", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_m32", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_m32_add", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_simd", launch_q4_0_linear);
+  add("llmopt_q4_0_linear_f16_simd_add", launch_q4_0_linear);
+  add("llmopt_q4_0_qkv_linear_f16", launch_q4_0_qkv_linear);
+  add("llmopt_q4_0_qkv_linear_f16_x8", launch_q4_0_qkv_linear);
+  add("llmopt_q4_0_qkv_linear_f16_x16", launch_q4_0_qkv_linear);
+  add("llmopt_q4_0_qkv_linear_f16_m4", launch_q4_0_qkv_linear);
+  add("llmopt_q4_0_qkv_linear_f16_m16", launch_q4_0_qkv_linear);
+  add("llmopt_q4_0_qkv_linear_f16_m32", launch_q4_0_qkv_linear);
+  add("llmopt_q4_0_gated_linear_f16_x8", launch_q4_0_gated_linear);
+  add("llmopt_q4_0_gated_linear_f16_m4", launch_q4_0_gated_linear);
+  add("llmopt_q4_0_gated_linear_f16_m16", launch_q4_0_gated_linear);
+  add("llmopt_q4_0_gated_linear_f16_m32", launch_q4_0_gated_linear);
   // tensor-parallel extensions (no reference counterpart)
   add("llmopt_w4a16_linear_partial_f32_g64", launch_w4a16_linear_partial_f32);
   add("llmopt_tp_exchange_sum_f16", launch_tp_exchange_sum);

@@ -276,6 +276,65 @@ def paged_attention_kernel_name(*, split8: bool, experimental_gqa3_split8: bool,
     return "llmopt_attention_q8_paged_simd_generic"
 
 
+# ---- Q4_0-block linears --------------------------------------------------------------------
+
+def _q4_0_weight_ok(weight: Tensor, n: int, k: int) -> bool:
+    return weight.dtype == "uint8" and k % 32 == 0 and weight.numel == n * (k // 32) * 18
+
+
+def dispatch_quant_linear(context: Context, *, m: int, n: int, k: int, input: Tensor, weight: Tensor,
+                          output: Tensor, additive: Optional[Tensor] = None, epilogue_mode: int = 0) -> list:
+    """dispatch_quant_linear for Q4_0 storage, lib/metal_dispatch_common.ml:299-420: buffers
+    [input, weight, additive, output], params {m, n, k, epilogue_mode} (0 none, 1 bias, 2 residual
+    add, which selects the ``_add`` entry).  The tactic is chosen by the row count like the
+    reference's costed selection; every tactic computes the same values."""
+    if epilogue_mode not in (0, 1, 2) or (epilogue_mode != 0) != (additive is not None):
+        raise DispatchError("quantized Linear epilogue mode and additive operand are inconsistent")
+    if not (m > 0 and n > 0 and input.dtype == "float16" and output.dtype == "float16" and input.numel == m * k
+            and output.numel == m * n and _q4_0_weight_ok(weight, n, k)):
+        raise DispatchError("quantized Linear input metadata is inconsistent")
+    tactic = "" if m == 1 else "_m2" if m == 2 else "_m4" if m <= 8 else "_m16" if m <= 16 else "_m32"
+    name = "llmopt_q4_0_linear_f16" + tactic + ("_add" if epilogue_mode == 2 else "")
+    entry = context.runtime.kernel_entry(name=name, operation=kernel_abi.LINEAR, input_dtype="q4_0",
+                                         output_dtype="float16")
+    extra = additive.buffer if additive is not None else input.buffer
+    return [_run(context, entry, [input.buffer, weight.buffer, extra, output.buffer],
+                 parameters.u32s([m, n, k, epilogue_mode]), (linear_f16_grid(m * n), 1, 1))]
+
+
+def dispatch_quant_qkv_linear(context: Context, *, m: int, k: int, input: Tensor, q_weight: Tensor, k_weight: Tensor,
+                              v_weight: Tensor, q_output: Tensor, k_output: Tensor, v_output: Tensor) -> list:
+    """Fused Q4_0 QKV (lib/metal_quant_qkv_source.ml:17-170): 7 buffers, params {m, k, n_q, n_k, n_v}."""
+    n_q, n_k, n_v = q_output.numel // m, k_output.numel // m, v_output.numel // m
+    if not (m > 0 and input.numel == m * k and _q4_0_weight_ok(q_weight, n_q, k) and _q4_0_weight_ok(k_weight, n_k, k)
+            and _q4_0_weight_ok(v_weight, n_v, k)):
+        raise DispatchError("quantized QKV Linear input metadata is inconsistent")
+    name = "llmopt_q4_0_qkv_linear_f16" + ("" if m == 1 else "_m4" if m <= 8 else "_m16" if m <= 16 else "_m32")
+    entry = context.runtime.kernel_entry(name=name, operation=kernel_abi.FUSED_LINEAR, input_dtype="q4_0",
+                                         output_dtype="float16")
+    buffers = [input.buffer, q_weight.buffer, k_weight.buffer, v_weight.buffer, q_output.buffer, k_output.buffer,
+               v_output.buffer]
+    return [_run(context, entry, buffers, parameters.w4a16_qkv_linear(m=m, k=k, n_q=n_q, n_k=n_k, n_v=n_v),
+                 (linear_f16_grid(m * (n_q + n_k + n_v)), 1, 1))]
+
+
+def dispatch_quant_gated_linear(context: Context, *, m: int, n: int, k: int, input: Tensor, gate_weight: Tensor,
+                                up_weight: Tensor, product: Tensor, activation: str = "silu") -> list:
+    """Q4_0 gated product (lib/metal_q4_0_source.ml:26-150, llmopt_gated_product): buffers
+    [input, gate, up, product], params {m, n, k, activation} with 0 silu, 1 gelu, 2 sigmoid."""
+    codes = {"silu": 0, "gelu": 1, "sigmoid": 2}
+    if activation not in codes:
+        raise DispatchError(f"gated Linear activation {activation} is unsupported")
+    if not (m > 0 and input.numel == m * k and product.numel == m * n and _q4_0_weight_ok(gate_weight, n, k)
+            and _q4_0_weight_ok(up_weight, n, k)):
+        raise DispatchError("quantized gated Linear input metadata is inconsistent")
+    name = "llmopt_q4_0_gated_linear_f16" + ("_x8" if m == 1 else "_m4" if m <= 8 else "_m16" if m <= 16 else "_m32")
+    entry = context.runtime.kernel_entry(name=name, operation=kernel_abi.GATED_LINEAR, input_dtype="q4_0",
+                                         output_dtype="float16")
+    return [_run(context, entry, [input.buffer, gate_weight.buffer, up_weight.buffer, product.buffer],
+                 parameters.u32s([m, n, k, codes[activation]]), (linear_f16_grid(m * n), 1, 1))]
+
+
 def dispatch_attention(context: Context, *, causal: bool, scale: float, query: Tensor, key: Tensor, value: Tensor,
                        output: Tensor, mask: Optional[Tensor] = None) -> list:
     """dispatch_attention, lib/metal_dispatch_attention.ml:6-102: dense fp16 attention (prefill).

@@ -9,6 +9,9 @@ from dataclasses import dataclass
 from typing import Optional
 
 # Kernel_abi.Operation.to_string, lib/kernel_abi.ml:36-70 (hot-path subset)
+LINEAR = "linear"
+GATED_LINEAR = "gated-linear"
+FUSED_LINEAR = "fused-linear"
 W4A16_LINEAR = "w4a16-linear-g64"
 W4A16_QKV_LINEAR = "w4a16-qkv-linear-g64"
 W4A16_SWIGLU_FFN = "w4a16-swiglu-ffn-g64"
@@ -23,7 +26,7 @@ EMBEDDING = "embedding"
 CACHE = "cache"
 
 OPERATIONS = (
-    W4A16_LINEAR, W4A16_QKV_LINEAR, W4A16_SWIGLU_FFN, W4A16_LM_HEAD_ARGMAX, RMS_NORM, ROTARY_QK, SHORT_CONV,
+    LINEAR, GATED_LINEAR, FUSED_LINEAR, W4A16_LINEAR, W4A16_QKV_LINEAR, W4A16_SWIGLU_FFN, W4A16_LM_HEAD_ARGMAX, RMS_NORM, ROTARY_QK, SHORT_CONV,
     SHORT_CONV_STEP, SHORT_CONV_PREFILL, ATTENTION, EMBEDDING, CACHE,
 )
 
@@ -62,6 +65,15 @@ def _entries() -> list[Entry]:
         add("llmopt_w4a16_dual_swiglu_f16_g64" + suffix, W4A16_SWIGLU_FFN)
         add("llmopt_w4a16_down_add_f16_g64" + suffix, W4A16_SWIGLU_FFN)
     add("llmopt_w4a16_linear_f16_g64_affine", W4A16_LINEAR)
+    # Q4_0-block family: input dtype is the quantised storage (Ir.Dtype.Quant Q4_0)
+    add("llmopt_dequant_q4_0", LINEAR, "q4_0", f16, threadgroup=(256, 1, 1))
+    for tactic in ("", "_x4", "_x8", "_x16", "_m2", "_m4", "_m16", "_m32", "_simd"):
+        add("llmopt_q4_0_linear_f16" + tactic, LINEAR, "q4_0", f16)
+        add("llmopt_q4_0_linear_f16" + tactic + "_add", LINEAR, "q4_0", f16)
+    for tactic in ("", "_x8", "_x16", "_m4", "_m16", "_m32"):
+        add("llmopt_q4_0_qkv_linear_f16" + tactic, FUSED_LINEAR, "q4_0", f16)
+    for tactic in ("_x8", "_m4", "_m16", "_m32"):
+        add("llmopt_q4_0_gated_linear_f16" + tactic, GATED_LINEAR, "q4_0", f16)
     add("llmopt_w4a16_swiglu_rms_f16_g64", W4A16_SWIGLU_FFN)
     add("llmopt_w4a16_swiglu_rms_f32_g64", W4A16_SWIGLU_FFN, f32, f16)
     for stem in ("llmopt_w4a16_lm_head_argmax", "llmopt_w4a16_lm_head_argmax_extra",

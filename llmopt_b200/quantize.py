@@ -54,3 +54,19 @@ def rope_tables(positions: int, head_dim: int, theta: float):
     cosine = np.cos(frequency.astype(np.float64)).astype(np.float32).astype(np.float16)
     sine = np.sin(frequency.astype(np.float64)).astype(np.float32).astype(np.float16)
     return np.concatenate([cosine, cosine], axis=1), np.concatenate([sine, sine], axis=1)
+
+
+def q4_0_blocks(scales, nibbles):
+    """Q4_0 weight rows from fp16 block scales [n, k/32] and nibbles 0..15 [n, k]
+    (element i of a block in the low nibble of byte i for i < 16, in the high nibble of
+    byte i - 16 otherwise; bin/ocaml_metal_primitives_smoke.ml:39-52): uint8 [n, (k/32)*18]."""
+    import numpy as np
+
+    scales = np.ascontiguousarray(scales, dtype=np.float16)
+    nibbles = np.ascontiguousarray(nibbles, dtype=np.uint8)
+    n, blocks = scales.shape
+    grouped = nibbles.reshape(n, blocks, 32)
+    out = np.empty((n, blocks, 18), np.uint8)
+    out[:, :, 0:2] = scales.view(np.uint8).reshape(n, blocks, 2)
+    out[:, :, 2:18] = grouped[:, :, :16] | (grouped[:, :, 16:] << 4)
+    return out.reshape(n, blocks * 18)

@@ -383,3 +383,34 @@ def add_f16(a, b):
 def argmax_f16(values):
     values = _f16(values).reshape(-1)
     return int(lib().orc_argmax_f16(_p(values), I64(values.size)))
+
+
+# ---- Q4_0 block family (lib/metal_q4_0_source.ml, lib/metal_quant_qkv_source.ml) ----
+
+def q4_0_dequant(blocks):
+    blocks = _u8(blocks).reshape(-1)
+    total = blocks.size // 18
+    out = np.empty((total * 32,), np.float16)
+    lib().orc_q4_0_dequant(_p(blocks), _p(out), I64(total))
+    return out
+
+
+def q4_0_linear(x, weight, additive=None, mode=0):
+    """weight: uint8 [n, (k/32)*18]; mode 0 none, 1 bias [n], 2 residual [m, n]."""
+    x, weight = _f16(x), _u8(weight)
+    m, k = x.shape
+    n = weight.shape[0]
+    y = np.empty((m, n), np.float16)
+    lib().orc_q4_0_linear(_p(x), _p(weight), _p(None if additive is None else _f16(additive)), ctypes.c_int(mode),
+                          _p(y), I64(m), I64(n), I64(k))
+    return y
+
+
+def q4_0_gated_linear(x, gate_weight, up_weight, activation=0):
+    x = _f16(x)
+    m, k = x.shape
+    n = gate_weight.shape[0]
+    product = np.empty((m, n), np.float16)
+    lib().orc_q4_0_gated_linear(_p(x), _p(_u8(gate_weight)), _p(_u8(up_weight)), ctypes.c_int(activation),
+                                _p(product), I64(m), I64(n), I64(k))
+    return product

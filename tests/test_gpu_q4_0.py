@@ -1,0 +1,99 @@
+"""GPU parity of the Q4_0-block linear family against the float64 oracle, through the named dispatches."""
+
+import numpy as np
+import pytest
+
+from conftest import assert_close_f16
+from test_gpu_w4a16 import _ctx, _tensor
+
+pytestmark = pytest.mark.gpu
+
+
+def _weights(rng, n, k):
+    from llmopt_b200.quantize import q4_0_blocks
+
+    scales = rng.uniform(0.005, 0.03, size=(n, k // 32)).astype(np.float16)
+    return q4_0_blocks(scales, rng.integers(0, 16, size=(n, k), dtype=np.uint8))
+
+
+def test_dequant_is_bit_exact(runtime, oracle):
+    from llmopt_b200 import parameters
+    from llmopt_b200.cuda_native import Batch, Buffer
+
+    rng = np.random.default_rng(30)
+    blocks = _weights(rng, 7, 96)  # 21 blocks
+    out = Buffer.create(runtime, 21 * 64)
+    batch = Batch(runtime)
+    batch.dispatch(name="llmopt_dequant_q4_0", buffers=[Buffer.of_array(runtime, blocks), out],
+                   parameters=parameters.u32s([21]), grid=(21 * 32, 1, 1), group=(256, 1, 1))
+    batch.commit()
+    assert np.array_equal(out.to_numpy(np.uint16), oracle.q4_0_dequant(blocks).view(np.uint16))
+
+
+def test_reference_fixture_block_layout(runtime, oracle):
+    # test/test_quant.ml:690-693: d = 1.0, byte i = (i & 15) | ((15 - i) & 15) << 4 -> elements i - 8 and 7 - i
+    from llmopt_b200 import parameters
+    from llmopt_b200.cuda_native import Batch, Buffer
+
+    block = np.zeros(18, np.uint8)
+    block[0:2] = np.array([0x3C00], np.uint16).view(np.uint8)
+    for i in range(16):
+        block[2 + i] = (i & 15) | (((15 - i) & 15) << 4)
+    want = np.array([i - 8 for i in range(16)] + [7 - i for i in range(16)], np.float16)
+    assert np.array_equal(oracle.q4_0_dequant(block), want)
+    out = Buffer.create(runtime, 64)
+    batch = Batch(runtime)
+    batch.dispatch(name="llmopt_dequant_q4_0", buffers=[Buffer.of_array(runtime, block), out],
+                   parameters=parameters.u32s([1]), grid=(32, 1, 1), group=(256, 1, 1))
+    batch.commit()
+    assert np.array_equal(out.to_numpy(np.float16), want)
+
+
+@pytest.mark.parametrize("m,k,n,mode", [(1, 576, 1536, 0), (1, 4096, 512, 2), (2, 1024, 96, 1), (5, 1536, 333, 2),
+                                        (16, 256, 40, 0), (37, 96, 17, 2)])
+def test_linear_matches_oracle(runtime, oracle, m, k, n, mode):
+    from llmopt_b200 import dispatch
+
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    weight = _weights(rng, n, k)
+    additive = None if mode == 0 else rng.standard_normal((n,) if mode == 1 else (m, n)).astype(np.float16)
+    out = _tensor(runtime, np.full((m, n), np.nan, np.float16))
+    kernels = dispatch.dispatch_quant_linear(
+        _ctx(runtime), m=m, n=n, k=k, input=_tensor(runtime, x), weight=_tensor(runtime, weight), output=out,
+        additive=None if additive is None else _tensor(runtime, additive), epilogue_mode=mode)
+    assert kernels[0].endswith("_add") == (mode == 2)
+    assert_close_f16(out.buffer.to_numpy(np.float16, (m, n)), oracle.q4_0_linear(x, weight, additive, mode),
+                     label=f"q4_0 linear m={m} k={k} n={n} mode={mode}")
+
+
+@pytest.mark.parametrize("m,k,nq,nk,nv", [(1, 576, 576, 192, 192), (3, 1024, 256, 64, 64)])
+def test_qkv_matches_oracle(runtime, oracle, m, k, nq, nk, nv):
+    from llmopt_b200 import dispatch
+
+    rng = np.random.default_rng(32)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    weights = [_weights(rng, n, k) for n in (nq, nk, nv)]
+    outs = [_tensor(runtime, np.full((m, n), np.nan, np.float16)) for n in (nq, nk, nv)]
+    dispatch.dispatch_quant_qkv_linear(
+        _ctx(runtime), m=m, k=k, input=_tensor(runtime, x), q_weight=_tensor(runtime, weights[0]),
+        k_weight=_tensor(runtime, weights[1]), v_weight=_tensor(runtime, weights[2]), q_output=outs[0],
+        k_output=outs[1], v_output=outs[2])
+    for out, weight, n in zip(outs, weights, (nq, nk, nv)):
+        assert_close_f16(out.buffer.to_numpy(np.float16, (m, n)), oracle.q4_0_linear(x, weight), label="q4_0 qkv")
+
+
+@pytest.mark.parametrize("activation,code", [("silu", 0), ("gelu", 1), ("sigmoid", 2)])
+def test_gated_matches_oracle(runtime, oracle, activation, code):
+    from llmopt_b200 import dispatch
+
+    rng = np.random.default_rng(33)
+    m, k, n = 3, 768, 200
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    gate, up = _weights(rng, n, k), _weights(rng, n, k)
+    product = _tensor(runtime, np.full((m, n), np.nan, np.float16))
+    dispatch.dispatch_quant_gated_linear(_ctx(runtime), m=m, n=n, k=k, input=_tensor(runtime, x),
+                                         gate_weight=_tensor(runtime, gate), up_weight=_tensor(runtime, up),
+                                         product=product, activation=activation)
+    assert_close_f16(product.buffer.to_numpy(np.float16, (m, n)), oracle.q4_0_gated_linear(x, gate, up, code),
+                     rel=3e-3, label=f"q4_0 gated {activation}")
