@@ -26,6 +26,7 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <cstdlib>
 
 #include "w4a16_gemv.cuh"
 #include "w4a16_gemv_device.cuh"
@@ -456,10 +457,35 @@ int run_tc(const KernelArgs& args, const CUtensorMap& map_x, const CUtensorMap& 
 
 }  // namespace
 
-// Tensor-core path for M >= 64; returns -1 when the shape or the pointers are outside its domain
+// Fewest rows that take the tensor-core path.  With one 128-row tile the kernel streams the
+// weights once at the rate of the tensor pipe, which beats the small-M kernel well below 64 rows;
+// LLMOPT_CUDA_TC_MIN_ROWS overrides the threshold.
+uint32_t tensor_core_min_rows() {
+  static const uint32_t rows = []() -> uint32_t {
+    const char* text = getenv("LLMOPT_CUDA_TC_MIN_ROWS");
+    const long value = text ? strtol(text, nullptr, 10) : 0;
+    return value > 0 ? (uint32_t)value : 64u;
+  }();
+  return rows;
+}
+
+// Tensor-core path for M >= tensor_core_min_rows(); returns -1 when the shape or the pointers are outside its domain
 // (the caller then falls back to passes of the small-M kernel).
 int launch_w4a16_gemm_tc(const KernelArgs& args, const GemvProblem& problem, int epilogue, bool affine) {
-  if (args.ctx == nullptr || problem.m < 64 || problem.k % 64 != 0) return -1;
+  if (args.ctx == nullptr || problem.m < tensor_core_min_rows() || problem.k % 64 != 0) return -1;
+  if (epilogue == kEpiQkv) {
+    // three independent products of the same activations: one launch each
+    for (uint32_t i = 0; i < problem.matrices; ++i) {
+      GemvProblem one = problem;
+      one.mat[0] = problem.mat[i];
+      one.matrices = 1;
+      one.out[0] = problem.out[i];
+      one.has_aux = 0;
+      const int status = launch_w4a16_gemm_tc(args, one, kEpiLinear, false);
+      if (status != 0) return i == 0 ? status : (status < 0 ? 1 : status);
+    }
+    return 0;
+  }
   if (epilogue != kEpiLinear && epilogue != kEpiDualSwiglu && epilogue != kEpiTagged) return -1;
   if (affine && epilogue != kEpiLinear) return -1;
   const uint32_t matrices = epilogue == kEpiDualSwiglu ? 2u : 1u;

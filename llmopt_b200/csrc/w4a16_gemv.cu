@@ -293,15 +293,15 @@ int launch_w4a16_gemv(const KernelArgs& args, GemvProblem problem, int epilogue,
   }
   if (problem.k_warps == 0) problem.k_warps = pick_k_warps(problem.k);
 
-  // K a multiple of 512 and at most 32 rows: the shared-memory pipelined kernel
-  if (!affine && problem.x_rows <= 32) {
-    const int status = launch_w4a16_gemv_pipe(args, problem, epilogue);
+  // 64 rows and more: the tensor-memory GEMM
+  if (problem.m >= tensor_core_min_rows() && problem.x_rows == problem.m) {
+    const int status = launch_w4a16_gemm_tc(args, problem, epilogue, affine);
     if (status >= 0) return status;
   }
 
-  // 64 rows and more: the tensor-memory GEMM
-  if (problem.m >= 64 && problem.x_rows == problem.m) {
-    const int status = launch_w4a16_gemm_tc(args, problem, epilogue, affine);
+  // K a multiple of 512 and at most 32 rows: the shared-memory pipelined kernel
+  if (!affine && problem.x_rows <= 32) {
+    const int status = launch_w4a16_gemv_pipe(args, problem, epilogue);
     if (status >= 0) return status;
   }
 

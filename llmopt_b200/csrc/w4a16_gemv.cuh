@@ -42,6 +42,7 @@ int launch_w4a16_gemv(const KernelArgs& args, GemvProblem problem, int epilogue,
 
 // Tensor-core GEMM for M >= 64 (tcgen05 / tensor memory); returns -1 outside its domain.
 int launch_w4a16_gemm_tc(const KernelArgs& args, const GemvProblem& problem, int epilogue, bool affine);
+uint32_t tensor_core_min_rows();
 
 // Pipelined fast path (K % 512 == 0, <= 32 rows); returns -1 if the shape is outside its domain.
 int launch_w4a16_gemv_pipe(const KernelArgs& args, const GemvProblem& problem, int epilogue);
