@@ -138,6 +138,98 @@ __global__ void __launch_bounds__(256) exchange_sum_kernel(Regions regions, cons
   complete_exchange(regions.base[p.rank], epoch != 0u ? epoch : *reinterpret_cast<volatile uint32_t*>(regions.base[p.rank]) + 1u);
 }
 
+struct SumNormParams {
+  uint32_t ranks, rank, rows, width, slot_offset, has_residual;
+  float epsilon;
+  uint32_t weight_first;
+};
+
+// The exchange sum followed by the RMS normalisation of the result, one CTA per row:
+//   hidden[row]     = half(residual[row] + sum over ranks of partial_r[row])      (as exchange_sum_kernel)
+//   normalized[row] = half(hidden * inverse_rms(hidden) * weight)                 (as rms_norm_row_kernel;
+//                     weight_first picks (x w) inv over (x inv) w)
+// The mean of squares is taken over the ROUNDED hidden values, which is what the separate kernels
+// compute.  Rows up to 8192 wide stay in registers between the passes.
+__global__ void __launch_bounds__(256) exchange_sum_norm_kernel(Regions regions, const __half* __restrict__ residual,
+                                                                __half* __restrict__ hidden,
+                                                                const __half* __restrict__ norm_weight,
+                                                                __half* __restrict__ normalized, SumNormParams p,
+                                                                uint32_t* error_word) {
+  grid_chain_prologue();
+  __shared__ float partial[8];
+  const uint32_t epoch = announce_and_wait(regions, p.ranks, p.rank, error_word);
+  if (epoch != 0u) {
+    constexpr int kVectors = 8;  // float4 per thread: 256 * 8 * 4 = 8192 columns
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    float4 values[kVectors];
+    float squares = 0.0f;
+#pragma unroll
+    for (int v = 0; v < kVectors; ++v) {
+      const uint32_t column = (tid + v * 256u) * 4u;
+      values[v] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (column >= p.width) continue;
+      const size_t index = (size_t)row * p.width + column;
+      float4 parts[kMaxRanks];
+#pragma unroll
+      for (uint32_t r = 0; r < kMaxRanks; ++r)
+        if (r < p.ranks) parts[r] = *reinterpret_cast<const float4*>(regions.base[r] + p.slot_offset + index * 4u);
+      float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (uint32_t r = 0; r < kMaxRanks; ++r)
+        if (r < p.ranks) {
+          sum.x += parts[r].x;
+          sum.y += parts[r].y;
+          sum.z += parts[r].z;
+          sum.w += parts[r].w;
+        }
+      if (p.has_residual) {
+        const __half2* add = reinterpret_cast<const __half2*>(residual + index);
+        const float2 low = __half22float2(add[0]), high = __half22float2(add[1]);
+        sum.x += low.x;
+        sum.y += low.y;
+        sum.z += high.x;
+        sum.w += high.y;
+      }
+      const __half2 low = __floats2half2_rn(sum.x, sum.y), high = __floats2half2_rn(sum.z, sum.w);
+      __half2* target = reinterpret_cast<__half2*>(hidden + index);
+      target[0] = low;
+      target[1] = high;
+      const float2 low_f = __half22float2(low), high_f = __half22float2(high);
+      values[v] = make_float4(low_f.x, low_f.y, high_f.x, high_f.y);
+      squares = fmaf(low_f.x, low_f.x, squares);
+      squares = fmaf(low_f.y, low_f.y, squares);
+      squares = fmaf(high_f.x, high_f.x, squares);
+      squares = fmaf(high_f.y, high_f.y, squares);
+    }
+    squares = warp_sum(squares);
+    if ((tid & 31u) == 0) partial[tid >> 5] = squares;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += partial[i];
+    const float inverse = rsqrtf(total / (float)p.width + p.epsilon);
+#pragma unroll
+    for (int v = 0; v < kVectors; ++v) {
+      const uint32_t column = (tid + v * 256u) * 4u;
+      if (column >= p.width) continue;
+      const __half2* weights = reinterpret_cast<const __half2*>(norm_weight + column);
+      const float2 w_low = __half22float2(weights[0]), w_high = __half22float2(weights[1]);
+      float4 y;
+      if (p.weight_first) {
+        y = make_float4((values[v].x * w_low.x) * inverse, (values[v].y * w_low.y) * inverse,
+                        (values[v].z * w_high.x) * inverse, (values[v].w * w_high.y) * inverse);
+      } else {
+        y = make_float4((values[v].x * inverse) * w_low.x, (values[v].y * inverse) * w_low.y,
+                        (values[v].z * inverse) * w_high.x, (values[v].w * inverse) * w_high.y);
+      }
+      __half2* target = reinterpret_cast<__half2*>(normalized + (size_t)row * p.width + column);
+      target[0] = __floats2half2_rn(y.x, y.y);
+      target[1] = __floats2half2_rn(y.z, y.w);
+    }
+  }
+  complete_exchange(regions.base[p.rank], epoch != 0u ? epoch : *reinterpret_cast<volatile uint32_t*>(regions.base[p.rank]) + 1u);
+}
+
 struct ArgmaxParams {
   uint32_t ranks, rank, rows, parts, slot_offset, shard_columns;
 };
@@ -218,6 +310,31 @@ int launch_tp_exchange_sum(const KernelArgs& args) {
   if (ctas > 32) ctas = 32;
   launch_kernel(args, exchange_sum_kernel, dim3(ctas), dim3(256), 0, regions, (const __half*)args.buffers[p.ranks],
                 (__half*)args.buffers[p.ranks + 1], p, context_device_error(args.ctx));
+  return check_launch(args);
+}
+
+// Buffers [region_0 .. region_{ranks-1}, residual, hidden output, norm weight, normalized output];
+// params {ranks, rank, rows, width, slot_offset, has_residual, epsilon f32, weight_first}.
+int launch_tp_exchange_sum_norm(const KernelArgs& args) {
+  SumNormParams p;
+  LLMOPT_REQUIRE(args.param_bytes == sizeof(p), "expects 32 parameter bytes");
+  memcpy(&p, args.params, sizeof(p));
+  LLMOPT_REQUIRE(p.ranks >= 1 && p.ranks <= kMaxRanks && p.rank < p.ranks, "needs 1 <= ranks <= 8 and rank < ranks");
+  LLMOPT_REQUIRE((uint32_t)args.buffer_count == p.ranks + 4, "expects one region per rank and four more buffers");
+  LLMOPT_REQUIRE(p.rows > 0 && p.width > 0 && p.width % 4 == 0 && p.width <= 8192 && p.slot_offset >= 256 &&
+                     p.slot_offset % 16 == 0 && p.epsilon > 0.0f,
+                 "needs rows > 0, width a multiple of 4 up to 8192, a 16-byte aligned slot and a positive epsilon");
+  const size_t elements = (size_t)p.rows * p.width;
+  Regions regions;
+  LLMOPT_REQUIRE(collect_regions(args, p.ranks, (size_t)p.slot_offset + elements * 4, &regions),
+                 "a region is too short or misaligned");
+  LLMOPT_REQUIRE((!p.has_residual || args.lengths[p.ranks] >= elements * 2) && args.lengths[p.ranks + 1] >= elements * 2 &&
+                     args.lengths[p.ranks + 2] >= (size_t)p.width * 2 && args.lengths[p.ranks + 3] >= elements * 2,
+                 "residual, output or weight buffer is too short");
+  launch_kernel(args, exchange_sum_norm_kernel, dim3(p.rows), dim3(256), 0, regions,
+                (const __half*)args.buffers[p.ranks], (__half*)args.buffers[p.ranks + 1],
+                (const __half*)args.buffers[p.ranks + 2], (__half*)args.buffers[p.ranks + 3], p,
+                context_device_error(args.ctx));
   return check_launch(args);
 }
 

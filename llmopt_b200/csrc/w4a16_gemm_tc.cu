@@ -347,14 +347,28 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
           tmem_load_32(lane_address + kBN / 2 + column, up);
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           if (out_row < p.m) {
-            __half* target = p.out + (size_t)out_row * p.n + n0 + column;
+            const size_t out_index = (size_t)out_row * p.n + n0 + column;
+            __half* target = p.out + out_index;
+            // silu in fp32, one rounding of the product: lib/metal_w4a16_source.ml:571-575
+            auto gated = [&](int i) {
+              const float g = __uint_as_float(gate[i]);
+              return (g / (1.0f + __expf(-g))) * __uint_as_float(up[i]);
+            };
+            if (n0 + column + 32u <= p.n && (out_index & 7u) == 0) {
+              uint32_t packed[16];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (n0 + column + i < p.n) {
-                const float g = __uint_as_float(gate[i]);
-                // silu in fp32, one rounding of the product: lib/metal_w4a16_source.ml:571-575
-                target[i] = __float2half_rn((g / (1.0f + expf(-g))) * __uint_as_float(up[i]));
+              for (int i = 0; i < 16; ++i) {
+                const __half2 pair = __floats2half2_rn(gated(2 * i), gated(2 * i + 1));
+                packed[i] = *reinterpret_cast<const uint32_t*>(&pair);
               }
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                reinterpret_cast<uint4*>(target)[i] =
+                    make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (n0 + column + i < p.n) target[i] = __float2half_rn(gated(i));
             }
           }
         }

@@ -122,23 +122,35 @@ class DecodeEngine:
             if slot_count > group.slot_count or max(batch * hidden * 4, min(batch, 32) * CANDIDATE_PARTS * 8) > group.slot_bytes:
                 raise ValueError("the exchange group's slots are too few or too small for this plan")
 
-        def row_split_linear(source, weight, scale, k_local, residual, output):
+        def row_split_linear(source, weight, scale, k_local, residual, output, norm=None):
             """x[:, K slice] . W[:, K slice]^T as an fp32 partial into this rank's slot, then the
-            exchange that adds all ranks' partial sums and the residual."""
+            exchange that adds all ranks' partial sums and the residual.  ``norm`` = (weight,
+            weight_first): the exchange also writes the RMS-normalised result into ``self.normed``,
+            replacing the norm kernel that would follow."""
             nonlocal exchange
             slot = slot_of[exchange]
             exchange += 1
             run("llmopt_w4a16_linear_partial_f32_g64",
                 [source.buffer, weight.buffer, scale.buffer, group.slot_view(slot, batch * hidden * 4)],
                 parameters.u32s([batch, hidden, k_local]))
-            group.sum_record(commands.dispatch, slot=slot, rows=batch, width=hidden, residual=residual.buffer,
-                             output=output.buffer)
+            if norm is None or hidden > 8192:
+                group.sum_record(commands.dispatch, slot=slot, rows=batch, width=hidden, residual=residual.buffer,
+                                 output=output.buffer)
+                return False
+            group.sum_norm_record(commands.dispatch, slot=slot, rows=batch, width=hidden, residual=residual.buffer,
+                                  output=output.buffer, norm_weight=norm[0].buffer, normalized=self.normed.buffer,
+                                  epsilon=config.epsilon, weight_first=norm[1])
+            return True
+
+        normed_ready = False  # self.normed already holds this layer's normalised input
         current, other = self.hidden_a, self.hidden_b
         attention_index = conv_index = 0
-        for kind, layer in zip(config.layers, self.layers):
-            run("llmopt_rms_norm_f16_simd", [current.buffer, layer["input_norm"].buffer, self.normed.buffer],
-                parameters.rms_norm(rows=batch, width=hidden, epsilon=config.epsilon),
-                (dispatch.simd_rows_grid(batch), 1, 1))
+        for layer_index, (kind, layer) in enumerate(zip(config.layers, self.layers)):
+            if not normed_ready:
+                run("llmopt_rms_norm_f16_simd", [current.buffer, layer["input_norm"].buffer, self.normed.buffer],
+                    parameters.rms_norm(rows=batch, width=hidden, epsilon=config.epsilon),
+                    (dispatch.simd_rows_grid(batch), 1, 1))
+            normed_ready = False
             if kind == "attention":
                 dispatch.dispatch_w4a16_qkv_linear_command(
                     context, input=self.normed, q_weight=layer["q"][0], q_scale=layer["q"][1], k_weight=layer["k"][0],
@@ -183,8 +195,9 @@ class DecodeEngine:
                                                    scale=layer["o"][1], output=other, bias=current,
                                                    bias_row_stride=hidden)
                 else:
-                    row_split_linear(self.attended, layer["o"][0], layer["o"][1], config.query_heads * dim, current,
-                                     other)
+                    ffn_normed = row_split_linear(self.attended, layer["o"][0], layer["o"][1],
+                                                  config.query_heads * dim, current, other,
+                                                  norm=(layer["ffn_norm"], True))
                 attention_index += 1
             else:
                 dispatch.dispatch_w4a16_linear(context, input=self.normed, weight=layer["in_proj"][0],
@@ -212,12 +225,16 @@ class DecodeEngine:
                 # the same three kernels on this rank's intermediate columns; the down projection is
                 # the row-split product
                 ffn = parameters.w4a16_swiglu_ffn(m=batch, n=config.intermediate, k=hidden, epsilon=config.epsilon)
-                run("llmopt_w4a16_swiglu_rms_f16_g64", [current.buffer, layer["ffn_norm"].buffer, self.normed.buffer],
-                    ffn, (batch * 256, 1, 1))
+                if not (kind == "attention" and ffn_normed):
+                    run("llmopt_w4a16_swiglu_rms_f16_g64",
+                        [current.buffer, layer["ffn_norm"].buffer, self.normed.buffer], ffn, (batch * 256, 1, 1))
                 run("llmopt_w4a16_dual_swiglu_f16_g64" + ("" if batch == 1 else "_m4"),
                     [self.normed.buffer, layer["gate"][0].buffer, layer["gate"][1].buffer, layer["up"][0].buffer,
                      layer["up"][1].buffer, self.product.buffer], ffn)
-                row_split_linear(self.product, layer["down"][0], layer["down"][1], config.intermediate, current, other)
+                following = self.layers[layer_index + 1] if layer_index + 1 < len(self.layers) else None
+                normed_ready = row_split_linear(
+                    self.product, layer["down"][0], layer["down"][1], config.intermediate, current, other,
+                    norm=None if following is None else (following["input_norm"], False))
             current, other = other, current
         for row0 in range(0, batch, 32):  # the LM head takes at most 32 rows per dispatch
             rows = min(32, batch - row0)

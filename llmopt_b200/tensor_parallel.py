@@ -155,6 +155,18 @@ class ExchangeGroup:
         return dispatch_item(name="llmopt_tp_exchange_sum_f16", buffers=buffers, parameters=params,
                              grid=(256, 1, 1), group=(256, 1, 1))
 
+    def sum_norm_record(self, dispatch_item, *, slot: int, rows: int, width: int, residual, output, norm_weight,
+                        normalized, epsilon: float, weight_first: bool):
+        """``llmopt_tp_exchange_sum_rms_f16``: the exchange sum and the RMS normalisation of its result
+        in one kernel (``normalized`` = what the following rms kernel would have written)."""
+        import struct
+
+        params = struct.pack("<6IfI", self.world, self.rank, rows, width, self.slot_offset(slot),
+                             1 if residual else 0, epsilon, 1 if weight_first else 0)
+        buffers = list(self.regions) + [residual if residual is not None else output, output, norm_weight, normalized]
+        return dispatch_item(name="llmopt_tp_exchange_sum_rms_f16", buffers=buffers, parameters=params,
+                             grid=(256 * rows, 1, 1), group=(256, 1, 1))
+
     def argmax_record(self, dispatch_item, *, slot: int, rows: int, shard_columns: int, output):
         """``llmopt_tp_exchange_argmax``: best of every rank's stage-1 candidates, global indices."""
         from . import parameters
