@@ -13,6 +13,17 @@ constexpr int kMaxParamBytes = 256;
 
 struct Context;
 
+// A row-wise RMS normalisation folded, by the plan builder, into the kernel that reads its
+// output: that kernel normalises the raw rows itself and one of its CTAs still writes the
+// normalised tensor, so the plan's buffers end up exactly as with the two separate kernels.
+struct FusedNorm {
+  const __half* input;    // un-normalised rows [m, k]
+  const __half* weight;   // [k]
+  __half* normalized;     // [m, k], what the separate kernel would have written
+  float epsilon;
+  uint32_t weight_first;  // (x w) inv instead of (x inv) w
+};
+
 // One dispatch as the reference's stubs receive it: kernel name already
 // resolved to a launcher, buffers in binding order, raw little-endian
 // parameter bytes, Metal-style grid (threads) and threadgroup.
@@ -32,6 +43,7 @@ struct KernelArgs {
   const uint32_t* checkpoint_cell;
   const char* name;
   std::string* error;
+  const FusedNorm* fused_norm;  // null unless the plan builder folded a norm into this dispatch
 };
 
 typedef int (*Launcher)(const KernelArgs&);

@@ -74,6 +74,8 @@ struct Context {
   std::vector<void*> scratch_blocks;
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
+  void* split = nullptr;  // K-split scratch of the tensor-core GEMM
+  size_t split_bytes = 0;
   void* flush_buffer = nullptr;  // L2 flush target for timing
   size_t flush_bytes = 0;
   int* argmax_result = nullptr;  // device int
@@ -166,6 +168,23 @@ void* context_scratch(Context* context, size_t bytes, std::string* error) {
   context->scratch_blocks.push_back(block);
   context->scratch = block;
   context->scratch_bytes = wanted;
+  return block;
+}
+void* context_split_scratch(Context* context, size_t zeroed_bytes, size_t bytes, cudaStream_t stream,
+                            std::string* error) {
+  if (bytes <= context->split_bytes) return context->split;
+  size_t wanted = context->split_bytes ? context->split_bytes : (size_t)32 << 20;
+  while (wanted < bytes) wanted *= 2;
+  void* block = nullptr;
+  cudaError_t status = cudaMalloc(&block, wanted);
+  if (status == cudaSuccess) status = cudaMemsetAsync(block, 0, zeroed_bytes, stream);  // ordered before the first user
+  if (status != cudaSuccess) {
+    if (error) *error = std::string("scratch allocation failed: ") + cudaGetErrorString(status);
+    return nullptr;
+  }
+  context->scratch_blocks.push_back(block);  // freed with the context; earlier blocks stay valid for captured plans
+  context->split = block;
+  context->split_bytes = wanted;
   return block;
 }
 int context_sm_count(Context* context) { return context->sm_count; }
@@ -354,8 +373,61 @@ static int own_record(llmopt_cuda_library* library, const llmopt_cuda_dispatch_r
   return LLMOPT_CUDA_OK;
 }
 
+// Plan-level fusion: a row RMS norm whose output is the activation input of the W4A16 product that
+// follows it is folded into that product (the product normalises the raw rows while it stages
+// them and still writes the normalised tensor).  Recognised by name and by buffer identity:
+//   norm    llmopt_rms_norm_f16{,_simd} [x, w, y] {rows, width, eps}      -> (x inv) w
+//           llmopt_w4a16_swiglu_rms_f16_g64 [x, w, y] {m, n, k, eps}      -> (x w) inv
+//   product llmopt_w4a16_{linear,qkv_linear,dual_swiglu}_f16_g64*  with buffers[0] == y, same rows / k
+static bool fold_norm(const OwnedRecord& norm, const OwnedRecord& product, FusedNorm* fused) {
+  if (norm.is_copy || product.is_copy || norm.buffers.size() != 3 || product.buffers.empty()) return false;
+  uint32_t rows, width;
+  float epsilon;
+  bool weight_first;
+  auto u32 = [](const OwnedRecord& record, size_t index) {
+    uint32_t value;
+    memcpy(&value, record.params.data() + 4 * index, 4);
+    return value;
+  };
+  if ((norm.name == "llmopt_rms_norm_f16_simd" || norm.name == "llmopt_rms_norm_f16") && norm.params.size() == 12) {
+    rows = u32(norm, 0), width = u32(norm, 1), weight_first = false;
+    memcpy(&epsilon, norm.params.data() + 8, 4);
+  } else if (norm.name == "llmopt_w4a16_swiglu_rms_f16_g64" && norm.params.size() == 16) {
+    rows = u32(norm, 0), width = u32(norm, 2), weight_first = true;
+    memcpy(&epsilon, norm.params.data() + 12, 4);
+  } else {
+    return false;
+  }
+  uint32_t m, k;
+  const std::string& name = product.name;
+  if (name.rfind("llmopt_w4a16_qkv_linear_f16_g64", 0) == 0 && product.params.size() == 20) {
+    m = u32(product, 0), k = u32(product, 1);
+  } else if ((name.rfind("llmopt_w4a16_dual_swiglu_f16_g64", 0) == 0 && product.params.size() == 16) ||
+             ((name == "llmopt_w4a16_linear_f16_g64" || name == "llmopt_w4a16_linear_f16_g64_m4" ||
+               name == "llmopt_w4a16_linear_f16_g64_m8") && product.params.size() == 20)) {
+    m = u32(product, 0), k = u32(product, 2);
+  } else {
+    return false;
+  }
+  llmopt_cuda_buffer* normalized = norm.buffers[2];
+  llmopt_cuda_buffer* consumed = product.buffers[0];
+  if (normalized->pointer() != consumed->pointer() || m != rows || k != width || rows == 0 || rows > 8) return false;
+  if (normalized->length < (size_t)rows * width * 2 || norm.buffers[0]->length < (size_t)rows * width * 2 ||
+      norm.buffers[1]->length < (size_t)width * 2)
+    return false;
+  // the product must not write what the norm reads (it reads the raw rows while it runs)
+  for (llmopt_cuda_buffer* buffer : product.buffers)
+    if (buffer != consumed && buffer->pointer() == norm.buffers[0]->pointer()) return false;
+  fused->input = (const __half*)norm.buffers[0]->pointer();
+  fused->weight = (const __half*)norm.buffers[1]->pointer();
+  fused->normalized = (__half*)normalized->pointer();
+  fused->epsilon = epsilon;
+  fused->weight_first = weight_first ? 1u : 0u;
+  return true;
+}
+
 static int run_record(Context* context, const OwnedRecord& record, const uint32_t* past_cell,
-                      const uint32_t* checkpoint_cell) {
+                      const uint32_t* checkpoint_cell, const FusedNorm* fused_norm = nullptr) {
   if (record.is_copy) {
     CUDA_TRY(cudaMemcpyAsync(record.buffers[1]->pointer(), record.buffers[0]->pointer(), record.buffers[0]->length,
                              cudaMemcpyDeviceToDevice, context->stream),
@@ -379,6 +451,7 @@ static int run_record(Context* context, const OwnedRecord& record, const uint32_
   args.name = record.name.c_str();
   args.past_tokens_cell = is_paged_attention_name(args.name) && record.params.size() >= 16 ? past_cell : nullptr;
   args.checkpoint_cell = is_checkpoint_pack_name(args.name) && record.params.size() >= 4 ? checkpoint_cell : nullptr;
+  args.fused_norm = fused_norm;
   std::string message;
   args.error = &message;
   if (record.launcher(args) != 0) return set_error(LLMOPT_CUDA_FAILURE, message);
@@ -453,6 +526,7 @@ struct llmopt_cuda_prebaked {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t executable = nullptr;
   int kernel_nodes = 0;
+  int folded_norms = 0;  // norm records folded into the product that follows them
   static constexpr int kStaging = 16;
 };
 
@@ -978,8 +1052,16 @@ int llmopt_cuda_prebaked_create_bound(llmopt_cuda_library* library, const llmopt
   plan_prologue_kernel<<<binding_count ? 4 : 1, 128, 0, context->stream>>>(
       plan->cells, plan->token_buffer ? (long long*)plan->token_buffer->pointer() : nullptr, device_bindings);
   int failure = LLMOPT_CUDA_OK;
-  for (OwnedRecord& record : plan->records) {
-    failure = run_record(context, record, &plan->cells->past_tokens, &plan->cells->checkpoint);
+  const bool fold = getenv("LLMOPT_CUDA_FOLD_NORMS") == nullptr || getenv("LLMOPT_CUDA_FOLD_NORMS")[0] != '0';
+  for (size_t index = 0; index < plan->records.size(); ++index) {
+    FusedNorm fused;
+    if (fold && index + 1 < plan->records.size() && fold_norm(plan->records[index], plan->records[index + 1], &fused)) {
+      failure = run_record(context, plan->records[index + 1], &plan->cells->past_tokens, &plan->cells->checkpoint, &fused);
+      ++index;
+      plan->folded_norms += 1;
+    } else {
+      failure = run_record(context, plan->records[index], &plan->cells->past_tokens, &plan->cells->checkpoint);
+    }
     if (failure != LLMOPT_CUDA_OK) break;
   }
   if (failure == LLMOPT_CUDA_OK && plan->output_buffer) {

@@ -35,6 +35,9 @@ namespace llmopt {
 using namespace gemv;
 
 uint32_t* context_device_error(Context* ctx);
+// Scratch of the K-split protocol: grows on demand, earlier blocks stay valid for captured plans;
+// the first `zeroed_bytes` of a new block are cleared on `stream` before its first user.
+void* context_split_scratch(Context* ctx, size_t zeroed_bytes, size_t bytes, cudaStream_t stream, std::string* error);
 
 namespace {
 
@@ -47,6 +50,7 @@ constexpr int kConvertWarps = 8;
 constexpr int kThreadsTc = (2 + kConvertWarps) * 32;
 constexpr uint32_t kTmemColumns = 256;
 constexpr uint32_t kWaitLimit = 1u << 20;
+constexpr uint32_t kSplitCounterTiles = 1u << 14;  // output tiles whose split counters fit the scratch header
 
 constexpr int kOffsetA = 0;
 constexpr int kOffsetB = kOffsetA + kLoadStages * kATileBytes;
@@ -55,7 +59,8 @@ constexpr int kOffsetBarriers = kOffsetRaw + kLoadStages * kRawTileBytes;
 constexpr int kBarrierCount = 2 * kLoadStages + 2 * kBStages + 1;
 constexpr int kOffsetTmemHolder = kOffsetBarriers + kBarrierCount * 8;
 constexpr int kOffsetAbort = kOffsetTmemHolder + 4;
-constexpr int kSharedBytesTc = kOffsetAbort + 4 + 1024;  // + slack to align the base to 1024 bytes
+constexpr int kOffsetLast = kOffsetAbort + 4;
+constexpr int kSharedBytesTc = kOffsetLast + 4 + 1024;  // + slack to align the base to 1024 bytes
 
 enum TcEpilogue { kTcLinear = 0, kTcDualSwiglu = 1, kTcTagged = 2 };
 
@@ -69,6 +74,12 @@ struct TcProblem {
   uint32_t aux_row_stride;
   uint32_t has_aux;
   uint32_t tag;
+  // K split over grid.z CTAs per output tile (few tiles, long K): every CTA parks its fp32 tile in
+  // partials[tile][split], bumps counters[tile]; the last one adds all splits in split order and
+  // runs the epilogue.  Nobody waits for anybody.
+  uint32_t splits;
+  float* partials;     // [tiles][splits][kBM][kBN]
+  uint32_t* counters;  // [tiles], zero between launches
 };
 
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
@@ -196,7 +207,10 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   constexpr uint32_t columns_per_tile = EPI == kTcDualSwiglu ? kBN / 2 : kBN;
   const uint32_t n0 = blockIdx.x * columns_per_tile, m0 = blockIdx.y * kBM;
-  const uint32_t k_blocks = p.k / kBK;
+  const uint32_t all_k_blocks = p.k / kBK;
+  const uint32_t split = blockIdx.z;
+  const uint32_t kb_begin = (uint32_t)((uint64_t)all_k_blocks * split / p.splits);
+  const uint32_t k_blocks = (uint32_t)((uint64_t)all_k_blocks * (split + 1u) / p.splits) - kb_begin;  // this CTA's share
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kLoadStages; ++s) {
@@ -232,21 +246,21 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       uint32_t issued = 0;
-      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-        const uint32_t s = kb % kLoadStages, round = kb / kLoadStages;
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {  // kb counts this CTA's k-blocks; k_at is the absolute one
+        const uint32_t s = kb % kLoadStages, round = kb / kLoadStages, k_at = kb_begin + kb;
         if (*abort_flag || !barrier_wait(load_empty + s * 8, (round & 1u) ^ 1u)) {
           give_up();
           break;
         }
         barrier_expect_tx(load_full + s * 8, kATileBytes + kRawTileBytes);
-        tma_load_2d(base + kOffsetA + s * kATileBytes, &map_x, (int32_t)(kb * kBK), (int32_t)m0, load_full + s * 8);
+        tma_load_2d(base + kOffsetA + s * kATileBytes, &map_x, (int32_t)(k_at * kBK), (int32_t)m0, load_full + s * 8);
         const uint32_t raw = base + kOffsetRaw + s * kRawTileBytes;
         if (EPI == kTcDualSwiglu) {
-          tma_load_2d(raw, &map_w0, (int32_t)(kb * (kBK / 2)), (int32_t)n0, load_full + s * 8);
-          tma_load_2d(raw + kRawTileBytes / 2, &map_w1, (int32_t)(kb * (kBK / 2)), (int32_t)n0, load_full + s * 8);
+          tma_load_2d(raw, &map_w0, (int32_t)(k_at * (kBK / 2)), (int32_t)n0, load_full + s * 8);
+          tma_load_2d(raw + kRawTileBytes / 2, &map_w1, (int32_t)(k_at * (kBK / 2)), (int32_t)n0, load_full + s * 8);
         } else {
-          tma_load_2d(raw, &map_w0, (int32_t)(kb * (kBK / 2)), (int32_t)n0, load_full + s * 8);
-          tma_load_2d(raw + kRawTileBytes / 2, &map_w0, (int32_t)(kb * (kBK / 2)), (int32_t)(n0 + kBN / 2),
+          tma_load_2d(raw, &map_w0, (int32_t)(k_at * (kBK / 2)), (int32_t)n0, load_full + s * 8);
+          tma_load_2d(raw + kRawTileBytes / 2, &map_w0, (int32_t)(k_at * (kBK / 2)), (int32_t)(n0 + kBN / 2),
                       load_full + s * 8);
         }
         issued = kb + 1;
@@ -292,14 +306,14 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const __half* zero_row = AFFINE ? p.zero[matrix] + (size_t)(row_present ? weight_row : 0u) * groups : nullptr;
     const uint32_t swizzle = (row & 7u) * 16u;
     bool ok = true;
-    __half next_scale = row_present ? __ldg(scale_row) : __float2half(0.0f);
-    __half next_zero = AFFINE && row_present ? __ldg(zero_row) : __float2half(0.0f);
+    __half next_scale = row_present ? __ldg(scale_row + kb_begin) : __float2half(0.0f);
+    __half next_zero = AFFINE && row_present ? __ldg(zero_row + kb_begin) : __float2half(0.0f);
     for (uint32_t kb = 0; kb < k_blocks; ++kb) {
       const uint32_t s = kb % kLoadStages, t = kb % kBStages;
       const __half scale = next_scale, zero = next_zero;
       if (kb + 1 < k_blocks && row_present) {
-        next_scale = __ldg(scale_row + kb + 1);
-        if (AFFINE) next_zero = __ldg(zero_row + kb + 1);
+        next_scale = __ldg(scale_row + kb_begin + kb + 1);
+        if (AFFINE) next_zero = __ldg(zero_row + kb_begin + kb + 1);
       }
       ok = !*abort_flag && barrier_wait(load_full + s * 8, (kb / kLoadStages) & 1u) &&
            barrier_wait(b_empty + t * 8, ((kb / kBStages) & 1u) ^ 1u);
@@ -332,20 +346,93 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     // epilogue: this warp reads its lane quarter and one half of the columns
     ok = ok && !*abort_flag && barrier_wait(accumulator_full, 0u);
     if (!ok) give_up();
+    {
+      // one verdict for all eight epilogue warps: the steps below synchronise among them
+      uint32_t all_ok;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\t"
+          "setp.ne.u32 q, %1, 0;\n\t"
+          "bar.red.and.pred p, 1, 256, q;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(all_ok)
+          : "r"(ok ? 1u : 0u)
+          : "memory");
+      ok = all_ok != 0u;
+    }
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t quarter = warp & 3u, half_index = (warp - 2u) >> 2;
-      const uint32_t out_row = m0 + quarter * 32u + lane;
+      const uint32_t tile_row = quarter * 32u + lane, out_row = m0 + tile_row;
       const uint32_t lane_address = tmem_base + ((quarter * 32u) << 16);
-      if (EPI == kTcDualSwiglu) {
+      bool combine = false;  // sums come from the parked tiles of all splits instead of tensor memory
+      const uint32_t tile = blockIdx.y * gridDim.x + blockIdx.x;
+      const float* tile_partials = p.partials + (size_t)tile * p.splits * (kBM * kBN);
+      if (p.splits > 1u) {
+        // park this CTA's fp32 tile (rows that exist only), count it, and go on only as the last split
+        float* mine = p.partials + ((size_t)tile * p.splits + split) * (kBM * kBN) + (size_t)tile_row * kBN;
+#pragma unroll 1
+        for (uint32_t piece = 0; piece < 4; ++piece) {
+          const uint32_t column = half_index * 128u + piece * 32u;
+          uint32_t values[32];
+          tmem_load_32(lane_address + column, values);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (out_row < p.m) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              reinterpret_cast<uint4*>(mine + column)[i] =
+                  make_uint4(values[4 * i], values[4 * i + 1], values[4 * i + 2], values[4 * i + 3]);
+          }
+        }
+        volatile uint32_t* last_flag = reinterpret_cast<volatile uint32_t*>(base_pointer + kOffsetLast);
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight epilogue warps
+        if (threadIdx.x == 64u) {
+          __threadfence();  // publishes the tile the barrier ordered before this thread
+          const uint32_t before = atomicAdd(p.counters + tile, 1u);
+          const bool last = before + 1u == p.splits;
+          if (last) p.counters[tile] = 0u;  // ready for the next launch
+          *last_flag = last ? 1u : 0u;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        combine = *last_flag != 0u;
+        if (combine) __threadfence();
+      }
+      // 32 consecutive accumulator columns of this thread's row
+      auto load_columns = [&](uint32_t column, uint32_t (&values)[32]) {
+        if (!combine) {
+          tmem_load_32(lane_address + column, values);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          return;
+        }
+        float sums[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sums[i] = 0.0f;
+        if (out_row < p.m) {
+          for (uint32_t s = 0; s < p.splits; ++s) {  // split order: the sum does not depend on who came last
+            const float4* source =
+                reinterpret_cast<const float4*>(tile_partials + (size_t)s * (kBM * kBN) + (size_t)tile_row * kBN + column);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 part = __ldcg(source + i);
+              sums[4 * i] += part.x;
+              sums[4 * i + 1] += part.y;
+              sums[4 * i + 2] += part.z;
+              sums[4 * i + 3] += part.w;
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) values[i] = __float_as_uint(sums[i]);
+      };
+      if (p.splits > 1u && !combine) {
+        // another CTA finishes this tile
+      } else if (EPI == kTcDualSwiglu) {
         // columns [0, 128) gate, [128, 256) up; this warp covers 64 output columns
 #pragma unroll 1
         for (uint32_t piece = 0; piece < 2; ++piece) {
           const uint32_t column = half_index * 64u + piece * 32u;
           uint32_t gate[32], up[32];
-          tmem_load_32(lane_address + column, gate);
-          tmem_load_32(lane_address + kBN / 2 + column, up);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          load_columns(column, gate);
+          load_columns(kBN / 2 + column, up);
           if (out_row < p.m) {
             const size_t out_index = (size_t)out_row * p.n + n0 + column;
             __half* target = p.out + out_index;
@@ -377,8 +464,7 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         for (uint32_t piece = 0; piece < 4; ++piece) {
           const uint32_t column = half_index * 128u + piece * 32u;
           uint32_t values[32];
-          tmem_load_32(lane_address + column, values);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          load_columns(column, values);
           if (out_row < p.m) {
             const size_t out_index = (size_t)out_row * p.n + n0 + column;
             const bool whole = n0 + column + 32u <= p.n && (out_index & 7u) == 0;
@@ -462,9 +548,30 @@ int run_tc(const KernelArgs& args, const CUtensorMap& map_x, const CUtensorMap& 
     return -1;
   }
   constexpr uint32_t columns_per_tile = EPI == kTcDualSwiglu ? kBN / 2 : kBN;
-  const dim3 grid((p.n + columns_per_tile - 1) / columns_per_tile, (p.m + kBM - 1) / kBM);
+  dim3 grid((p.n + columns_per_tile - 1) / columns_per_tile, (p.m + kBM - 1) / kBM, 1);
+  TcProblem problem = p;
+  // Few output tiles and a long K (decode batches, narrow projections): split K over enough CTAs to
+  // occupy the machine; every split keeps at least four k-blocks.
+  const uint32_t tiles = grid.x * grid.y, sms = (uint32_t)context_sm_count(args.ctx), k_blocks = p.k / kBK;
+  problem.splits = 1;
+  if (tiles * 2u <= sms) {
+    uint32_t splits = sms / tiles;
+    if (splits > k_blocks / 4u) splits = k_blocks / 4u;
+    if (splits > 32u) splits = 32u;
+    if (splits > 1u && tiles <= kSplitCounterTiles) problem.splits = splits;
+  }
+  if (problem.splits > 1u) {
+    constexpr size_t counter_bytes = kSplitCounterTiles * sizeof(uint32_t);
+    const size_t partial_bytes = (size_t)tiles * problem.splits * kBM * kBN * sizeof(float);
+    uint8_t* scratch =
+        (uint8_t*)context_split_scratch(args.ctx, counter_bytes, counter_bytes + partial_bytes, args.stream, args.error);
+    if (scratch == nullptr) return 1;
+    problem.counters = reinterpret_cast<uint32_t*>(scratch);
+    problem.partials = reinterpret_cast<float*>(scratch + counter_bytes);
+    grid.z = problem.splits;
+  }
   static std::atomic<uint32_t> launches{0};
-  launch_kernel(args, kernel, grid, dim3(kThreadsTc), kSharedBytesTc, map_x, map_w0, map_w1, p,
+  launch_kernel(args, kernel, grid, dim3(kThreadsTc), kSharedBytesTc, map_x, map_w0, map_w1, problem,
                 context_device_error(args.ctx), launches.fetch_add(1) + 1u);
   return check_launch(args);
 }

@@ -27,6 +27,7 @@
 //     memory (deterministic), then the epilogue writes half once.
 // The k index inside an MMA is a fixed permutation of the real k (pairs
 // (i, i+4) of a byte quad); activations are permuted to match with PRMT.
+#include "rms_norm.cuh"
 #include "w4a16_gemv_device.cuh"
 
 namespace llmopt {
@@ -292,6 +293,27 @@ int launch_w4a16_gemv(const KernelArgs& args, GemvProblem problem, int epilogue,
     LLMOPT_REQUIRE(((uintptr_t)problem.mat[i].packed & 7u) == 0, "packed weight must be 8-byte aligned");
   }
   if (problem.k_warps == 0) problem.k_warps = pick_k_warps(problem.k);
+
+  // A norm folded into this product: only the pipelined small-batch kernel stages activations in a
+  // form that can absorb it; otherwise run the norm as its own kernel first.
+  if (problem.norm_weight != nullptr) {
+    const bool absorbs = !affine && problem.x_rows <= 8 && (size_t)problem.x_rows * problem.k <= 16384 &&
+                         epilogue != kEpiSplitF32 && problem.k % 512 == 0;
+    if (absorbs) {
+      const int status = launch_w4a16_gemv_pipe(args, problem, epilogue);
+      if (status >= 0) return status;
+    }
+    if (problem.norm_weight_first)
+      launch_rms_norm_rows<__half, true>(args, problem.x, problem.norm_weight, problem.norm_out, problem.x_rows,
+                                         problem.k, problem.norm_epsilon);
+    else
+      launch_rms_norm_rows<__half, false>(args, problem.x, problem.norm_weight, problem.norm_out, problem.x_rows,
+                                          problem.k, problem.norm_epsilon);
+    if (int status = check_launch(args)) return status;
+    problem.x = problem.norm_out;
+    problem.norm_weight = nullptr;
+    problem.norm_out = nullptr;
+  }
 
   // 64 rows and more: the tensor-memory GEMM
   if (problem.m >= tensor_core_min_rows() && problem.x_rows == problem.m) {

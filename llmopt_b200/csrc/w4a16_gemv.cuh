@@ -34,6 +34,12 @@ struct GemvProblem {
   uint32_t has_aux;
   uint32_t tag;        // kEpiTagged: lib/epilogue.ml variant index (0..9)
   uint32_t k_warps;    // warps that split K for one 16-column tile (1,2,4,8)
+  // Folded RMS norm: x holds the RAW rows; the kernel normalises them with norm_weight while it
+  // stages the activations and writes the normalised rows to norm_out (null: no folded norm).
+  const __half* norm_weight;
+  __half* norm_out;
+  float norm_epsilon;
+  uint32_t norm_weight_first;
 };
 
 // Host entry: validates alignment, picks the tile shape and launches on `stream`.

@@ -220,10 +220,49 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
     // activations -> shared in MMA fragment order: unit ((g*2 + h)*x_rows + row)*4 + c holds
     // x[row][64g + 16c + 8h + {0,4,1,5,2,6,3,7}]
     const uint32_t units = groups * 2 * p.x_rows * 4;
+    // A folded RMS norm: warp w owns row w (at most 8 rows here) and leaves 1 / rms in shared memory.
+    float* inverse_rms = reinterpret_cast<float*>(reduce);  // free until the first tile is reduced
+    if (p.norm_weight != nullptr) {
+      if (warp < p.x_rows) {
+        float squares = 0.0f;
+        for (uint32_t i = lane * 8u; i < p.k; i += 256u) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(p.x + (size_t)warp * p.k + i);
+          const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 pair = __half22float2(*reinterpret_cast<const __half2*>(&words[j]));
+            squares = fmaf(pair.x, pair.x, squares);
+            squares = fmaf(pair.y, pair.y, squares);
+          }
+        }
+        squares = warp_sum(squares);
+        if (lane == 0) inverse_rms[warp] = rsqrtf(squares / (float)p.k + p.norm_epsilon);
+      }
+      consumer_barrier();
+    }
     for (uint32_t unit = threadIdx.x; unit < units; unit += kConsumerWarps * 32) {
       const uint32_t cc = unit & 3u, row = (unit >> 2) % p.x_rows, gh = (unit >> 2) / p.x_rows;
-      const uint4 source =
-          *reinterpret_cast<const uint4*>(p.x + (size_t)row * p.k + (gh >> 1) * 64 + cc * 16 + (gh & 1u) * 8);
+      const uint32_t k_at = (gh >> 1) * 64 + cc * 16 + (gh & 1u) * 8;
+      uint4 source = *reinterpret_cast<const uint4*>(p.x + (size_t)row * p.k + k_at);
+      if (p.norm_weight != nullptr) {
+        // half((x inv) w) or half((x w) inv), exactly what the stand-alone norm kernels round to
+        const uint4 weights = *reinterpret_cast<const uint4*>(p.norm_weight + k_at);
+        const float inverse = inverse_rms[row];
+        const uint32_t x_words[4] = {source.x, source.y, source.z, source.w};
+        const uint32_t w_words[4] = {weights.x, weights.y, weights.z, weights.w};
+        uint32_t y_words[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&x_words[j]));
+          const float2 w = __half22float2(*reinterpret_cast<const __half2*>(&w_words[j]));
+          const __half2 y = p.norm_weight_first ? __floats2half2_rn((x.x * w.x) * inverse, (x.y * w.y) * inverse)
+                                                : __floats2half2_rn((x.x * inverse) * w.x, (x.y * inverse) * w.y);
+          y_words[j] = *reinterpret_cast<const uint32_t*>(&y);
+        }
+        source = make_uint4(y_words[0], y_words[1], y_words[2], y_words[3]);
+        if (blockIdx.x == 0 && p.norm_out != nullptr)
+          *reinterpret_cast<uint4*>(p.norm_out + (size_t)row * p.k + k_at) = source;
+      }
       uint4 permuted;
       permuted.x = prmt(source.x, source.z, 0x5410u);
       permuted.y = prmt(source.x, source.z, 0x7632u);
@@ -507,6 +546,7 @@ template <int EPI, int NMAT>
 int launch_pipe_by_rows(const KernelArgs& args, const GemvProblem& p) {
   const uint32_t rows = p.x_rows;
   const bool small = (size_t)rows * p.k <= 16384 && rows <= 8 && EPI != kEpiSplitF32;
+  if (p.norm_weight != nullptr && !small) return -1;  // only the staged-activation form absorbs a norm
   if (rows <= 8) {
     if (small) return launch_pipe<1, NMAT, EPI, true>(args, p);
     return launch_pipe<1, NMAT, EPI, false>(args, p);
@@ -528,6 +568,9 @@ int launch_w4a16_gemv_pipe(const KernelArgs& args, const GemvProblem& problem, i
     if (problem.mat[i].n == 0) return -1;
   }
   if (((uintptr_t)problem.x & 15u) != 0) return -1;
+  if (problem.norm_weight != nullptr &&
+      ((((uintptr_t)problem.norm_weight | (uintptr_t)problem.norm_out) & 15u) != 0 || problem.x_rows > 8))
+    return -1;
   switch (epilogue) {
     case kEpiLinear: return launch_pipe_by_rows<kEpiLinear, 1>(args, problem);
     case kEpiQkv: return launch_pipe_by_rows<kEpiQkv, 1>(args, problem);

@@ -165,6 +165,16 @@ int lm_head_stage(const KernelArgs& args, bool input_f32, const void* input, con
   return check_launch(args);
 }
 
+// The plan builder may have folded the norm that produced this dispatch's input into it.
+void apply_fused_norm(const KernelArgs& args, GemvProblem* problem) {
+  if (args.fused_norm == nullptr) return;
+  problem->x = args.fused_norm->input;
+  problem->norm_weight = args.fused_norm->weight;
+  problem->norm_out = args.fused_norm->normalized;
+  problem->norm_epsilon = args.fused_norm->epsilon;
+  problem->norm_weight_first = args.fused_norm->weight_first;
+}
+
 bool weight_sizes_ok(const KernelArgs& args, int weight_index, int scale_index, uint32_t n, uint32_t k) {
   return args.lengths[weight_index] >= (size_t)n * (k / 2) && args.lengths[scale_index] >= (size_t)n * (k / 64) * 2;
 }
@@ -196,6 +206,7 @@ int launch_w4a16_linear(const KernelArgs& args) {
   problem.aux0 = (const __half*)args.buffers[3];
   problem.aux_row_stride = stride;
   problem.has_aux = has_bias;
+  apply_fused_norm(args, &problem);
   return launch_w4a16_gemv(args, problem, kEpiLinear, false);
 }
 
@@ -270,6 +281,7 @@ int launch_w4a16_qkv_linear(const KernelArgs& args) {
     problem.mat[i] = {(const uint8_t*)args.buffers[1 + 2 * i], (const __half*)args.buffers[2 + 2 * i], nullptr, n[i]};
     problem.out[i] = (__half*)args.buffers[7 + i];
   }
+  apply_fused_norm(args, &problem);
   return launch_w4a16_gemv(args, problem, kEpiQkv, false);
 }
 
@@ -315,6 +327,7 @@ int launch_w4a16_dual_swiglu(const KernelArgs& args) {
   problem.mat[0] = {(const uint8_t*)args.buffers[1], (const __half*)args.buffers[2], nullptr, n};
   problem.mat[1] = {(const uint8_t*)args.buffers[3], (const __half*)args.buffers[4], nullptr, n};
   problem.out[0] = (__half*)args.buffers[5];
+  apply_fused_norm(args, &problem);
   return launch_w4a16_gemv(args, problem, kEpiDualSwiglu, false);
 }
 
