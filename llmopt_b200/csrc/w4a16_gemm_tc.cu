@@ -42,21 +42,27 @@ void* context_split_scratch(Context* ctx, size_t zeroed_bytes, size_t bytes, cud
 namespace {
 
 constexpr int kBM = 128, kBN = 256, kBK = 64;
-constexpr int kLoadStages = 5, kBStages = 3;
-constexpr int kATileBytes = kBM * kBK * 2;   // 16 KiB
-constexpr int kRawTileBytes = kBN * kBK / 2;  // 8 KiB
-constexpr int kBTileBytes = kBN * kBK * 2;    // 32 KiB
+// Rings: X tiles per k-block; packed weights per GROUP of four k-blocks (128 bytes per weight row and
+// TMA request: full DRAM bursts and 96 KiB of weight stream in flight per SM, which is what keeps
+// HBM busy when the weights are read once, i.e. for decode batches); converted B tiles per k-block.
+constexpr int kAStages = 4, kRawStages = 3, kBStages = 2, kGroupBlocks = 4;
+constexpr int kATileBytes = kBM * kBK * 2;                    // 16 KiB
+constexpr int kRawTileBytes = kBN * kGroupBlocks * kBK / 2;   // 32 KiB: 256 rows x 128 bytes, 128-byte swizzle
+constexpr int kBTileBytes = kBN * kBK * 2;                    // 32 KiB
 constexpr int kConvertWarps = 8;
-constexpr int kThreadsTc = (2 + kConvertWarps) * 32;
+// X producer, MMA issuer, 8 conversion warps, 2 weight-producer warps
+constexpr int kWeightProducerWarps = 2;
+constexpr int kThreadsTc = (2 + kConvertWarps + kWeightProducerWarps) * 32;
+constexpr int kWeightProducerWarp = 2 + kConvertWarps;  // first of them
 constexpr uint32_t kTmemColumns = 256;
 constexpr uint32_t kWaitLimit = 1u << 20;
 constexpr uint32_t kSplitCounterTiles = 1u << 14;  // output tiles whose split counters fit the scratch header
 
 constexpr int kOffsetA = 0;
-constexpr int kOffsetB = kOffsetA + kLoadStages * kATileBytes;
+constexpr int kOffsetB = kOffsetA + kAStages * kATileBytes;
 constexpr int kOffsetRaw = kOffsetB + kBStages * kBTileBytes;
-constexpr int kOffsetBarriers = kOffsetRaw + kLoadStages * kRawTileBytes;
-constexpr int kBarrierCount = 2 * kLoadStages + 2 * kBStages + 1;
+constexpr int kOffsetBarriers = kOffsetRaw + kRawStages * kRawTileBytes;
+constexpr int kBarrierCount = 2 * kAStages + 2 * kRawStages + 2 * kBStages + 1;
 constexpr int kOffsetTmemHolder = kOffsetBarriers + kBarrierCount * 8;
 constexpr int kOffsetAbort = kOffsetTmemHolder + 4;
 constexpr int kOffsetLast = kOffsetAbort + 4;
@@ -66,6 +72,7 @@ enum TcEpilogue { kTcLinear = 0, kTcDualSwiglu = 1, kTcTagged = 2 };
 
 struct TcProblem {
   uint32_t m, n, k;  // n: output columns
+  const uint8_t* packed[2];
   const __half* scale[2];
   const __half* zero[2];
   __half* out;
@@ -198,8 +205,9 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   // 128-byte-swizzled tiles need 1024-byte alignment
   const uint32_t base = (smem_u32(shared_raw) + 1023u) & ~1023u;
   unsigned char* base_pointer = shared_raw + (base - smem_u32(shared_raw));
-  const uint32_t load_full = base + kOffsetBarriers, load_empty = load_full + kLoadStages * 8;
-  const uint32_t b_full = load_empty + kLoadStages * 8, b_empty = b_full + kBStages * 8;
+  const uint32_t a_full = base + kOffsetBarriers, a_empty = a_full + kAStages * 8;
+  const uint32_t raw_full = a_empty + kAStages * 8, raw_empty = raw_full + kRawStages * 8;
+  const uint32_t b_full = raw_empty + kRawStages * 8, b_empty = b_full + kBStages * 8;
   const uint32_t accumulator_full = b_empty + kBStages * 8;
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(base_pointer + kOffsetTmemHolder);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(base_pointer + kOffsetAbort);
@@ -207,15 +215,22 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
   constexpr uint32_t columns_per_tile = EPI == kTcDualSwiglu ? kBN / 2 : kBN;
   const uint32_t n0 = blockIdx.x * columns_per_tile, m0 = blockIdx.y * kBM;
-  const uint32_t all_k_blocks = p.k / kBK;
+  // this CTA's share of K: whole groups of four k-blocks (the last group of K may be short)
+  const uint32_t all_k_blocks = p.k / kBK, all_groups = (all_k_blocks + kGroupBlocks - 1u) / kGroupBlocks;
   const uint32_t split = blockIdx.z;
-  const uint32_t kb_begin = (uint32_t)((uint64_t)all_k_blocks * split / p.splits);
-  const uint32_t k_blocks = (uint32_t)((uint64_t)all_k_blocks * (split + 1u) / p.splits) - kb_begin;  // this CTA's share
+  const uint32_t group_begin = (uint32_t)((uint64_t)all_groups * split / p.splits);
+  const uint32_t group_end = (uint32_t)((uint64_t)all_groups * (split + 1u) / p.splits);
+  const uint32_t kb_begin = group_begin * kGroupBlocks;
+  const uint32_t k_blocks = min(group_end * kGroupBlocks, all_k_blocks) - kb_begin;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kLoadStages; ++s) {
-      barrier_init(load_full + s * 8, 1);   // the producer's expect_tx arrival; completes by byte count
-      barrier_init(load_empty + s * 8, 1);  // one tcgen05.commit
+    for (int s = 0; s < kAStages; ++s) {
+      barrier_init(a_full + s * 8, 1);   // the producer's expect_tx arrival; completes by byte count
+      barrier_init(a_empty + s * 8, 1);  // one tcgen05.commit
+    }
+    for (int s = 0; s < kRawStages; ++s) {
+      barrier_init(raw_full + s * 8, kWeightProducerWarps * 32);  // one arrival per producer lane, when its copies land
+      barrier_init(raw_empty + s * 8, 1);  // the commit after the group's last k-block
     }
     for (int s = 0; s < kBStages; ++s) {
       barrier_init(b_full + s * 8, kConvertWarps);  // one arrival per conversion warp
@@ -246,39 +261,67 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       uint32_t issued = 0;
-      for (uint32_t kb = 0; kb < k_blocks; ++kb) {  // kb counts this CTA's k-blocks; k_at is the absolute one
-        const uint32_t s = kb % kLoadStages, round = kb / kLoadStages, k_at = kb_begin + kb;
-        if (*abort_flag || !barrier_wait(load_empty + s * 8, (round & 1u) ^ 1u)) {
+      for (uint32_t kb = 0; kb < k_blocks; ++kb) {  // kb counts this CTA's k-blocks
+        const uint32_t s = kb % kAStages;
+        if (*abort_flag || !barrier_wait(a_empty + s * 8, ((kb / kAStages) & 1u) ^ 1u)) {
           give_up();
           break;
         }
-        barrier_expect_tx(load_full + s * 8, kATileBytes + kRawTileBytes);
-        tma_load_2d(base + kOffsetA + s * kATileBytes, &map_x, (int32_t)(k_at * kBK), (int32_t)m0, load_full + s * 8);
-        const uint32_t raw = base + kOffsetRaw + s * kRawTileBytes;
-        if (EPI == kTcDualSwiglu) {
-          tma_load_2d(raw, &map_w0, (int32_t)(k_at * (kBK / 2)), (int32_t)n0, load_full + s * 8);
-          tma_load_2d(raw + kRawTileBytes / 2, &map_w1, (int32_t)(k_at * (kBK / 2)), (int32_t)n0, load_full + s * 8);
-        } else {
-          tma_load_2d(raw, &map_w0, (int32_t)(k_at * (kBK / 2)), (int32_t)n0, load_full + s * 8);
-          tma_load_2d(raw + kRawTileBytes / 2, &map_w0, (int32_t)(k_at * (kBK / 2)), (int32_t)(n0 + kBN / 2),
-                      load_full + s * 8);
-        }
+        barrier_expect_tx(a_full + s * 8, kATileBytes);
+        tma_load_2d(base + kOffsetA + s * kATileBytes, &map_x, (int32_t)((kb_begin + kb) * kBK), (int32_t)m0, a_full + s * 8);
         issued = kb + 1;
       }
       if (*abort_flag) {
         // the copies already started must land before the shared memory goes away
-        const uint32_t first = issued > kLoadStages ? issued - kLoadStages : 0u;
-        for (uint32_t kb = first; kb < issued; ++kb)
-          barrier_wait(load_full + (kb % kLoadStages) * 8, (kb / kLoadStages) & 1u);
+        const uint32_t first = issued > kAStages ? issued - kAStages : 0u;
+        for (uint32_t kb = first; kb < issued; ++kb) barrier_wait(a_full + (kb % kAStages) * 8, (kb / kAStages) & 1u);
       }
     }
+  } else if (warp >= kWeightProducerWarp) {
+    // ------------------------------ producers of the packed weights ------------------------------
+    // 16-byte cp.async from every lane of two warps (one per 128 weight rows) instead of TMA: when the
+    // weights are read once (decode batches) they come from HBM, and a TMA unit keeps too few requests
+    // in flight for that latency (measured: ~10 GB/s per SM against ~30 needed).  The stream runs up
+    // to kRawStages groups (twelve k-blocks) ahead of the math, whatever the depth of the X ring.
+    const uint32_t half_index = warp - kWeightProducerWarp;  // rows [0,128) or [128,256) of the tile
+    const uint8_t* packed = (EPI == kTcDualSwiglu && half_index == 1u) ? p.packed[1] : p.packed[0];
+    const uint32_t first_row = EPI == kTcDualSwiglu ? n0 : n0 + half_index * (kBN / 2);
+    const uint32_t row_bytes = p.k / 2;
+    const uint32_t groups = (k_blocks + kGroupBlocks - 1u) / kGroupBlocks;
+    const uint32_t chunk = lane & 7u, row_in_pass = lane >> 3;  // 8 lanes copy one row's 128 bytes
+    uint32_t issued = 0;
+    bool ok = true;
+    for (uint32_t group = 0; group < groups; ++group) {
+      const uint32_t rs = group % kRawStages;
+      ok = !*abort_flag && barrier_wait(raw_empty + rs * 8, ((group / kRawStages) & 1u) ^ 1u);
+      if (!ok) {
+        give_up();
+        break;
+      }
+      const uint32_t stage = base + kOffsetRaw + rs * kRawTileBytes + half_index * (kRawTileBytes / 2);
+      const uint32_t byte_at = (group_begin + group) * (kGroupBlocks * kBK / 2) + chunk * 16u;
+      const uint32_t bytes = byte_at < row_bytes ? 16u : 0u;  // beyond the row end: zeros (K not a multiple of 256)
+#pragma unroll 4
+      for (uint32_t pass = 0; pass < (kBN / 2) / 4; ++pass) {
+        const uint32_t row = pass * 4u + row_in_pass;                     // row of this half tile
+        const uint32_t weight_row = min(first_row + row, p.n - 1u);        // absent rows re-read the last one
+        const uint8_t* source = packed + (size_t)weight_row * row_bytes + (bytes ? byte_at : 0u);
+        const uint32_t target = stage + row * 128u + ((chunk ^ (row & 7u)) * 16u);  // 128-byte swizzle
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(target), "l"(source), "r"(bytes) : "memory");
+      }
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(raw_full + rs * 8) : "memory");
+      issued = group + 1;
+    }
+    // the copies must have landed before this warp's shared memory can go away
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    (void)issued;
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       bool ok = true;
       for (uint32_t kb = 0; kb < k_blocks && ok; ++kb) {
-        const uint32_t s = kb % kLoadStages, t = kb % kBStages;
-        ok = !*abort_flag && barrier_wait(load_full + s * 8, (kb / kLoadStages) & 1u) &&
+        const uint32_t s = kb % kAStages, t = kb % kBStages;
+        ok = !*abort_flag && barrier_wait(a_full + s * 8, (kb / kAStages) & 1u) &&
              barrier_wait(b_full + t * 8, (kb / kBStages) & 1u);
         if (!ok) {
           give_up();
@@ -290,8 +333,11 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         for (int j = 0; j < kBK / 16; ++j)
           mma_f16(tmem_base, operand_descriptor(a_tile + j * 32), operand_descriptor(b_tile + j * 32),
                   (kb > 0 || j > 0) ? 1u : 0u);
-        mma_commit(load_empty + s * 8);
+        mma_commit(a_empty + s * 8);
         mma_commit(b_empty + t * 8);
+        // the conversions of a group's last k-block are behind these MMAs: its packed bytes are free
+        if (kb % kGroupBlocks == kGroupBlocks - 1u || kb + 1u == k_blocks)
+          mma_commit(raw_empty + ((kb / kGroupBlocks) % kRawStages) * 8);
       }
       if (ok) mma_commit(accumulator_full);
     }
@@ -309,20 +355,23 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     __half next_scale = row_present ? __ldg(scale_row + kb_begin) : __float2half(0.0f);
     __half next_zero = AFFINE && row_present ? __ldg(zero_row + kb_begin) : __float2half(0.0f);
     for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-      const uint32_t s = kb % kLoadStages, t = kb % kBStages;
+      const uint32_t t = kb % kBStages, group = kb / kGroupBlocks, quarter_of_group = kb % kGroupBlocks;
+      const uint32_t rs = group % kRawStages;
       const __half scale = next_scale, zero = next_zero;
       if (kb + 1 < k_blocks && row_present) {
         next_scale = __ldg(scale_row + kb_begin + kb + 1);
         if (AFFINE) next_zero = __ldg(zero_row + kb_begin + kb + 1);
       }
-      ok = !*abort_flag && barrier_wait(load_full + s * 8, (kb / kLoadStages) & 1u) &&
+      ok = !*abort_flag && (quarter_of_group != 0u || barrier_wait(raw_full + rs * 8, (group / kRawStages) & 1u)) &&
            barrier_wait(b_empty + t * 8, ((kb / kBStages) & 1u) ^ 1u);
       if (!ok) {
         give_up();
         break;
       }
-      const unsigned char* raw = base_pointer + kOffsetRaw + s * kRawTileBytes + row * 32u;
-      const uint4 first = *reinterpret_cast<const uint4*>(raw), second = *reinterpret_cast<const uint4*>(raw + 16);
+      // the row's 128 packed bytes of the group sit 128-byte swizzled: 16-byte chunk c at (c ^ (row & 7))
+      const unsigned char* raw = base_pointer + kOffsetRaw + rs * kRawTileBytes + row * 128u;
+      const uint4 first = *reinterpret_cast<const uint4*>(raw + (((2u * quarter_of_group) * 16u) ^ swizzle));
+      const uint4 second = *reinterpret_cast<const uint4*>(raw + (((2u * quarter_of_group + 1u) * 16u) ^ swizzle));
       const uint32_t words[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
       const __half2 scale_pair = __halves2half2(scale, __hmul(scale, __float2half(0.0625f)));
       const __half2 zero_pair = __halves2half2(zero, __hmul(zero, __float2half(16.0f)));
@@ -555,9 +604,10 @@ int run_tc(const KernelArgs& args, const CUtensorMap& map_x, const CUtensorMap& 
   const uint32_t tiles = grid.x * grid.y, sms = (uint32_t)context_sm_count(args.ctx), k_blocks = p.k / kBK;
   problem.splits = 1;
   if (tiles * 2u <= sms) {
+    const uint32_t groups = (k_blocks + kGroupBlocks - 1u) / kGroupBlocks;
     uint32_t splits = sms / tiles;
-    if (splits > k_blocks / 4u) splits = k_blocks / 4u;
-    if (splits > 32u) splits = 32u;
+    if (splits > groups / 2u) splits = groups / 2u;  // at least two groups (eight k-blocks) per split
+    if (splits > 16u) splits = 16u;
     if (splits > 1u && tiles <= kSplitCounterTiles) problem.splits = splits;
   }
   if (problem.splits > 1u) {
@@ -620,8 +670,8 @@ int launch_w4a16_gemm_tc(const KernelArgs& args, const GemvProblem& problem, int
     return -1;
   for (uint32_t i = 0; i < 2; ++i) {
     const GemvMatrix& mat = problem.mat[i < matrices ? i : 0];
-    if (!make_map(&map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, mat.packed, problem.k / 2, mat.n, problem.k / 2, kBK / 2,
-                  kBN / 2, CU_TENSOR_MAP_SWIZZLE_NONE))
+    if (!make_map(&map_w[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, mat.packed, problem.k / 2, mat.n, problem.k / 2,
+                  kGroupBlocks * kBK / 2, kBN / 2, CU_TENSOR_MAP_SWIZZLE_128B))
       return -1;
   }
   TcProblem p = {};
@@ -629,6 +679,7 @@ int launch_w4a16_gemm_tc(const KernelArgs& args, const GemvProblem& problem, int
   p.n = problem.mat[0].n;
   p.k = problem.k;
   for (uint32_t i = 0; i < 2; ++i) {
+    p.packed[i] = problem.mat[i < matrices ? i : 0].packed;
     p.scale[i] = problem.mat[i < matrices ? i : 0].scale;
     p.zero[i] = problem.mat[i < matrices ? i : 0].zero;
   }
