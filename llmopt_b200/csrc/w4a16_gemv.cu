@@ -315,6 +315,12 @@ int launch_w4a16_gemv(const KernelArgs& args, GemvProblem problem, int epilogue,
     problem.norm_out = nullptr;
   }
 
+  // decode batches (9..64 rows): weights as the M side of the tensor-core product, bound by HBM
+  if (!affine) {
+    const int status = launch_w4a16_gemm_tc_batch(args, problem, epilogue);
+    if (status >= 0) return status;
+  }
+
   // 64 rows and more: the tensor-memory GEMM
   if (problem.m >= tensor_core_min_rows() && problem.x_rows == problem.m) {
     const int status = launch_w4a16_gemm_tc(args, problem, epilogue, affine);

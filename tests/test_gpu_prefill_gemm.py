@@ -78,3 +78,46 @@ def test_prefill_swiglu_ffn_matches_oracle(runtime, oracle, m, k, n):
         down_scale=_tensor(runtime, down[1]), norm_weight=_tensor(runtime, norm), output=out, reference_guards=False)
     want, _, _ = oracle.w4a16_swiglu_ffn(activation, residual, gate[0], gate[1], up[0], up[1], down[0], down[1], norm, 1e-5)
     assert_close_f16(out.buffer.to_numpy(np.float16, (m, k)), want, rel=3e-3, label="prefill swiglu ffn")
+
+
+# ---- decode batches (33..64 rows by default): the tensor-core kernel with the weights on the M side ----
+
+@pytest.mark.parametrize("m,k,n", [(33, 128, 128), (36, 64, 40), (40, 1024, 384), (33, 576, 192), (48, 2048, 1000),
+                                   (64, 4096, 512), (56, 14336, 256)])
+def test_decode_batch_linear_matches_oracle(runtime, oracle, m, k, n):
+    rng = np.random.default_rng(40)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    packed, scale = random_w4(rng, n, k)
+    residual = rng.standard_normal((m, n)).astype(np.float16)
+    assert_close_f16(_linear(runtime, x, packed, scale), oracle.w4a16_linear(x, packed, scale),
+                     label=f"decode batch linear m={m} k={k} n={n}")
+    assert_close_f16(_linear(runtime, x, packed, scale, residual, n), oracle.w4a16_linear(x, packed, scale, residual, n),
+                     label=f"decode batch linear + residual m={m} k={k} n={n}")
+
+
+def test_decode_batch_dyadic_inputs_are_bit_exact(runtime, oracle):
+    rng = np.random.default_rng(41)
+    m, k, n = 40, 4096, 256  # few tiles, long K: the K-split path with its split-ordered sum
+    x = (rng.integers(-8, 9, size=(m, k)) / 8.0).astype(np.float16)
+    packed, _ = random_w4(rng, n, k)
+    scale = (2.0 ** rng.integers(-6, -2, size=(n, k // 64))).astype(np.float16)
+    got = _linear(runtime, x, packed, scale)
+    assert np.array_equal(got.view(np.uint16), oracle.w4a16_linear(x, packed, scale).view(np.uint16))
+
+
+@pytest.mark.parametrize("m,k,n", [(33, 256, 256), (48, 576, 1536), (40, 1024, 192)])
+def test_decode_batch_swiglu_ffn_matches_oracle(runtime, oracle, m, k, n):
+    from llmopt_b200 import dispatch
+
+    rng = np.random.default_rng(42)
+    activation = rng.standard_normal((m, k)).astype(np.float16)
+    gate, up, down = random_w4(rng, n, k), random_w4(rng, n, k), random_w4(rng, k, n)
+    norm = rng.uniform(0.5, 1.5, size=k).astype(np.float16)
+    out = _tensor(runtime, np.full((m, k), np.nan, np.float16))
+    dispatch.dispatch_w4a16_swiglu_ffn_command(
+        _ctx(runtime), m=m, n=n, k=k, epsilon=1e-5, activation=_tensor(runtime, activation),
+        residual=_tensor(runtime, activation), gate_weight=_tensor(runtime, gate[0]), gate_scale=_tensor(runtime, gate[1]),
+        up_weight=_tensor(runtime, up[0]), up_scale=_tensor(runtime, up[1]), down_weight=_tensor(runtime, down[0]),
+        down_scale=_tensor(runtime, down[1]), norm_weight=_tensor(runtime, norm), output=out, reference_guards=False)
+    want, _, _ = oracle.w4a16_swiglu_ffn(activation, activation, gate[0], gate[1], up[0], up[1], down[0], down[1], norm, 1e-5)
+    assert_close_f16(out.buffer.to_numpy(np.float16, (m, k)), want, rel=3e-3, label="decode batch swiglu ffn")
