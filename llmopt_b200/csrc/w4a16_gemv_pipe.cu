@@ -95,8 +95,19 @@ __device__ __forceinline__ void nibbles_biased(uint32_t word, uint32_t& even_pai
   odd_pair = lop3_and_xor(word, 0x00F000F0u, 0x54805480u);
 }
 
+// The LM-head form (fp32 candidates, tens of tiles per CTA, light epilogue) gains from a fourth
+// resident CTA per SM (more warps to hide the LOP3 -> MMA latency: 109 -> 87 us at 128256 x 4096);
+// the projections, with two or three tiles per CTA, do not.
+// With one batch tile a single warp can finish a tile's reduction quickly enough that the others
+// need not wait for it (see the end of the tile loop); wider accumulators keep the CTA-wide form,
+// and so does the LM-head form, whose tiles are shorter than its ring (the warps that ran ahead
+// would only spin on the reducer).
+template <int NT, int EPI> constexpr bool kLazyReduce = NT == 1 && EPI != kEpiSplitF32;
+
+template <int NT, int EPI> constexpr int kDenseResidency = NT == 1 ? (EPI == kEpiSplitF32 ? 4 : 3) : 1;
+
 template <int NT, int NMAT, int EPI, bool SMALLX, int GPW>
-__global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvProblem p, const uint32_t stage_count,
+__global__ void __launch_bounds__(kThreads, kDenseResidency<NT, EPI>) w4a16_gemv_pipe_kernel(const GemvProblem p, const uint32_t stage_count,
                                                                    uint32_t* error_word) {
   extern __shared__ __align__(16) unsigned char shared[];
   // The next kernel of the stream may start its launch now; the producer warp below
@@ -108,9 +119,11 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
   constexpr int kStageWeights = Stage<GPW>::kWeights, kScaleRow = Stage<GPW>::kScaleRow;
   constexpr int kStageBytes = Stage<GPW>::kBytes;
   const uint32_t groups = p.k >> 6;
-  // [full barriers | empty barriers] [ring] [reduce] [x fragments] [x bias]
+  // [full barriers | empty barriers | reduction words] [ring] [reduce] [x fragments] [x bias]
   uint64_t* barriers = reinterpret_cast<uint64_t*>(shared);
-  unsigned char* stages = shared + ((stage_count * 16u + 15u) & ~15u);
+  // two words after the barriers: arrivals at the current tile's reduction, tiles reduced so far
+  volatile uint32_t* reduce_sync = reinterpret_cast<volatile uint32_t*>(shared + stage_count * 16u);
+  unsigned char* stages = shared + stage_count * 16u + 16u;
   float* reduce = reinterpret_cast<float*>(stages + stage_count * (NMAT * kStageBytes));  // [8][kAcc][32]
   uint4* x_fragments = reinterpret_cast<uint4*>(reduce + kConsumerWarps * kAcc * 32);     // [groups][2][x_rows][4]
   float* x_bias = reinterpret_cast<float*>(x_fragments + (SMALLX ? groups * 2 * p.x_rows * 4 + 1 : 0));
@@ -148,6 +161,8 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
       mbarrier_init(empty_base + s * 8u, kConsumerWarps);   // one arrival per consumer warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    reduce_sync[0] = 0u;
+    reduce_sync[1] = 0u;
   }
   __syncthreads();
 
@@ -220,6 +235,7 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
     // activations -> shared in MMA fragment order: unit ((g*2 + h)*x_rows + row)*4 + c holds
     // x[row][64g + 16c + 8h + {0,4,1,5,2,6,3,7}]
     const uint32_t units = groups * 2 * p.x_rows * 4;
+    const bool single_row = p.x_rows == 1u;
     // A folded RMS norm: warp w owns row w (at most 8 rows here) and leaves 1 / rms in shared memory.
     float* inverse_rms = reinterpret_cast<float*>(reduce);  // free until the first tile is reduced
     if (p.norm_weight != nullptr) {
@@ -269,11 +285,26 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
       permuted.z = prmt(source.y, source.w, 0x5410u);
       permuted.w = prmt(source.y, source.w, 0x7632u);
       x_fragments[unit] = permuted;
+      if (single_row) {
+        // one row: the eight units of a group sit in eight neighbouring lanes, so the group's
+        // bias term is a fixed-order butterfly over them and needs no second pass
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&source.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&source.y));
+        const float2 c2 = __half22float2(*reinterpret_cast<const __half2*>(&source.z));
+        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&source.w));
+        float even = (a.x + b.x) + (c2.x + d.x), odd = (a.y + b.y) + (c2.y + d.y);
+#pragma unroll
+        for (int step = 1; step < 8; step <<= 1) {
+          even += __shfl_xor_sync(0xffffffffu, even, step);
+          odd += __shfl_xor_sync(0xffffffffu, odd, step);
+        }
+        if ((unit & 7u) == 0u) x_bias[unit >> 3] = 1032.0f * even + 72.0f * odd;
+      }
     }
-    consumer_barrier();
-    // per (row, group): 1032 * sum of the even-k activations + 72 * sum of the odd-k ones, read
-    // back from the fragment units (words x, z hold even k, words y, w odd k), fixed order
-    for (uint32_t index = threadIdx.x; index < p.x_rows * groups; index += kConsumerWarps * 32) {
+    if (!single_row) consumer_barrier();
+    // several rows: per (row, group) 1032 * sum of the even-k activations + 72 * sum of the odd-k
+    // ones, read back from the fragment units (words x, z hold even k, words y, w odd k), fixed order
+    for (uint32_t index = threadIdx.x; !single_row && index < p.x_rows * groups; index += kConsumerWarps * 32) {
       const uint32_t row = index / groups, g = index - row * groups;
       float even = 0.0f, odd = 0.0f;
 #pragma unroll
@@ -433,23 +464,78 @@ __global__ void __launch_bounds__(kThreads) w4a16_gemv_pipe_kernel(const GemvPro
     }
 
     // tile finished: fixed-order sum of the eight warps' partials, then the writeback
-    consumer_barrier();  // the previous tile's reader is done with the buffer
+    uint32_t matrix, local_tile;
+    locate(blockIdx.x + slot * gridDim.x, matrix, local_tile);
+    const uint32_t n = p.mat[EPI == kEpiQkv ? matrix : 0].n;
+    if (kLazyReduce<NT, EPI>) {
+      // No CTA-wide barrier: every warp leaves its partials and goes on with the next tile; the
+      // warp that arrives last adds them (warp order, so the sum does not depend on who that is)
+      // and writes the tile.  The buffer is reused once the previous tile's reader has announced
+      // that it is done, which the ring's depth all but guarantees; the check is a bounded spin.
+      if (slot > 0 && !aborted) {
+        uint32_t spin = 0;
+        while (reduce_sync[1] < slot && ++spin < kSpinLimit) {
+        }
+        if (spin >= kSpinLimit) {
+          atomicExch(error_word, 1u);
+          aborted = true;
+        }
+      }
 #pragma unroll
-    for (int a = 0; a < NMAT; ++a)
-#pragma unroll
-      for (int t = 0; t < NT; ++t)
+      for (int a = 0; a < NMAT; ++a)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          reduce[(warp * kAcc + (a * NT + t) * 4 + j) * 32 + lane] = acc[a][t][j];
-          acc[a][t][j] = 0.0f;
+          reduce[(warp * kAcc + a * 4 + j) * 32 + lane] = acc[a][0][j];
+          acc[a][0][j] = 0.0f;
         }
-    consumer_barrier();
-    // every consumer thread finishes some accumulator positions: fixed-order sum over the
-    // eight warps' partials, then the writeback of that position
-    {
-      uint32_t matrix, local_tile;
-      locate(blockIdx.x + slot * gridDim.x, matrix, local_tile);
-      const uint32_t n = p.mat[EPI == kEpiQkv ? matrix : 0].n;
+      __threadfence_block();
+      __syncwarp();
+      uint32_t arrived = 0;
+      if (lane == 0) arrived = atomicAdd(const_cast<uint32_t*>(reduce_sync), 1u);
+      arrived = __shfl_sync(0xffffffffu, arrived, 0);
+      if (arrived == kConsumerWarps - 1) {
+        __threadfence_block();
+#pragma unroll 1
+        for (uint32_t j = 0; j < 4; ++j) {
+          // positions whose batch row does not exist are not summed at all
+          const bool wanted = EPI == kEpiSplitF32 ? c < 2u : 2u * c + (j & 1u) < p.m;
+          if (!wanted) continue;
+          float value[NMAT];
+#pragma unroll
+          for (int a = 0; a < NMAT; ++a) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) sum += reduce[(w * kAcc + a * 4 + j) * 32 + lane];
+            value[a] = sum;
+          }
+          float partner = 0.0f;
+          if (EPI == kEpiSplitF32) {
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) partner += reduce[(w * kAcc + j) * 32 + (lane ^ 2u)];
+          }
+          write_position<NT, NMAT, EPI>(p, value, partner, matrix, local_tile, n, 0u, j, lane);
+        }
+        __syncwarp();
+        if (lane == 0) {
+          reduce_sync[0] = 0u;
+          __threadfence_block();
+          reduce_sync[1] = slot + 1u;
+        }
+      }
+    } else {
+      consumer_barrier();  // the previous tile's reader is done with the buffer
+#pragma unroll
+      for (int a = 0; a < NMAT; ++a)
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            reduce[(warp * kAcc + (a * NT + t) * 4 + j) * 32 + lane] = acc[a][t][j];
+            acc[a][t][j] = 0.0f;
+          }
+      consumer_barrier();
+      // every consumer thread finishes some accumulator positions: fixed-order sum over the
+      // eight warps' partials, then the writeback of that position
       for (uint32_t position = threadIdx.x; position < NT * 4 * 32; position += kConsumerWarps * 32) {
         const uint32_t tj = position >> 5, position_lane = position & 31u;
         float value[NMAT];
@@ -480,8 +566,8 @@ struct PipePlan {
 
 // Ring depth and grid: consumer warps are the scarce resource (the math is a chain of
 // dependent instructions per group), bytes in flight the second: take the most
-// resident CTAs per SM (up to 3) whose ring still holds at least three stages, and one
-// CTA per slot.
+// resident CTAs per SM (up to 3; 4 for the LM-head form) whose ring still holds at least three
+// stages (two at 4 CTAs), and one CTA per slot.
 template <int NT, int NMAT, int EPI, bool SMALLX, int GPW>
 bool plan_pipe(const KernelArgs& args, const GemvProblem& p, PipePlan* plan) {
   uint32_t total_tiles = 0;
@@ -494,11 +580,13 @@ bool plan_pipe(const KernelArgs& args, const GemvProblem& p, PipePlan* plan) {
   const uint32_t sms = (uint32_t)context_sm_count(args.ctx);
   constexpr size_t kSharedPerSm = 220 * 1024;  // usable shared memory of one SM
   const uint32_t chunks_per_tile = p.k / Stage<GPW>::kChunkK;
-  for (uint32_t resident = 3; resident >= 1; --resident) {
+  // a fourth resident CTA only where the kernel was compiled for it and every CTA still gets four tiles
+  const uint32_t most = kDenseResidency<NT, EPI> == 4 && total_tiles >= 16u * sms ? 4u : 3u;
+  for (uint32_t resident = most; resident >= 1; --resident) {
     const size_t per_cta = kSharedPerSm / resident - 1024;
     if (per_cta <= fixed_bytes + 2 * stage_bytes) continue;
     uint32_t stages = (uint32_t)((per_cta - fixed_bytes) / stage_bytes);
-    if (stages < 3 && resident > 1) continue;
+    if (stages < (resident == 4 ? 2u : 3u) && resident > 1) continue;
     const uint32_t slots = sms * resident;
     const uint32_t ctas = total_tiles < slots ? total_tiles : slots;
     const uint32_t chunks = ((total_tiles + ctas - 1u) / ctas) * chunks_per_tile;
