@@ -30,6 +30,7 @@
 // tiles of the split round-robin and keep private (max, denominator, O^T);
 // the CTA merges its warps in shared memory and writes one record to scratch;
 // paged_merge_kernel merges the records of all splits and the current token.
+#include <cstdlib>
 #include "q8_attention.cuh"
 
 namespace llmopt {
@@ -533,6 +534,13 @@ uint32_t paged_pick_splits(const KernelArgs& args, const PagedParams& p) {
   uint32_t limit = args.past_tokens_cell ? kMaxAttentionSplits : (p.past_length + 63u) / 64u;
   if (limit > kMaxAttentionSplits) limit = kMaxAttentionSplits;
   if (limit == 0) return 1;
+  // LLMOPT_CUDA_ATTENTION_SPLITS pins the count (within the limit), for tuning
+  static const uint32_t pinned = []() -> uint32_t {
+    const char* text = getenv("LLMOPT_CUDA_ATTENTION_SPLITS");
+    const long value = text ? strtol(text, nullptr, 10) : 0;
+    return value > 0 ? (uint32_t)value : 0u;
+  }();
+  if (pinned != 0u) return pinned < limit ? pinned : limit;
   const uint32_t fill_target = (resident * 85u + 99u) / 100u;
   const uint32_t first = (fill_target + pairs - 1u) / pairs;
   if (first >= limit) return limit;
