@@ -93,6 +93,58 @@ __global__ void pack_attention_pair_kernel(const __half* __restrict__ key_source
                  scales + p.value_segment_offset / p.group_size + local_group, lane);
 }
 
+struct RotaryQkParams {  // lib/metal_normalization_source.ml:760-763
+  uint32_t batches, tokens, q_heads, k_heads, width, half_dimension, trig_batches;
+};
+
+// One decode token per sequence: the rotary embedding of Q and K (llmopt_rotary_qk_f16_simd_h64,
+// lib/metal_normalization_source.ml:765-802) and the Q8 pack of the rotated K row and the V row
+// into the new cache slot (llmopt_cache_pack_attention_q8_pair_simd) as one launch; a prebaked
+// plan takes it when the two records are adjacent and the pack reads what the rotary wrote.
+// One warp per head row; every lane quantises the columns it rotated itself, with the same
+// half-precision operation sequence and the same codec as the two kernels, so all bytes are equal.
+__global__ void rotary_pack_kernel(const __half* __restrict__ q_input, const __half* __restrict__ k_input,
+                                   const __half* __restrict__ v_input, const __half* __restrict__ cosine,
+                                   const __half* __restrict__ sine, __half* __restrict__ q_output, __half* k_output,
+                                   const uint32_t* __restrict__ slots, uint8_t* __restrict__ pool, RotaryQkParams r,
+                                   AttentionCachePairParams c) {
+  grid_chain_prologue();
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t q_rows = r.batches * r.q_heads, k_rows = r.batches * r.k_heads;
+  if (row >= q_rows + 2u * k_rows) return;
+  const bool is_q = row < q_rows, is_v = row >= q_rows + k_rows;
+  const uint32_t local_row = is_q ? row : (is_v ? row - q_rows - k_rows : row - q_rows);
+  const uint32_t heads = is_q ? r.q_heads : r.k_heads;
+  const uint32_t batch = local_row / heads, head = local_row % heads;
+  const size_t base = (size_t)local_row * r.width;  // one token: token-first and head-major rows coincide
+  if (!is_v) {
+    const __half* input = is_q ? q_input : k_input;
+    __half* output = is_q ? q_output : k_output;
+    const size_t trig_base = (size_t)(r.trig_batches == 1 ? 0 : batch) * r.width;
+    for (uint32_t col = lane; col < r.width; col += 32) {
+      const uint32_t rotated_col = col < r.half_dimension ? col + r.half_dimension : col - r.half_dimension;
+      __half rotated = input[base + rotated_col];
+      if (col < r.half_dimension) rotated = __hneg(rotated);
+      const __half direct = __hmul_rn(input[base + col], cosine[trig_base + col]);
+      const __half turned = __hmul_rn(rotated, sine[trig_base + col]);
+      output[base + col] = __hadd_rn(direct, turned);
+    }
+    if (is_q) return;
+    __syncwarp();
+  }
+  const __half* source = is_v ? v_input + base : k_output + base;
+  const size_t slot_base = (size_t)slots[batch] * c.token_stride;
+  int8_t* values = reinterpret_cast<int8_t*>(pool + slot_base);
+  __half* scales = reinterpret_cast<__half*>(pool + slot_base + c.token_elements);
+  const uint32_t segment = is_v ? c.value_segment_offset : c.key_segment_offset;
+  for (uint32_t group = 0; group < r.width / c.group_size; ++group) {
+    const uint32_t local = head * r.width + group * c.group_size;
+    quantize_group(source + group * c.group_size, c.group_size, values + segment + local,
+                   scales + (segment + local) / c.group_size, lane);
+  }
+}
+
 __global__ void unpack_attention_kernel(const uint8_t* __restrict__ pool, const uint32_t* __restrict__ slots,
                                         __half* __restrict__ destination, AttentionCacheParams p) {
   grid_chain_prologue();
@@ -185,6 +237,35 @@ int launch_cache_pack_attention_q8_pair(const KernelArgs& args) {
       (const __half*)args.buffers[0], (const __half*)args.buffers[1], (const uint32_t*)args.buffers[2],
       (uint8_t*)args.buffers[3], p);
   return check_launch(args);
+}
+
+// The fused form of a rotary record followed by the pair-pack record of the same token.  Returns -1
+// when the two do not fit it (the caller then runs them one after the other), 0 on success, 1 on a
+// launch failure.  rotary: [q_in, k_in, cosine, sine, q_out, k_out]; pack: [key, value, slots, pool].
+int launch_rotary_pack_fused(const KernelArgs& rotary, const KernelArgs& pack) {
+  RotaryQkParams r;
+  AttentionCachePairParams c;
+  if (rotary.buffer_count != 6 || rotary.param_bytes != sizeof(r) || pack.buffer_count != 4 || !read_params(pack, &c))
+    return -1;
+  memcpy(&r, rotary.params, sizeof(r));
+  if (r.tokens != 1 || r.width == 0 || r.half_dimension * 2 > r.width || r.batches == 0 || r.k_heads == 0) return -1;
+  if (pack.buffers[0] != rotary.buffers[5] || c.items != r.batches || c.source_items != c.items || c.source_offset != 0)
+    return -1;
+  if (c.group_size == 0 || r.width % c.group_size != 0 || !valid_geometry(c.head_dim, c.group_size)) return -1;
+  if ((size_t)c.heads * c.head_dim != (size_t)r.k_heads * r.width || (c.heads != 1 && c.items != 1)) return -1;
+  if ((c.key_segment_offset | c.value_segment_offset) % c.group_size != 0) return -1;
+  const size_t q_bytes = (size_t)r.batches * r.q_heads * r.width * 2, k_bytes = (size_t)r.batches * r.k_heads * r.width * 2;
+  const size_t trig_bytes = (size_t)(r.trig_batches == 1 ? 1 : r.batches) * r.width * 2;
+  if (rotary.lengths[0] < q_bytes || rotary.lengths[4] < q_bytes || rotary.lengths[1] < k_bytes ||
+      rotary.lengths[5] < k_bytes || rotary.lengths[2] < trig_bytes || rotary.lengths[3] < trig_bytes ||
+      pack.lengths[1] < k_bytes || pack.lengths[2] < (size_t)c.items * 4)
+    return -1;
+  const uint32_t rows = r.batches * (r.q_heads + 2u * r.k_heads);
+  launch_kernel(rotary, rotary_pack_kernel, dim3((rows + 7) / 8), dim3(256), 0, (const __half*)rotary.buffers[0],
+                (const __half*)rotary.buffers[1], (const __half*)pack.buffers[1], (const __half*)rotary.buffers[2],
+                (const __half*)rotary.buffers[3], (__half*)rotary.buffers[4], (__half*)rotary.buffers[5],
+                (const uint32_t*)pack.buffers[2], (uint8_t*)pack.buffers[3], r, c);
+  return check_launch(rotary);
 }
 
 // Buffers: [pool, slots, destination]; params 40 bytes.

@@ -57,6 +57,7 @@ int launch_short_conv_step(const KernelArgs&);
 int launch_short_conv_prefill(const KernelArgs&);
 template <bool INPUT_F32> int launch_rms_norm(const KernelArgs&);
 int launch_rotary_qk(const KernelArgs&);
+int launch_rotary_pack_fused(const KernelArgs& rotary, const KernelArgs& pack);
 int launch_embedding_f16(const KernelArgs&);
 int launch_chain_token_id(const KernelArgs&);
 int launch_chain_token_ids(const KernelArgs&);
@@ -426,15 +427,9 @@ static bool fold_norm(const OwnedRecord& norm, const OwnedRecord& product, Fused
   return true;
 }
 
-static int run_record(Context* context, const OwnedRecord& record, const uint32_t* past_cell,
-                      const uint32_t* checkpoint_cell, const FusedNorm* fused_norm = nullptr) {
-  if (record.is_copy) {
-    CUDA_TRY(cudaMemcpyAsync(record.buffers[1]->pointer(), record.buffers[0]->pointer(), record.buffers[0]->length,
-                             cudaMemcpyDeviceToDevice, context->stream),
-             "CUDA batch copy failed");
-    return LLMOPT_CUDA_OK;
-  }
-  KernelArgs args = {};
+static void fill_args(Context* context, const OwnedRecord& record, const uint32_t* past_cell,
+                      const uint32_t* checkpoint_cell, KernelArgs* out) {
+  KernelArgs& args = *out;
   args.ctx = context;
   args.stream = context->stream;
   args.buffer_count = (int)record.buffers.size();
@@ -451,11 +446,40 @@ static int run_record(Context* context, const OwnedRecord& record, const uint32_
   args.name = record.name.c_str();
   args.past_tokens_cell = is_paged_attention_name(args.name) && record.params.size() >= 16 ? past_cell : nullptr;
   args.checkpoint_cell = is_checkpoint_pack_name(args.name) && record.params.size() >= 4 ? checkpoint_cell : nullptr;
+}
+
+static int run_record(Context* context, const OwnedRecord& record, const uint32_t* past_cell,
+                      const uint32_t* checkpoint_cell, const FusedNorm* fused_norm = nullptr) {
+  if (record.is_copy) {
+    CUDA_TRY(cudaMemcpyAsync(record.buffers[1]->pointer(), record.buffers[0]->pointer(), record.buffers[0]->length,
+                             cudaMemcpyDeviceToDevice, context->stream),
+             "CUDA batch copy failed");
+    return LLMOPT_CUDA_OK;
+  }
+  KernelArgs args = {};
+  fill_args(context, record, past_cell, checkpoint_cell, &args);
   args.fused_norm = fused_norm;
   std::string message;
   args.error = &message;
   if (record.launcher(args) != 0) return set_error(LLMOPT_CUDA_FAILURE, message);
   return LLMOPT_CUDA_OK;
+}
+
+// Plan-capture peephole: a rotary record directly followed by the pair-pack record of the same
+// decode token runs as one kernel.  Returns -1 when the pair does not fit the fused form.
+static int run_rotary_pack(Context* context, const OwnedRecord& rotary, const OwnedRecord& pack) {
+  if (rotary.is_copy || pack.is_copy || rotary.name != "llmopt_rotary_qk_f16_simd_h64" ||
+      pack.name != "llmopt_cache_pack_attention_q8_pair_simd")
+    return -1;
+  KernelArgs rotary_args = {}, pack_args = {};
+  fill_args(context, rotary, nullptr, nullptr, &rotary_args);
+  fill_args(context, pack, nullptr, nullptr, &pack_args);
+  std::string message;
+  rotary_args.error = &message;
+  pack_args.error = &message;
+  const int status = launch_rotary_pack_fused(rotary_args, pack_args);
+  if (status > 0) return set_error(LLMOPT_CUDA_FAILURE, message);
+  return status < 0 ? -1 : LLMOPT_CUDA_OK;
 }
 
 static int wait_stream(Context* context, const char* what) {
@@ -1053,8 +1077,18 @@ int llmopt_cuda_prebaked_create_bound(llmopt_cuda_library* library, const llmopt
       plan->cells, plan->token_buffer ? (long long*)plan->token_buffer->pointer() : nullptr, device_bindings);
   int failure = LLMOPT_CUDA_OK;
   const bool fold = getenv("LLMOPT_CUDA_FOLD_NORMS") == nullptr || getenv("LLMOPT_CUDA_FOLD_NORMS")[0] != '0';
+  const bool fuse_pack = getenv("LLMOPT_CUDA_FUSE_ROTARY_PACK") == nullptr || getenv("LLMOPT_CUDA_FUSE_ROTARY_PACK")[0] != '0';
   for (size_t index = 0; index < plan->records.size(); ++index) {
     FusedNorm fused;
+    if (fuse_pack && index + 1 < plan->records.size()) {
+      const int fused_status = run_rotary_pack(context, plan->records[index], plan->records[index + 1]);
+      if (fused_status >= 0) {
+        failure = fused_status;
+        ++index;
+        if (failure != LLMOPT_CUDA_OK) break;
+        continue;
+      }
+    }
     if (fold && index + 1 < plan->records.size() && fold_norm(plan->records[index], plan->records[index + 1], &fused)) {
       failure = run_record(context, plan->records[index + 1], &plan->cells->past_tokens, &plan->cells->checkpoint, &fused);
       ++index;

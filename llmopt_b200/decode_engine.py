@@ -167,6 +167,19 @@ class DecodeEngine:
                     token_elements=self.layout.token_elements, key_offset=region.key_offset,
                     value_offset=region.value_offset, group_size=self.layout.group_size,
                     token_stride=self.layout.bytes_per_token, scale=float(np.float32(1.0 / math.sqrt(dim))))
+                # Q8 pack of the new token: one item per sequence; a sequence's K (or V)
+                # row is kv_heads * D contiguous halves, packed as one "head" of that width
+                # (recorded before the attention, which reads only the slots of the past tokens and takes the
+                # new token from k_rot / v: a plan runs the rotary and this pack as one kernel)
+                pack = parameters.cache_attention_pair(
+                    items=batch, key_segment_offset=region.key_offset, value_segment_offset=region.value_offset,
+                    heads=1, head_dim=config.kv_heads * dim, group_size=self.layout.group_size,
+                    token_elements=self.layout.token_elements, token_groups=self.layout.token_groups,
+                    token_stride=self.layout.bytes_per_token, source_items=batch, source_offset=0)
+                groups = batch * config.kv_heads * dim // self.layout.group_size
+                run("llmopt_cache_pack_attention_q8_pair_simd",
+                    [self.k_rot.buffer, self.v.buffer, self.new_slots.buffer, self.cache.token_pool], pack,
+                    (dispatch.round_up(groups, 8) * 32, 1, 1))
                 value_now = dispatch.Tensor(self.v.buffer, (batch, config.kv_heads, 1, dim))
                 attended = dispatch.Tensor(self.attended.buffer, (batch, 1, config.query_heads, dim))
                 if batch == 1:
@@ -179,17 +192,6 @@ class DecodeEngine:
                         context, config=paged, query=self.q_rot, current_key=self.k_rot, current_value=value_now,
                         pool=dispatch.Tensor(self.cache.token_pool, (0,), "uint8"), slots=self.slot_table,
                         output=attended, slot_batch_stride=self.capacity)
-                # Q8 pack of the new token: one item per sequence; a sequence's K (or V)
-                # row is kv_heads * D contiguous halves, packed as one "head" of that width
-                pack = parameters.cache_attention_pair(
-                    items=batch, key_segment_offset=region.key_offset, value_segment_offset=region.value_offset,
-                    heads=1, head_dim=config.kv_heads * dim, group_size=self.layout.group_size,
-                    token_elements=self.layout.token_elements, token_groups=self.layout.token_groups,
-                    token_stride=self.layout.bytes_per_token, source_items=batch, source_offset=0)
-                groups = batch * config.kv_heads * dim // self.layout.group_size
-                run("llmopt_cache_pack_attention_q8_pair_simd",
-                    [self.k_rot.buffer, self.v.buffer, self.new_slots.buffer, self.cache.token_pool], pack,
-                    (dispatch.round_up(groups, 8) * 32, 1, 1))
                 if group is None:
                     dispatch.dispatch_w4a16_linear(context, input=self.attended, weight=layer["o"][0],
                                                    scale=layer["o"][1], output=other, bias=current,

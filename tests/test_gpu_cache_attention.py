@@ -367,3 +367,57 @@ def test_buffers_batches_and_prebaked(runtime):
     assert plan.execute(token=9, past_tokens=11) == 11
     assert emb_out.to_numpy(np.float16).tolist() == [36, 37, 38, 39]
     assert plan.kernel_count() >= 2
+
+
+@pytest.mark.parametrize("batch,q_heads,k_heads,dim,group", [(1, 8, 2, 128, 64), (3, 4, 4, 64, 32), (2, 6, 2, 128, 64)])
+def test_plan_fuses_rotary_and_pair_pack_byte_for_byte(runtime, monkeypatch, batch, q_heads, k_heads, dim, group):
+    """A plan runs a rotary record followed by the pair pack of the same token as one kernel; its
+    outputs (rotated Q and K, cache bytes and scales) equal the two kernels' bit for bit."""
+    from llmopt_b200 import parameters
+    from llmopt_b200.cuda_native import Buffer, DispatchItem, Prebaked
+
+    rng = np.random.default_rng(70 + batch)
+    q = rng.standard_normal((batch, 1, q_heads, dim)).astype(np.float16)
+    k = rng.standard_normal((batch, 1, k_heads, dim)).astype(np.float16)
+    v = rng.standard_normal((batch, k_heads, 1, dim)).astype(np.float16)
+    v[0, 0, 0, :group] = 0  # an all-zero group takes the scale 1
+    angle = rng.uniform(0, 6.28, size=(1, 1, dim))
+    cos, sin = np.cos(angle).astype(np.float16), np.sin(angle).astype(np.float16)
+    segment = k_heads * dim
+    token_elements = 4 * segment  # two layers' K and V; this record packs the second layer
+    token_groups = token_elements // group
+    token_stride = token_elements + 2 * token_groups
+    capacity = 8
+    slots = np.array([5, 2, 7][:batch], np.uint32)
+
+    def run(fuse: bool):
+        monkeypatch.setenv("LLMOPT_CUDA_FUSE_ROTARY_PACK", "1" if fuse else "0")
+        pool = Buffer.of_array(runtime, np.full(capacity * token_stride, 0x55, np.uint8))
+        q_out = Buffer.of_array(runtime, np.full(q.shape, np.nan, np.float16))
+        k_out = Buffer.of_array(runtime, np.full(k.shape, np.nan, np.float16))
+        records = [
+            DispatchItem("llmopt_rotary_qk_f16_simd_h64",
+                         [Buffer.of_array(runtime, q), Buffer.of_array(runtime, k), Buffer.of_array(runtime, cos),
+                          Buffer.of_array(runtime, sin), q_out, k_out],
+                         parameters.rotary_qk(batches=batch, tokens=1, q_heads=q_heads, k_heads=k_heads, width=dim,
+                                              half_dimension=dim // 2, trig_batches=1),
+                         (32 * batch * (q_heads + k_heads), 1, 1), (256, 1, 1)),
+            DispatchItem("llmopt_cache_pack_attention_q8_pair_simd",
+                         [k_out, Buffer.of_array(runtime, v), Buffer.of_array(runtime, slots), pool],
+                         parameters.cache_attention_pair(
+                             items=batch, key_segment_offset=2 * segment, value_segment_offset=3 * segment, heads=1,
+                             head_dim=segment, group_size=group, token_elements=token_elements,
+                             token_groups=token_groups, token_stride=token_stride, source_items=batch, source_offset=0),
+                         (32 * batch * segment // group, 1, 1), (256, 1, 1)),
+        ]
+        plan = Prebaked(runtime, records, None, None)
+        plan.execute(token=0, past_tokens=0)
+        return plan.kernel_count(), q_out.to_numpy(np.float16), k_out.to_numpy(np.float16), pool.to_numpy(np.uint8)
+
+    fused_kernels, fused_q, fused_k, fused_pool = run(True)
+    plain_kernels, plain_q, plain_k, plain_pool = run(False)
+    assert fused_kernels == plain_kernels - 1
+    assert np.array_equal(fused_q.view(np.uint16), plain_q.view(np.uint16))
+    assert np.array_equal(fused_k.view(np.uint16), plain_k.view(np.uint16))
+    assert np.array_equal(fused_pool, plain_pool)
+    assert not np.array_equal(plain_pool, np.full_like(plain_pool, 0x55))
