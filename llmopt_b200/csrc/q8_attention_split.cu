@@ -424,10 +424,13 @@ paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__
 // One CTA per (batch, query head): merges the split records and the current
 // token (key position past_length, fp16, lib/metal_cache_source.ml:446-470),
 // writes half(result / denominator) token-first.  Thread s first weighs split s
-// (maxima and denominators are read side by side, not one after the other); then
-// thread d sums dimension d over the splits with the loads of several splits in flight.
+// (maxima and denominators are read side by side, not one after the other); then the
+// kMergeParts thread groups each sum dimension d over a quarter of the splits with all of
+// their loads in flight at once (the kernel is a chain of L2 latencies, not of bytes), and
+// the quarters are added in order.
+constexpr int kMergeParts = 4;
 template <int D>
-__global__ void __launch_bounds__(D)
+__global__ void __launch_bounds__(D * kMergeParts)
 paged_merge_kernel(const __half* __restrict__ query, const __half* __restrict__ current_key,
                    const __half* __restrict__ current_value, const float* __restrict__ scratch,
                    __half* __restrict__ output, PagedParams p, uint32_t splits) {
@@ -436,21 +439,33 @@ paged_merge_kernel(const __half* __restrict__ query, const __half* __restrict__ 
   static_assert(D >= (int)kMaxAttentionSplits, "one thread per split in the weighing phase");
   __shared__ float partial[3][D / 32];
   __shared__ float weights[kMaxAttentionSplits];
-  const uint32_t head = blockIdx.x, batch = blockIdx.y, d = threadIdx.x;
+  __shared__ float part_sums[kMergeParts - 1][D];
+  const uint32_t head = blockIdx.x, batch = blockIdx.y, d = threadIdx.x % D, part = threadIdx.x / D;
   const uint32_t heads_per_kv = p.query_heads / p.kv_heads;
   const uint32_t kv_head = head / heads_per_kv, local_head = head % heads_per_kv;
   const size_t query_base = ((size_t)batch * p.query_heads + head) * D;
   const size_t current_base = ((size_t)batch * p.kv_heads + kv_head) * D;
   const float* records = scratch + ((size_t)batch * p.kv_heads + kv_head) * splits * kRecord;
 
-  // issue every global load of the first phase before the first reduction
-  const float split_max = d < splits ? records[d * kRecord + local_head] : -INFINITY;
-  const float split_sum = d < splits ? records[d * kRecord + 8 + local_head] : 0.0f;
+  // this part's share of the split columns: issued first, consumed last
+  constexpr int kShare = (int)kMaxAttentionSplits / kMergeParts;
+  const uint32_t first_split = part * kShare;
+  const float* column = records + 16 + local_head * D + d;
+  float values[kShare];
+#pragma unroll
+  for (int i = 0; i < kShare; ++i)
+    values[i] = first_split + i < splits ? column[(size_t)(first_split + i) * kRecord] : 0.0f;
+
+  // the weighing phase runs on the first D threads; every global load of it is issued before
+  // the first reduction
+  const bool weigher = part == 0;
+  const float split_max = weigher && d < splits ? records[d * kRecord + local_head] : -INFINITY;
+  const float split_sum = weigher && d < splits ? records[d * kRecord + 8 + local_head] : 0.0f;
   const float current_v = __half2float(current_value[current_base + d]);
   float dot = __half2float(query[query_base + d]) * __half2float(current_key[current_base + d]);
   dot = warp_sum(dot);
   const float warp_maximum = warp_max(split_max);
-  if ((d & 31u) == 0) {
+  if (weigher && (d & 31u) == 0) {
     partial[0][d >> 5] = dot;
     partial[1][d >> 5] = warp_maximum;
   }
@@ -465,18 +480,23 @@ paged_merge_kernel(const __half* __restrict__ query, const __half* __restrict__ 
   maximum = fmaxf(maximum, current_score);
   const float current_weight = expf(current_score - maximum);
   const float weight = split_max == -INFINITY ? 0.0f : expf(split_max - maximum);
-  if (d < splits) weights[d] = weight;
+  if (weigher && d < splits) weights[d] = weight;
   const float weighted = warp_sum(weight * split_sum);
-  if ((d & 31u) == 0) partial[2][d >> 5] = weighted;
+  if (weigher && (d & 31u) == 0) partial[2][d >> 5] = weighted;
   __syncthreads();
   float denominator = current_weight;
 #pragma unroll
   for (int i = 0; i < D / 32; ++i) denominator += partial[2][i];
 
-  float result = current_weight * current_v;
-  const float* column = records + 16 + local_head * D + d;
-#pragma unroll 8
-  for (uint32_t s = 0; s < splits; ++s) result = fmaf(weights[s], column[(size_t)s * kRecord], result);
+  float result = weigher ? current_weight * current_v : 0.0f;
+#pragma unroll
+  for (int i = 0; i < kShare; ++i)
+    if (first_split + i < splits) result = fmaf(weights[first_split + i], values[i], result);
+  if (!weigher) part_sums[part - 1][d] = result;
+  __syncthreads();
+  if (!weigher) return;
+#pragma unroll
+  for (int other = 0; other < kMergeParts - 1; ++other) result += part_sums[other][d];
   const size_t output_base = ((size_t)batch * p.query_heads + head) * D;  // [b, q = 1, hq, D]
   output[output_base + d] = __float2half_rn(denominator == 0.0f ? 0.0f : result / denominator);
 }
@@ -503,7 +523,7 @@ int launch_split(const KernelArgs& args, const PagedParams& p, uint32_t slot_bat
   const int status = aligned ? launch_split_copy<D, GROUP, 16>(args, p, slot_batch_stride, scratch, splits)
                              : launch_split_copy<D, GROUP, 8>(args, p, slot_batch_stride, scratch, splits);
   if (status) return status;
-  launch_kernel(args, paged_merge_kernel<D>, dim3(p.query_heads, p.batches), dim3(D), 0,
+  launch_kernel(args, paged_merge_kernel<D>, dim3(p.query_heads, p.batches), dim3(D * kMergeParts), 0,
       (const __half*)args.buffers[0], (const __half*)args.buffers[1], (const __half*)args.buffers[2], scratch,
       (__half*)args.buffers[6], p, splits);
   return check_launch(args);
