@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, RES) w4a16_gemv_pipe_kernel(const Ge
           even += __shfl_xor_sync(0xffffffffu, even, step);
           odd += __shfl_xor_sync(0xffffffffu, odd, step);
         }
-        if ((unit & 7u) == 0u) x_bias[unit >> 3] = 1032.0f * even + 72.0f * odd;
+        if ((unit & 7u) == 0u) x_bias[unit >> 3] = -(1032.0f * even + 72.0f * odd);  // stored negated
       }
     }
     if (!single_row) consumer_barrier();
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, RES) w4a16_gemv_pipe_kernel(const Ge
           even += (e0.x + e0.y) + (e1.x + e1.y);
           odd += (o0.x + o0.y) + (o1.x + o1.y);
         }
-      x_bias[index] = 1032.0f * even + 72.0f * odd;
+      x_bias[index] = -(1032.0f * even + 72.0f * odd);
     }
     if (threadIdx.x == 0) {
       x_fragments[units] = make_uint4(0u, 0u, 0u, 0u);
@@ -381,7 +381,7 @@ __global__ void __launch_bounds__(kThreads, RES) w4a16_gemv_pipe_kernel(const Ge
             const float scale_b =
                 __half2float(*reinterpret_cast<const __half*>(base + scale_offset + jg * 2 + 8 * kScaleRow));
             // the group's bias term rides in as the accumulator's start value
-            float sum[4] = {-bias0, -bias1, -bias0, -bias1};
+            float sum[4] = {bias0, bias1, bias0, bias1};  // the table holds the negated term
             uint32_t a_even, a_odd, b_even, b_odd;
             nibbles_biased(word_a.x, a_even, a_odd);
             nibbles_biased(word_b.x, b_even, b_odd);
