@@ -251,7 +251,7 @@ def time_kernels(engine, runtime) -> dict:
 # bytes of the same launch, from the captures summarised under profiles/ (GEMV: batch 1 gate/up;
 # attention: batch 8, 8192 tokens; both grow in proportion to the units processed).
 TRAFFIC_RATIO = {
-    "gate_up_swiglu": (62_610_176 / 62_427_136, "profiles/w4a16_gemv_pipe_m1_llama3_8b.md"),
+    "gate_up_swiglu": (62_625_536 / 62_427_136, "profiles/w4a16_gemv_pipe_m1_llama3_8b.md"),
     "paged_attention_q8": (147_036_160 / 138_838_016, "profiles/paged_attention_q8_split_llama3_8b.md"),
 }
 
