@@ -150,22 +150,26 @@ struct SumNormParams {
 //                     weight_first picks (x w) inv over (x inv) w)
 // The mean of squares is taken over the ROUNDED hidden values, which is what the separate kernels
 // compute.  Rows up to 8192 wide stay in registers between the passes.
-__global__ void __launch_bounds__(256) exchange_sum_norm_kernel(Regions regions, const __half* __restrict__ residual,
+// One CTA of 1024 threads per row: a 4096-wide row is one float4 per thread, so all of a row's peer loads
+// are one round trip over NVLink (with 256 threads the four vectors of a thread were four trips in a row,
+// because the stores to `hidden` between them may alias the regions).
+constexpr int kSumNormThreads = 1024;
+__global__ void __launch_bounds__(kSumNormThreads) exchange_sum_norm_kernel(Regions regions, const __half* __restrict__ residual,
                                                                 __half* __restrict__ hidden,
                                                                 const __half* __restrict__ norm_weight,
                                                                 __half* __restrict__ normalized, SumNormParams p,
                                                                 uint32_t* error_word) {
   grid_chain_prologue();
-  __shared__ float partial[8];
+  __shared__ float partial[kSumNormThreads / 32];
   const uint32_t epoch = announce_and_wait(regions, p.ranks, p.rank, error_word);
   if (epoch != 0u) {
-    constexpr int kVectors = 8;  // float4 per thread: 256 * 8 * 4 = 8192 columns
+    constexpr int kVectors = 2;  // float4 per thread: 1024 * 2 * 4 = 8192 columns
     const uint32_t row = blockIdx.x, tid = threadIdx.x;
     float4 values[kVectors];
     float squares = 0.0f;
 #pragma unroll
     for (int v = 0; v < kVectors; ++v) {
-      const uint32_t column = (tid + v * 256u) * 4u;
+      const uint32_t column = (tid + v * (uint32_t)kSumNormThreads) * 4u;
       values[v] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       if (column >= p.width) continue;
       const size_t index = (size_t)row * p.width + column;
@@ -206,11 +210,11 @@ __global__ void __launch_bounds__(256) exchange_sum_norm_kernel(Regions regions,
     __syncthreads();
     float total = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) total += partial[i];
+    for (int i = 0; i < kSumNormThreads / 32; ++i) total += partial[i];
     const float inverse = rsqrtf(total / (float)p.width + p.epsilon);
 #pragma unroll
     for (int v = 0; v < kVectors; ++v) {
-      const uint32_t column = (tid + v * 256u) * 4u;
+      const uint32_t column = (tid + v * (uint32_t)kSumNormThreads) * 4u;
       if (column >= p.width) continue;
       const __half2* weights = reinterpret_cast<const __half2*>(norm_weight + column);
       const float2 w_low = __half22float2(weights[0]), w_high = __half22float2(weights[1]);
@@ -331,7 +335,7 @@ int launch_tp_exchange_sum_norm(const KernelArgs& args) {
   LLMOPT_REQUIRE((!p.has_residual || args.lengths[p.ranks] >= elements * 2) && args.lengths[p.ranks + 1] >= elements * 2 &&
                      args.lengths[p.ranks + 2] >= (size_t)p.width * 2 && args.lengths[p.ranks + 3] >= elements * 2,
                  "residual, output or weight buffer is too short");
-  launch_kernel(args, exchange_sum_norm_kernel, dim3(p.rows), dim3(256), 0, regions,
+  launch_kernel(args, exchange_sum_norm_kernel, dim3(p.rows), dim3(kSumNormThreads), 0, regions,
                 (const __half*)args.buffers[p.ranks], (__half*)args.buffers[p.ranks + 1],
                 (const __half*)args.buffers[p.ranks + 2], (__half*)args.buffers[p.ranks + 3], p,
                 context_device_error(args.ctx));
