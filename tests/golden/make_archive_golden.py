@@ -33,7 +33,9 @@ def tensors():
 
 
 def main() -> None:
-    reference = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_archive_golden.py /path/to/reference")
+    reference = sys.argv[1]
     sys.path.insert(0, os.path.join(reference, "python"))
     from llmopt_backend import tensor_archive
 

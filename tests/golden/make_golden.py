@@ -4,7 +4,7 @@ pack_int4_weight, unpack_int4_weight, the fp32-accumulate `w4a16_linear`
 fallback and the W4A16Linear module) on seeded inputs.  Run where the reference
 checkout is mounted:
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /root/reference
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference
 
 The fixture travels with the repository; the tests never import the reference.
 """
@@ -49,4 +49,6 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py /path/to/reference")
+    main(sys.argv[1])
