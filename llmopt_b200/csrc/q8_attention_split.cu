@@ -400,7 +400,8 @@ paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__
     }
   __syncthreads();
   float* record = scratch + (((size_t)batch * p.kv_heads + kv_head) * splits + split) * kRecord;
-  for (uint32_t index = threadIdx.x; index < 8u * D; index += kWarps * 32) {
+  // only the columns of heads that exist are merged and written (the merge kernel reads no others)
+  for (uint32_t index = threadIdx.x; index < min(heads_per_kv, 8u) * D; index += kWarps * 32) {
     const uint32_t head = index / D;
     float merged_max = kLowest;
 #pragma unroll
