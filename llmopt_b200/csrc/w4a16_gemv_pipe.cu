@@ -620,13 +620,16 @@ int run_pipe(const KernelArgs& args, const GemvProblem& p, const PipePlan& plan)
 
 // Groups per warp and stage: the most (4, 2, 1) that K allows and that still leaves at
 // least two CTAs (18 warps) resident per SM; a fat stage that forces one CTA per SM
-// loses more to idle issue slots than it gains from amortised waits.
+// loses more to idle issue slots than it gains from amortised waits.  Four groups only for
+// one matrix and one or four batch tiles (measured at the Llama-8B shapes: with two batch
+// tiles four groups lose to two; with four tiles they win: batch-32 step 9.22 -> 8.13 ms
+// together with two groups for the dual form).
 template <int NT, int NMAT, int EPI, bool SMALLX>
 int launch_pipe(const KernelArgs& args, const GemvProblem& p) {
   PipePlan plan4 = {}, plan2 = {}, plan1 = {};
-  const bool ok4 = NT == 1 && NMAT == 1 && p.k % 2048 == 0 && plan_pipe<NT, NMAT, EPI, SMALLX, 4>(args, p, &plan4);
+  const bool ok4 = (NT == 1 || NT == 4) && NMAT == 1 && p.k % 2048 == 0 && plan_pipe<NT, NMAT, EPI, SMALLX, 4>(args, p, &plan4);
   if (ok4 && plan4.resident >= 2) return run_pipe<NT, NMAT, EPI, SMALLX, 4>(args, p, plan4);
-  const bool ok2 = NT <= 2 && p.k % 1024 == 0 && plan_pipe<NT, NMAT, EPI, SMALLX, 2>(args, p, &plan2);
+  const bool ok2 = p.k % 1024 == 0 && plan_pipe<NT, NMAT, EPI, SMALLX, 2>(args, p, &plan2);
   if (ok2 && plan2.resident >= 2) return run_pipe<NT, NMAT, EPI, SMALLX, 2>(args, p, plan2);
   const bool ok1 = plan_pipe<NT, NMAT, EPI, SMALLX, 1>(args, p, &plan1);
   if (ok1 && plan1.resident >= 2) return run_pipe<NT, NMAT, EPI, SMALLX, 1>(args, p, plan1);
