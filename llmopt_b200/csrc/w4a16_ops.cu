@@ -160,7 +160,16 @@ int lm_head_stage(const KernelArgs& args, bool input_f32, const void* input, con
   problem.mat[0] = {weight, scale, nullptr, n};
   problem.matrices = 1;
   problem.out_f32 = logits_f32;
-  if (int status = launch_w4a16_gemv(args, problem, kEpiSplitF32, false)) return status;
+  // At most 16 rows (32 hi/lo slot rows) per launch: that is what the pipelined kernel takes, and two
+  // passes over the weights through it beat one pass through the direct-load kernel (batch 32: 583 -> ~500 us).
+  for (uint32_t first = 0; first < m; first += 16u) {
+    const uint32_t rows = m - first < 16u ? m - first : 16u;
+    problem.x = slots + (size_t)(first / 4u) * 8u * k;
+    problem.x_rows = ((rows + 3u) / 4u) * 8u;
+    problem.m = rows;
+    problem.out_f32 = logits_f32 + (size_t)first * n;
+    if (int status = launch_w4a16_gemv(args, problem, kEpiSplitF32, false)) return status;
+  }
   launch_kernel(args, argmax_partial_kernel, dim3(kCandidateParts, m), dim3(256), 0, logits_f32, candidates, logits, n);
   return check_launch(args);
 }
