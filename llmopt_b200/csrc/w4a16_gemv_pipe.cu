@@ -572,6 +572,22 @@ struct PipePlan {
 // dependent instructions per group), bytes in flight the second: take the most
 // resident CTAs per SM (up to 3; 4 for the LM-head form) whose ring still holds at least three
 // stages (two at 4 CTAs), and one CTA per slot.
+// CTAs per SM that this instantiation's registers allow (the wide-batch forms use up to 168 per thread).
+template <int NT, int NMAT, int EPI, bool SMALLX, int GPW>
+uint32_t register_resident_limit() {
+  static const uint32_t limit = []() -> uint32_t {
+    cudaFuncAttributes attributes;
+    if (cudaFuncGetAttributes(&attributes, w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX, GPW>) != cudaSuccess) {
+      cudaGetLastError();
+      return 3u;
+    }
+    const uint32_t per_cta = (uint32_t)((attributes.numRegs + 7) / 8 * 8) * kThreads;
+    const uint32_t fit = 65536u / per_cta;
+    return fit < 1u ? 1u : fit;
+  }();
+  return limit;
+}
+
 template <int NT, int NMAT, int EPI, bool SMALLX, int GPW>
 bool plan_pipe(const KernelArgs& args, const GemvProblem& p, PipePlan* plan) {
   uint32_t total_tiles = 0;
@@ -585,7 +601,13 @@ bool plan_pipe(const KernelArgs& args, const GemvProblem& p, PipePlan* plan) {
   constexpr size_t kSharedPerSm = 220 * 1024;  // usable shared memory of one SM
   const uint32_t chunks_per_tile = p.k / Stage<GPW>::kChunkK;
   // a fourth resident CTA only where the kernel was compiled for it and every CTA still gets four tiles
-  const uint32_t most = kDenseResidency<NT, EPI> == 4 && total_tiles >= 16u * sms ? 4u : 3u;
+  uint32_t most = kDenseResidency<NT, EPI> == 4 && total_tiles >= 16u * sms ? 4u : 3u;
+  // Wide-batch forms on few, short tiles (QKV, o_proj): size grid and ring for the CTAs the registers really
+  // let reside (batch 32: QKV 17.8 -> 14.6, o_proj 12.4 -> 10.9 us).  On many or long tiles the oversubscribed
+  // grid measured faster (gate/up, down, LM head), so those keep it.
+  if (NT > 1 && total_tiles <= 3u * sms && chunks_per_tile <= 4u &&
+      register_resident_limit<NT, NMAT, EPI, SMALLX, GPW>() < most)
+    most = register_resident_limit<NT, NMAT, EPI, SMALLX, GPW>();
   for (uint32_t resident = most; resident >= 1; --resident) {
     const size_t per_cta = kSharedPerSm / resident - 1024;
     if (per_cta <= fixed_bytes + 2 * stage_bytes) continue;
@@ -628,9 +650,10 @@ template <int NT, int NMAT, int EPI, bool SMALLX>
 int launch_pipe(const KernelArgs& args, const GemvProblem& p) {
   PipePlan plan4 = {}, plan2 = {}, plan1 = {};
   const bool ok4 = (NT == 1 || NT == 4) && NMAT == 1 && p.k % 2048 == 0 && plan_pipe<NT, NMAT, EPI, SMALLX, 4>(args, p, &plan4);
-  if (ok4 && plan4.resident >= 2) return run_pipe<NT, NMAT, EPI, SMALLX, 4>(args, p, plan4);
+  // (four batch tiles: the fat forms win even at one CTA per SM, which is all their registers allow)
+  if (ok4 && (plan4.resident >= 2 || NT == 4)) return run_pipe<NT, NMAT, EPI, SMALLX, 4>(args, p, plan4);
   const bool ok2 = p.k % 1024 == 0 && plan_pipe<NT, NMAT, EPI, SMALLX, 2>(args, p, &plan2);
-  if (ok2 && plan2.resident >= 2) return run_pipe<NT, NMAT, EPI, SMALLX, 2>(args, p, plan2);
+  if (ok2 && (plan2.resident >= 2 || NT == 4)) return run_pipe<NT, NMAT, EPI, SMALLX, 2>(args, p, plan2);
   const bool ok1 = plan_pipe<NT, NMAT, EPI, SMALLX, 1>(args, p, &plan1);
   if (ok1 && plan1.resident >= 2) return run_pipe<NT, NMAT, EPI, SMALLX, 1>(args, p, plan1);
   if (ok2) return run_pipe<NT, NMAT, EPI, SMALLX, 2>(args, p, plan2);
