@@ -189,6 +189,12 @@ int llmopt_cuda_prebaked_execute_chained(llmopt_cuda_prebaked* plan, int64_t fir
                                          float* elapsed_ms);
 /* Number of kernel nodes in the captured graph. */
 int llmopt_cuda_prebaked_kernel_count(llmopt_cuda_prebaked* plan);
+/* Largest past_tokens a replay of this plan accepts: every row-binding table must
+ * hold row `past_tokens` and every paged-attention slot table `past_tokens` entries
+ * per sequence. execute / execute_chained / the ring refuse larger values with
+ * LLMOPT_CUDA_INVALID_ARGUMENT instead of reading past a table (the reference
+ * patches byte 12 unchecked, native/ocaml_metal_stubs.m:2182-2185). */
+int64_t llmopt_cuda_prebaked_token_capacity(llmopt_cuda_prebaked* plan);
 void llmopt_cuda_release_prebaked(llmopt_cuda_prebaked* plan);
 
 /* ---- ring queue ------------------------------------------------------------------ */
@@ -238,7 +244,7 @@ int llmopt_cuda_w4a16_linear(llmopt_cuda_context* context, const void* input, co
  *   block (lib/metal_parameters.ml:119-140).
  * Decode shape only (one query token, no mask, no window, D 64 or 128, group 32 or
  * 64, <= 8 query heads per KV head); batches x kv_heads may not exceed 2016
- * (D = 128) or 3954 (D = 64) — larger problems are rejected with
+ * (D = 128) or 3971 (D = 64) — larger problems are rejected with
  * LLMOPT_CUDA_INVALID_ARGUMENT. Runs on `stream` (a cudaStream_t; NULL = default
  * stream) without synchronising. The first call on each device resolves the
  * array's device address; make it before any stream capture begins. Calls share

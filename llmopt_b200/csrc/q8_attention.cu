@@ -36,7 +36,8 @@ __global__ void paged_rows_kernel(const __half* __restrict__ query, const __half
                                   const __half* __restrict__ current_value, const uint8_t* __restrict__ pool,
                                   const uint32_t* __restrict__ slots, const uint8_t* __restrict__ mask,
                                   __half* __restrict__ output, PagedParams p, uint32_t slot_batch_stride,
-                                  const uint32_t* __restrict__ past_cell) {
+                                  const uint32_t* __restrict__ past_cell, uint32_t pool_tokens,
+                                  uint32_t* error_word) {
   grid_chain_prologue();
   if (past_cell) p.past_length = *past_cell;
   const uint32_t lane = threadIdx.x & 31u;
@@ -76,7 +77,13 @@ __global__ void paged_rows_kernel(const __half* __restrict__ query, const __half
     const int8_t* values = nullptr;
     const __half* scales = nullptr;
     if (past) {
-      const size_t slot_base = (size_t)batch_slots[key] * p.token_stride;
+      // a slot outside the pool is skipped (the key contributes nothing) and reported
+      const uint32_t slot = batch_slots[key];
+      if (slot >= pool_tokens) {
+        if (lane == 0 && error_word) atomicExch(error_word, 1u);
+        continue;
+      }
+      const size_t slot_base = (size_t)slot * p.token_stride;
       values = reinterpret_cast<const int8_t*>(pool + slot_base);
       scales = reinterpret_cast<const __half*>(pool + slot_base + p.token_elements);
     }
@@ -125,8 +132,10 @@ __global__ void paged_rows_kernel(const __half* __restrict__ query, const __half
 
 }  // namespace
 
-int launch_paged_attention_split(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride);
+int launch_paged_attention_split(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride,
+                                 uint32_t pool_tokens);
 bool paged_split_supported(const PagedParams& p);
+uint32_t* context_device_error(Context* ctx);
 
 // Buffers: [query, current_key, current_value, pool, slots, mask, output]
 // (lib/metal_dispatch_attention.ml:154-157); with no mask the dispatcher binds the
@@ -148,19 +157,40 @@ int launch_attention_q8_paged(const KernelArgs& args) {
   const size_t rows = (size_t)p.batches * p.query_heads * q_len;
   LLMOPT_REQUIRE(args.lengths[0] >= rows * p.head_dim * 2, "query buffer is too short");
   LLMOPT_REQUIRE(args.lengths[6] >= rows * p.head_dim * 2, "output buffer is too short");
-  // With a replayed plan the live past length sits in a device cell; the slot
-  // table must then cover the plan's capacity, which only the caller knows.
+  LLMOPT_REQUIRE(args.lengths[1] >= (size_t)p.batches * p.kv_heads * q_len * p.head_dim * 2 &&
+                     args.lengths[2] >= (size_t)p.batches * p.kv_heads * q_len * p.head_dim * 2,
+                 "current key / value buffer is too short");
+  // With a replayed plan the live past length sits in a device cell; the plan refuses
+  // past lengths beyond the slot tables it captured (plan_token_capacity in runtime.cu).
   if (!args.past_tokens_cell)
     LLMOPT_REQUIRE(args.lengths[4] >= ((size_t)(p.batches - 1) * slot_batch_stride + p.past_length) * 4,
                    "slots buffer is shorter than past_length");
+  // Pool geometry: every byte a kernel addresses inside a token row lies in it, and only whole
+  // rows of the pool buffer are addressable (slots beyond them are refused on the device).
+  const uint32_t groups_per_head = p.head_dim / p.group_size;
+  const size_t segment = (size_t)p.kv_heads * p.head_dim;
+  LLMOPT_REQUIRE(p.token_stride > 0, "token_stride must be positive");
+  LLMOPT_REQUIRE(p.key_offset + segment <= p.token_elements && p.value_offset + segment <= p.token_elements,
+                 "key / value segment lies outside token_elements");
+  LLMOPT_REQUIRE((size_t)p.token_elements + 2 * ((size_t)max(p.key_offset, p.value_offset) / p.group_size +
+                                                 (size_t)p.kv_heads * groups_per_head) <= p.token_stride,
+                 "token_elements plus the group scales exceed token_stride");
+  const size_t pool_rows = args.lengths[3] / p.token_stride;
+  const uint32_t pool_tokens = pool_rows > 0xffffffffull ? 0xffffffffu : (uint32_t)pool_rows;
   const uint8_t* mask = p.mask_batches == 0 ? nullptr : (const uint8_t*)args.buffers[5];
+  if (mask != nullptr) {
+    const size_t mask_rows = (size_t)p.mask_batches * p.mask_heads * q_len;
+    LLMOPT_REQUIRE(args.past_tokens_cell != nullptr ||
+                       args.lengths[5] >= mask_rows * ((size_t)p.past_length + q_len) * (p.mask_dtype == 2 ? 2 : 1),
+                   "mask buffer is too short");
+  }
   if (mask == nullptr && q_len == 1 && p.window == 0 && paged_split_supported(p))
-    return launch_paged_attention_split(args, p, slot_batch_stride);
+    return launch_paged_attention_split(args, p, slot_batch_stride, pool_tokens);
   const uint32_t blocks = (uint32_t)((rows + 7) / 8);
   launch_kernel(args, paged_rows_kernel, dim3(blocks), dim3(256), 0,
       (const __half*)args.buffers[0], (const __half*)args.buffers[1], (const __half*)args.buffers[2],
       (const uint8_t*)args.buffers[3], (const uint32_t*)args.buffers[4], mask, (__half*)args.buffers[6], p,
-      slot_batch_stride, args.past_tokens_cell);
+      slot_batch_stride, args.past_tokens_cell, pool_tokens, args.ctx ? context_device_error(args.ctx) : nullptr);
   return check_launch(args);
 }
 

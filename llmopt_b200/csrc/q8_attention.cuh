@@ -20,9 +20,10 @@ constexpr uint32_t kMaxAttentionSplits = 64;
 // and 8 x head_dim accumulators.
 inline size_t paged_split_record_floats(uint32_t head_dim) { return 16 + 8 * (size_t)head_dim; }
 
-// The split path proper, on caller-provided scratch (no allocation inside).
+// The split path proper, on caller-provided scratch (no allocation inside).  Slot values
+// >= pool_tokens are never dereferenced (0xffffffff: the caller vouches for its slot table).
 int launch_paged_attention_split_on(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride,
-                                    float* scratch, uint32_t splits);
+                                    float* scratch, uint32_t splits, uint32_t pool_tokens);
 uint32_t paged_pick_splits(const KernelArgs& args, const PagedParams& p);
 
 }  // namespace llmopt

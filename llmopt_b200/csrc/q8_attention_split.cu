@@ -34,6 +34,7 @@
 #include "q8_attention.cuh"
 
 namespace llmopt {
+uint32_t* context_device_error(Context* ctx);
 namespace {
 
 constexpr int kTileKeys = 16;
@@ -129,7 +130,8 @@ template <int D, int GROUP, int CP>
 __global__ void __launch_bounds__(kWarps * 32, kResidentCtas)
 paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__ pool,
                    const uint32_t* __restrict__ slots, float* __restrict__ scratch, PagedParams p,
-                   uint32_t slot_batch_stride, uint32_t splits, const uint32_t* __restrict__ past_cell) {
+                   uint32_t slot_batch_stride, uint32_t splits, const uint32_t* __restrict__ past_cell,
+                   uint32_t pool_tokens, uint32_t* error_word) {
   grid_chain_prologue();
   using Shape = SplitShape<D, CP>;
   constexpr int kSteps = D / 16;  // k-steps of QK^T, m-tiles of PV
@@ -194,10 +196,17 @@ paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__
 #pragma unroll
     for (int j = 0; j < 4; ++j) out[s][j] = 0.0f;
 
-  // Slot of key (lane % 16) of this warp's tile `index`, or kNoSlot.
+  // Slot of key (lane % 16) of this warp's tile `index`, or kNoSlot.  A slot outside the pool
+  // is reported through the error word and read as slot 0, so no copy leaves the pool.
   auto load_slot = [&](uint32_t index) -> uint32_t {
     const uint32_t position = range_begin + (warp + index * kWarps) * kTileKeys + (lane & 15u);
-    return (index < my_tiles && position < range_end) ? __ldg(batch_slots + position) : kNoSlot;
+    if (!(index < my_tiles && position < range_end)) return kNoSlot;
+    uint32_t slot = __ldg(batch_slots + position);
+    if (slot >= pool_tokens) {
+      if (error_word) atomicExch(error_word, 1u);
+      slot = 0u;
+    }
+    return slot;
   };
   // A tile's row addresses depend on its slots, so the slots run four tiles ahead of
   // the copies.
@@ -504,7 +513,7 @@ paged_merge_kernel(const __half* __restrict__ query, const __half* __restrict__ 
 
 template <int D, int GROUP, int CP>
 int launch_split_copy(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride, float* scratch,
-                      uint32_t splits) {
+                      uint32_t splits, uint32_t pool_tokens) {
   auto kernel = paged_split_kernel<D, GROUP, CP>;
   constexpr int ring_bytes = SplitShape<D, CP>::kRingBytes;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes) != cudaSuccess) {
@@ -513,16 +522,17 @@ int launch_split_copy(const KernelArgs& args, const PagedParams& p, uint32_t slo
   }
   launch_kernel(args, kernel, dim3(splits, p.kv_heads, p.batches), dim3(kWarps * 32), ring_bytes,
       (const __half*)args.buffers[0], (const uint8_t*)args.buffers[3], (const uint32_t*)args.buffers[4], scratch, p,
-      slot_batch_stride, splits, args.past_tokens_cell);
+      slot_batch_stride, splits, args.past_tokens_cell, pool_tokens,
+      args.ctx ? context_device_error(args.ctx) : nullptr);
   return check_launch(args);
 }
 
 template <int D, int GROUP>
 int launch_split(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride, float* scratch,
-                 uint32_t splits) {
+                 uint32_t splits, uint32_t pool_tokens) {
   const bool aligned = (p.token_stride % 16 == 0) && (((uintptr_t)args.buffers[3]) % 16 == 0);
-  const int status = aligned ? launch_split_copy<D, GROUP, 16>(args, p, slot_batch_stride, scratch, splits)
-                             : launch_split_copy<D, GROUP, 8>(args, p, slot_batch_stride, scratch, splits);
+  const int status = aligned ? launch_split_copy<D, GROUP, 16>(args, p, slot_batch_stride, scratch, splits, pool_tokens)
+                             : launch_split_copy<D, GROUP, 8>(args, p, slot_batch_stride, scratch, splits, pool_tokens);
   if (status) return status;
   launch_kernel(args, paged_merge_kernel<D>, dim3(p.query_heads, p.batches), dim3(D * kMergeParts), 0,
       (const __half*)args.buffers[0], (const __half*)args.buffers[1], (const __half*)args.buffers[2], scratch,
@@ -582,23 +592,24 @@ uint32_t paged_pick_splits(const KernelArgs& args, const PagedParams& p) {
 }
 
 int launch_paged_attention_split_on(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride,
-                                    float* scratch, uint32_t splits) {
+                                    float* scratch, uint32_t splits, uint32_t pool_tokens) {
   LLMOPT_REQUIRE(((uintptr_t)args.buffers[3]) % 8 == 0, "pool must be 8-byte aligned");
   LLMOPT_REQUIRE(((uintptr_t)args.buffers[0]) % 4 == 0, "query must be 4-byte aligned");
   if (p.head_dim == 64)
-    return p.group_size == 64 ? launch_split<64, 64>(args, p, slot_batch_stride, scratch, splits)
-                              : launch_split<64, 32>(args, p, slot_batch_stride, scratch, splits);
-  return p.group_size == 64 ? launch_split<128, 64>(args, p, slot_batch_stride, scratch, splits)
-                            : launch_split<128, 32>(args, p, slot_batch_stride, scratch, splits);
+    return p.group_size == 64 ? launch_split<64, 64>(args, p, slot_batch_stride, scratch, splits, pool_tokens)
+                              : launch_split<64, 32>(args, p, slot_batch_stride, scratch, splits, pool_tokens);
+  return p.group_size == 64 ? launch_split<128, 64>(args, p, slot_batch_stride, scratch, splits, pool_tokens)
+                            : launch_split<128, 32>(args, p, slot_batch_stride, scratch, splits, pool_tokens);
 }
 
-int launch_paged_attention_split(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride) {
+int launch_paged_attention_split(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride,
+                                 uint32_t pool_tokens) {
   const uint32_t splits = paged_pick_splits(args, p);
   const size_t bytes =
       (size_t)p.batches * p.kv_heads * splits * paged_split_record_floats(p.head_dim) * sizeof(float);
   float* scratch = (float*)context_scratch(args.ctx, bytes, args.error);
   if (scratch == nullptr) return 1;
-  return launch_paged_attention_split_on(args, p, slot_batch_stride, scratch, splits);
+  return launch_paged_attention_split_on(args, p, slot_batch_stride, scratch, splits, pool_tokens);
 }
 
 }  // namespace llmopt

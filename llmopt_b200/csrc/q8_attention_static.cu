@@ -30,7 +30,7 @@ bool paged_split_supported(const PagedParams& p);
 
 namespace {
 
-// 8 MiB: 2016 split records at head_dim 128 (4160 bytes each), 3954 at head_dim 64.
+// 8 MiB: 2016 split records at head_dim 128 (4160 bytes each), 3971 at head_dim 64 (2112 bytes each).
 constexpr size_t kStaticScratchBytes = (size_t)8 << 20;
 static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
 
@@ -134,7 +134,7 @@ extern "C" int llmopt_cuda_attention_q8_paged_static(const void* query, const vo
   args.name = "llmopt_cuda_attention_q8_paged_static";
   std::string message;
   args.error = &message;
-  if (launch_paged_attention_split_on(args, p, slot_batch_stride, setup->scratch, splits) != 0)
+  if (launch_paged_attention_split_on(args, p, slot_batch_stride, setup->scratch, splits, 0xffffffffu) != 0)
     return fail_with(LLMOPT_CUDA_FAILURE, message);
   return LLMOPT_CUDA_OK;
 }

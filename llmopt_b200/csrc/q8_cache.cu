@@ -13,7 +13,20 @@
 #include "common.cuh"
 
 namespace llmopt {
+uint32_t* context_device_error(Context* ctx);
 namespace {
+
+// Token rows the pool buffer holds; slot values at or beyond it are refused on the device
+// (the access is skipped and the context's error word raised).
+struct PoolBound {
+  uint32_t tokens;
+  uint32_t* error_word;
+};
+__device__ __forceinline__ bool slot_in_pool(uint32_t slot, const PoolBound& bound, uint32_t lane) {
+  if (slot < bound.tokens) return true;
+  if (lane == 0 && bound.error_word) atomicExch(bound.error_word, 1u);
+  return false;
+}
 
 struct AttentionCacheParams {  // lib/metal_cache_source.ml:9-20
   uint32_t items, segment_offset, heads, head_dim, group_size, token_elements, token_groups,
@@ -46,7 +59,7 @@ __device__ __forceinline__ void quantize_group(const __half* __restrict__ source
 }
 
 __global__ void pack_attention_kernel(const __half* __restrict__ source, const uint32_t* __restrict__ slots,
-                                      uint8_t* __restrict__ pool, AttentionCacheParams p) {
+                                      uint8_t* __restrict__ pool, AttentionCacheParams p, PoolBound bound) {
   grid_chain_prologue();
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t logical_group = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -59,6 +72,7 @@ __global__ void pack_attention_kernel(const __half* __restrict__ source, const u
   const uint32_t group_in_head = local_group - head * groups_per_head;
   const size_t source_base = ((size_t)head * p.source_items + p.source_offset + item) * p.head_dim +
                              (size_t)group_in_head * p.group_size;
+  if (!slot_in_pool(slots[item], bound, lane)) return;
   const size_t slot_base = (size_t)slots[item] * p.token_stride;
   int8_t* values = reinterpret_cast<int8_t*>(pool + slot_base);
   __half* scales = reinterpret_cast<__half*>(pool + slot_base + p.token_elements);
@@ -70,7 +84,7 @@ __global__ void pack_attention_kernel(const __half* __restrict__ source, const u
 __global__ void pack_attention_pair_kernel(const __half* __restrict__ key_source,
                                            const __half* __restrict__ value_source,
                                            const uint32_t* __restrict__ slots, uint8_t* __restrict__ pool,
-                                           AttentionCachePairParams p) {
+                                           AttentionCachePairParams p, PoolBound bound) {
   grid_chain_prologue();
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t logical_group = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -83,6 +97,7 @@ __global__ void pack_attention_pair_kernel(const __half* __restrict__ key_source
   const uint32_t group_in_head = local_group - head * groups_per_head;
   const size_t source_base = ((size_t)head * p.source_items + p.source_offset + item) * p.head_dim +
                              (size_t)group_in_head * p.group_size;
+  if (!slot_in_pool(slots[item], bound, lane)) return;
   const size_t slot_base = (size_t)slots[item] * p.token_stride;
   int8_t* values = reinterpret_cast<int8_t*>(pool + slot_base);
   __half* scales = reinterpret_cast<__half*>(pool + slot_base + p.token_elements);
@@ -107,7 +122,7 @@ __global__ void rotary_pack_kernel(const __half* __restrict__ q_input, const __h
                                    const __half* __restrict__ v_input, const __half* __restrict__ cosine,
                                    const __half* __restrict__ sine, __half* __restrict__ q_output, __half* k_output,
                                    const uint32_t* __restrict__ slots, uint8_t* __restrict__ pool, RotaryQkParams r,
-                                   AttentionCachePairParams c) {
+                                   AttentionCachePairParams c, PoolBound bound) {
   grid_chain_prologue();
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -134,6 +149,7 @@ __global__ void rotary_pack_kernel(const __half* __restrict__ q_input, const __h
     __syncwarp();
   }
   const __half* source = is_v ? v_input + base : k_output + base;
+  if (!slot_in_pool(slots[batch], bound, lane)) return;
   const size_t slot_base = (size_t)slots[batch] * c.token_stride;
   int8_t* values = reinterpret_cast<int8_t*>(pool + slot_base);
   __half* scales = reinterpret_cast<__half*>(pool + slot_base + c.token_elements);
@@ -146,7 +162,8 @@ __global__ void rotary_pack_kernel(const __half* __restrict__ q_input, const __h
 }
 
 __global__ void unpack_attention_kernel(const uint8_t* __restrict__ pool, const uint32_t* __restrict__ slots,
-                                        __half* __restrict__ destination, AttentionCacheParams p) {
+                                        __half* __restrict__ destination, AttentionCacheParams p,
+                                        PoolBound bound) {
   grid_chain_prologue();
   const uint32_t gid = blockIdx.x * blockDim.x + threadIdx.x;
   const uint32_t segment_elements = p.heads * p.head_dim;
@@ -157,23 +174,29 @@ __global__ void unpack_attention_kernel(const uint8_t* __restrict__ pool, const 
   const uint32_t within_head = local - head * p.head_dim;
   const uint32_t groups_per_head = p.head_dim / p.group_size;
   const uint32_t local_group = head * groups_per_head + within_head / p.group_size;
+  const size_t destination_index = ((size_t)head * p.items + item) * p.head_dim + within_head;
+  if (!slot_in_pool(slots[item], bound, 0u)) {
+    destination[destination_index] = __float2half_rn(0.0f);
+    return;
+  }
   const size_t slot_base = (size_t)slots[item] * p.token_stride;
   const int8_t* values = reinterpret_cast<const int8_t*>(pool + slot_base);
   const __half* scales = reinterpret_cast<const __half*>(pool + slot_base + p.token_elements);
-  const size_t destination_index = ((size_t)head * p.items + item) * p.head_dim + within_head;
   destination[destination_index] = __float2half_rn(
       (float)values[p.segment_offset + local] *
       __half2float(scales[p.segment_offset / p.group_size + local_group]));
 }
 
 __global__ void pack_checkpoint_kernel(const __half* __restrict__ source, uint8_t* __restrict__ pool,
-                                       CheckpointCacheParams p, const uint32_t* __restrict__ checkpoint_cell) {
+                                       CheckpointCacheParams p, const uint32_t* __restrict__ checkpoint_cell,
+                                       PoolBound bound) {
   grid_chain_prologue();
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t logical_group = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const uint32_t layer_groups = p.layer_elements / p.group_size;
   if (logical_group >= layer_groups) return;
   const uint32_t checkpoint = checkpoint_cell ? *checkpoint_cell : p.checkpoint;
+  if (!slot_in_pool(checkpoint, bound, lane)) return;
   const size_t base = (size_t)checkpoint * p.checkpoint_stride;
   int8_t* values = reinterpret_cast<int8_t*>(pool + base);
   __half* scales = reinterpret_cast<__half*>(pool + base + p.checkpoint_elements);
@@ -206,6 +229,20 @@ bool valid_geometry(uint32_t head_dim, uint32_t group_size) {
   return group_size > 0 && head_dim > 0 && head_dim % group_size == 0;
 }
 
+// A token row holds the int8 payload of every segment and, after token_elements bytes, one fp16
+// scale per group: both the segment and its scales must lie inside the row.
+bool segment_in_token(uint32_t segment_offset, uint32_t heads, uint32_t head_dim, uint32_t group_size,
+                      uint32_t token_elements, uint32_t token_stride) {
+  const size_t segment_end = (size_t)segment_offset + (size_t)heads * head_dim;
+  return token_stride > 0 && segment_end <= token_elements &&
+         (size_t)token_elements + 2 * ((segment_end + group_size - 1) / group_size) <= token_stride;
+}
+
+PoolBound pool_bound(const KernelArgs& args, int pool_index, uint32_t row_stride) {
+  const size_t rows = row_stride ? args.lengths[pool_index] / row_stride : 0;
+  return {rows > 0xffffffffull ? 0xffffffffu : (uint32_t)rows, args.ctx ? context_device_error(args.ctx) : nullptr};
+}
+
 }  // namespace
 
 // Buffers: [source f16, slots u32, pool u8]; params 40 bytes (lib/metal_cache.ml:315-318).
@@ -217,10 +254,13 @@ int launch_cache_pack_attention_q8(const KernelArgs& args) {
   LLMOPT_REQUIRE(args.lengths[1] >= (size_t)p.items * 4, "slots buffer is shorter than items");
   LLMOPT_REQUIRE(args.lengths[0] >= ((size_t)(p.heads - 1) * p.source_items + p.source_offset + p.items) * p.head_dim * 2,
                  "source buffer is shorter than the packed range");
+  LLMOPT_REQUIRE(segment_in_token(p.segment_offset, p.heads, p.head_dim, p.group_size, p.token_elements, p.token_stride),
+                 "segment or its scales lie outside the token row");
   const uint32_t groups = p.items * p.heads * (p.head_dim / p.group_size);
   if (groups == 0) return 0;
   launch_kernel(args, pack_attention_kernel, dim3((groups + 7) / 8), dim3(256), 0,
-      (const __half*)args.buffers[0], (const uint32_t*)args.buffers[1], (uint8_t*)args.buffers[2], p);
+      (const __half*)args.buffers[0], (const uint32_t*)args.buffers[1], (uint8_t*)args.buffers[2], p,
+      pool_bound(args, 2, p.token_stride));
   return check_launch(args);
 }
 
@@ -231,11 +271,17 @@ int launch_cache_pack_attention_q8_pair(const KernelArgs& args) {
   LLMOPT_REQUIRE(read_params(args, &p), "expects 44 parameter bytes");
   LLMOPT_REQUIRE(valid_geometry(p.head_dim, p.group_size), "head_dim must be a multiple of group_size");
   LLMOPT_REQUIRE(args.lengths[2] >= (size_t)p.items * 4, "slots buffer is shorter than items");
+  const size_t source_bytes = ((size_t)(p.heads - 1) * p.source_items + p.source_offset + p.items) * p.head_dim * 2;
+  LLMOPT_REQUIRE(p.heads > 0 && args.lengths[0] >= source_bytes && args.lengths[1] >= source_bytes,
+                 "source buffer is shorter than the packed range");
+  LLMOPT_REQUIRE(segment_in_token(p.key_segment_offset, p.heads, p.head_dim, p.group_size, p.token_elements, p.token_stride) &&
+                     segment_in_token(p.value_segment_offset, p.heads, p.head_dim, p.group_size, p.token_elements, p.token_stride),
+                 "segment or its scales lie outside the token row");
   const uint32_t groups = p.items * p.heads * (p.head_dim / p.group_size);
   if (groups == 0) return 0;
   launch_kernel(args, pack_attention_pair_kernel, dim3((groups + 7) / 8), dim3(256), 0,
       (const __half*)args.buffers[0], (const __half*)args.buffers[1], (const uint32_t*)args.buffers[2],
-      (uint8_t*)args.buffers[3], p);
+      (uint8_t*)args.buffers[3], p, pool_bound(args, 3, p.token_stride));
   return check_launch(args);
 }
 
@@ -254,6 +300,9 @@ int launch_rotary_pack_fused(const KernelArgs& rotary, const KernelArgs& pack) {
   if (c.group_size == 0 || r.width % c.group_size != 0 || !valid_geometry(c.head_dim, c.group_size)) return -1;
   if ((size_t)c.heads * c.head_dim != (size_t)r.k_heads * r.width || (c.heads != 1 && c.items != 1)) return -1;
   if ((c.key_segment_offset | c.value_segment_offset) % c.group_size != 0) return -1;
+  if (!segment_in_token(c.key_segment_offset, c.heads, c.head_dim, c.group_size, c.token_elements, c.token_stride) ||
+      !segment_in_token(c.value_segment_offset, c.heads, c.head_dim, c.group_size, c.token_elements, c.token_stride))
+    return -1;  // the stand-alone pack launcher reports it
   const size_t q_bytes = (size_t)r.batches * r.q_heads * r.width * 2, k_bytes = (size_t)r.batches * r.k_heads * r.width * 2;
   const size_t trig_bytes = (size_t)(r.trig_batches == 1 ? 1 : r.batches) * r.width * 2;
   if (rotary.lengths[0] < q_bytes || rotary.lengths[4] < q_bytes || rotary.lengths[1] < k_bytes ||
@@ -264,7 +313,7 @@ int launch_rotary_pack_fused(const KernelArgs& rotary, const KernelArgs& pack) {
   launch_kernel(rotary, rotary_pack_kernel, dim3((rows + 7) / 8), dim3(256), 0, (const __half*)rotary.buffers[0],
                 (const __half*)rotary.buffers[1], (const __half*)pack.buffers[1], (const __half*)rotary.buffers[2],
                 (const __half*)rotary.buffers[3], (__half*)rotary.buffers[4], (__half*)rotary.buffers[5],
-                (const uint32_t*)pack.buffers[2], (uint8_t*)pack.buffers[3], r, c);
+                (const uint32_t*)pack.buffers[2], (uint8_t*)pack.buffers[3], r, c, pool_bound(pack, 3, c.token_stride));
   return check_launch(rotary);
 }
 
@@ -277,9 +326,12 @@ int launch_cache_unpack_attention_q8(const KernelArgs& args) {
   LLMOPT_REQUIRE(args.lengths[1] >= (size_t)p.items * 4, "slots buffer is shorter than items");
   const size_t elements = (size_t)p.items * p.heads * p.head_dim;
   LLMOPT_REQUIRE(args.lengths[2] >= elements * 2, "destination buffer is too short");
+  LLMOPT_REQUIRE(segment_in_token(p.segment_offset, p.heads, p.head_dim, p.group_size, p.token_elements, p.token_stride),
+                 "segment or its scales lie outside the token row");
   if (elements == 0) return 0;
   launch_kernel(args, unpack_attention_kernel, dim3((uint32_t)((elements + 255) / 256)), dim3(256), 0,
-      (const uint8_t*)args.buffers[0], (const uint32_t*)args.buffers[1], (__half*)args.buffers[2], p);
+      (const uint8_t*)args.buffers[0], (const uint32_t*)args.buffers[1], (__half*)args.buffers[2], p,
+      pool_bound(args, 0, p.token_stride));
   return check_launch(args);
 }
 
@@ -291,9 +343,14 @@ int launch_cache_pack_checkpoint_q8(const KernelArgs& args) {
   LLMOPT_REQUIRE(p.group_size > 0 && p.layer_elements % p.group_size == 0, "layer_elements must be a multiple of group_size");
   LLMOPT_REQUIRE(args.lengths[0] >= (size_t)p.layer_elements * 2, "source buffer is too short");
   const uint32_t groups = p.layer_elements / p.group_size;
+  LLMOPT_REQUIRE(((size_t)p.layer + 1) * p.layer_elements <= p.checkpoint_elements &&
+                     (size_t)p.checkpoint_elements + 2 * ((size_t)p.layer + 1) * groups <= p.checkpoint_stride,
+                 "layer or its scales lie outside the checkpoint row");
+  const PoolBound bound = pool_bound(args, 1, p.checkpoint_stride);
+  LLMOPT_REQUIRE(args.checkpoint_cell != nullptr || p.checkpoint < bound.tokens, "checkpoint lies outside the pool");
   if (groups == 0) return 0;
   launch_kernel(args, pack_checkpoint_kernel, dim3((groups + 7) / 8), dim3(256), 0,
-      (const __half*)args.buffers[0], (uint8_t*)args.buffers[1], p, args.checkpoint_cell);
+      (const __half*)args.buffers[0], (uint8_t*)args.buffers[1], p, args.checkpoint_cell, bound);
   return check_launch(args);
 }
 
@@ -304,6 +361,11 @@ int launch_cache_unpack_checkpoint_q8(const KernelArgs& args) {
   LLMOPT_REQUIRE(read_params(args, &p), "expects 28 parameter bytes");
   LLMOPT_REQUIRE(p.group_size > 0 && p.layer_elements % p.group_size == 0, "layer_elements must be a multiple of group_size");
   LLMOPT_REQUIRE(args.lengths[1] >= (size_t)p.layer_elements * 2, "destination buffer is too short");
+  LLMOPT_REQUIRE(((size_t)p.layer + 1) * p.layer_elements <= p.checkpoint_elements &&
+                     (size_t)p.checkpoint_elements + 2 * ((size_t)p.layer + 1) * (p.layer_elements / p.group_size) <=
+                         p.checkpoint_stride,
+                 "layer or its scales lie outside the checkpoint row");
+  LLMOPT_REQUIRE(p.checkpoint < pool_bound(args, 0, p.checkpoint_stride).tokens, "checkpoint lies outside the pool");
   if (p.layer_elements == 0) return 0;
   launch_kernel(args, unpack_checkpoint_kernel, dim3((p.layer_elements + 255) / 256), dim3(256), 0,
       (const uint8_t*)args.buffers[0], (__half*)args.buffers[1], p);

@@ -8,6 +8,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <atomic>
 #include <condition_variable>
 #include <cstdlib>
@@ -75,8 +76,9 @@ struct Context {
   std::vector<void*> scratch_blocks;
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
-  void* split = nullptr;  // K-split scratch of the tensor-core GEMM
+  void* split = nullptr;  // K-split scratch of the tensor-core GEMM: [arrival counters | fp32 partials]
   size_t split_bytes = 0;
+  size_t split_counter_bytes = 0;  // leading bytes that must read zero between launches
   void* flush_buffer = nullptr;  // L2 flush target for timing
   size_t flush_bytes = 0;
   int* argmax_result = nullptr;  // device int
@@ -186,6 +188,7 @@ void* context_split_scratch(Context* context, size_t zeroed_bytes, size_t bytes,
   context->scratch_blocks.push_back(block);  // freed with the context; earlier blocks stay valid for captured plans
   context->split = block;
   context->split_bytes = wanted;
+  context->split_counter_bytes = zeroed_bytes;
   return block;
 }
 int context_sm_count(Context* context) { return context->sm_count; }
@@ -416,15 +419,55 @@ static bool fold_norm(const OwnedRecord& norm, const OwnedRecord& product, Fused
   if (normalized->length < (size_t)rows * width * 2 || norm.buffers[0]->length < (size_t)rows * width * 2 ||
       norm.buffers[1]->length < (size_t)width * 2)
     return false;
-  // the product must not write what the norm reads (it reads the raw rows while it runs)
+  // The product reads the raw rows while one of its CTAs writes the normalised ones, and writes its
+  // outputs while other CTAs still read the raw rows: the raw rows [input, +rows*width*2) must be
+  // disjoint from the normalised rows (no in-place norm, no overlapping views) and from every
+  // other buffer the product binds.
+  const size_t row_bytes = (size_t)rows * width * 2;
+  auto overlaps = [](const uint8_t* a, size_t a_bytes, const uint8_t* b, size_t b_bytes) {
+    return a < b + b_bytes && b < a + a_bytes;
+  };
+  const uint8_t* raw = norm.buffers[0]->pointer();
+  if (overlaps(raw, row_bytes, normalized->pointer(), row_bytes)) return false;
   for (llmopt_cuda_buffer* buffer : product.buffers)
-    if (buffer != consumed && buffer->pointer() == norm.buffers[0]->pointer()) return false;
+    if (buffer != consumed && overlaps(raw, row_bytes, buffer->pointer(), buffer->length)) return false;
+  // likewise nothing else the product binds may alias the normalised rows it is about to write
+  for (llmopt_cuda_buffer* buffer : product.buffers)
+    if (buffer != consumed && overlaps(normalized->pointer(), row_bytes, buffer->pointer(), buffer->length)) return false;
   fused->input = (const __half*)norm.buffers[0]->pointer();
   fused->weight = (const __half*)norm.buffers[1]->pointer();
   fused->normalized = (__half*)normalized->pointer();
   fused->epsilon = epsilon;
   fused->weight_first = weight_first ? 1u : 0u;
   return true;
+}
+
+// The per-token values of a replayed plan index device tables the plan captured: row bindings
+// read row `past_tokens` of their table, paged attention reads `past_tokens` slot entries per
+// sequence.  The smallest of those bounds is the largest past_tokens a replay accepts.
+static int64_t plan_token_capacity(const std::vector<OwnedRecord>& records, const llmopt_cuda_row_binding* bindings,
+                                   size_t binding_count) {
+  int64_t capacity = INT32_MAX;
+  for (size_t i = 0; i < binding_count; ++i) {
+    const int64_t rows = (int64_t)(bindings[i].table->length / bindings[i].row_bytes);
+    capacity = std::min(capacity, rows - 1);
+  }
+  for (const OwnedRecord& record : records) {
+    if (record.is_copy || !is_paged_attention_name(record.name.c_str()) || record.params.size() < 64 ||
+        record.buffers.size() < 5)
+      continue;
+    uint32_t batches = 0, stride = 0;
+    memcpy(&batches, record.params.data(), 4);
+    if (record.params.size() >= 68) memcpy(&stride, record.params.data() + 64, 4);
+    const int64_t entries = (int64_t)(record.buffers[4]->length / 4);
+    int64_t per_sequence = entries;
+    if (batches > 1) {
+      per_sequence = entries - (int64_t)(batches - 1) * stride;
+      if (stride > 0) per_sequence = std::min<int64_t>(per_sequence, stride);
+    }
+    capacity = std::min(capacity, per_sequence);
+  }
+  return capacity < 0 ? -1 : capacity;
 }
 
 static void fill_args(Context* context, const OwnedRecord& record, const uint32_t* past_cell,
@@ -487,7 +530,14 @@ static int wait_stream(Context* context, const char* what) {
   if (status != cudaSuccess) return cuda_failure(what, status);
   if (context->device_error && *(volatile uint32_t*)context->device_error != 0) {
     *(volatile uint32_t*)context->device_error = 0;
-    return set_error(LLMOPT_CUDA_FAILURE, std::string(what) + ": a bounded device-side wait ran out (results are invalid)");
+    // A split-K GEMM CTA that gave up never bumped its tile's arrival counter, so the counter was
+    // not returned to zero by a last arrival: clear them all, or the next launch would elect its
+    // last split too early.
+    if (context->split && context->split_counter_bytes) {
+      cudaMemsetAsync(context->split, 0, context->split_counter_bytes, context->stream);
+      cudaStreamSynchronize(context->stream);
+    }
+    return set_error(LLMOPT_CUDA_FAILURE, std::string(what) + ": a device-side check failed: a bounded wait ran out or a slot / checkpoint index lay outside its pool (results are invalid)");
   }
   return LLMOPT_CUDA_OK;
 }
@@ -551,6 +601,9 @@ struct llmopt_cuda_prebaked {
   cudaGraphExec_t executable = nullptr;
   int kernel_nodes = 0;
   int folded_norms = 0;  // norm records folded into the product that follows them
+  // Largest past_tokens a replay may run with: every row binding must hold row `past_tokens`
+  // and every paged-attention slot table `past_tokens` entries per sequence.
+  int64_t token_capacity = INT32_MAX;
   static constexpr int kStaging = 16;
 };
 
@@ -1054,6 +1107,7 @@ int llmopt_cuda_prebaked_create_bound(llmopt_cuda_library* library, const llmopt
     device_bindings.item[i] = {binding.destination->pointer(), binding.table->pointer(), (uint32_t)binding.row_bytes};
   }
   device_bindings.count = (int)binding_count;
+  plan->token_capacity = plan_token_capacity(plan->records, bindings, binding_count);
 
   cudaError_t status = cudaMalloc((void**)&plan->cells, sizeof(PlanCells));
   if (status == cudaSuccess) status = cudaMemset(plan->cells, 0, sizeof(PlanCells));
@@ -1139,6 +1193,14 @@ int llmopt_cuda_prebaked_create(llmopt_cuda_library* library, const llmopt_cuda_
   return llmopt_cuda_prebaked_create_bound(library, records, count, token_buffer, output_buffer, nullptr, 0, out);
 }
 
+static int check_plan_tokens(llmopt_cuda_prebaked* plan, int64_t last_past_tokens) {
+  if (last_past_tokens > plan->token_capacity)
+    return set_error(LLMOPT_CUDA_INVALID_ARGUMENT,
+                     "past_tokens " + std::to_string(last_past_tokens) + " exceeds the plan's token capacity " +
+                         std::to_string(plan->token_capacity) + " (row-binding tables and slot tables it captured)");
+  return LLMOPT_CUDA_OK;
+}
+
 static int publish_cells(llmopt_cuda_prebaked* plan, int64_t token, int32_t past_tokens, int32_t checkpoint) {
   PlanCells* slot = &plan->staging[plan->staging_next];
   plan->staging_next = (plan->staging_next + 1) % llmopt_cuda_prebaked::kStaging;
@@ -1154,6 +1216,7 @@ int llmopt_cuda_prebaked_execute(llmopt_cuda_prebaked* plan, int64_t token, int3
                                  int32_t checkpoint, int32_t* next_token) {
   if (plan == nullptr) return set_error(LLMOPT_CUDA_FAILURE, "prebaked plan has been finalized");
   if (past_tokens < 0 || checkpoint < 0) return set_error(LLMOPT_CUDA_INVALID_ARGUMENT, "negative plan uniform");
+  if (int status = check_plan_tokens(plan, past_tokens)) return status;
   if (int status = publish_cells(plan, token, past_tokens, checkpoint)) return status;
   CUDA_TRY(cudaGraphLaunch(plan->executable, plan->context->stream), "Prebaked CUDA batch failed");
   if (int status = wait_stream(plan->context, "Prebaked CUDA batch failed")) return status;
@@ -1167,6 +1230,8 @@ int llmopt_cuda_prebaked_execute_chained(llmopt_cuda_prebaked* plan, int64_t fir
   if (plan == nullptr) return set_error(LLMOPT_CUDA_FAILURE, "prebaked plan has been finalized");
   if (steps <= 0 || tokens_out == nullptr || plan->output_buffer == nullptr)
     return set_error(LLMOPT_CUDA_INVALID_ARGUMENT, "chained execution needs steps > 0, a result array and an output buffer");
+  if (past_tokens < 0 || checkpoint < 0) return set_error(LLMOPT_CUDA_INVALID_ARGUMENT, "negative plan uniform");
+  if (int status = check_plan_tokens(plan, (int64_t)past_tokens + steps - 1)) return status;
   Context* context = plan->context;
   if (plan->chained_capacity < steps) {
     if (plan->chained_tokens) {
@@ -1203,6 +1268,8 @@ int llmopt_cuda_prebaked_execute_chained(llmopt_cuda_prebaked* plan, int64_t fir
 }
 
 int llmopt_cuda_prebaked_kernel_count(llmopt_cuda_prebaked* plan) { return plan ? plan->kernel_nodes : 0; }
+
+int64_t llmopt_cuda_prebaked_token_capacity(llmopt_cuda_prebaked* plan) { return plan ? plan->token_capacity : 0; }
 
 // ---- ring ------------------------------------------------------------------------------------
 

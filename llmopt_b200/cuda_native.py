@@ -99,6 +99,7 @@ SIGNATURES = {
     "llmopt_cuda_prebaked_execute_chained": (
         _I, [_P, _I64, _I32, _I32, _I32, ctypes.POINTER(_I32), ctypes.POINTER(ctypes.c_float)]),
     "llmopt_cuda_prebaked_kernel_count": (_I, [_P]),
+    "llmopt_cuda_prebaked_token_capacity": (_I64, [_P]),
     "llmopt_cuda_release_prebaked": (None, [_P]),
     "llmopt_cuda_ring_create": (_I, [_PP]),
     "llmopt_cuda_ring_start_worker": (_I, [_P, _P, _REC, _SZ, _P, _P]),
@@ -475,6 +476,11 @@ class Prebaked:
 
     def kernel_count(self) -> int:
         return int(load_library().llmopt_cuda_prebaked_kernel_count(self._handle))
+
+    def token_capacity(self) -> int:
+        """Largest ``past_tokens`` a replay accepts (bounded by the row-binding tables and the
+        paged-attention slot tables the plan captured)."""
+        return int(load_library().llmopt_cuda_prebaked_token_capacity(self._handle))
 
     def __del__(self):
         handle, self._handle = getattr(self, "_handle", None), None

@@ -421,3 +421,139 @@ def test_plan_fuses_rotary_and_pair_pack_byte_for_byte(runtime, monkeypatch, bat
     assert np.array_equal(fused_k.view(np.uint16), plain_k.view(np.uint16))
     assert np.array_equal(fused_pool, plain_pool)
     assert not np.array_equal(plain_pool, np.full_like(plain_pool, 0x55))
+
+
+def test_plan_refuses_tokens_beyond_its_tables(runtime):
+    """A replayed plan indexes device tables with the per-token values it is given: a row binding
+    reads row ``past_tokens``, paged attention reads ``past_tokens`` slot entries.  Values beyond
+    the captured tables are refused on the host instead of read on the device."""
+    from llmopt_b200 import dispatch, parameters
+    from llmopt_b200.cuda_native import Batch, Buffer, DispatchItem, Prebaked
+
+    table = np.arange(40, dtype=np.float16).reshape(10, 4)
+    token_buffer, emb_out, result = Buffer.create(runtime, 8), Buffer.create(runtime, 8), Buffer.create(runtime, 4)
+    rows = Buffer.of_array(runtime, np.arange(12, dtype=np.uint32))
+    plan = Prebaked(runtime, [
+        DispatchItem("llmopt_embedding_f16", [token_buffer, Buffer.of_array(runtime, table), emb_out],
+                     parameters.embedding(tokens=1, vocabulary=10, width=4), (4, 1, 1), (256, 1, 1)),
+    ], token_buffer, result, row_bindings=[(result, rows, 4)])
+    assert plan.token_capacity() == 11
+    assert plan.execute(token=3, past_tokens=11) == 11
+    with pytest.raises(ValueError, match="token capacity"):
+        plan.execute(token=3, past_tokens=12)
+    with pytest.raises(ValueError, match="token capacity"):
+        plan.execute_chained(token=3, past_tokens=10, steps=3)
+    with pytest.raises(ValueError, match="negative"):
+        plan.execute(token=3, past_tokens=-1)
+    # a paged-attention record bounds the plan by its slot table: 2 sequences x 20 entries
+    pool = random_pool(np.random.default_rng(0), 64, 132, 128, 64)
+    config = dispatch.PagedAttentionConfig(token_elements=128, key_offset=0, value_offset=64, group_size=64,
+                                           token_stride=132, scale=1.0)
+    commands = Batch(runtime)
+    context = dispatch.Context(runtime, batch=commands, decode_uniforms_past_tokens=4)
+    slots = np.arange(40, dtype=np.uint32).reshape(2, 20)
+    out = _tensor(runtime, np.zeros((2, 1, 2, 64), np.float16))
+    dispatch.dispatch_paged_attention_q8(
+        context, config=config, query=_tensor(runtime, np.ones((2, 2, 1, 64), np.float16)),
+        current_key=_tensor(runtime, np.ones((2, 1, 1, 64), np.float16)),
+        current_value=_tensor(runtime, np.ones((2, 1, 1, 64), np.float16)),
+        pool=dispatch.Tensor(_buf(runtime, pool), (pool.size,), "uint8"),
+        slots=dispatch.Tensor(_buf(runtime, slots), slots.shape, "uint32"), output=out, slot_batch_stride=20)
+    records = list(commands.pending)
+    commands.abort()
+    plan = Prebaked(runtime, records, None, None)
+    assert plan.token_capacity() == 20
+    plan.execute(token=0, past_tokens=20)
+    with pytest.raises(ValueError, match="token capacity"):
+        plan.execute(token=0, past_tokens=21)
+
+
+def test_slots_outside_the_pool_are_refused_on_the_device(runtime):
+    """A slot value beyond the pool's rows is never dereferenced: the pack skips the item, the
+    attention reads nothing outside the pool, and the next stream wait reports the error; the
+    context stays usable."""
+    from llmopt_b200 import dispatch, parameters
+    from llmopt_b200.cuda_native import Buffer, NativeError
+
+    rng = np.random.default_rng(5)
+    capacity = 8
+    pool_bytes = np.full(capacity * 132, 0x11, np.uint8)
+    pool = Buffer.of_array(runtime, pool_bytes)
+    key = Buffer.of_array(runtime, rng.standard_normal((2, 64)).astype(np.float16))
+    value = Buffer.of_array(runtime, rng.standard_normal((2, 64)).astype(np.float16))
+    pair = parameters.cache_attention_pair(items=2, key_segment_offset=0, value_segment_offset=64, heads=1, head_dim=64,
+                                           group_size=64, token_elements=128, token_groups=2, token_stride=132,
+                                           source_items=2, source_offset=0)
+    with pytest.raises(NativeError, match="outside its pool"):
+        runtime.dispatch("llmopt_cache_pack_attention_q8_pair_simd",
+                         buffers=[key, value, Buffer.of_array(runtime, np.array([3, capacity], np.uint32)), pool],
+                         parameters=pair, grid=(64, 1, 1))
+    after = pool.to_numpy(np.uint8).reshape(capacity, 132)
+    assert not np.array_equal(after[3], pool_bytes[:132])           # the valid item was packed
+    assert np.array_equal(np.delete(after, 3, axis=0).reshape(-1), np.delete(pool_bytes.reshape(capacity, 132), 3, axis=0).reshape(-1))
+    # a segment that does not fit the token row is refused before any launch
+    bad = parameters.cache_attention_pair(items=1, key_segment_offset=64, value_segment_offset=128, heads=1, head_dim=64,
+                                          group_size=64, token_elements=128, token_groups=2, token_stride=132,
+                                          source_items=1, source_offset=0)
+    with pytest.raises(NativeError, match="outside the token row"):
+        runtime.dispatch("llmopt_cache_pack_attention_q8_pair_simd",
+                         buffers=[key, value, Buffer.of_array(runtime, np.array([0], np.uint32)), pool],
+                         parameters=bad, grid=(64, 1, 1))
+    # attention (split path and row path) with a slot beyond the pool
+    real_pool = random_pool(rng, capacity, 132, 128, 64)
+    config = dispatch.PagedAttentionConfig(token_elements=128, key_offset=0, value_offset=64, group_size=64,
+                                           token_stride=132, scale=0.125)
+    for window in (None, 64):
+        slots = np.array([0, 1, capacity + 5, 2] + [3] * 76, np.uint32)
+        out = _tensor(runtime, np.full((1, 1, 2, 64), np.nan, np.float16))
+        with pytest.raises(NativeError, match="outside its pool"):
+            dispatch.dispatch_paged_attention_q8(
+                dispatch.Context(runtime), config=dispatch.PagedAttentionConfig(**{**config.__dict__, "window": window}),
+                query=_tensor(runtime, rng.standard_normal((1, 2, 1, 64)).astype(np.float16)),
+                current_key=_tensor(runtime, rng.standard_normal((1, 1, 1, 64)).astype(np.float16)),
+                current_value=_tensor(runtime, rng.standard_normal((1, 1, 1, 64)).astype(np.float16)),
+                pool=dispatch.Tensor(_buf(runtime, real_pool), (real_pool.size,), "uint8"),
+                slots=dispatch.Tensor(_buf(runtime, slots), slots.shape, "uint32"), output=out)
+            runtime.synchronize()
+        assert np.all(np.isfinite(out.buffer.to_numpy(np.float16)))
+    runtime.synchronize()  # the context is still usable
+
+
+@pytest.mark.parametrize("in_place", [False, True])
+def test_plan_folds_only_norms_whose_rows_do_not_alias(runtime, monkeypatch, in_place):
+    """An RMS norm is folded into the W4A16 product that consumes it only when the raw rows and the
+    normalised rows are different memory; an in-place norm (or overlapping views) keeps its own
+    kernel.  Either way the plan's buffers equal the unfolded plan's byte for byte."""
+    from helpers import random_w4
+    from llmopt_b200 import parameters
+    from llmopt_b200.cuda_native import Buffer, DispatchItem, Prebaked
+
+    rng = np.random.default_rng(31)
+    rows, k, n = 2, 1024, 320
+    x = rng.standard_normal((rows, k)).astype(np.float16)
+    weight = rng.uniform(0.5, 1.5, size=k).astype(np.float16)
+    packed, scale = random_w4(rng, n, k)
+
+    def run(fold: bool):
+        monkeypatch.setenv("LLMOPT_CUDA_FOLD_NORMS", "1" if fold else "0")
+        raw = Buffer.of_array(runtime, x)
+        normed = raw if in_place else Buffer.create(runtime, rows * k * 2)
+        out = Buffer.of_array(runtime, np.full((rows, n), np.nan, np.float16))
+        scales = Buffer.of_array(runtime, scale)
+        records = [
+            DispatchItem("llmopt_rms_norm_f16_simd", [raw, Buffer.of_array(runtime, weight), normed],
+                         parameters.rms_norm(rows=rows, width=k, epsilon=1e-5), (256, 1, 1), (256, 1, 1)),
+            DispatchItem("llmopt_w4a16_linear_f16_g64_m4",
+                         [normed, Buffer.of_array(runtime, packed), scales, scales, out],
+                         parameters.u32s([rows, n, k, 0, 0]), (256, 1, 1), (256, 1, 1)),
+        ]
+        plan = Prebaked(runtime, records, None, None)
+        plan.execute(token=0, past_tokens=0)
+        return plan.kernel_count(), normed.to_numpy(np.uint16), out.to_numpy(np.uint16)
+
+    folded_kernels, folded_rows, folded_out = run(True)
+    plain_kernels, plain_rows, plain_out = run(False)
+    assert folded_kernels == (plain_kernels if in_place else plain_kernels - 1)
+    assert np.array_equal(folded_rows, plain_rows)
+    assert np.array_equal(folded_out, plain_out)
+    assert not np.any(np.isnan(plain_out.view(np.float16)))
