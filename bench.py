@@ -7,14 +7,19 @@ LM-head argmax).  Inputs are synthetic: random-init weights of the named shape,
 a context of random Q8 K/V with valid scales, random token ids.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--workload llama3-8b|smollm2-135m|lfm2.5-350m]
-                  [--batch B] [--context C] [--impl reference]
+                  [--batch B] [--context C] [--impl reference] [--no-extra-legs]
 
 Prints ONE JSON line (rank 0).  `value` is device-timed (CUDA events around K
-chained graph replays, inputs resident in HBM); `e2e` is the same metric through
-the host-driven `Prebaked.execute` call with host<->device copies every step.
-`--impl reference` times the CPU restatement of the reference's own loop nest
-(oracle/) on a bounded sample of the same workload; it is the only place this
-file executes the oracle apart from the `cpu_baseline` leg.
+chained graph replays, inputs resident in HBM; the median of several repetitions
+of the K steps); `e2e` is the same metric through the host-driven
+`Prebaked.execute` call with host<->device copies every step.  The headline is
+batch 1; the same line carries the batch-32 leg (`batch32`), the small-model
+legs (`smollm2_135m`, `lfm25_350m`), the prefill GEMM sweep (`prefill_gemm`,
+`prefill_gemm_c5`), timings of the zero-point / group-32 input mode
+(`baseline_mode`) and, at N > 1, a correctness check of the tensor-parallel
+run (`tp_check`).  `--impl reference` times the CPU restatement of the
+reference's own loop nest (oracle/) on a bounded sample of the same workload; it
+is the only place this file executes the oracle apart from the `cpu_baseline` leg.
 """
 
 from __future__ import annotations
@@ -22,11 +27,13 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
 import tempfile
 import time
+import types
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -36,6 +43,7 @@ import numpy as np  # noqa: E402
 WORKLOADS = {"llama3-8b": "LLAMA3_8B", "smollm2-135m": "SMOLLM2_135M", "lfm2.5-350m": "LFM25_350M"}
 DEFAULT_CONTEXT = {"llama3-8b": 8192, "smollm2-135m": 512, "lfm2.5-350m": 1024}
 METRIC = "decode_tokens_per_s"
+REPETITIONS = 5  # the K timed steps are repeated this often; the median repetition is reported
 
 
 def measured_peaks() -> dict:
@@ -46,6 +54,46 @@ def measured_peaks() -> dict:
         return {"hbm_gbs": float(peaks["hbm_gbs"]), "bf16_tflops": float(peaks.get("bf16_tflops", 1590.0)),
                 "bf16_tflops_sustained": float(peaks.get("bf16_tflops_sustained", 1400.0)), "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def profile_traffic(relative_path: str, heading_key: str):
+    """(algorithmic bytes, DRAM bytes read + written) of one captured launch, read from the
+    section of a profile summary under profiles/ whose heading contains ``heading_key``."""
+    path = os.path.join(ROOT, relative_path)
+    if not os.path.exists(path):
+        return None
+    algorithmic = read = written = None
+    inside = False
+    with open(path) as handle:
+        for line in handle:
+            if line.startswith("## "):
+                if inside:
+                    break
+                inside = heading_key in line
+                if inside:
+                    found = re.search(r"([\d,]+) algorithmic bytes", line)
+                    algorithmic = int(found.group(1).replace(",", "")) if found else None
+                continue
+            if not inside:
+                continue
+            cells = [cell.strip() for cell in line.split("|")]
+            if len(cells) >= 3 and cells[1] == "dram__bytes_read.sum":
+                read = int(cells[2])
+            if len(cells) >= 3 and cells[1] == "dram__bytes_write.sum":
+                written = int(cells[2])
+    if algorithmic is None or read is None or written is None:
+        return None
+    return algorithmic, read + written
+
+
+# kernel label -> (profile summary, heading of the capture that matches this batch size best)
+TRAFFIC_SOURCES = {
+    "gate_up_swiglu": ("profiles/w4a16_gemv_pipe_m1_llama3_8b.md", "gate/up"),
+    "down_add": ("profiles/w4a16_gemv_pipe_m1_llama3_8b.md", "down + residual"),
+    "qkv": ("profiles/w4a16_gemv_pipe_m1_llama3_8b.md", "fused QKV"),
+    "lm_head_argmax": ("profiles/w4a16_gemv_pipe_m1_llama3_8b.md", "LM head"),
+    "paged_attention_q8": ("profiles/paged_attention_q8_split_llama3_8b.md", "batch 8"),
+}
 
 
 class ClockSampler:
@@ -112,65 +160,129 @@ def distributed_setup(gpus: int):
     return rank, world, local, group
 
 
-def cpu_reference_rate(config, batch: int, seconds: float = 12.0) -> dict:
-    """Tokens/s of the reference's CPU loop nest (lib/cpu.ml:128-152, restated in
-    oracle/llmopt_oracle.c) on a bounded sample: a column slice of one gate
-    projection, all host threads, extrapolated by weight elements per token."""
+# ---- the reference's CPU path ------------------------------------------------------------------
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def weight_elements_per_token(config) -> int:
+    hidden, inter, dim = config.hidden, config.intermediate, config.head_dim
+    total = 0
+    for kind in config.layers:
+        if kind == "attention":
+            total += (config.query_heads + 2 * config.kv_heads) * dim * hidden + hidden * config.query_heads * dim
+        else:
+            total += 4 * hidden * hidden
+        total += 3 * inter * hidden
+    return total + config.vocabulary * hidden
+
+
+def cpu_reference_rate(config, batch: int, context: int, seconds: float = 12.0) -> dict:
+    """Tokens/s of the reference's CPU path on a bounded sample of the decode step: the
+    Cpu.w4a16_linear loop nest (lib/cpu.ml:128-152, restated in oracle/llmopt_oracle.c) over a
+    column slice of one gate projection, once on one thread (the reference interpreter is single
+    threaded) and once with OpenMP over all host threads, plus one layer of paged Q8 attention
+    over the context (one thread); each scaled to a whole token by the units it stands for."""
     from oracle import oracle
 
-    hidden, inter = config.hidden, config.intermediate
+    hidden, inter, dim = config.hidden, config.intermediate, config.head_dim
     rng = np.random.default_rng(0)
-    cores = os.cpu_count() or 1
-    columns = min(inter, 64 * cores)
+    threads = host_threads()
+    columns = min(inter, 64 * threads)
     packed = rng.integers(0, 256, size=(columns, hidden // 2), dtype=np.uint8)
     scale = rng.uniform(0.005, 0.02, size=(columns, hidden // 64)).astype(np.float16)
     x = rng.standard_normal((batch, hidden)).astype(np.float16)
-    oracle.w4a16_linear_cols_mt(x, packed, scale, 0, min(columns, 8))  # warm up the thread pool
-    elapsed, repeats = 0.0, 0
-    while elapsed < seconds and repeats < 2000:
+    total_elements = weight_elements_per_token(config)
+
+    def timed(columns_used: int, budget: float):
+        oracle.w4a16_linear_cols_mt(x, packed, scale, 0, min(columns_used, 8))  # warm up the thread pool
+        elapsed, repeats = 0.0, 0
+        while elapsed < budget and repeats < 2000:
+            start = time.perf_counter()
+            oracle.w4a16_linear_cols_mt(x, packed, scale, 0, columns_used)
+            elapsed += time.perf_counter() - start
+            repeats += 1
+        return elapsed / repeats, repeats
+
+    oracle.set_threads(1)
+    single_columns = min(columns, 64)
+    single_sample, single_repeats = timed(single_columns, min(3.0, seconds / 4))
+    used = oracle.set_threads(threads)
+    per_sample, repeats = timed(columns, seconds)
+    linear_seconds = per_sample * total_elements / (columns * hidden)
+    linear_seconds_single = single_sample * total_elements / (single_columns * hidden)
+
+    # one layer of paged attention over the context for one sequence, single thread
+    attention_seconds = 0.0
+    attention_note = "no attention layers"
+    if config.attention_layers:
+        from llmopt_b200.kv_cache import AttentionLayer, Layout
+
+        layout = Layout([AttentionLayer(config.kv_heads, dim)], group_size=config.kv_group_size)
+        keys = min(context, 2048)
+        pool = np.zeros((keys, layout.bytes_per_token), np.uint8)
+        pool[:, :layout.token_elements] = rng.integers(-127, 128, size=(keys, layout.token_elements),
+                                                       dtype=np.int8).view(np.uint8)
+        pool[:, layout.token_elements:] = rng.uniform(0.004, 0.02, size=(keys, layout.token_groups)).astype(
+            np.float16).view(np.uint8).reshape(keys, -1)
+        region = layout.attentions[0]
+        params = oracle.paged_params_bytes(
+            batches=1, query_heads=config.query_heads, kv_heads=config.kv_heads, past_length=keys, head_dim=dim,
+            token_elements=layout.token_elements, key_offset=region.key_offset, value_offset=region.value_offset,
+            group_size=layout.group_size, token_stride=layout.bytes_per_token, scale=float(1.0 / np.sqrt(dim)))
+        query = rng.standard_normal((1, config.query_heads, 1, dim)).astype(np.float16)
+        current = rng.standard_normal((1, config.kv_heads, 1, dim)).astype(np.float16)
         start = time.perf_counter()
-        oracle.w4a16_linear_cols_mt(x, packed, scale, 0, columns)
-        elapsed += time.perf_counter() - start
-        repeats += 1
-    per_sample = elapsed / repeats
-    sample_elements = columns * hidden
-    total_elements = 0
-    dim = config.head_dim
-    for kind in config.layers:
-        if kind == "attention":
-            total_elements += (config.query_heads + 2 * config.kv_heads) * dim * hidden + hidden * config.query_heads * dim
-        else:
-            total_elements += 4 * hidden * hidden
-        total_elements += 3 * inter * hidden
-    total_elements += config.vocabulary * hidden
-    seconds_per_step = per_sample * total_elements / sample_elements
+        oracle.attention_q8_paged(query, current, current, pool.reshape(-1), np.arange(keys, dtype=np.uint32), None, params)
+        layer_seconds = (time.perf_counter() - start) * context / keys
+        attention_seconds = layer_seconds * config.attention_layers * batch
+        attention_note = (f"paged Q8 attention of one layer over {keys} keys on one thread ({layer_seconds * 1e3:.0f} ms "
+                          f"scaled to {context} keys), x{config.attention_layers} layers x{batch} sequences")
+    seconds_per_step = linear_seconds + attention_seconds
     return {
-        "value": batch / seconds_per_step, "unit": "tokens/s", "cores": cores, "kind": "port",
-        "sample": (f"{columns} columns of one gate projection (K={hidden}, M={batch}) x{repeats} repeats, "
-                   f"{per_sample * 1e3:.2f} ms each, scaled by weight elements per token "
-                   f"({total_elements / sample_elements:.0f}x); linears only, attention not included"),
-        "seconds_per_step": seconds_per_step,
+        "value": batch / seconds_per_step, "unit": "tokens/s", "cores": used, "kind": "port",
+        "sample": (f"{columns} columns of one gate projection (K={hidden}, M={batch}) x{repeats} repeats on {used} OpenMP "
+                   f"threads, {per_sample * 1e3:.2f} ms each, scaled by weight elements per token "
+                   f"({total_elements / (columns * hidden):.0f}x); {attention_note}"),
+        "single_thread": {
+            "value": batch / (linear_seconds_single + attention_seconds), "unit": "tokens/s", "cores": 1,
+            "sample": f"{single_columns} columns x{single_repeats} repeats on one thread (the reference interpreter's "
+                      f"own loop order), {single_sample * 1e3:.2f} ms each; same attention sample"},
+        "linears_only": {"value": batch / linear_seconds, "unit": "tokens/s",
+                         "note": "the same all-thread linear sample without the attention term"},
+        "seconds_per_step": seconds_per_step, "seconds_per_sample": per_sample,
+        "linear_seconds": linear_seconds, "attention_seconds": attention_seconds,
     }
 
 
 def run_reference(args, config) -> dict:
-    baseline = cpu_reference_rate(config, args.batch, seconds=max(4.0, min(30.0, 0.4 * (args.steps + args.warmup))))
+    budget = max(4.0, min(30.0, 0.4 * (args.steps + args.warmup)))
+    baseline = cpu_reference_rate(config, args.batch, args.context, seconds=budget)
     return {
         "impl": "reference", "metric": METRIC, "value": baseline["value"], "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": baseline["seconds_per_step"] * 1e3,
-        "higher_is_better": True, "scaling": "weak" if args.gpus > 1 else "strong", "vs_baseline": None,
+        "steps": args.steps, "warmup": args.warmup,
+        # each "step" of this arm is one bounded sample (a column slice of one projection); a whole token is
+        # `seconds_per_token` of such work
+        "ms_per_step": baseline["seconds_per_sample"] * 1e3, "seconds_per_token": baseline["seconds_per_step"],
+        "higher_is_better": True, "scaling": scaling_label(args, config), "vs_baseline": None,
         "dtype": "f64 accumulate (CPU loop nest)",
         "data": "synthetic", "config": workload_config(args, config),
-        "cpu_baseline": {k: baseline[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "cpu_baseline": {k: baseline[k] for k in ("value", "unit", "cores", "kind", "sample", "single_thread", "linears_only")},
         "e2e": {"value": baseline["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
 
 
-def workload_config(args, config) -> dict:
+def workload_config(args, config, batch=None, context=None) -> dict:
+    batch = args.batch if batch is None else batch
+    context = args.context if context is None else context
     return {
-        "workload": f"{config.name} greedy decode, batch {args.batch}, context {args.context} tokens of Q8 KV "
+        "workload": f"{config.name} greedy decode, batch {batch}, context {context} tokens of Q8 KV "
                     f"(group {config.kv_group_size}), W4A16 group-64 linears",
-        "batch": args.batch, "context": args.context,
+        "batch": batch, "context": context,
         "parallelism": parallelism_label(args, config),
         "l2": "every step streams its weights and KV once; the working set per step is far larger than the "
               "126 MB L2, so nothing is flushed between steps",
@@ -183,6 +295,10 @@ def tensor_parallel_run(args, config) -> bool:
     return args.gpus > 1 and args.parallel == "tp" and tensor_parallel.shards(config, args.gpus)
 
 
+def scaling_label(args, config) -> str:
+    return "weak" if args.gpus > 1 and not tensor_parallel_run(args, config) else "strong"
+
+
 def parallelism_label(args, config) -> str:
     if args.gpus <= 1:
         return "single"
@@ -191,6 +307,8 @@ def parallelism_label(args, config) -> str:
                 f"reduced over peer memory (NVLink), attention split by KV head; one sequence set for all GPUs")
     return f"{args.gpus} independent replicas (one per GPU, no exchange)"
 
+
+# ---- per-kernel timing ----------------------------------------------------------------------------
 
 def time_kernels(engine, runtime) -> dict:
     """Device time of each W4A16 / attention dispatch of one token, measured the way a
@@ -247,107 +365,150 @@ def time_kernels(engine, runtime) -> dict:
     return table
 
 
-# DRAM bytes per launch (ncu: dram__bytes_read.sum + dram__bytes_write.sum) over the algorithmic
-# bytes of the same launch, from the captures summarised under profiles/ (GEMV: batch 1 gate/up;
-# attention: batch 8, 8192 tokens; both grow in proportion to the units processed).
-TRAFFIC_RATIO = {
-    "gate_up_swiglu": (62_625_536 / 62_427_136, "profiles/w4a16_gemv_pipe_m1_llama3_8b.md"),
-    "paged_attention_q8": (147_036_160 / 138_838_016, "profiles/paged_attention_q8_split_llama3_8b.md"),
-}
+def roofline_entry(kernel: dict, peaks: dict) -> dict:
+    entry = {
+        "bound": "hbm", "kernel": kernel["name"], "achieved": kernel["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "frac": kernel["gbs"] / peaks["hbm_gbs"], "peak_source": peaks["source"],
+        "frac_of_spec_8000": kernel["gbs"] / 8000.0, "traffic": None, "traffic_source": None,
+        "bytes_per_launch": kernel["bytes"], "ms_per_launch": kernel["ms"],
+    }
+    source = TRAFFIC_SOURCES.get(kernel["kernel"])
+    captured = profile_traffic(*source) if source else None
+    if captured:
+        algorithmic, dram = captured
+        # the captured launch's DRAM bytes, scaled to this launch by the algorithmic bytes (traffic grows in
+        # proportion to the units processed)
+        entry["traffic"] = round(kernel["bytes"] * dram / algorithmic)
+        entry["traffic_source"] = f"{source[0]} ({source[1]}: {dram} DRAM bytes for {algorithmic} algorithmic)"
+    return entry
 
 
-def time_prefill_gemm(engine, runtime, peaks) -> dict:
-    """The prefill side of the path: the gate/up projection of the first layers at M = 2048 rows
-    (one prefill chunk) on the tcgen05 GEMM, device-timed back to back; dense-equivalent FLOPs."""
+def time_prefill_gemm(runtime, peaks, *, m, k, n, form, weights=None) -> dict:
+    """One prefill product on the tcgen05 GEMM, device-timed back to back over distinct weights.
+    ``form`` = "dual" (gate and up with the SwiGLU epilogue, two products), "affine" (unsigned
+    nibbles with fp16 zero points, w = (u - z) s) or "linear"."""
     from llmopt_b200 import dispatch
     from llmopt_b200.cuda_native import Batch, Buffer
 
-    config = engine.config
-    m, k, n = 2048, config.hidden, config.intermediate
     rng = np.random.default_rng(1)
     x = dispatch.Tensor(Buffer.of_array(runtime, rng.standard_normal((m, k)).astype(np.float16)), (m, k))
-    residual = dispatch.Tensor(Buffer.create(runtime, m * k * 2), (m, k))
-    output = dispatch.Tensor(Buffer.create(runtime, m * k * 2), (m, k))
     commands = Batch(runtime)
     context = dispatch.Context(runtime, batch=commands)
-    items = []
-    for layer in engine.layers[:4]:
-        dispatch.dispatch_w4a16_swiglu_ffn_command(
-            context, m=m, n=n, k=k, epsilon=config.epsilon, activation=x, residual=residual,
-            gate_weight=layer["gate"][0], gate_scale=layer["gate"][1], up_weight=layer["up"][0],
-            up_scale=layer["up"][1], down_weight=layer["down"][0], down_scale=layer["down"][1],
-            norm_weight=layer["ffn_norm"], output=output, reference_guards=False)
-    items = [item for item in commands.pending if item.name.startswith("llmopt_w4a16_dual_swiglu")]
+
+    def w4(rows, cols, low, high, zero=False):
+        packed = dispatch.Tensor(Buffer.of_array(runtime, rng.integers(0, 256, size=(rows, cols // 2), dtype=np.uint8)),
+                                 (rows, cols // 2), "uint8")
+        scale = dispatch.Tensor(Buffer.of_array(runtime, rng.uniform(low, high, size=(rows, cols // 64)).astype(np.float16)),
+                                (rows, cols // 64))
+        if not zero:
+            return packed, scale
+        zeros = dispatch.Tensor(Buffer.of_array(runtime, rng.uniform(6, 9, size=(rows, cols // 64)).astype(np.float16)),
+                                (rows, cols // 64))
+        return packed, scale, zeros
+
+    copies = max(2, min(4, (256 << 20) // max(n * k // 2, 1)))  # distinct weights so the L2 holds none of them
+    products = 1
+    if form == "dual":
+        products = 2
+        output = dispatch.Tensor(Buffer.create(runtime, m * k * 2), (m, k))
+        for index in range(copies):
+            layer = weights[index] if weights else None
+            gate = layer["gate"] if layer else w4(n, k, 0.005, 0.02)
+            up = layer["up"] if layer else w4(n, k, 0.005, 0.02)
+            down = layer["down"] if layer else w4(k, n, 0.005, 0.02)
+            norm = layer["ffn_norm"] if layer else dispatch.Tensor(Buffer.of_array(runtime, np.ones(k, np.float16)), (k,))
+            dispatch.dispatch_w4a16_swiglu_ffn_command(
+                context, m=m, n=n, k=k, epsilon=1e-5, activation=x, residual=x, gate_weight=gate[0], gate_scale=gate[1],
+                up_weight=up[0], up_scale=up[1], down_weight=down[0], down_scale=down[1], norm_weight=norm,
+                output=output, reference_guards=False)
+        items = [item for item in commands.pending if item.name.startswith("llmopt_w4a16_dual_swiglu")]
+    else:
+        output = dispatch.Tensor(Buffer.create(runtime, m * n * 2), (m, n))
+        for _ in range(copies):
+            if form == "affine":
+                packed, scale, zeros = w4(n, k, 0.002, 0.01, zero=True)
+                dispatch.dispatch_w4a16_linear_affine(context, input=x, weight=packed, scale=scale, zero=zeros, output=output)
+            else:
+                packed, scale = w4(n, k, 0.002, 0.01)
+                dispatch.dispatch_w4a16_linear(context, input=x, weight=packed, scale=scale, output=output)
+        items = list(commands.pending)
     name = items[0].name
     milliseconds = runtime.time_dispatches(items, warmup=1, iterations=3)
     commands.abort()
-    tflops = 2.0 * 2 * m * k * n / milliseconds / 1e9
-    return {"kernel": name, "m": m, "k": k, "n": n, "products": 2, "ms": milliseconds, "bound": "tensor",
-            "achieved": tflops, "unit": "TFLOP/s", "peak": peaks["bf16_tflops"], "frac": tflops / peaks["bf16_tflops"],
-            "peak_sustained": peaks.get("bf16_tflops_sustained"), "peak_source": peaks["source"]}
+    tflops = 2.0 * products * m * k * n / milliseconds / 1e9
+    return {"kernel": name, "form": form, "m": m, "k": k, "n": n, "products": products, "ms": milliseconds,
+            "bound": "tensor", "achieved": tflops, "unit": "TFLOP/s", "peak": peaks["bf16_tflops"],
+            "frac": tflops / peaks["bf16_tflops"], "peak_sustained": peaks.get("bf16_tflops_sustained"),
+            "frac_of_sustained": tflops / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"]}
 
 
-def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
-    from llmopt_b200 import cuda_native
-    from llmopt_b200.decode_engine import DecodeEngine
-    from llmopt_b200.model import decode_bytes_per_token, random_weights
+def time_baseline_mode(runtime, peaks) -> dict:
+    """The zero-point / group-32 input mode of the stated configurations, timed alone: the decode
+    GEMV on unsigned nibbles with fp16 zero points (w = (u - z) s) at the gate shape, and the
+    paged attention over a Q8 cache with one scale per 32 elements."""
+    from llmopt_b200 import kernel_bench
 
-    # N > 1: tensor parallel when the model splits over N ranks (every rank decodes the same
-    # sequences with its share of every layer), else one independent replica of the whole model
-    # per GPU (no exchange on the data path).
-    runtime = cuda_native.Runtime(local)
-    whole_config = config
-    fast = config.hidden >= 2048
-    weights = random_weights(config, seed=0, fast=fast)
-    capacity = args.context + args.steps * 2 + args.warmup * 2 + 16
-    tensor_parallel_mode = tensor_parallel_run(args, config)
-    if tensor_parallel_mode:
-        from llmopt_b200 import tensor_parallel
+    out = {}
+    for label, fields in (
+            ("gemv_affine_m1", dict(op="linear_affine", m=1, k=4096, n=14336)),
+            ("gemv_contract_m1", dict(op="linear", m=1, k=4096, n=14336)),
+            ("attention_group32_b8", dict(op="attention", m=8, group=32, layers=32)),
+            ("attention_group64_b8", dict(op="attention", m=8, group=64, layers=32))):
+        options = types.SimpleNamespace(op="linear", m=1, k=4096, n=14336, heads=32, kv_heads=8, dim=128, group=64,
+                                        layers=2, past=8192)
+        options.__dict__.update(fields)
+        item, nbytes, keep = kernel_bench.build_item(runtime, options)
+        milliseconds = runtime.time_dispatch(item, warmup=3, iterations=20, flush_l2=True)
+        out[label] = {"kernel": item.name, "ms": round(milliseconds, 5), "bytes": nbytes,
+                      "gbs": round(nbytes / milliseconds / 1e6, 1),
+                      "frac": round(nbytes / milliseconds / 1e6 / peaks["hbm_gbs"], 3),
+                      "mode": "isolated launch, L2 flushed before each"}
+        del keep
+    return out
 
-        exchange_group = tensor_parallel.ExchangeGroup.create(
-            runtime, rank, world, max(args.batch * config.hidden * 4, min(args.batch, 32) * 256 * 8), 7,
-            tensor_parallel.torch_all_gather())
-        shard = tensor_parallel.shard_weights(config, weights, rank, world)
-        del weights
-        weights = shard
-        config = tensor_parallel.local_config(config, world)
-        engine = DecodeEngine(runtime, config, weights, batch=args.batch, capacity=capacity, group=exchange_group)
-    else:
-        engine = DecodeEngine(runtime, config, weights, batch=args.batch, capacity=capacity)
-    del weights
-    engine.fill_cache_random(args.context, seed=0)
-    engine.build(args.context)
+
+# ---- decode measurement ---------------------------------------------------------------------------
+
+def measure_decode(engine, runtime, args, group, *, context: int, jobs: int, device_index: int, peaks: dict) -> dict:
+    """Device-timed chained decode (median of REPETITIONS x K steps, max over ranks), the host-driven
+    end-to-end loop, the per-kernel table and the roofline of the dominant kernel."""
+    batch, config = engine.batch, engine.config
     rng = np.random.default_rng(0)
-    first = rng.integers(0, config.vocabulary, size=args.batch).tolist()
+    first = rng.integers(0, config.vocabulary, size=batch).tolist()
+    warmup = max(args.warmup, 3)
+    engine.generate_chained(first, context, warmup)
+    sampler = ClockSampler(device_index)
+    repetitions = []
+    token_streams = []
+    for _ in range(REPETITIONS):
+        if group is not None:
+            group.barrier()
+        runtime.synchronize()
+        tokens, elapsed_ms = engine.generate_chained(first, context, args.steps)
+        runtime.synchronize()
+        if group is not None:
+            import torch
 
-    # device-timed region: K chained replays, CUDA events on the launching stream
-    engine.generate_chained(first, args.context, max(args.warmup, 3))
-    sampler = ClockSampler(local)
+            slowest = torch.tensor([elapsed_ms], dtype=torch.float64)
+            group.all_reduce(slowest, op=group.ReduceOp.MAX)  # device-timed on every rank, max over ranks
+            elapsed_ms = float(slowest.item())
+        repetitions.append(elapsed_ms)
+        token_streams.append(tokens)
     if group is not None:
-        group.barrier()
-    runtime.synchronize()
-    _, elapsed_ms = engine.generate_chained(first, args.context, args.steps)
-    runtime.synchronize()
-    if group is not None:
-        import torch
-
-        slowest = torch.tensor([elapsed_ms], dtype=torch.float64)
-        group.all_reduce(slowest, op=group.ReduceOp.MAX)  # device-timed on every rank, max over ranks
-        elapsed_ms = float(slowest.item())
         group.barrier()
     clocks = sampler.stop()
+    elapsed_ms = statistics.median(repetitions)
     ms_per_step = elapsed_ms / args.steps
-    jobs = 1 if tensor_parallel_mode else world  # tensor parallel: all GPUs decode the same sequences
-    value = jobs * args.batch * 1000.0 / ms_per_step
+    value = jobs * batch * 1000.0 / ms_per_step
 
     # end to end: the host drives every token (token id in, H2D; next id out, D2H)
     tokens = first
-    for step in range(max(args.warmup, 3)):
-        tokens = engine.step(tokens, args.context + step)
+    for step in range(warmup):
+        tokens = engine.step(tokens, context + step)
     runtime.synchronize()
     start = time.perf_counter()
     for step in range(args.steps):
-        tokens = engine.step(tokens, args.context + step)
+        tokens = engine.step(tokens, context + step)
     runtime.synchronize()
     e2e_seconds = time.perf_counter() - start
     if group is not None:
@@ -356,37 +517,28 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         slowest = torch.tensor([e2e_seconds], dtype=torch.float64)
         group.all_reduce(slowest, op=group.ReduceOp.MAX)
         e2e_seconds = float(slowest.item())
-    e2e_value = jobs * args.batch * args.steps / e2e_seconds
-    h2d = 16 + (8 * args.batch if args.batch > 1 else 0)
-    d2h = 4 + (4 * args.batch if args.batch > 1 else 0)
+    e2e_value = jobs * batch * args.steps / e2e_seconds
+    h2d = 16 + (8 * batch if batch > 1 else 0)
+    d2h = 4 + (4 * batch if batch > 1 else 0)
 
-    peaks = measured_peaks()
     kernels = time_kernels(engine, runtime)
     dominant = kernels.get("gate_up_swiglu") or next(iter(kernels.values()))
-    if args.batch >= 8 and "paged_attention_q8" in kernels:
+    if batch >= 8 and "paged_attention_q8" in kernels:
         attention_ms = kernels["paged_attention_q8"]["ms"] * config.attention_layers
         if attention_ms > dominant["ms"] * len(config.layers):
             dominant = kernels["paged_attention_q8"]
-    step_bytes = decode_bytes_per_token(config, args.batch, args.context)
-    result = {
-        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak" if world > 1 and not tensor_parallel_mode else "strong",
-        "vs_baseline": None, "dtype": "w4a16 (int4 weights, f16 activations, f32 accumulate); q8 KV",
-        "data": "synthetic", "config": workload_config(args, whole_config),
+    from llmopt_b200.model import decode_bytes_per_token
+
+    step_bytes = decode_bytes_per_token(config, batch, context)
+    return {
+        "value": value, "unit": "tokens/s", "ms_per_step": ms_per_step, "batch": batch, "context": context,
+        "repetitions_ms": [round(v, 4) for v in repetitions],
+        "tokens_identical_across_repetitions": all(stream == token_streams[0] for stream in token_streams),
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": (engine.plan.kernel_count() + 1) * args.steps,
         "kernels_per_step": engine.plan.kernel_count(),
         "clocks": clocks,
-        "roofline": {
-            "bound": "hbm", "kernel": dominant["name"], "achieved": dominant["gbs"], "peak": peaks["hbm_gbs"],
-            "unit": "GB/s", "frac": dominant["gbs"] / peaks["hbm_gbs"], "peak_source": peaks["source"],
-            "frac_of_spec_8000": dominant["gbs"] / 8000.0,
-            "traffic": round(dominant["bytes"] * TRAFFIC_RATIO[dominant["kernel"]][0])
-            if dominant["kernel"] in TRAFFIC_RATIO else None,
-            "traffic_source": TRAFFIC_RATIO.get(dominant["kernel"], (None, None))[1],
-            "bytes_per_launch": dominant["bytes"], "ms_per_launch": dominant["ms"],
-        },
+        "roofline": roofline_entry(dominant, peaks),
         "step_roofline": {
             "algorithmic_bytes_per_step": step_bytes["total"], "weights": step_bytes["weights"],
             "attention": step_bytes["attention"], "achieved_gbs": step_bytes["total"] / ms_per_step / 1e6,
@@ -394,14 +546,188 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         },
         "kernels": {k: {"ms": round(v["ms"], 5), "gbs": round(v["gbs"], 1), "frac": round(v["gbs"] / peaks["hbm_gbs"], 3)}
                     for k, v in kernels.items()},
+        "_tokens": token_streams[0],
     }
-    if config.hidden >= 2048 and world == 1:
-        result["prefill_gemm"] = time_prefill_gemm(engine, runtime, peaks)
+
+
+def small_model_leg(runtime, args, name: str, peaks: dict, batch: int = 1) -> dict:
+    """A launch-latency-bound model of the stated configurations: tokens/s next to the floor the
+    launches alone set (the same plan's kernel count times the measured cost of an empty dependent
+    launch is not separable on the device, so the floor reported is bytes / HBM peak)."""
+    from llmopt_b200 import model
+    from llmopt_b200.decode_engine import DecodeEngine
+
+    config = getattr(model, WORKLOADS[name])
+    context = DEFAULT_CONTEXT[name]
+    weights = model.random_weights(config, seed=0, fast=True)
+    engine = DecodeEngine(runtime, config, weights, batch=batch, capacity=context + 8 * (args.steps + args.warmup) + 64)
+    del weights
+    engine.fill_cache_random(context, seed=0)
+    engine.build(context)
+    first = np.random.default_rng(0).integers(0, config.vocabulary, size=batch).tolist()
+    engine.generate_chained(first, context, max(args.warmup, 3))
+    times = []
+    for _ in range(REPETITIONS):
+        _, elapsed = engine.generate_chained(first, context, args.steps)
+        times.append(elapsed / args.steps)
+    ms_per_step = statistics.median(times)
+    step_bytes = model.decode_bytes_per_token(config, batch, context)
+    return {
+        "workload": f"{config.name}, batch {batch}, context {context}", "value": batch * 1000.0 / ms_per_step,
+        "unit": "tokens/s", "ms_per_step": ms_per_step, "kernels_per_step": engine.plan.kernel_count(),
+        "us_per_kernel": 1000.0 * ms_per_step / engine.plan.kernel_count(),
+        "algorithmic_bytes_per_step": step_bytes["total"],
+        "hbm_floor_ms": step_bytes["total"] / peaks["hbm_gbs"] / 1e6,
+        "frac_of_hbm": step_bytes["total"] / ms_per_step / 1e6 / peaks["hbm_gbs"],
+        "bound": "launch latency: the whole step moves less than the L2 holds per launch",
+    }
+
+
+def tensor_parallel_check(args, whole_config, whole_weights, runtime, rank, world, group, timed_tokens) -> dict:
+    """Correctness of the tensor-parallel run on real peers: (1) every rank produced the same token
+    stream in the timed run; (2) a short decode from an empty cache gives, on every rank, the same
+    tokens, and its final hidden state equals an unsharded single-GPU run of the same seeded
+    weights (rank 0) within 2e-3 of the state's scale."""
+    from llmopt_b200 import tensor_parallel
+    from llmopt_b200.decode_engine import DecodeEngine
+
+    gathered = [None] * world
+    group.all_gather_object(gathered, list(timed_tokens))
+    ranks_identical = all(stream == gathered[0] for stream in gathered)
+
+    steps, batch = 16, 1
+    exchange_group = tensor_parallel.ExchangeGroup.create(
+        runtime, rank, world, max(batch * whole_config.hidden * 4, 256 * 8), 7, tensor_parallel.torch_all_gather())
+    shard = tensor_parallel.shard_weights(whole_config, whole_weights, rank, world)
+    engine = DecodeEngine(runtime, tensor_parallel.local_config(whole_config, world), shard, batch=batch, capacity=64,
+                          group=exchange_group)
+    del shard
+    engine.build(0)
+    first = [int(np.random.default_rng(7).integers(0, whole_config.vocabulary))]
+    sharded_tokens, hidden_states = [], []
+    tokens = first
+    for step in range(steps):
+        tokens = engine.step(tokens, step)
+        sharded_tokens.append(int(tokens[0]))
+        hidden_states.append(engine.final_hidden.buffer.to_numpy(np.float16).astype(np.float64))
+    group.barrier()
+    streams = [None] * world
+    group.all_gather_object(streams, sharded_tokens)
+    result = {"timed_tokens_identical_across_ranks": ranks_identical,
+              "short_run_tokens_identical_across_ranks": all(stream == streams[0] for stream in streams),
+              "steps": steps}
+    if rank == 0:
+        single = DecodeEngine(runtime, whole_config, whole_weights, batch=batch, capacity=64)
+        single.build(0)
+        tokens, equal_prefix, worst = first, 0, 0.0
+        diverged = False
+        for step in range(steps):
+            # teacher-forced with the sharded run's tokens so every step compares the same input
+            tokens = single.step(first if step == 0 else [sharded_tokens[step - 1]], step)
+            reference_hidden = single.final_hidden.buffer.to_numpy(np.float16).astype(np.float64)
+            scale = max(float(np.max(np.abs(reference_hidden))), 1e-6)
+            worst = max(worst, float(np.max(np.abs(hidden_states[step] - reference_hidden))) / scale)
+            if not diverged and int(tokens[0]) == sharded_tokens[step]:
+                equal_prefix += 1
+            else:
+                diverged = True
+        result.update({"hidden_max_rel_err_vs_single_gpu": worst, "hidden_tolerance": 2e-3,
+                       "tokens_equal_to_single_gpu": equal_prefix, "hidden_within_tolerance": worst <= 2e-3})
+        del single
+    group.barrier()
+    result["tokens_match"] = bool(result["timed_tokens_identical_across_ranks"]
+                                  and result["short_run_tokens_identical_across_ranks"]
+                                  and result.get("hidden_within_tolerance", True))
+    return result
+
+
+def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
+    from llmopt_b200 import cuda_native
+    from llmopt_b200.decode_engine import DecodeEngine
+    from llmopt_b200.model import random_weights
+
+    # N > 1: tensor parallel when the model splits over N ranks (every rank decodes the same
+    # sequences with its share of every layer), else one independent replica of the whole model
+    # per GPU (no exchange on the data path).
+    runtime = cuda_native.Runtime(local)
+    whole_config = config
+    fast = config.hidden >= 2048
+    whole_weights = random_weights(config, seed=0, fast=fast)
+    weights = whole_weights
+    # the repetitions and the end-to-end loop restart at `context`; only the longest run matters
+    capacity = args.context + max(args.steps, args.warmup, 3) + 16
+    tensor_parallel_mode = tensor_parallel_run(args, config)
+    peaks = measured_peaks()
+    extra_legs = not args.no_extra_legs and args.workload == "llama3-8b" and args.batch == 1
+
+    def make_engine(batch, share=None):
+        if tensor_parallel_mode:
+            from llmopt_b200 import tensor_parallel
+
+            exchange_group = tensor_parallel.ExchangeGroup.create(
+                runtime, rank, world, max(batch * whole_config.hidden * 4, min(batch, 32) * 256 * 8), 7,
+                tensor_parallel.torch_all_gather())
+            local_weights = None if share is not None else tensor_parallel.shard_weights(whole_config, whole_weights, rank, world)
+            return DecodeEngine(runtime, tensor_parallel.local_config(whole_config, world), local_weights, batch=batch,
+                                capacity=capacity, group=exchange_group, share_weights_of=share)
+        return DecodeEngine(runtime, whole_config, None if share is not None else weights, batch=batch,
+                            capacity=capacity, share_weights_of=share)
+
+    engine = make_engine(args.batch)
+    engine.fill_cache_random(args.context, seed=0)
+    engine.build(args.context)
+    jobs = 1 if tensor_parallel_mode else world  # tensor parallel: all GPUs decode the same sequences
+    head = measure_decode(engine, runtime, args, group, context=args.context, jobs=jobs, device_index=local, peaks=peaks)
+    timed_tokens = head.pop("_tokens")
+    result = {
+        "metric": METRIC, "value": head["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+        "scaling": scaling_label(args, whole_config),
+        "vs_baseline": None, "dtype": "w4a16 (int4 weights, f16 activations, f32 accumulate); q8 KV",
+        "data": "synthetic", "config": workload_config(args, whole_config),
+        "repetitions": REPETITIONS, "timing": f"median of {REPETITIONS} repetitions of the {args.steps} steps",
+    }
+    for key in ("e2e", "gpu_launches", "kernels_per_step", "clocks", "roofline", "step_roofline", "kernels",
+                "repetitions_ms", "tokens_identical_across_repetitions"):
+        result[key] = head[key]
+
+    if extra_legs:
+        # the metric's second batch size, same weights, same process
+        wide = make_engine(32, share=engine)
+        wide.fill_cache_random(args.context, seed=0)
+        wide.build(args.context)
+        leg = measure_decode(wide, runtime, args, group, context=args.context, jobs=jobs, device_index=local, peaks=peaks)
+        leg.pop("_tokens")
+        leg["config"] = workload_config(args, whole_config, batch=32)
+        result["batch32"] = leg
+        result["gpu_launches"] += leg["gpu_launches"]
+        del wide
+
+    if tensor_parallel_mode:
+        result["tp_check"] = tensor_parallel_check(args, whole_config, whole_weights, runtime, rank, world, group, timed_tokens)
+        result["tokens_match"] = result["tp_check"]["tokens_match"]
+    del whole_weights, weights
+
+    if world == 1 and config.hidden >= 2048:
+        result["prefill_gemm"] = time_prefill_gemm(runtime, peaks, m=2048, k=config.hidden, n=config.intermediate,
+                                                   form="dual", weights=engine.layers[:4])
+    if world == 1 and extra_legs:
+        del engine
+        sweep = []
+        for m in (512, 2048, 8192):
+            sweep.append(time_prefill_gemm(runtime, peaks, m=m, k=8192, n=28672, form="affine"))   # gate or up
+            sweep.append(time_prefill_gemm(runtime, peaks, m=m, k=28672, n=8192, form="affine"))   # down
+        sweep.append(time_prefill_gemm(runtime, peaks, m=2048, k=8192, n=28672, form="linear"))
+        result["prefill_gemm_c5"] = sweep
+        result["baseline_mode"] = time_baseline_mode(runtime, peaks)
+        result["smollm2_135m"] = small_model_leg(runtime, args, "smollm2-135m", peaks)
+        result["lfm25_350m"] = small_model_leg(runtime, args, "lfm2.5-350m", peaks)
+        result["lfm25_350m_batch16"] = small_model_leg(runtime, args, "lfm2.5-350m", peaks, batch=16)
     if group is not None:
         group.barrier()  # no rank leaves (and unmaps its exchange region) while a peer still runs
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        baseline = cpu_reference_rate(config, args.batch)
-        result["cpu_baseline"] = {k: baseline[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        baseline = cpu_reference_rate(whole_config, args.batch, args.context)
+        result["cpu_baseline"] = {k: baseline[k] for k in ("value", "unit", "cores", "kind", "sample", "single_thread", "linears_only")}
     return result
 
 
@@ -415,6 +741,8 @@ def main() -> None:
     parser.add_argument("--batch", type=int, default=1)
     parser.add_argument("--context", type=int, default=None)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-extra-legs", action="store_true",
+                        help="only the headline batch: no batch-32, small-model, prefill-sweep or input-mode legs")
     parser.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
                         help="with --gpus N > 1: tensor parallel (when the model splits over N) or N replicas")
     args = parser.parse_args()

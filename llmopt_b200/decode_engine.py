@@ -32,11 +32,13 @@ from .quantize import rope_tables
 
 
 class DecodeEngine:
-    def __init__(self, runtime: Runtime, config: ModelConfig, weights: dict, *, batch: int = 1, capacity: int = 1024,
-                 group=None):
+    def __init__(self, runtime: Runtime, config: ModelConfig, weights: Optional[dict], *, batch: int = 1,
+                 capacity: int = 1024, group=None, share_weights_of: Optional["DecodeEngine"] = None):
         """``config`` and ``weights`` are the whole model's, or, with ``group`` (an
         ``ExchangeGroup`` of more than one rank), this rank's ``tensor_parallel.local_config`` /
-        ``shard_weights`` share; the embedding table is always whole."""
+        ``shard_weights`` share; the embedding table is always whole.  ``share_weights_of``:
+        another engine of the same model and capacity on the same runtime whose uploaded weights
+        and RoPE tables this one binds instead of uploading its own (``weights`` is then unused)."""
         self.runtime, self.config, self.batch, self.capacity = runtime, config, batch, capacity
         self.group = group  # a group of one rank still takes the exchange kernels (single-GPU check of the plan)
         self.full_vocabulary = config.vocabulary * (self.group.world if self.group else 1)
@@ -44,7 +46,15 @@ class DecodeEngine:
                              group_size=config.kv_group_size)
         self.cache = dispatch.Cache(runtime, self.layout, token_capacity=batch * capacity)
         self._keep = []
-        self._upload(weights)
+        if share_weights_of is not None:
+            if share_weights_of.runtime is not runtime or share_weights_of.capacity < capacity:
+                raise ValueError("weights can only be shared between engines of one runtime and capacity")
+            other = share_weights_of
+            self.embedding, self.lm_head, self.final_norm, self.layers = (
+                other.embedding, other.lm_head, other.final_norm, other.layers)
+            self.cos_table, self.sin_table = other.cos_table, other.sin_table
+        else:
+            self._upload(weights)
         self._workspace()
         self.plan = None
         self.records = None
@@ -263,6 +273,7 @@ class DecodeEngine:
             run("llmopt_chain_token_ids", [self.out_tokens.buffer, self.token_ids.buffer], parameters.u32s([batch]),
                 (batch, 1, 1))
         self.records = list(commands.pending)
+        self.final_hidden = current  # [batch, hidden] f16: the last block's output, input of the LM head
         self._context = context
         commands.abort()
         row = self.config.head_dim * 2

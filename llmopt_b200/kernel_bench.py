@@ -4,7 +4,7 @@ as achieved GB/s over the algorithmic bytes.  The counterpart of the reference's
 stand-alone Metal tile probes (bench/metal_q4_tile_probe.swift); also the small,
 self-terminating command used for profiler captures.
 
-  python -m llmopt_b200.kernel_bench --op linear|qkv|gate_up|down|lm_head|attention \\
+  python -m llmopt_b200.kernel_bench --op linear|linear_affine|qkv|gate_up|down|lm_head|attention \\
          --m 1 --k 4096 --n 14336 [--heads 32 --kv-heads 8 --dim 128 --past 8192] [--iters 20]
 """
 
@@ -44,6 +44,14 @@ def build_item(runtime, args):
         dispatch.dispatch_w4a16_linear(context, input=_f16(runtime, rng, (m, k)), weight=w, scale=s,
                                        output=_f16(runtime, rng, (m, n)))
         nbytes = weight_bytes(n, k) + m * k * 2 + m * n * 2
+    elif args.op == "linear_affine":
+        # unsigned nibbles with fp16 zero points, w = (u - z) s (the stated configurations' input mode)
+        w, s = _w4(runtime, rng, n, k)
+        zero = rng.uniform(6, 9, size=(n, k // 64)).astype(np.float16)
+        dispatch.dispatch_w4a16_linear_affine(
+            context, input=_f16(runtime, rng, (m, k)), weight=w, scale=s,
+            zero=dispatch.Tensor(Buffer.of_array(runtime, zero), zero.shape, "float16"), output=_f16(runtime, rng, (m, n)))
+        nbytes = weight_bytes(n, k) + n * (k // 64) * 2 + m * k * 2 + m * n * 2
     elif args.op == "qkv":
         nq, nkv = args.heads * args.dim, args.kv_heads * args.dim
         (qw, qs), (kw, ks), (vw, vs) = _w4(runtime, rng, nq, k), _w4(runtime, rng, nkv, k), _w4(runtime, rng, nkv, k)
@@ -132,7 +140,7 @@ def main() -> None:
     runtime = cuda_native.Runtime()
     item, nbytes, _keep = build_item(runtime, args)
     result = {"op": args.op, "kernel": item.name, "m": args.m, "k": args.k, "n": args.n, "algorithmic_bytes": nbytes}
-    products = {"linear": 1, "gate_up": 2, "down": 1, "lm_head": 1}.get(args.op)
+    products = {"linear": 1, "linear_affine": 1, "gate_up": 2, "down": 1, "lm_head": 1}.get(args.op)
     flops = 2.0 * args.m * args.k * args.n * products if products else None
     if args.copies > 1:
         # distinct operands per launch, launched back to back: in-plan conditions (cold

@@ -127,6 +127,12 @@ def w4a16_linear_f64(x, packed, scale, zero=None):
     return y
 
 
+def set_threads(threads: int) -> int:
+    """Sets the OpenMP thread count of the ``_mt`` functions; returns the count in force."""
+    lib().orc_set_threads(ctypes.c_int(int(threads)))
+    return int(lib().orc_max_threads())
+
+
 def w4a16_linear_cols_mt(x, packed, scale, col_begin, col_end):
     """Timing helper: reference loop nest over a column range, OpenMP threads."""
     x, packed, scale = _f16(x), _u8(packed), _f16(scale)

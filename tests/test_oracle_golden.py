@@ -166,3 +166,49 @@ def test_lm_head_tie_and_msl_order(oracle):
     a = oracle.w4a16_linear(x, packed, scale[:1].repeat(64, 0)).astype(np.float64)
     b = oracle.w4a16_linear(x, packed, scale[:1].repeat(64, 0), order="msl_m1").astype(np.float64)
     assert np.max(np.abs(a - b)) <= 2e-3 * np.max(np.abs(a))
+
+
+@pytest.mark.parametrize("hq,hkv,dim,group,past", [(6, 2, 64, 64, 37), (8, 8, 128, 32, 21), (4, 1, 64, 32, 1)])
+def test_paged_attention_equals_dense_attention_on_the_unpacked_pool(oracle, hq, hkv, dim, group, past):
+    """The reference has no CPU paged attention (lib/cpu.ml:995-996); its dense attention
+    (lib/cpu.ml:606-717) on the dequantised cache is the same function.  This pins what the
+    degenerate known-answer vector cannot: the K/V dequantisation, the scale index
+    segment_offset/group + kv_head*groups_per_head + d/group, the slot indirection and the layer
+    offsets of the paged restatement (lib/metal_cache_source.ml:382-489)."""
+    from helpers import random_pool
+    from llmopt_b200.kv_cache import AttentionLayer, Layout
+
+    rng = np.random.default_rng(hq * 100 + past)
+    layout = Layout([AttentionLayer(hkv, dim)] * 3, group_size=group)
+    capacity = past + 4
+    pool = random_pool(rng, capacity, layout.bytes_per_token, layout.token_elements, group, scale_range=(0.004, 0.03))
+    slots = rng.permutation(capacity)[:past].astype(np.uint32)
+    region = layout.attentions[1]
+    query = (rng.standard_normal((1, hq, 1, dim)) * 2).astype(np.float16)
+    current_key = rng.standard_normal((1, hkv, 1, dim)).astype(np.float16)
+    current_value = rng.standard_normal((1, hkv, 1, dim)).astype(np.float16)
+    scale = float(np.float32(1 / np.sqrt(dim)))
+    params = oracle.paged_params_bytes(batches=1, query_heads=hq, kv_heads=hkv, past_length=past, head_dim=dim,
+                                       mask_batches=0, mask_heads=0, token_elements=layout.token_elements,
+                                       key_offset=region.key_offset, value_offset=region.value_offset,
+                                       group_size=group, token_stride=layout.bytes_per_token, scale=scale,
+                                       query_length=1, mask_dtype=0)
+    paged = oracle.attention_q8_paged(query, current_key, current_value, pool, slots, None, params)
+    fields = dict(heads=hkv, head_dim=dim, group_size=group, token_elements=layout.token_elements,
+                  token_stride=layout.bytes_per_token)
+    keys = oracle.cache_unpack_attention_q8(pool, slots, segment_offset=region.key_offset, **fields)      # [hkv, past, D]
+    values = oracle.cache_unpack_attention_q8(pool, slots, segment_offset=region.value_offset, **fields)
+    keys = np.concatenate([keys, current_key[0]], axis=1)[None]
+    values = np.concatenate([values, current_value[0]], axis=1)[None]
+    dense = oracle.attention_dense(query, keys, values, None, causal=0, scale=scale, kv_heads=hkv, token_first_output=1)
+    assert paged.shape == dense.shape == (1, 1, hq, dim)
+    error = np.max(np.abs(paged.astype(np.float64) - dense.astype(np.float64))) / np.max(np.abs(dense.astype(np.float64)))
+    assert error <= 2e-3, error
+    # and the cross-check has teeth: another layer's segment gives a different answer
+    other = layout.attentions[2]
+    wrong = oracle.paged_params_bytes(batches=1, query_heads=hq, kv_heads=hkv, past_length=past, head_dim=dim,
+                                      mask_batches=0, mask_heads=0, token_elements=layout.token_elements,
+                                      key_offset=other.key_offset, value_offset=other.value_offset,
+                                      group_size=group, token_stride=layout.bytes_per_token, scale=scale,
+                                      query_length=1, mask_dtype=0)
+    assert not np.array_equal(oracle.attention_q8_paged(query, current_key, current_value, pool, slots, None, wrong), paged)
