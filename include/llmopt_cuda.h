@@ -218,6 +218,28 @@ int llmopt_cuda_ring_destroy(llmopt_cuda_ring* ring);
 /* caml_llmopt_f16_argmax (:2565-2579): argmax over `count` halves in host memory. */
 int64_t llmopt_cuda_f16_argmax(const void* halves, size_t count);
 
+/* caml_llmopt_sample_f16_native / _bytecode (:2629-2771, bound at lib/sampling.ml:192-194):
+ * samples one token from `count` fp16 logits in HOST memory.  temperature <= 1e-4 or
+ * top_k == 1 is greedy (first maximum).  Otherwise the top_k largest logits (64 when
+ * top_k <= 0, at most 256) are weighted by exp((logit - max) / temperature) in fp32, cut by
+ * min_p (tail below min_p times the best probability) and then by top_p (shortest prefix
+ * whose probability reaches top_p), and one xoroshiro128+ draw seeded from `seed` picks
+ * among them; seed 0 takes a clock value.  The same seed gives the same token as the
+ * reference's sampler. */
+int llmopt_cuda_sample_f16(const void* halves, size_t count, double temperature, int top_k, double top_p,
+                           double min_p, uint64_t seed, int64_t* token);
+
+/* caml_llmopt_metal_measure_hardware (:477-611, bound at bin/hardware_probe.ml:11): device
+ * name, the largest thread block, the median launch-to-completion time of an empty kernel
+ * (host clock, seconds) and the median bandwidth of a device-to-device copy of `bytes`
+ * bytes (2 * bytes / device time, GB/s) over `repeats` samples after `warmup`.  Requires
+ * warmup >= 0, repeats > 0, bytes >= 4096 and a multiple of 16 (else
+ * LLMOPT_CUDA_INVALID_ARGUMENT).  `device` < 0 probes the current device.  Only queries and
+ * two small kernels: no device setting is read-modified or changed. */
+int llmopt_cuda_measure_hardware(int device, int warmup, int repeats, int64_t bytes, char* name,
+                                 size_t name_capacity, int* max_threads_per_block, double* dispatch_seconds,
+                                 double* bandwidth_gbps);
+
 /* ---- second boundary: the Python single-op entry ------------------------------------ */
 
 /* native/metal_runtime.cpp:58-136 `w4a16_linear(input, packed_weight, scale, bias)`

@@ -29,6 +29,8 @@
 // Every wait on an mbarrier is bounded: after kSpinLimit polls the warp records
 // an error word the host checks and goes on without waiting, still taking part in
 // every later barrier, so the kernel always terminates.
+#include <cstdlib>
+
 #include "w4a16_gemv_device.cuh"
 
 namespace llmopt {
@@ -95,6 +97,36 @@ __device__ __forceinline__ void nibbles_biased(uint32_t word, uint32_t& even_pai
   odd_pair = lop3_and_xor(word, 0x00F000F0u, 0x54805480u);
 }
 
+// D = A B + C with C in registers of its own (the first MMA of a group takes the group's bias
+// term as C, so the sum needs no seeding moves).
+__device__ __forceinline__ void mma_16816_from(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1, float c0, float c1, float c2, float c3) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%11,%12,%13};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
+}
+
+// The GPW consecutive fp16 group scales of one weight row as floats: one shared-memory load.
+template <int GPW>
+__device__ __forceinline__ void load_scales(const unsigned char* address, float (&scales)[GPW]) {
+  if (GPW == 1) {
+    scales[0] = __half2float(*reinterpret_cast<const __half*>(address));
+  } else if (GPW == 2) {
+    const float2 pair = __half22float2(*reinterpret_cast<const __half2*>(address));
+    scales[0] = pair.x;
+    scales[GPW - 1] = pair.y;
+  } else {
+    const uint2 raw = *reinterpret_cast<const uint2*>(address);
+    const float2 low = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+    const float2 high = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+    scales[0] = low.x;
+    scales[1 % GPW] = low.y;
+    scales[2 % GPW] = high.x;
+    scales[3 % GPW] = high.y;
+  }
+}
+
 // The LM-head form (fp32 candidates, tens of tiles per CTA, light epilogue) gains from a fourth
 // resident CTA per SM (more warps to hide the LOP3 -> MMA latency: 109 -> 87 us at 128256 x 4096);
 // the projections, with two or three tiles per CTA, do not.
@@ -110,9 +142,15 @@ template <int NT, int EPI> constexpr int kDenseResidency = NT == 1 ? (EPI == kEp
 // most two CTA slots per SM take the RES = 2 build of the one-batch-tile forms: with up to 112
 // registers the compiler keeps several groups' loads and LOP3 -> MMA chains in flight per warp
 // (o_proj at 4096 x 4096: 6.8 -> 5.4 us).
-template <int NT, int NMAT, int EPI, bool SMALLX, int GPW, int RES = kDenseResidency<NT, EPI>>
+//
+// ONE: the activation block is a single row (the decode shape).  Only column 0 of every MMA result
+// is a real output then, so the kernel keeps two accumulators per matrix instead of four, applies two
+// scale FMAs per group instead of four, reads one bias term per group instead of two, and hands
+// the bias to the first MMA of a group as its C operand (no register moves to seed the sum).
+template <int NT, int NMAT, int EPI, bool SMALLX, int GPW, int RES = kDenseResidency<NT, EPI>, bool ONE = false>
 __global__ void __launch_bounds__(kThreads, RES) w4a16_gemv_pipe_kernel(const GemvProblem p, const uint32_t stage_count,
                                                                    uint32_t* error_word) {
+  static_assert(!ONE || (SMALLX && NT == 1), "the one-row form is a staged-activation, one-batch-tile form");
   extern __shared__ __align__(16) unsigned char shared[];
   // The next kernel of the stream may start its launch now; the producer warp below
   // streams weights (which no kernel writes) without waiting for the previous kernel,
@@ -363,44 +401,44 @@ __global__ void __launch_bounds__(kThreads, RES) w4a16_gemv_pipe_kernel(const Ge
     for (uint32_t chunk = 0; chunk < chunks_per_tile; ++chunk) {
       if (!aborted) aborted = !mbarrier_wait(full_base + stage_index * 8u, parity, error_word);
       const unsigned char* stage = stages + stage_index * (NMAT * kStageBytes);
+      float stage_scale_a[NMAT][GPW], stage_scale_b[NMAT][GPW];  // ONE: this warp's group scales, rows r and r + 8
+      if (ONE) {
+#pragma unroll
+        for (int a = 0; a < NMAT; ++a) {
+          load_scales<GPW>(stage + a * kStageBytes + scale_offset, stage_scale_a[a]);
+          load_scales<GPW>(stage + a * kStageBytes + scale_offset + 8 * kScaleRow, stage_scale_b[a]);
+        }
+      }
 #pragma unroll
       for (int jg = 0; jg < GPW; ++jg) {
         const uint32_t g = (chunk * 8 + warp) * GPW + jg;  // one of this warp's groups
-        if (SMALLX) {
+        if (ONE) {
           const uint4 first = first_base[g * unit_stride];
           const uint4 second = second_base[g * unit_stride];
-          const uint32_t frag[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
           const float bias0 = bias_base0[g * bias_stride0];
-          const float bias1 = bias_base1[g * bias_stride1];
 #pragma unroll
           for (int a = 0; a < NMAT; ++a) {
             const unsigned char* base = stage + a * kStageBytes;
             const uint2 word_a = *reinterpret_cast<const uint2*>(base + word_offset + jg * 32);
             const uint2 word_b = *reinterpret_cast<const uint2*>(base + word_offset + jg * 32 + 8 * kRowBytes);
-            const float scale_a = __half2float(*reinterpret_cast<const __half*>(base + scale_offset + jg * 2));
-            const float scale_b =
-                __half2float(*reinterpret_cast<const __half*>(base + scale_offset + jg * 2 + 8 * kScaleRow));
-            // the group's bias term rides in as the accumulator's start value
-            float sum[4] = {bias0, bias1, bias0, bias1};  // the table holds the negated term
+            float sum[4];
             uint32_t a_even, a_odd, b_even, b_odd;
             nibbles_biased(word_a.x, a_even, a_odd);
             nibbles_biased(word_b.x, b_even, b_odd);
-            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[0], frag[1]);
+            mma_16816_from(sum, a_even, b_even, a_odd, b_odd, first.x, first.y, bias0, 0.0f, bias0, 0.0f);
             nibbles_biased(word_a.x >> 8, a_even, a_odd);
             nibbles_biased(word_b.x >> 8, b_even, b_odd);
-            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[2], frag[3]);
+            mma_16816(sum, a_even, b_even, a_odd, b_odd, first.z, first.w);
             nibbles_biased(word_a.y, a_even, a_odd);
             nibbles_biased(word_b.y, b_even, b_odd);
-            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[4], frag[5]);
+            mma_16816(sum, a_even, b_even, a_odd, b_odd, second.x, second.y);
             nibbles_biased(word_a.y >> 8, a_even, a_odd);
             nibbles_biased(word_b.y >> 8, b_even, b_odd);
-            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[6], frag[7]);
-            acc[a][0][0] = fmaf(scale_a, sum[0], acc[a][0][0]);
-            acc[a][0][1] = fmaf(scale_a, sum[1], acc[a][0][1]);
-            acc[a][0][2] = fmaf(scale_b, sum[2], acc[a][0][2]);
-            acc[a][0][3] = fmaf(scale_b, sum[3], acc[a][0][3]);
+            mma_16816(sum, a_even, b_even, a_odd, b_odd, second.z, second.w);
+            acc[a][0][0] = fmaf(stage_scale_a[a][jg], sum[0], acc[a][0][0]);
+            acc[a][0][2] = fmaf(stage_scale_b[a][jg], sum[2], acc[a][0][2]);
           }
-        } else {
+        } else if (SMALLX) {        } else {
           uint32_t a_frag[NMAT][4][4];
           float scale_a[NMAT], scale_b[NMAT];
 #pragma unroll
@@ -489,6 +527,7 @@ __global__ void __launch_bounds__(kThreads, RES) w4a16_gemv_pipe_kernel(const Ge
       for (int a = 0; a < NMAT; ++a)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
+          if (ONE && (j & 1)) continue;  // column 1 of the tile does not exist with one row
           reduce[(warp * kAcc + a * 4 + j) * 32 + lane] = acc[a][0][j];
           acc[a][0][j] = 0.0f;
         }
@@ -629,9 +668,19 @@ bool plan_pipe(const KernelArgs& args, const GemvProblem& p, PipePlan* plan) {
 
 template <int NT, int NMAT, int EPI, bool SMALLX, int GPW>
 int run_pipe(const KernelArgs& args, const GemvProblem& p, const PipePlan& plan) {
+  constexpr int kDense = kDenseResidency<NT, EPI>;
+  constexpr int kSparse = kDense == 3 ? 2 : kDense;  // the build for launches that fill at most two CTA slots per SM
+  constexpr bool kOneRow = SMALLX && NT == 1;       // forms that have a single-row build
+  const bool sparse = kDense == 3 && plan.ctas <= 2u * (uint32_t)context_sm_count(args.ctx);
+  // LLMOPT_CUDA_GEMV_ONE_ROW=0 runs single-row launches on the general build (for comparison)
+  static const bool one_row_allowed = getenv("LLMOPT_CUDA_GEMV_ONE_ROW") == nullptr || getenv("LLMOPT_CUDA_GEMV_ONE_ROW")[0] != '0';
+  const bool one_row = kOneRow && p.x_rows == 1u && one_row_allowed;
   auto kernel = w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX, GPW>;
-  if (kDenseResidency<NT, EPI> == 3 && plan.ctas <= 2u * (uint32_t)context_sm_count(args.ctx))
-    kernel = w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX, GPW, (kDenseResidency<NT, EPI> == 3 ? 2 : kDenseResidency<NT, EPI>)>;
+  if (one_row)
+    kernel = sparse ? w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX, GPW, kSparse, kOneRow>
+                    : w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX, GPW, kDense, kOneRow>;
+  else if (sparse)
+    kernel = w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX, GPW, kSparse>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.shared_bytes) != cudaSuccess) {
     cudaGetLastError();
     return -1;

@@ -109,6 +109,10 @@ SIGNATURES = {
         _I, [_P, ctypes.POINTER(_I), ctypes.POINTER(_I64), ctypes.POINTER(_I32), ctypes.POINTER(_I32)]),
     "llmopt_cuda_ring_destroy": (_I, [_P]),
     "llmopt_cuda_f16_argmax": (_I64, [_P, _SZ]),
+    "llmopt_cuda_sample_f16": (_I, [_P, _SZ, ctypes.c_double, _I, ctypes.c_double, ctypes.c_double, ctypes.c_uint64,
+                                   ctypes.POINTER(_I64)]),
+    "llmopt_cuda_measure_hardware": (_I, [_I, _I, _I, _I64, ctypes.c_char_p, _SZ, ctypes.POINTER(_I),
+                                         ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]),
     "llmopt_cuda_w4a16_linear": (_I, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P]),
     "llmopt_cuda_attention_q8_paged_static": (_I, [_P, _P, _P, _P, _P, _P, _P, _SZ, ctypes.c_uint32, _P]),
     "llmopt_cuda_time_dispatch": (_I, [_P, _REC, _I, _I, _I, ctypes.POINTER(ctypes.c_float)]),
@@ -282,6 +286,8 @@ class _RecordArray:
             record.buffer_count = len(item.buffers)
             record.parameters = ctypes.cast(params, ctypes.c_void_p)
             record.parameter_bytes = len(item.parameters)
+            if any(int(v) > 0x7FFFFFFF for v in tuple(item.grid) + tuple(item.group)):
+                raise ValueError(f"{item.name}: grid dimension overflows the 32-bit record field")
             record.grid = (ctypes.c_int * 3)(*[int(v) for v in item.grid])
             record.group = (ctypes.c_int * 3)(*[int(v) for v in item.group])
             record.barrier_before = int(item.barrier_before)
@@ -540,3 +546,25 @@ def f16_argmax(data: bytes, count: int) -> int:
     """``caml_llmopt_f16_argmax``: first maximum of ``count`` halves held on the host."""
     buffer = ctypes.create_string_buffer(bytes(data), max(len(data), 1))
     return int(load_library().llmopt_cuda_f16_argmax(buffer, count))
+
+
+def sample_f16(data: bytes, count: int, *, temperature: float, top_k: int, top_p: float, min_p: float,
+               seed: int) -> int:
+    """``Sampling.f16_sample_native`` (lib/sampling.ml:192-194): one token from ``count`` fp16
+    logits held on the host."""
+    buffer = ctypes.create_string_buffer(bytes(data), max(len(data), 1))
+    out = ctypes.c_int64()
+    _check(load_library().llmopt_cuda_sample_f16(buffer, count, float(temperature), int(top_k), float(top_p),
+                                                 float(min_p), int(seed) & 0xFFFFFFFFFFFFFFFF, ctypes.byref(out)))
+    return int(out.value)
+
+
+def measure_hardware(*, warmup: int, repeats: int, nbytes: int, device: int = -1) -> tuple:
+    """``caml_llmopt_metal_measure_hardware`` (bin/hardware_probe.ml:9-11): (device name, largest
+    thread block, median empty-dispatch seconds, median copy bandwidth in GB/s)."""
+    name = ctypes.create_string_buffer(256)
+    threads, seconds, bandwidth = ctypes.c_int(), ctypes.c_double(), ctypes.c_double()
+    _check(load_library().llmopt_cuda_measure_hardware(int(device), int(warmup), int(repeats), int(nbytes), name, 256,
+                                                       ctypes.byref(threads), ctypes.byref(seconds),
+                                                       ctypes.byref(bandwidth)))
+    return name.value.decode(), int(threads.value), float(seconds.value), float(bandwidth.value)

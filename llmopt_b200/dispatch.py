@@ -129,9 +129,10 @@ def dispatch_w4a16_linear_affine(context: Context, *, input: Tensor, weight: Ten
                                          operation=kernel_abi.W4A16_LINEAR, input_dtype="float16",
                                          output_dtype="float16")
     bias_buffer = bias.buffer if bias is not None else scale.buffer
+    grid = linear_f16_grid(m * n) if m == 1 else linear_f16_grid(((m + 3) // 4) * n)  # as the contract form
     return [_run(context, entry,
                  [input.buffer, weight.buffer, scale.buffer, zero.buffer, bias_buffer, output.buffer], params,
-                 (linear_f16_grid(m * n), 1, 1))]
+                 (grid, 1, 1))]
 
 
 def dispatch_w4a16_qkv_linear_command(context: Context, *, input: Tensor, q_weight: Tensor, q_scale: Tensor,

@@ -420,3 +420,12 @@ def q4_0_gated_linear(x, gate_weight, up_weight, activation=0):
     lib().orc_q4_0_gated_linear(_p(x), _p(_u8(gate_weight)), _p(_u8(up_weight)), ctypes.c_int(activation),
                                 _p(product), I64(m), I64(n), I64(k))
     return product
+
+
+def sample_f16(logits, *, temperature, top_k, top_p, min_p, seed):
+    """Restatement of the reference's host sampler (native/ocaml_metal_stubs.m:2629-2765)."""
+    logits = _f16(logits).reshape(-1)
+    function = lib().orc_sample_f16
+    function.restype = ctypes.c_int64
+    return int(function(_p(logits), I64(logits.size), F32(temperature), ctypes.c_int(top_k), F32(top_p), F32(min_p),
+                        ctypes.c_uint64(seed)))

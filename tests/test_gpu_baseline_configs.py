@@ -1,0 +1,88 @@
+"""Greedy decode on the full-size model shapes of the headline configurations against the CPU
+oracle's token streams (tests/golden/decode_streams.npz, written by
+tests/golden/make_decode_golden.py from the same seeds): SmolLM2-135M shape (30 blocks,
+vocabulary 49152, 512-token prompt, 128 steps) and LFM2.5-350M shape (10 gated short-conv + 6
+attention blocks, vocabulary 65536; one sequence with a 1024-token prompt and 256 steps, and 16
+sequences side by side).
+
+The GPU consumes the oracle's stream (teacher forcing: prompt tokens, then the oracle's picks), so
+every step is compared on the same input and one disagreement cannot hide later ones.  A pick
+must equal the oracle's; the only excuse is a near-tie: the oracle's two best logits closer than
+the parity bound of the path (2e-3 of the step's largest |logit|) and the GPU choosing the
+runner-up.  The number of such near-ties and the smallest gap seen are reported on failure."""
+
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "decode_streams.npz")
+NEAR_TIE = 2e-3
+# every W4A16 product and attention is within 2e-3 of its output scale; through 16-30 blocks of residual
+# stream the differences (one fp16 rounding flips per few hundred elements per operation) add up to this much
+HIDDEN_DRIFT = 2e-2
+
+
+def _decode_against_stream(runtime, config_name, case):
+    from llmopt_b200 import model
+    from llmopt_b200.decode_engine import DecodeEngine
+
+    data = np.load(GOLDEN)
+    if f"{case}_picks" not in data:
+        pytest.skip(f"tests/golden/decode_streams.npz holds no '{case}' stream (run tests/golden/make_decode_golden.py {case})")
+    prompts, picks = data[f"{case}_prompts"], data[f"{case}_picks"]
+    runner_up, gap = data[f"{case}_runner_up"], data[f"{case}_gap"]
+    sequences, prompt_length = prompts.shape
+    steps = picks.shape[1] - 1
+    config = getattr(model, config_name)
+    weights = model.random_weights(config, seed=0)
+    engine = DecodeEngine(runtime, config, weights, batch=sequences, capacity=prompt_length + steps + 1)
+    del weights
+    got = None
+    for position in range(prompt_length):  # the prompt goes through the decode path token by token
+        got = engine.step(prompts[:, position].tolist(), position)
+    near_ties, wrong = [], []
+    for step in range(steps + 1):
+        for s in range(sequences):
+            if got[s] != picks[s, step]:
+                record = (step, s, int(got[s]), int(picks[s, step]), float(gap[s, step]))
+                (near_ties if got[s] == runner_up[s, step] and gap[s, step] <= NEAR_TIE else wrong).append(record)
+        if step < steps:
+            got = engine.step(picks[:, step].tolist(), prompt_length + step)
+    # accumulated difference of the whole stack: the hidden state that entered the LM head at the last step
+    want_hidden = data[f"{case}_last_hidden"].astype(np.float64)
+    got_hidden = engine.final_hidden.buffer.to_numpy(np.float16).reshape(want_hidden.shape).astype(np.float64)
+    drift = float(np.max(np.abs(got_hidden - want_hidden)) / max(np.max(np.abs(want_hidden)), 1e-9))
+    assert drift <= HIDDEN_DRIFT, f"{case}: last hidden state differs by {drift:.3e} of its scale after {len(config.layers)} blocks"
+    print(f"{case}: last-step hidden state within {drift:.3e} of its scale after {len(config.layers)} blocks; "
+          f"{len(near_ties)} near-tie picks")
+    return engine, near_ties, wrong, float(gap.min()), picks
+
+
+def _report(case, near_ties, wrong, smallest_gap):
+    return (f"{case}: {len(wrong)} wrong picks {wrong[:5]}, {len(near_ties)} near-tie picks {near_ties[:5]} "
+            f"(step, sequence, gpu, oracle, oracle top-2 gap); smallest top-2 gap of the stream {smallest_gap:.3e}")
+
+
+def test_smollm2_135m_shape_512_prompt_128_steps(runtime):
+    engine, near_ties, wrong, smallest, picks = _decode_against_stream(runtime, "SMOLLM2_135M", "smollm2")
+    assert not wrong and len(near_ties) <= 1, _report("smollm2", near_ties, wrong, smallest)
+    if not near_ties:
+        # free running on the device (chained replays, no host in the loop) gives the same stream
+        prompt_length = 512
+        tokens, _ = engine.generate_chained([int(picks[0, 0])], prompt_length, 32)
+        assert tokens[:31] == picks[0, 1:32].tolist()
+
+
+def test_lfm25_350m_shape_1024_prompt_256_steps(runtime):
+    _, near_ties, wrong, smallest, _ = _decode_against_stream(runtime, "LFM25_350M", "lfm25")
+    assert not wrong and len(near_ties) <= 2, _report("lfm25", near_ties, wrong, smallest)
+
+
+def test_lfm25_350m_shape_batch_16(runtime):
+    """16 sequences side by side, 32-token prompts and 32 steps each (the oracle needs hours for
+    1024 + 256 tokens of 16 sequences; the single-sequence test covers that length)."""
+    _, near_ties, wrong, smallest, _ = _decode_against_stream(runtime, "LFM25_350M", "lfm25_batch16")
+    assert not wrong and len(near_ties) <= 2, _report("lfm25_batch16", near_ties, wrong, smallest)

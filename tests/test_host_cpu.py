@@ -223,3 +223,42 @@ def test_model_byte_accounting():
     llama = decode_bytes_per_token(LLAMA3_8B, 1, 8192)
     assert abs(llama["weights"] - 3.99e9) < 0.02e9 and abs(llama["attention"] - 0.5547e9) < 0.001e9
     assert SMOLLM2_135M.attention_layers == 30
+
+
+def test_host_sampler_matches_the_reference_restatement(oracle):
+    """llmopt_cuda_sample_f16 is host code (it samples logits the caller read back): the same seed
+    must give the same token as the reference's sampler, restated in the oracle — across
+    temperatures, top-k sizes, min-p / top-p cuts and rows full of ties."""
+    from llmopt_b200 import cuda_native
+
+    rng = np.random.default_rng(11)
+    cases = 0
+    for vocabulary in (1, 2, 50, 300, 5000):
+        for kind in ("normal", "ties", "peaked"):
+            if kind == "normal":
+                logits = rng.standard_normal(vocabulary).astype(np.float16)
+            elif kind == "ties":
+                logits = rng.integers(-2, 3, size=vocabulary).astype(np.float16)
+            else:
+                logits = (rng.standard_normal(vocabulary) * 8).astype(np.float16)
+            for temperature, top_k, top_p, min_p in ((0.0, 0, 0.0, 0.0), (1.0, 1, 0.9, 0.0), (0.7, 40, 0.95, 0.05),
+                                                     (1.3, 0, 0.0, 0.0), (1.0, 300, 0.5, 0.0), (0.3, 5, 1.0, 0.2),
+                                                     (2.0, 256, 0.99, 0.01)):
+                for seed in (1, 7, 123456789, 2 ** 62 + 3):
+                    got = cuda_native.sample_f16(logits.tobytes(), vocabulary, temperature=temperature, top_k=top_k,
+                                                 top_p=top_p, min_p=min_p, seed=seed)
+                    want = oracle.sample_f16(logits, temperature=temperature, top_k=top_k, top_p=top_p, min_p=min_p,
+                                             seed=seed)
+                    assert got == want, (vocabulary, kind, temperature, top_k, top_p, min_p, seed, got, want)
+                    cases += 1
+    assert cases == 5 * 3 * 7 * 4
+    # greedy: first maximum wins; an empty row gives token 0
+    row = np.array([1, 5, 5, -2], np.float16)
+    assert cuda_native.sample_f16(row.tobytes(), 4, temperature=0.0, top_k=0, top_p=0.0, min_p=0.0, seed=1) == 1
+    assert cuda_native.sample_f16(b"", 0, temperature=1.0, top_k=0, top_p=0.0, min_p=0.0, seed=1) == 0
+    # the distribution is the softmax of the kept candidates: seeds spread over 64 bits split two equal
+    # logits about evenly (the first draw of small seeds is dominated by the seeding constant)
+    row = np.array([3.0, 3.0, -20.0], np.float16)
+    picks = [cuda_native.sample_f16(row.tobytes(), 3, temperature=1.0, top_k=0, top_p=0.0, min_p=0.0, seed=int(seed))
+             for seed in rng.integers(1, 2 ** 63, size=400)]
+    assert set(picks) == {0, 1} and 140 <= picks.count(0) <= 260
