@@ -63,6 +63,11 @@ int launch_embedding_f16(const KernelArgs&);
 int launch_chain_token_id(const KernelArgs&);
 int launch_chain_token_ids(const KernelArgs&);
 void launch_argmax_f16(const __half* values, uint32_t count, int* result, cudaStream_t stream);
+struct NamedLauncher {
+  const char* name;
+  Launcher launcher;
+};
+const NamedLauncher* norm_family_launchers(size_t* count);
 
 // ---- objects -----------------------------------------------------------------------
 
@@ -314,6 +319,10 @@ static void register_kernels(llmopt_cuda_library* library) {
   add("llmopt_embedding_f16", launch_embedding_f16);
   add("llmopt_chain_token_id", launch_chain_token_id);
   add("llmopt_chain_token_ids", launch_chain_token_ids);
+  // norm variants, fused norm + rotary, casts, pointwise (norm_family.cu)
+  size_t extra = 0;
+  const NamedLauncher* table = norm_family_launchers(&extra);
+  for (size_t i = 0; i < extra; ++i) add(table[i].name, table[i].launcher);
 }
 
 static bool is_paged_attention_name(const char* name) {

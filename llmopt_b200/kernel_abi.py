@@ -17,7 +17,11 @@ W4A16_QKV_LINEAR = "w4a16-qkv-linear-g64"
 W4A16_SWIGLU_FFN = "w4a16-swiglu-ffn-g64"
 W4A16_LM_HEAD_ARGMAX = "w4a16-lm-head-argmax"
 RMS_NORM = "rms-norm"
+RMS_ROPE = "rms-rope"
+RMS_ROPE_QK = "rms-rope-qk"
 ROTARY_QK = "rotary-qk"
+CAST = "cast"
+POINTWISE = "pointwise"
 SHORT_CONV = "short-conv"
 SHORT_CONV_STEP = "short-conv-step"
 SHORT_CONV_PREFILL = "short-conv-prefill"
@@ -27,7 +31,7 @@ CACHE = "cache"
 
 OPERATIONS = (
     LINEAR, GATED_LINEAR, FUSED_LINEAR, W4A16_LINEAR, W4A16_QKV_LINEAR, W4A16_SWIGLU_FFN, W4A16_LM_HEAD_ARGMAX, RMS_NORM, ROTARY_QK, SHORT_CONV,
-    SHORT_CONV_STEP, SHORT_CONV_PREFILL, ATTENTION, EMBEDDING, CACHE,
+    SHORT_CONV_STEP, SHORT_CONV_PREFILL, ATTENTION, EMBEDDING, CACHE, RMS_ROPE, RMS_ROPE_QK, CAST, POINTWISE,
 )
 
 
@@ -110,6 +114,31 @@ def _entries() -> list[Entry]:
     add("llmopt_rms_norm_f16_simd", RMS_NORM)
     add("llmopt_rms_norm_f32_f16", RMS_NORM, f32, f16)
     add("llmopt_rms_norm_f32_f16_simd", RMS_NORM, f32, f16)
+    # lib/metal_normalization_source.ml:449-516 (entries of the norm variants), :586-590, :660-668, :737-757
+    for name in ("llmopt_rms_norm_f16_wf32_simd", "llmopt_rms_norm_f16_wf32_wide", "llmopt_rms_norm_add_f16_wf32_simd",
+                 "llmopt_rms_norm_add_f16_wf32_wide", "llmopt_rms_norm_scale_f16_wf32_simd",
+                 "llmopt_rms_norm_scale_f16_wf32_wide", "llmopt_rms_norm_add_scale_f16_wf32_simd",
+                 "llmopt_rms_norm_add_scale_f16_wf32_wide", "llmopt_rms_norm_unweighted_f16_simd",
+                 "llmopt_rms_norm_unweighted_f16_wide", "llmopt_rms_norm_unweighted_add_f16_simd",
+                 "llmopt_rms_norm_unweighted_add_f16_wide", "llmopt_l2_norm_f16_simd", "llmopt_l2_norm_slice_f16_simd"):
+        add(name, RMS_NORM)
+    add("llmopt_rms_norm_f32_f16_wf32_simd", RMS_NORM, f32, f16)
+    add("llmopt_rms_rope_f16_simd_h64", RMS_ROPE)
+    add("llmopt_rms_rope_f16_wf32_simd", RMS_ROPE)
+    add("llmopt_rms_rope_qk_f16_simd_h64", RMS_ROPE_QK)
+    add("llmopt_rms_rope_qk_f16_wf32_simd", RMS_ROPE_QK)
+    add("llmopt_cast_f16_f32", CAST, f16, f32)   # lib/metal_tensor_source.ml:928-938
+    add("llmopt_cast_f32_f16", CAST, f32, f16)
+    add("llmopt_cast_i64_f32", CAST, i64, f32)
+    for name in ("llmopt_add_f16", "llmopt_mul_f16", "llmopt_div_f16", "llmopt_silu_mul_f16", "llmopt_gelu_mul_f16",
+                 "llmopt_sigmoid_mul_f16", "llmopt_neg_f16", "llmopt_silu_f16", "llmopt_sigmoid_f16", "llmopt_tanh_f16",
+                 "llmopt_rsqrt_f16", "llmopt_mul_f32_f16_f16"):
+        add(name, POINTWISE)
+    for name in ("llmopt_add_f32", "llmopt_sub_f32", "llmopt_mul_f32", "llmopt_neg_f32", "llmopt_silu_f32",
+                 "llmopt_exp_f32", "llmopt_rsqrt_f32", "llmopt_cos_f32", "llmopt_sin_f32", "llmopt_softplus_f32"):
+        add(name, POINTWISE, f32, f32)
+    add("llmopt_mul_f16_f32", POINTWISE, f16, f32)
+    add("llmopt_mul_f16_f32_f16", POINTWISE, f16, f16)
     add("llmopt_rotary_qk_f16_simd_h64", ROTARY_QK)
     add("llmopt_embedding_f16", EMBEDDING, i64, f16)
     add("llmopt_chain_token_id", EMBEDDING, i64, i64, (32, 1, 1))

@@ -110,3 +110,55 @@ def short_conv_prefill(*, tokens, channels, has_initial_state) -> bytes:  # :138
 
 def embedding(*, tokens, vocabulary, width) -> bytes:  # lib/metal_tensor_source.ml:237
     return u32s([tokens, vocabulary, width])
+
+
+def rms_rope(*, batches, tokens, heads, width, half_dimension, trig_batches, epsilon) -> bytes:  # :52-61, 28 bytes
+    return struct.pack("<6If", *[_u32(v) for v in (batches, tokens, heads, width, half_dimension, trig_batches)], epsilon)
+
+
+def rms_rope_qk(*, batches, tokens, q_heads, k_heads, width, half_dimension, trig_batches, epsilon) -> bytes:  # :63-72
+    return struct.pack("<7If", *[_u32(v) for v in (batches, tokens, q_heads, k_heads, width, half_dimension,
+                                                   trig_batches)], epsilon)
+
+
+def l2_norm_slice(*, input_rows, groups, width, input_width, offset, epsilon) -> bytes:
+    """L2NormSliceParams, lib/metal_normalization_source.ml:553-556 (24 bytes)."""
+    return struct.pack("<5If", *[_u32(v) for v in (input_rows, groups, width, input_width, offset)], epsilon)
+
+
+def count(*, count) -> bytes:  # CastParams / UnaryParams {count}
+    return u32s([count])
+
+
+def pointwise(*, output_shape, left_shape=None, right_shape=None, left_scalar=None, right_scalar=None) -> bytes:
+    """``Metal_parameters.pointwise`` (lib/metal_parameters.ml:331-382), 136 bytes: count, rank, scalar
+    flags, the output shape and both operand shapes aligned to it from the right (missing or
+    scalar operands are all ones), padded with ones to rank 8, then the scalars as int64 and f32."""
+    output_shape = [int(v) for v in output_shape]
+    rank = len(output_shape)
+    if rank > 8:
+        raise ValueError("Metal pointwise kernels support rank at most eight")
+
+    def aligned(shape):
+        if shape is None:
+            return [1] * rank
+        shape = [int(v) for v in shape]
+        if len(shape) > rank:
+            raise ValueError("pointwise input rank exceeds output rank")
+        shape = [1] * (rank - len(shape)) + shape
+        if any(i != 1 and i != o for i, o in zip(shape, output_shape)):
+            raise ValueError("pointwise input shape is not broadcastable to output")
+        return shape
+
+    pad = lambda dims: [_u32(v) for v in dims] + [1] * (8 - rank)
+    total = 1
+    for v in output_shape:
+        total *= v
+    block = bytearray(struct.pack("<4I", _u32(total), rank, 1 if left_scalar is not None else 0,
+                                  1 if right_scalar is not None else 0))
+    for dims in (output_shape, aligned(left_shape), aligned(right_shape)):
+        block += struct.pack("<8I", *pad(dims))
+    block += struct.pack("<qqff", int(left_scalar or 0), int(right_scalar or 0), float(left_scalar or 0.0),
+                         float(right_scalar or 0.0))
+    assert len(block) == 136
+    return bytes(block)

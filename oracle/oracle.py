@@ -429,3 +429,56 @@ def sample_f16(logits, *, temperature, top_k, top_p, min_p, seed):
     function.restype = ctypes.c_int64
     return int(function(_p(logits), I64(logits.size), F32(temperature), ctypes.c_int(top_k), F32(top_p), F32(min_p),
                         ctypes.c_uint64(seed)))
+
+
+def norm_family(x, *, weight=None, residual=None, layer_scalar=None, epsilon, l2=False, groups=1, offset=0, width=None):
+    """The RMS / L2 norm variants (lib/metal_normalization_source.ml:92-585): input f16 or f32,
+    weight None / f16 / f32, optional half-precision residual add, optional layer scalar;
+    ``groups`` / ``offset`` / ``width`` select the slice form."""
+    x = np.ascontiguousarray(x)
+    is_f32 = x.dtype == np.float32
+    if not is_f32:
+        x = _f16(x)
+    input_rows, input_width = x.shape
+    width = input_width if width is None else width
+    rows = input_rows * groups
+    kind = 0
+    if weight is not None:
+        weight = np.ascontiguousarray(weight)
+        kind = 2 if weight.dtype == np.float32 else 1
+        if kind == 1:
+            weight = _f16(weight)
+    out = np.empty((rows, width), np.float16)
+    scalar = None if layer_scalar is None else np.asarray([layer_scalar], np.float32)
+    lib().orc_norm_family(_p(x), ctypes.c_int(int(is_f32)), _p(weight), ctypes.c_int(kind),
+                          _p(None if residual is None else _f16(residual)), _p(scalar), _p(out), I64(rows), I64(width),
+                          F32(epsilon), ctypes.c_int(int(l2)), I64(groups), I64(input_width), I64(offset))
+    return out
+
+
+def rms_rope(x, weight, cosine, sine, *, half_dimension, epsilon, trig_batches=1):
+    """x token-first [b,t,h,w] -> head-major [b,h,t,w]; weight f16 or f32 [w]."""
+    x = _f16(x)
+    b, t, h, w = x.shape
+    weight = np.ascontiguousarray(weight)
+    is_f32 = weight.dtype == np.float32
+    out = np.empty((b, h, t, w), np.float16)
+    lib().orc_rms_rope(_p(x), _p(weight if is_f32 else _f16(weight)), ctypes.c_int(int(is_f32)), _p(_f16(cosine)),
+                       _p(_f16(sine)), _p(out), U32(b), U32(t), U32(h), U32(w), U32(half_dimension), U32(trig_batches),
+                       F32(epsilon))
+    return out
+
+
+def rms_rope_qk(q, q_weight, k, k_weight, cosine, sine, *, half_dimension, epsilon, trig_batches=1):
+    q, k = _f16(q), _f16(k)
+    b, t, qh, w = q.shape
+    kh = k.shape[2]
+    q_weight, k_weight = np.ascontiguousarray(q_weight), np.ascontiguousarray(k_weight)
+    is_f32 = q_weight.dtype == np.float32
+    if not is_f32:
+        q_weight, k_weight = _f16(q_weight), _f16(k_weight)
+    q_out, k_out = np.empty((b, qh, t, w), np.float16), np.empty((b, kh, t, w), np.float16)
+    lib().orc_rms_rope_qk(_p(q), _p(q_weight), _p(k), _p(k_weight), ctypes.c_int(int(is_f32)), _p(_f16(cosine)),
+                          _p(_f16(sine)), _p(q_out), _p(k_out), U32(b), U32(t), U32(qh), U32(kh), U32(w),
+                          U32(half_dimension), U32(trig_batches), F32(epsilon))
+    return q_out, k_out
