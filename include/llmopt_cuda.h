@@ -86,6 +86,19 @@ const char* llmopt_cuda_function_name(llmopt_cuda_library* library, int index);
 /* Registers `alias` (for example a digest-named epilogue kernel,
  * lib/epilogue.ml:217-229) as another name of the existing kernel `target`. */
 int llmopt_cuda_register_alias(llmopt_cuda_library* library, const char* alias, const char* target);
+/* Registers `name` (a digest name, lib/epilogue.ml:217-229) as a group-64 W4A16 linear whose
+ * writeback is a free-form expression over the accumulator (Epilogue.Expr, lib/epilogue.ml:16;
+ * lib/metal_parametric_codegen.ml:4-39 compiles one Metal kernel per expression).  `program`
+ * is the expression in postfix form, one byte per operation: 1 accumulator, 2 constant (+ 4
+ * bytes f32), 3 operand read (+ operand index, + 0 f16 / 1 f32; read at the output column),
+ * 10 neg, 11 abs, 12 silu, 13 gelu, 14 exp, 15 log, 16 rsqrt, 17 round-to-half, 20 add, 21 sub,
+ * 22 mul, 23 div, 24 min, 25 max, 30 clamp(x, lo, hi), 31 where(c, a, b); at most 192 bytes, 8
+ * operands, 12 stack slots.  A dispatch of `name` binds [input, weight, scale, bias_or_scale,
+ * output, operand 0 ...] with the 20-byte linear parameter block and computes
+ * half(expression) in fp32, like the generated kernel.  llmopt_b200/epilogue.py derives names
+ * and programs from expression trees. */
+int llmopt_cuda_register_expr_epilogue(llmopt_cuda_library* library, const char* name, const void* program,
+                                       size_t program_bytes, int operand_count);
 
 /* ---- buffers ---------------------------------------------------------------- */
 

@@ -68,6 +68,13 @@ struct NamedLauncher {
   Launcher launcher;
 };
 const NamedLauncher* norm_family_launchers(size_t* count);
+struct ExprProgram {
+  uint8_t code[192];
+  uint32_t length;
+  uint32_t operands;
+};
+const char* validate_expr_program(const uint8_t* code, size_t length, int operand_count);
+int launch_w4a16_linear_expr(const KernelArgs&);
 
 // ---- objects -----------------------------------------------------------------------
 
@@ -92,6 +99,8 @@ struct Context {
   uint32_t* device_error = nullptr;
   // Launches may overlap the tail of their predecessor (programmatic dependent launch).
   bool overlap = true;
+  // Expression epilogues registered by digest name (llmopt_cuda_register_expr_epilogue).
+  std::map<std::string, ExprProgram> expr_programs;
 };
 
 struct Allocation {
@@ -195,6 +204,10 @@ void* context_split_scratch(Context* context, size_t zeroed_bytes, size_t bytes,
   context->split_bytes = wanted;
   context->split_counter_bytes = zeroed_bytes;
   return block;
+}
+const ExprProgram* context_expr_program(Context* context, const char* name) {
+  auto found = context->expr_programs.find(name ? name : "");
+  return found == context->expr_programs.end() ? nullptr : &found->second;
 }
 int context_sm_count(Context* context) { return context->sm_count; }
 bool context_overlap(Context* context) { return context != nullptr && context->overlap; }
@@ -738,6 +751,28 @@ int llmopt_cuda_register_alias(llmopt_cuda_library* library, const char* alias, 
     return set_error(LLMOPT_CUDA_FAILURE, std::string("CUDA kernel function is missing: ") + target);
   if (!library->launchers.count(alias)) library->names.push_back(alias);
   library->launchers[alias] = found->second;
+  // an expression epilogue is found by the name it is dispatched under: the alias gets the program too
+  auto program = library->context->expr_programs.find(target);
+  if (program != library->context->expr_programs.end()) library->context->expr_programs[alias] = program->second;
+  return LLMOPT_CUDA_OK;
+}
+
+int llmopt_cuda_register_expr_epilogue(llmopt_cuda_library* library, const char* name, const void* program,
+                                       size_t program_bytes, int operand_count) {
+  if (library == nullptr) return set_error(LLMOPT_CUDA_FAILURE, "CUDA library has been finalized");
+  if (name == nullptr || name[0] == '\0' || program == nullptr)
+    return set_error(LLMOPT_CUDA_INVALID_ARGUMENT, "expression epilogue needs a name and a program");
+  if (library->launchers.count(name))
+    return set_error(LLMOPT_CUDA_INVALID_ARGUMENT, std::string("kernel name is already taken: ") + name);
+  if (const char* problem = validate_expr_program((const uint8_t*)program, program_bytes, operand_count))
+    return set_error(LLMOPT_CUDA_INVALID_ARGUMENT, problem);
+  ExprProgram stored = {};
+  memcpy(stored.code, program, program_bytes);
+  stored.length = (uint32_t)program_bytes;
+  stored.operands = (uint32_t)operand_count;
+  library->context->expr_programs[name] = stored;
+  library->launchers[name] = launch_w4a16_linear_expr;
+  library->names.push_back(name);
   return LLMOPT_CUDA_OK;
 }
 

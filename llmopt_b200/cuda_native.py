@@ -67,6 +67,7 @@ SIGNATURES = {
     "llmopt_cuda_function_count": (_I, [_P]),
     "llmopt_cuda_function_name": (ctypes.c_char_p, [_P, _I]),
     "llmopt_cuda_register_alias": (_I, [_P, ctypes.c_char_p, ctypes.c_char_p]),
+    "llmopt_cuda_register_expr_epilogue": (_I, [_P, ctypes.c_char_p, _P, _SZ, _I]),
     "llmopt_cuda_buffer_of_bytes": (_I, [_P, _P, _SZ, _PP]),
     "llmopt_cuda_create_buffer": (_I, [_P, _I64, _PP]),
     "llmopt_cuda_map_file": (_I, [_P, ctypes.c_char_p, _PP]),
@@ -322,6 +323,12 @@ class Runtime:
 
     def register_alias(self, alias: str, target: str) -> None:
         _check(load_library().llmopt_cuda_register_alias(self._library, alias.encode(), target.encode()))
+
+    def register_expr_epilogue(self, name: str, program: bytes, operand_count: int) -> None:
+        """Registers a digest-named W4A16 linear with an expression epilogue (``epilogue.bind``)."""
+        code = ctypes.create_string_buffer(bytes(program), max(len(program), 1))
+        _check(load_library().llmopt_cuda_register_expr_epilogue(
+            self._library, name.encode(), code, len(program), int(operand_count)))
 
     def synchronize(self) -> None:
         _check(load_library().llmopt_cuda_synchronize(self._context))

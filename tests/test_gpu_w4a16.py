@@ -256,3 +256,49 @@ def test_dispatch_errors(runtime):
         runtime.dispatch("llmopt_w4a16_linear_f16_g64", buffers=[small] * 5, parameters=b"\0" * 20, grid=(0, 1, 1))
     with pytest.raises(ValueError):
         small.view(32, 64)
+
+
+def test_digest_named_epilogue_kernels(runtime, oracle):
+    """A compiled package names an algebraic epilogue kernel by digest
+    (base_<8 hex of MD5(dtypes | writeback)>, lib/epilogue.ml:217-229).  epilogue.bind makes such a
+    name resolve: to the built-in tagged kernel when the expression is one of the ten forms, else to
+    a registered expression program run by the interpreter kernel."""
+    from llmopt_b200 import epilogue as ep, parameters
+    from llmopt_b200.cuda_native import Buffer
+
+    rng = np.random.default_rng(21)
+    m, k, n = 3, 1024, 200
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    packed, scale = random_w4(rng, n, k)
+    up = rng.standard_normal(n).astype(np.float16)
+    ceiling = rng.uniform(0.2, 2.0, size=n).astype(np.float32)
+    base = "llmopt_w4a16_linear_f16_g64"
+    buffers = [Buffer.of_array(runtime, a) for a in (x, packed, scale)]
+    block = parameters.w4a16_linear(m=m, n=n, k=k, has_bias=False, bias_row_stride=0)
+    acc = oracle.w4a16_linear_f64(x, packed, scale)
+
+    def run(name, operands):
+        out = Buffer.of_array(runtime, np.full((m, n), np.nan, np.float16))
+        runtime.dispatch(name, buffers=buffers + [buffers[2], out] + [Buffer.of_array(runtime, a) for a in operands],
+                         parameters=block, grid=(256, 1, 1))
+        return out.to_numpy(np.float16, (m, n))
+
+    # a tagged form under its digest name: an alias of the built-in kernel, bit-identical to it
+    gated = ep.of_expr(ep.Binop("mul", ep.Unop("silu", ep.ACC), ep.Read(ep.Value(17))))
+    name = ep.bind(runtime, base, gated)
+    assert name == ep.algebraic_kernel_name(base, ep.tagged("silu_mul", ep.Value(0))) and runtime.has_function(name)
+    assert np.array_equal(run(name, [up]).view(np.uint16), run(base + "_epi_silu_mul", [up]).view(np.uint16))
+    want = (acc / (1 + np.exp(-acc))) * up.astype(np.float64)
+    assert_close_f16(run(name, [up]), want, label="digest-named silu_mul")
+    # a free-form tree: clamp(silu(acc) * up + 0.5, -1, ceiling) with an fp32 operand
+    tree = ep.Triop("clamp", ep.Binop("add", ep.Binop("mul", ep.Unop("silu", ep.ACC), ep.Read(ep.Value(4))), ep.Const(0.5)),
+                    ep.Const(-1.0), ep.Read(ep.Value(9, "f32")))
+    free = ep.of_expr(tree)
+    assert ep.matching_tag(free) is None
+    name = ep.bind(runtime, base, free)
+    assert runtime.has_function(name) and ep.bind(runtime, base, free) == name  # binding twice is harmless
+    want = np.clip(want + 0.5, -1.0, ceiling.astype(np.float64))
+    assert_close_f16(run(name, [up, ceiling]), want, label="expression epilogue")
+    # a program that pops an empty stack is refused at registration
+    with pytest.raises(ValueError, match="empty stack"):
+        runtime.register_expr_epilogue("llmopt_w4a16_linear_f16_g64_deadbeef", bytes([20]), 0)

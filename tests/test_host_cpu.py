@@ -264,3 +264,40 @@ def test_host_sampler_matches_the_reference_restatement(oracle):
     picks = [cuda_native.sample_f16(row.tobytes(), 3, temperature=1.0, top_k=0, top_p=0.0, min_p=0.0, seed=int(seed))
              for seed in rng.integers(1, 2 ** 63, size=400)]
     assert set(picks) == {0, 1} and 140 <= picks.count(0) <= 260
+
+
+def test_epilogue_digest_names_and_programs():
+    """Kernel names of algebraic epilogues are base + '_' + the first 8 hex digits of
+    MD5(dtypes | canonical writeback text) (lib/epilogue.ml:217-229, text of
+    lib/applicative_expr.ml:205-283); the texts below are what that emitter prints."""
+    import hashlib
+
+    from llmopt_b200 import epilogue as ep
+
+    base = "llmopt_w4a16_linear_f16_g64"
+    digest = lambda text: base + "_" + hashlib.md5(text.encode()).hexdigest()[:8]
+    bias, up, residual = ep.Value(41), ep.Value(7), ep.Value(99)
+    silu = "(acc * (1.0f / (1.0f + metal::exp(-acc))))"
+    assert ep.algebraic_kernel_name(base, ep.tagged("none")) == digest("|acc")
+    assert ep.algebraic_kernel_name(base, ep.tagged("silu")) == digest("|" + silu)
+    assert ep.algebraic_kernel_name(base, ep.tagged("bias", bias)) == digest("f16|(acc + ((float)buf_0[col]))")
+    assert ep.algebraic_kernel_name(base, ep.tagged("silu_mul_residual_add", up, residual)) == digest(
+        "f16,f16|((" + silu + " * ((float)buf_0[col])) + ((float)buf_1[col]))")
+    # value ids do not matter (canonical ordinals), operand dtypes and order do
+    assert ep.algebraic_kernel_name(base, ep.tagged("bias", ep.Value(5))) == ep.algebraic_kernel_name(base, ep.tagged("bias", bias))
+    assert ep.algebraic_kernel_name(base, ep.tagged("bias", ep.Value(5, "f32"))) != ep.algebraic_kernel_name(base, ep.tagged("bias", bias))
+    # a free-form tree: clamp(silu(acc) * b0 + 0.5, -1, b1) with an fp32 second operand
+    tree = ep.Triop("clamp", ep.Binop("add", ep.Binop("mul", ep.Unop("silu", ep.ACC), ep.Read(up)), ep.Const(0.5)),
+                    ep.Const(-1.0), ep.Read(ep.Value(3, "f32")))
+    free = ep.of_expr(tree)
+    assert ep.algebraic_kernel_name(base, free) == digest(
+        "f16,f32|metal::clamp(((" + silu + " * ((float)buf_0[col])) + 0.5000000f), -1.0000000f, ((float)buf_1[col]))")
+    assert ep.matching_tag(free) is None
+    assert ep.matching_tag(ep.of_expr(ep.Binop("mul", ep.Unop("gelu", ep.ACC), ep.Read(up)))) == "gelu_mul"
+    assert ep.matching_tag(ep.of_expr(ep.Binop("add", ep.ACC, ep.Read(bias)))) == "bias"  # same expression as residual_add
+    program, dtypes = ep.compile_program(free)
+    assert dtypes == ["f16", "f32"]
+    assert program == (bytes([1, 12, 3, 0, 0, 22, 2]) + struct.pack("<f", 0.5) + bytes([20, 2]) + struct.pack("<f", -1.0)
+                       + bytes([3, 1, 1, 30]))
+    with pytest.raises(ValueError):
+        ep.tagged("bias")
