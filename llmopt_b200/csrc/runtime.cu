@@ -75,6 +75,9 @@ struct ExprProgram {
 };
 const char* validate_expr_program(const uint8_t* code, size_t length, int operand_count);
 int launch_w4a16_linear_expr(const KernelArgs&);
+int launch_gated_delta_f32(const KernelArgs&);
+int launch_gated_delta_tm_f16(const KernelArgs&);
+int launch_triangular_recurrence(const KernelArgs&);
 
 // ---- objects -----------------------------------------------------------------------
 
@@ -332,6 +335,18 @@ static void register_kernels(llmopt_cuda_library* library) {
   add("llmopt_embedding_f16", launch_embedding_f16);
   add("llmopt_chain_token_id", launch_chain_token_id);
   add("llmopt_chain_token_ids", launch_chain_token_ids);
+  // gated-delta scan (one name per state width) and the triangular recurrence (gated_delta.cu)
+  static const char* const kGatedDeltaF32[] = {
+      "llmopt_gated_delta_f32_d32",  "llmopt_gated_delta_f32_d64",  "llmopt_gated_delta_f32_d96",
+      "llmopt_gated_delta_f32_d128", "llmopt_gated_delta_f32_d160", "llmopt_gated_delta_f32_d192",
+      "llmopt_gated_delta_f32_d224", "llmopt_gated_delta_f32_d256"};
+  static const char* const kGatedDeltaF16[] = {
+      "llmopt_gated_delta_tm_f16_d32",  "llmopt_gated_delta_tm_f16_d64",  "llmopt_gated_delta_tm_f16_d96",
+      "llmopt_gated_delta_tm_f16_d128", "llmopt_gated_delta_tm_f16_d160", "llmopt_gated_delta_tm_f16_d192",
+      "llmopt_gated_delta_tm_f16_d224", "llmopt_gated_delta_tm_f16_d256"};
+  for (const char* name : kGatedDeltaF32) add(name, launch_gated_delta_f32);
+  for (const char* name : kGatedDeltaF16) add(name, launch_gated_delta_tm_f16);
+  add("llmopt_triangular_recurrence_f32", launch_triangular_recurrence);
   // norm variants, fused norm + rotary, casts, pointwise (norm_family.cu)
   size_t extra = 0;
   const NamedLauncher* table = norm_family_launchers(&extra);

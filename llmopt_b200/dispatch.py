@@ -590,3 +590,44 @@ class Cache:
                                              operation=kernel_abi.CACHE, input_dtype="uint8", output_dtype="float16")
         return [_run(context, entry, [self.checkpoint_pool, destination], params,
                      (round_up(self.layout.recurrent_layer_elements // 4, 256), 1, 1))]
+
+
+def dispatch_gated_delta(context: Context, *, query: Tensor, key: Tensor, value: Tensor, gate: Tensor, beta: Tensor,
+                         output: Tensor) -> list:
+    """dispatch_gated_delta, lib/metal_dispatch_recurrent.ml:34-89: f32 head-major [b,h,t,w] or f16
+    token-major [b,t,h,w] vectors, width a multiple of 32, gate f32, output f16 token-major."""
+    if len(query.shape) != 4:
+        raise DispatchError("unsupported Metal gated-delta layout or dtype contract")
+    if query.dtype == "float32":
+        batch, heads, tokens, width = query.shape
+        scalar_shape, beta_dtype, stem = (batch, heads, tokens), "float32", "llmopt_gated_delta_f32_d"
+    elif query.dtype == "float16":
+        batch, tokens, heads, width = query.shape
+        scalar_shape, beta_dtype, stem = (batch, tokens, heads), "float16", "llmopt_gated_delta_tm_f16_d"
+    else:
+        raise DispatchError("unsupported Metal gated-delta layout or dtype contract")
+    ok = (width > 0 and width % 32 == 0 and tuple(output.shape) == (batch, tokens, heads, width)
+          and key.dtype == query.dtype and value.dtype == query.dtype and gate.dtype == "float32"
+          and beta.dtype == beta_dtype and tuple(key.shape) == tuple(query.shape)
+          and tuple(value.shape) == tuple(query.shape) and tuple(gate.shape) == scalar_shape
+          and tuple(beta.shape) == scalar_shape)
+    if not ok:
+        raise DispatchError("unsupported Metal gated-delta layout or dtype contract")
+    entry = context.runtime.kernel_entry(name=f"{stem}{width}", operation=kernel_abi.GATED_DELTA,
+                                         input_dtype=query.dtype, output_dtype="float16")
+    grid = round_up(batch * heads * width, 4) * 32  # gated_delta_grid, lib/metal_dispatch_common.ml:80-86
+    return [_run(context, entry, [query.buffer, key.buffer, value.buffer, gate.buffer, beta.buffer, output.buffer],
+                 parameters.u32s([batch, heads, tokens, width]), (grid, 1, 1))]
+
+
+def dispatch_triangular_recurrence(context: Context, *, start: int, stop: int, input: Tensor, output: Tensor) -> list:
+    """dispatch_triangular_recurrence, lib/metal_dispatch_recurrent.ml:6-32: square matrices up to 64 wide."""
+    width, rows = input.shape[-1], input.shape[-2]
+    if width > 64 or rows != width:
+        raise DispatchError("unsupported Metal triangular recurrence shape")
+    outer = input.numel // (width * width)
+    entry = context.runtime.kernel_entry(name="llmopt_triangular_recurrence_f32",
+                                         operation=kernel_abi.TRIANGULAR_RECURRENCE, input_dtype="float32",
+                                         output_dtype="float32")
+    return [_run(context, entry, [input.buffer, output.buffer], parameters.u32s([outer, width, start, stop]),
+                 (outer * 64, 1, 1))]

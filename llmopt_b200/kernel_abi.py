@@ -22,6 +22,8 @@ RMS_ROPE_QK = "rms-rope-qk"
 ROTARY_QK = "rotary-qk"
 CAST = "cast"
 POINTWISE = "pointwise"
+GATED_DELTA = "gated-delta"
+TRIANGULAR_RECURRENCE = "triangular-recurrence"
 SHORT_CONV = "short-conv"
 SHORT_CONV_STEP = "short-conv-step"
 SHORT_CONV_PREFILL = "short-conv-prefill"
@@ -32,6 +34,7 @@ CACHE = "cache"
 OPERATIONS = (
     LINEAR, GATED_LINEAR, FUSED_LINEAR, W4A16_LINEAR, W4A16_QKV_LINEAR, W4A16_SWIGLU_FFN, W4A16_LM_HEAD_ARGMAX, RMS_NORM, ROTARY_QK, SHORT_CONV,
     SHORT_CONV_STEP, SHORT_CONV_PREFILL, ATTENTION, EMBEDDING, CACHE, RMS_ROPE, RMS_ROPE_QK, CAST, POINTWISE,
+    GATED_DELTA, TRIANGULAR_RECURRENCE,
 )
 
 
@@ -140,6 +143,10 @@ def _entries() -> list[Entry]:
     add("llmopt_mul_f16_f32", POINTWISE, f16, f32)
     add("llmopt_mul_f16_f32_f16", POINTWISE, f16, f16)
     add("llmopt_rotary_qk_f16_simd_h64", ROTARY_QK)
+    for width in range(32, 257, 32):  # lib/metal_recurrent_source.ml:309-327, 400-410
+        add(f"llmopt_gated_delta_f32_d{width}", GATED_DELTA, f32, f16, threadgroup=(128, 1, 1))
+        add(f"llmopt_gated_delta_tm_f16_d{width}", GATED_DELTA, f16, f16, threadgroup=(128, 1, 1))
+    add("llmopt_triangular_recurrence_f32", TRIANGULAR_RECURRENCE, f32, f32, threadgroup=(64, 1, 1))
     add("llmopt_embedding_f16", EMBEDDING, i64, f16)
     add("llmopt_chain_token_id", EMBEDDING, i64, i64, (32, 1, 1))
     add("llmopt_chain_token_ids", EMBEDDING, "int32", i64, (128, 1, 1))

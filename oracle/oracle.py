@@ -482,3 +482,28 @@ def rms_rope_qk(q, q_weight, k, k_weight, cosine, sine, *, half_dimension, epsil
                           _p(_f16(sine)), _p(q_out), _p(k_out), U32(b), U32(t), U32(qh), U32(kh), U32(w),
                           U32(half_dimension), U32(trig_batches), F32(epsilon))
     return q_out, k_out
+
+
+def gated_delta(query, key, value, gate, beta, *, token_major):
+    """Cpu.gated_delta (lib/cpu.ml:909-976). token_major: f16 vectors [b,t,h,w], beta f16 [b,t,h];
+    else f32 vectors [b,h,t,w], beta f32 [b,h,t]; gate f32. Output f16 [b,t,h,w]."""
+    cast = _f16 if token_major else (lambda a: np.ascontiguousarray(a, dtype=np.float32))
+    query, key, value, beta = cast(query), cast(key), cast(value), cast(beta)
+    gate = np.ascontiguousarray(gate, dtype=np.float32)
+    if token_major:
+        b, t, h, w = query.shape
+    else:
+        b, h, t, w = query.shape
+    out = np.empty((b, t, h, w), np.float16)
+    lib().orc_gated_delta(_p(query), _p(key), _p(value), _p(gate), _p(beta), _p(out), ctypes.c_int(int(token_major)),
+                          I64(b), I64(h), I64(t), I64(w))
+    return out
+
+
+def triangular_recurrence(matrices, *, start, stop):
+    """Cpu.triangular_recurrence (lib/cpu.ml:424-460) on f32 [outer, w, w]."""
+    matrices = np.ascontiguousarray(matrices, dtype=np.float32)
+    outer, width = int(np.prod(matrices.shape[:-2])), matrices.shape[-1]
+    out = np.empty_like(matrices)
+    lib().orc_triangular_recurrence(_p(matrices), _p(out), I64(outer), I64(width), I64(start), I64(stop))
+    return out

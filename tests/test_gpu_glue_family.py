@@ -167,3 +167,48 @@ def test_casts_and_pointwise_kernels(runtime):
         bad[48 + 4:48 + 8] = (2).to_bytes(4, "little")  # left_shape[1] = 2 against output 3
         runtime.dispatch("llmopt_add_f16", buffers=[_buf(runtime, left), _buf(runtime, right), out], parameters=bytes(bad),
                          grid=(48, 1, 1))
+
+
+@pytest.mark.parametrize("token_major,width,tokens", [(False, 64, 40), (True, 128, 33), (True, 32, 5), (False, 256, 9)])
+def test_gated_delta_matches_oracle(runtime, oracle, token_major, width, tokens):
+    """Gated-delta scan against the CPU statement (lib/cpu.ml:909-976) in float64: fp16 output,
+    fp32 state kept in registers over the whole scan."""
+    from llmopt_b200 import dispatch
+
+    rng = np.random.default_rng(width + tokens)
+    batch, heads = 2, 3
+    dtype, name = (np.float16, "float16") if token_major else (np.float32, "float32")
+    shape = (batch, tokens, heads, width) if token_major else (batch, heads, tokens, width)
+    scalars = shape[:3]
+    # unit-norm keys and queries, decays below one, betas in (0, 1): the regime the scan is used in
+    unit = lambda a: a / np.linalg.norm(a, axis=-1, keepdims=True)
+    query = unit(rng.standard_normal(shape)).astype(dtype)
+    key = unit(rng.standard_normal(shape)).astype(dtype)
+    value = rng.standard_normal(shape).astype(dtype)
+    gate = -rng.uniform(0.01, 0.5, size=scalars).astype(np.float32)
+    beta = rng.uniform(0.1, 0.9, size=scalars).astype(dtype)
+    tensor = lambda a, d: dispatch.Tensor(_buf(runtime, a), a.shape, d)
+    out = dispatch.Tensor(_out(runtime, (batch, tokens, heads, width)), (batch, tokens, heads, width), "float16")
+    names = dispatch.dispatch_gated_delta(dispatch.Context(runtime), query=tensor(query, name), key=tensor(key, name),
+                                          value=tensor(value, name), gate=tensor(gate, "float32"),
+                                          beta=tensor(beta, name), output=out)
+    assert names == [("llmopt_gated_delta_tm_f16_d" if token_major else "llmopt_gated_delta_f32_d") + str(width)]
+    want = oracle.gated_delta(query, key, value, gate, beta, token_major=token_major)
+    assert_close_f16(out.buffer.to_numpy(np.float16, want.shape), want, rel=2e-3, label=names[0])
+
+
+def test_triangular_recurrence_is_bit_exact(runtime, oracle):
+    """Every product and partial sum of the recurrence is rounded to fp32 on its own, in a fixed
+    order, in the reference's CPU statement and kernel alike (lib/cpu.ml:424-460,
+    lib/metal_recurrent_source.ml:290-299): results are compared bit for bit."""
+    from llmopt_b200 import dispatch
+
+    rng = np.random.default_rng(3)
+    for outer, width, start, stop in ((3, 64, 1, 64), (2, 33, 0, 20), (1, 1, 0, 1)):
+        matrices = (rng.standard_normal((outer, width, width)) * 0.2).astype(np.float32)
+        out = dispatch.Tensor(_out(runtime, matrices.shape, np.float32), matrices.shape, "float32")
+        dispatch.dispatch_triangular_recurrence(dispatch.Context(runtime), start=start, stop=stop,
+                                                input=dispatch.Tensor(_buf(runtime, matrices), matrices.shape, "float32"),
+                                                output=out)
+        want = oracle.triangular_recurrence(matrices, start=start, stop=stop)
+        assert np.array_equal(out.buffer.to_numpy(np.float32, matrices.shape).view(np.uint32), want.view(np.uint32))

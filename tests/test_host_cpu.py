@@ -97,9 +97,8 @@ def test_kernel_abi_surface():
         kernel_abi.Entry("", kernel_abi.CACHE, "float16", "uint8")
     # every entry name is registered in the native library's table (checked textually: no GPU here)
     source = open(os.path.join(ROOT, "llmopt_b200", "csrc", "runtime.cu")).read()
-    registered = set(re.findall(r'add\("([a-z0-9_]+)"', source))
     family = open(os.path.join(ROOT, "llmopt_b200", "csrc", "norm_family.cu")).read()  # its own name table
-    registered |= set(re.findall(r'\{"([a-z0-9_]+)", launch_', family))
+    registered = set(re.findall(r'"(llmopt_[a-z0-9_]+)"', source + family))
     assert {e.name for e in kernel_abi.ENTRIES} <= registered
 
 
