@@ -7,6 +7,13 @@
 // tiling tactic (_x4, _x8, _x16, _m2, _m4, _m16, _m32, ...); the tactic only changes how rows and
 // columns are tiled, not the arithmetic, so all of those names resolve to the kernels below.
 //
+// The same kernel serves the Tile32 affine formats (lib/block_schema.ml:706-741; kernels
+// llmopt_tile32_affine{4,8}_linear_f16_{x8,m16,m32,simd}, lib/metal_block_codegen.ml:54-722): a block
+// of 32 weights is {f16 scale; f16 minimum; codes}, 20 bytes with 4-bit codes (low nibble of byte
+// j = element j, high nibble = element j + 16, as in Q4_0) or 36 bytes with 8-bit codes, and
+// w = scale * code + minimum; the block's contribution is scale * sum(x code) + minimum * sum(x),
+// the association the reference kernels use (:108-143).
+//
 // One warp per output column: the lanes take the row's blocks round-robin (a warp reads 32 x 18
 // contiguous bytes per step), each lane multiplies its block with the 32 matching activations of up
 // to four batch rows, fp32 accumulation, one warp reduction per (row, column).  More rows are
@@ -53,19 +60,78 @@ __device__ __forceinline__ float block_dot(const __half* x, const uint32_t (&qs)
   return acc;
 }
 
+enum BlockFormat { kQ4_0 = 0, kAffine4 = 1, kAffine8 = 2 };
+template <int FORMAT> constexpr uint32_t kBlockBytes = FORMAT == kQ4_0 ? 18u : (FORMAT == kAffine4 ? 20u : 36u);
+
+// Tile32 affine blocks are 4-byte aligned (20 / 36-byte stride on a 4-byte aligned row).
+// scale * sum(x[i] * code[i]) + minimum * sum(x[i]) for one activation row.
+template <int FORMAT>
+__device__ __forceinline__ float affine_block_dot(const __half* x, const uint8_t* block) {
+  const uint32_t* words = reinterpret_cast<const uint32_t*>(block);
+  const uint32_t header = __ldg(words);
+  const float scale = __half2float(__ushort_as_half((unsigned short)(header & 0xffffu)));
+  const float minimum = __half2float(__ushort_as_half((unsigned short)(header >> 16)));
+  const uint4* vectors = reinterpret_cast<const uint4*>(x);
+  uint32_t x_words[16];
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint4 raw = vectors[v];
+    x_words[4 * v] = raw.x, x_words[4 * v + 1] = raw.y, x_words[4 * v + 2] = raw.z, x_words[4 * v + 3] = raw.w;
+  }
+  float coded = 0.0f, plain = 0.0f;
+  if (FORMAT == kAffine4) {
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const uint32_t codes = __ldg(words + 1 + w);  // bytes 4w .. 4w+3: elements 4w+j (low) and 16+4w+j (high)
+#pragma unroll
+      for (int pair = 0; pair < 2; ++pair) {
+        const float2 low = __half22float2(*reinterpret_cast<const __half2*>(&x_words[2 * w + pair]));
+        const float2 high = __half22float2(*reinterpret_cast<const __half2*>(&x_words[8 + 2 * w + pair]));
+        const uint32_t two = (codes >> (16 * pair)) & 0xffffu;
+        coded = fmaf(low.x, (float)(two & 15u), coded);
+        coded = fmaf(high.x, (float)((two >> 4) & 15u), coded);
+        coded = fmaf(low.y, (float)((two >> 8) & 15u), coded);
+        coded = fmaf(high.y, (float)(two >> 12), coded);
+        plain += (low.x + high.x) + (low.y + high.y);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const uint32_t codes = __ldg(words + 1 + w);  // elements 4w .. 4w+3
+      const float2 first = __half22float2(*reinterpret_cast<const __half2*>(&x_words[2 * w]));
+      const float2 second = __half22float2(*reinterpret_cast<const __half2*>(&x_words[2 * w + 1]));
+      coded = fmaf(first.x, (float)(codes & 255u), coded);
+      coded = fmaf(first.y, (float)((codes >> 8) & 255u), coded);
+      coded = fmaf(second.x, (float)((codes >> 16) & 255u), coded);
+      coded = fmaf(second.y, (float)(codes >> 24), coded);
+      plain += (first.x + first.y) + (second.x + second.y);
+    }
+  }
+  return fmaf(scale, coded, minimum * plain);
+}
+
 // acc[r] = x[row0 + r, :] . w[col, :] for r < rows (<= kRowTile), all lanes hold the sums
+template <int FORMAT = kQ4_0>
 __device__ __forceinline__ void column_dots(const __half* x, const uint8_t* weight_row, uint32_t k, uint32_t row0,
                                             uint32_t rows, uint32_t lane, float (&acc)[kRowTile]) {
 #pragma unroll
   for (int r = 0; r < kRowTile; ++r) acc[r] = 0.0f;
   const uint32_t blocks = k >> 5;
   for (uint32_t b = lane; b < blocks; b += 32) {
-    float d;
-    uint32_t qs[4];
-    load_block(weight_row + (size_t)b * 18u, d, qs);
+    if (FORMAT == kQ4_0) {
+      float d;
+      uint32_t qs[4];
+      load_block(weight_row + (size_t)b * 18u, d, qs);
 #pragma unroll
-    for (int r = 0; r < kRowTile; ++r)
-      if ((uint32_t)r < rows) acc[r] = fmaf(d, block_dot(x + (size_t)(row0 + r) * k + b * 32u, qs), acc[r]);
+      for (int r = 0; r < kRowTile; ++r)
+        if ((uint32_t)r < rows) acc[r] = fmaf(d, block_dot(x + (size_t)(row0 + r) * k + b * 32u, qs), acc[r]);
+    } else {
+#pragma unroll
+      for (int r = 0; r < kRowTile; ++r)
+        if ((uint32_t)r < rows)
+          acc[r] += affine_block_dot<FORMAT>(x + (size_t)(row0 + r) * k + b * 32u, weight_row + (size_t)b * kBlockBytes<FORMAT>);
+    }
   }
 #pragma unroll
   for (int r = 0; r < kRowTile; ++r) acc[r] = warp_sum(acc[r]);
@@ -75,19 +141,20 @@ struct QuantLinearParams {  // lib/metal_quant_source.ml:17-22
   uint32_t m, n, k, mode;
 };
 
-// llmopt_q4_0_linear_f16*: mode 0 none, 1 bias[n], 2 residual[m, n]
-__global__ void __launch_bounds__(256) q4_0_linear_kernel(const __half* __restrict__ x,
-                                                          const uint8_t* __restrict__ weight,
-                                                          const __half* __restrict__ additive,
-                                                          __half* __restrict__ y, QuantLinearParams p) {
+// llmopt_q4_0_linear_f16* / llmopt_tile32_affine{4,8}_linear_f16_*: mode 0 none, 1 bias[n], 2 residual[m, n]
+template <int FORMAT>
+__global__ void __launch_bounds__(256) quant_linear_kernel(const __half* __restrict__ x,
+                                                           const uint8_t* __restrict__ weight,
+                                                           const __half* __restrict__ additive,
+                                                           __half* __restrict__ y, QuantLinearParams p) {
   grid_chain_prologue();
   const uint32_t lane = threadIdx.x & 31u, col = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (col >= p.n) return;
-  const uint8_t* weight_row = weight + (size_t)col * (p.k >> 5) * 18u;
+  const uint8_t* weight_row = weight + (size_t)col * (p.k >> 5) * kBlockBytes<FORMAT>;
   for (uint32_t row0 = 0; row0 < p.m; row0 += kRowTile) {
     const uint32_t rows = min((uint32_t)kRowTile, p.m - row0);
     float acc[kRowTile];
-    column_dots(x, weight_row, p.k, row0, rows, lane, acc);
+    column_dots<FORMAT>(x, weight_row, p.k, row0, rows, lane, acc);
     if (lane < rows) {
       float value = acc[0];
 #pragma unroll
@@ -206,20 +273,25 @@ bool shape_ok(uint32_t k, const void* x) { return k > 0 && k % 32 == 0 && ((uint
 }  // namespace
 
 // Buffers [input, weight, additive, output]; params {m, n, k, epilogue_mode}.
-int launch_q4_0_linear(const KernelArgs& args) {
+template <int FORMAT>
+static int launch_quant_linear(const KernelArgs& args) {
   QuantLinearParams p;
   LLMOPT_REQUIRE(args.buffer_count == 4 && args.param_bytes == sizeof(p), "expects 4 buffers and 16 parameter bytes");
   memcpy(&p, args.params, sizeof(p));
   LLMOPT_REQUIRE(p.m > 0 && p.n > 0 && shape_ok(p.k, args.buffers[0]), "needs m, n > 0, k a multiple of 32, aligned input");
   LLMOPT_REQUIRE(p.mode <= 2, "epilogue mode must be 0, 1 or 2");
-  LLMOPT_REQUIRE(args.lengths[0] >= (size_t)p.m * p.k * 2 && args.lengths[1] >= (size_t)p.n * (p.k / 32) * 18 &&
+  LLMOPT_REQUIRE(FORMAT == kQ4_0 || ((uintptr_t)args.buffers[1] & 3u) == 0, "affine weight blocks must be 4-byte aligned");
+  LLMOPT_REQUIRE(args.lengths[0] >= (size_t)p.m * p.k * 2 && args.lengths[1] >= (size_t)p.n * (p.k / 32) * kBlockBytes<FORMAT> &&
                      args.lengths[3] >= (size_t)p.m * p.n * 2, "buffer is too short");
   if (p.mode == 1) LLMOPT_REQUIRE(args.lengths[2] >= (size_t)p.n * 2, "bias buffer is too short");
   if (p.mode == 2) LLMOPT_REQUIRE(args.lengths[2] >= (size_t)p.m * p.n * 2, "residual buffer is too short");
-  launch_kernel(args, q4_0_linear_kernel, dim3((p.n + 7) / 8), dim3(256), 0, (const __half*)args.buffers[0],
+  launch_kernel(args, quant_linear_kernel<FORMAT>, dim3((p.n + 7) / 8), dim3(256), 0, (const __half*)args.buffers[0],
                 (const uint8_t*)args.buffers[1], (const __half*)args.buffers[2], (__half*)args.buffers[3], p);
   return check_launch(args);
 }
+int launch_q4_0_linear(const KernelArgs& args) { return launch_quant_linear<kQ4_0>(args); }
+int launch_tile32_affine4_linear(const KernelArgs& args) { return launch_quant_linear<kAffine4>(args); }
+int launch_tile32_affine8_linear(const KernelArgs& args) { return launch_quant_linear<kAffine8>(args); }
 
 // Buffers [input, gate_weight, up_weight, product]; params {m, n, k, activation}.
 int launch_q4_0_gated_linear(const KernelArgs& args) {

@@ -218,6 +218,93 @@ __global__ void unpack_checkpoint_kernel(const uint8_t* __restrict__ pool, __hal
                                      __half2float(scales[(size_t)p.layer * layer_groups + gid / p.group_size]));
 }
 
+// ---- Tile32 affine cache with a 32-point Walsh-Hadamard rotation ------------------------------------
+// llmopt_cache_{pack,unpack}_attention_tile32_affine{8,4}_fwht_simd, lib/metal_cache_source.ml:1249-1393.
+// One warp per tile of 32 consecutive head dimensions: the tile is rotated by the normalised
+// Hadamard transform (butterflies over lane distance 1, 2, 4, 8, 16, then * 1 / sqrt(32)),
+// quantised with a per-tile fp16 scale = range / (2^bits - 1) and fp16 minimum, and stored as
+// {scale, minimum, codes} — 36 bytes with 8-bit codes, 20 bytes with 4-bit codes (low nibble =
+// lanes 0..15, high nibble = lanes 16..31).  Unpack dequantises and applies the same transform
+// (it is its own inverse).  Every operation is an fp32 operation in the reference's order, so pack
+// and unpack results equal the reference's byte for byte.
+__device__ __forceinline__ float fwht32(float x, uint32_t lane) {
+#pragma unroll
+  for (uint32_t s = 1; s < 32; s <<= 1) {
+    const float partner = __shfl_xor_sync(0xffffffffu, x, s);
+    x = (lane & s) == 0u ? __fadd_rn(x, partner) : __fsub_rn(partner, x);
+  }
+  return __fmul_rn(x, 0.17677669529663689f);
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+  return v;
+}
+
+template <int BITS>
+__global__ void pack_attention_fwht_kernel(const __half* __restrict__ source, const uint32_t* __restrict__ slots,
+                                           uint8_t* __restrict__ pool, AttentionCacheParams p, PoolBound bound) {
+  grid_chain_prologue();
+  constexpr uint32_t kTileBytes = BITS == 8 ? 36u : 20u;
+  constexpr float kLevels = BITS == 8 ? 255.0f : 15.0f;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t logical_tile = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t tiles_per_head = p.head_dim >> 5, segment_tiles = p.heads * tiles_per_head;
+  if (logical_tile >= p.items * segment_tiles) return;
+  const uint32_t item = logical_tile / segment_tiles, local_tile = logical_tile - item * segment_tiles;
+  const uint32_t head = local_tile / tiles_per_head, tile_in_head = local_tile - head * tiles_per_head;
+  const size_t source_base = ((size_t)head * p.source_items + p.source_offset + item) * p.head_dim + (tile_in_head << 5);
+  const float rotated = fwht32(__half2float(source[source_base + lane]), lane);
+  const float low = warp_min(rotated), high = warp_max(rotated);
+  const float range = fmaxf(0.0f, __fsub_rn(high, low));
+  const __half stored_scale = __float2half_rn(__fdiv_rn(range, kLevels)), stored_minimum = __float2half_rn(low);
+  const float scale = __half2float(stored_scale), minimum = __half2float(stored_minimum);
+  if (!slot_in_pool(slots[item], bound, lane)) return;
+  uint8_t* tile = pool + (size_t)slots[item] * p.token_stride + (size_t)((p.segment_offset >> 5) + local_tile) * kTileBytes;
+  if (lane == 0) {
+    *reinterpret_cast<__half*>(tile) = stored_scale;
+    *reinterpret_cast<__half*>(tile + 2) = stored_minimum;
+  }
+  uint32_t code = 0;
+  if (scale > 1e-8f) code = (uint32_t)max(0, min((int)kLevels, (int)rintf(__fdiv_rn(__fsub_rn(rotated, minimum), scale))));
+  if (BITS == 8) {
+    tile[4 + lane] = (uint8_t)code;
+  } else {
+    const uint32_t upper = __shfl_xor_sync(0xffffffffu, code, 16);
+    if (lane < 16) tile[4 + lane] = (uint8_t)((code & 15u) | ((upper & 15u) << 4));
+  }
+}
+
+template <int BITS>
+__global__ void unpack_attention_fwht_kernel(const uint8_t* __restrict__ pool, const uint32_t* __restrict__ slots,
+                                             __half* __restrict__ destination, AttentionCacheParams p, PoolBound bound) {
+  grid_chain_prologue();
+  constexpr uint32_t kTileBytes = BITS == 8 ? 36u : 20u;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t logical_tile = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const uint32_t tiles_per_head = p.head_dim >> 5, segment_tiles = p.heads * tiles_per_head;
+  if (logical_tile >= p.items * segment_tiles) return;
+  const uint32_t item = logical_tile / segment_tiles, local_tile = logical_tile - item * segment_tiles;
+  const uint32_t head = local_tile / tiles_per_head, tile_in_head = local_tile - head * tiles_per_head;
+  const size_t destination_index = ((size_t)head * p.items + item) * p.head_dim + (tile_in_head << 5) + lane;
+  if (!slot_in_pool(slots[item], bound, lane)) {
+    destination[destination_index] = __float2half_rn(0.0f);
+    return;
+  }
+  const uint8_t* tile = pool + (size_t)slots[item] * p.token_stride + (size_t)((p.segment_offset >> 5) + local_tile) * kTileBytes;
+  const float scale = __half2float(*reinterpret_cast<const __half*>(tile));
+  const float minimum = __half2float(*reinterpret_cast<const __half*>(tile + 2));
+  uint32_t code;
+  if (BITS == 8) {
+    code = tile[4 + lane];
+  } else {
+    const uint8_t packed = tile[4 + (lane & 15u)];
+    code = lane < 16 ? (packed & 15u) : (packed >> 4);
+  }
+  const float rotated = __fadd_rn(__fmul_rn(scale, (float)code), minimum);
+  destination[destination_index] = __float2half_rn(fwht32(rotated, lane));
+}
+
 template <typename P>
 bool read_params(const KernelArgs& args, P* out) {
   if (args.param_bytes != sizeof(P)) return false;
@@ -263,6 +350,38 @@ int launch_cache_pack_attention_q8(const KernelArgs& args) {
       pool_bound(args, 2, p.token_stride));
   return check_launch(args);
 }
+
+// Tile32 affine + FWHT cache: buffers and the 40-byte block of the Q8 pack / unpack; segment_offset
+// counts ELEMENTS (32 per tile), a token row holds token_elements / 32 tiles of 36 or 20 bytes.
+template <int BITS, bool PACK>
+static int launch_cache_fwht(const KernelArgs& args) {
+  AttentionCacheParams p;
+  LLMOPT_REQUIRE(args.buffer_count == 3, PACK ? "expects buffers [source, slots, pool]" : "expects buffers [pool, slots, destination]");
+  LLMOPT_REQUIRE(read_params(args, &p), "expects 40 parameter bytes");
+  LLMOPT_REQUIRE(p.head_dim > 0 && p.head_dim % 32 == 0 && p.segment_offset % 32 == 0, "head_dim and segment_offset must be multiples of 32");
+  constexpr size_t kTileBytes = BITS == 8 ? 36 : 20;
+  const int pool_index = PACK ? 2 : 0, data_index = PACK ? 0 : 2;
+  LLMOPT_REQUIRE(args.lengths[1] >= (size_t)p.items * 4, "slots buffer is shorter than items");
+  const size_t segment_end = (size_t)p.segment_offset + (size_t)p.heads * p.head_dim;
+  LLMOPT_REQUIRE(p.token_stride > 0 && segment_end / 32 * kTileBytes <= p.token_stride, "segment lies outside the token row");
+  const size_t elements = PACK ? ((size_t)(p.heads ? p.heads - 1 : 0) * p.source_items + p.source_offset + p.items) * p.head_dim
+                               : (size_t)p.items * p.heads * p.head_dim;
+  LLMOPT_REQUIRE(args.lengths[data_index] >= elements * 2, PACK ? "source buffer is shorter than the packed range" : "destination buffer is too short");
+  const uint32_t tiles = p.items * p.heads * (p.head_dim / 32);
+  if (tiles == 0) return 0;
+  const PoolBound bound = pool_bound(args, pool_index, p.token_stride);
+  if (PACK)
+    launch_kernel(args, pack_attention_fwht_kernel<BITS>, dim3((tiles + 7) / 8), dim3(256), 0, (const __half*)args.buffers[0],
+                  (const uint32_t*)args.buffers[1], (uint8_t*)args.buffers[2], p, bound);
+  else
+    launch_kernel(args, unpack_attention_fwht_kernel<BITS>, dim3((tiles + 7) / 8), dim3(256), 0, (const uint8_t*)args.buffers[0],
+                  (const uint32_t*)args.buffers[1], (__half*)args.buffers[2], p, bound);
+  return check_launch(args);
+}
+int launch_cache_pack_tile32_affine8_fwht(const KernelArgs& args) { return launch_cache_fwht<8, true>(args); }
+int launch_cache_unpack_tile32_affine8_fwht(const KernelArgs& args) { return launch_cache_fwht<8, false>(args); }
+int launch_cache_pack_tile32_affine4_fwht(const KernelArgs& args) { return launch_cache_fwht<4, true>(args); }
+int launch_cache_unpack_tile32_affine4_fwht(const KernelArgs& args) { return launch_cache_fwht<4, false>(args); }
 
 // Buffers: [key source, value source, slots, pool]; params 44 bytes (lib/metal_cache.ml:344-347).
 int launch_cache_pack_attention_q8_pair(const KernelArgs& args) {

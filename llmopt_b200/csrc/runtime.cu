@@ -44,6 +44,12 @@ int launch_tp_exchange_sum_norm(const KernelArgs&);
 int launch_attention_dense(const KernelArgs&);
 int launch_q4_0_linear(const KernelArgs&);
 int launch_q4_0_gated_linear(const KernelArgs&);
+int launch_tile32_affine4_linear(const KernelArgs&);
+int launch_cache_pack_tile32_affine8_fwht(const KernelArgs&);
+int launch_cache_unpack_tile32_affine8_fwht(const KernelArgs&);
+int launch_cache_pack_tile32_affine4_fwht(const KernelArgs&);
+int launch_cache_unpack_tile32_affine4_fwht(const KernelArgs&);
+int launch_tile32_affine8_linear(const KernelArgs&);
 int launch_q4_0_qkv_linear(const KernelArgs&);
 int launch_q4_0_dequant(const KernelArgs&);
 int launch_cache_pack_attention_q8(const KernelArgs&);
@@ -335,6 +341,21 @@ static void register_kernels(llmopt_cuda_library* library) {
   add("llmopt_embedding_f16", launch_embedding_f16);
   add("llmopt_chain_token_id", launch_chain_token_id);
   add("llmopt_chain_token_ids", launch_chain_token_ids);
+  add("llmopt_cache_pack_attention_tile32_affine8_fwht_simd", launch_cache_pack_tile32_affine8_fwht);
+  add("llmopt_cache_unpack_attention_tile32_affine8_fwht_simd", launch_cache_unpack_tile32_affine8_fwht);
+  add("llmopt_cache_pack_attention_tile32_affine4_fwht_simd", launch_cache_pack_tile32_affine4_fwht);
+  add("llmopt_cache_unpack_attention_tile32_affine4_fwht_simd", launch_cache_unpack_tile32_affine4_fwht);
+  // Tile32 affine linears: every tiling tactic of the format runs the same kernel
+  static const char* const kTile32Affine4[] = {
+      "llmopt_tile32_affine4_linear_f16_x8",   "llmopt_tile32_affine4_linear_f16_m16",
+      "llmopt_tile32_affine4_linear_f16_m32",  "llmopt_tile32_affine4_linear_f16_simd",
+      "llmopt_tile32_affine4_linear_f16_m16_add", "llmopt_tile32_affine4_linear_f16_m32_add"};
+  static const char* const kTile32Affine8[] = {
+      "llmopt_tile32_affine8_linear_f16_x8",   "llmopt_tile32_affine8_linear_f16_m16",
+      "llmopt_tile32_affine8_linear_f16_m32",  "llmopt_tile32_affine8_linear_f16_simd",
+      "llmopt_tile32_affine8_linear_f16_m16_add", "llmopt_tile32_affine8_linear_f16_m32_add"};
+  for (const char* name : kTile32Affine4) add(name, launch_tile32_affine4_linear);
+  for (const char* name : kTile32Affine8) add(name, launch_tile32_affine8_linear);
   // gated-delta scan (one name per state width) and the triangular recurrence (gated_delta.cu)
   static const char* const kGatedDeltaF32[] = {
       "llmopt_gated_delta_f32_d32",  "llmopt_gated_delta_f32_d64",  "llmopt_gated_delta_f32_d96",

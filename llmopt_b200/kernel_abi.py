@@ -81,6 +81,11 @@ def _entries() -> list[Entry]:
         add("llmopt_q4_0_qkv_linear_f16" + tactic, FUSED_LINEAR, "q4_0", f16)
     for tactic in ("_x8", "_m4", "_m16", "_m32"):
         add("llmopt_q4_0_gated_linear_f16" + tactic, GATED_LINEAR, "q4_0", f16)
+    for bits in (4, 8):  # lib/metal_block_codegen.ml:144-722; input dtype is the quantised storage
+        for tactic in ("_x8", "_m16", "_m32", "_simd", "_m16_add", "_m32_add"):
+            add(f"llmopt_tile32_affine{bits}_linear_f16{tactic}", LINEAR, f"tile32_affine{bits}", f16)
+        add(f"llmopt_cache_pack_attention_tile32_affine{bits}_fwht_simd", CACHE, f16, f"tile32_affine{bits}")
+        add(f"llmopt_cache_unpack_attention_tile32_affine{bits}_fwht_simd", CACHE, f"tile32_affine{bits}", f16)
     add("llmopt_w4a16_swiglu_rms_f16_g64", W4A16_SWIGLU_FFN)
     add("llmopt_w4a16_swiglu_rms_f32_g64", W4A16_SWIGLU_FFN, f32, f16)
     for stem in ("llmopt_w4a16_lm_head_argmax", "llmopt_w4a16_lm_head_argmax_extra",

@@ -31,7 +31,7 @@ def build(force: bool = False) -> str:
     if force or stale:
         os.makedirs(os.path.dirname(_LIB_PATH), exist_ok=True)
         subprocess.check_call(
-            ["gcc", "-O2", "-fopenmp", "-fPIC", "-shared", "-o", _LIB_PATH, source, "-lm"]
+            ["gcc", "-O2", "-ffp-contract=off", "-fopenmp", "-fPIC", "-shared", "-o", _LIB_PATH, source, "-lm"]
         )
     return _LIB_PATH
 
@@ -506,4 +506,49 @@ def triangular_recurrence(matrices, *, start, stop):
     outer, width = int(np.prod(matrices.shape[:-2])), matrices.shape[-1]
     out = np.empty_like(matrices)
     lib().orc_triangular_recurrence(_p(matrices), _p(out), I64(outer), I64(width), I64(start), I64(stop))
+    return out
+
+
+def tile32_affine_linear(x, weight, *, bits, additive=None, mode=0):
+    """weight: uint8 [n, (k/32) * (20 if bits == 4 else 36)] Tile32 affine blocks."""
+    x, weight = _f16(x), _u8(weight)
+    m, k = x.shape
+    n = weight.shape[0]
+    y = np.empty((m, n), np.float16)
+    lib().orc_tile32_affine_linear(_p(x), _p(weight), _p(None if additive is None else _f16(additive)), ctypes.c_int(mode),
+                                   ctypes.c_int(bits), _p(y), I64(m), I64(n), I64(k))
+    return y
+
+
+def tile32_affine_blocks(weight, *, bits):
+    """Quantises fp32 [n, k] to Tile32 affine blocks (scale = range / (2^bits - 1), minimum = min
+    of each 32-wide block, both stored as f16): test data in the storage format."""
+    weight = np.asarray(weight, np.float32)
+    n, k = weight.shape
+    blocks = weight.reshape(n, k // 32, 32)
+    low = blocks.min(-1).astype(np.float16)
+    scale = ((blocks.max(-1) - low.astype(np.float32)) / (2 ** bits - 1)).astype(np.float16)
+    safe = np.where(scale.astype(np.float32) > 0, scale.astype(np.float32), 1.0)
+    codes = np.clip(np.rint((blocks - low.astype(np.float32)[..., None]) / safe[..., None]), 0, 2 ** bits - 1).astype(np.uint8)
+    out = np.zeros((n, k // 32, 36 if bits == 8 else 20), np.uint8)
+    out[..., 0:2] = scale.view(np.uint8).reshape(n, k // 32, 2)
+    out[..., 2:4] = low.view(np.uint8).reshape(n, k // 32, 2)
+    out[..., 4:] = codes if bits == 8 else (codes[..., :16] | (codes[..., 16:] << 4))
+    return out.reshape(n, -1)
+
+
+def cache_pack_attention_fwht(source, slots, pool, *, bits, segment_offset, heads, head_dim, token_stride,
+                              source_items, source_offset=0):
+    """Packs in place into ``pool`` (np.uint8, 1-D); source [heads, source_items, head_dim] f16."""
+    source, slots = _f16(source), _u32(slots)
+    lib().orc_cache_pack_attention_fwht(_p(source), _p(slots), _p(pool), ctypes.c_int(bits), U32(len(slots)),
+                                        U32(segment_offset), U32(heads), U32(head_dim), U32(token_stride),
+                                        U32(source_items), U32(source_offset))
+
+
+def cache_unpack_attention_fwht(pool, slots, *, bits, segment_offset, heads, head_dim, token_stride):
+    slots = _u32(slots)
+    out = np.empty((heads, len(slots), head_dim), np.float16)
+    lib().orc_cache_unpack_attention_fwht(_p(_u8(pool)), _p(slots), _p(out), ctypes.c_int(bits), U32(len(slots)),
+                                          U32(segment_offset), U32(heads), U32(head_dim), U32(token_stride))
     return out
