@@ -583,6 +583,25 @@ def small_model_leg(runtime, args, name: str, peaks: dict, batch: int = 1) -> di
     }
 
 
+def time_prefill(engine, runtime, tokens: int) -> dict:
+    """Time to first token through the prefill path: the whole prompt in one pass (one row per
+    token through every linear, dense causal attention, bulk cache pack), wall clock around the
+    call that returns the first generated token; the prompt ids go host to device, the token comes back."""
+    rng = np.random.default_rng(5)
+    prompt = rng.integers(0, engine.config.vocabulary, size=tokens).tolist()
+    engine.prefill(prompt)  # warm-up (scratch growth, first-use kernel loads)
+    runtime.synchronize()
+    samples = []
+    for _ in range(3):
+        start = time.perf_counter()
+        engine.prefill(prompt)
+        samples.append(time.perf_counter() - start)
+    seconds = statistics.median(samples)
+    return {"prompt_tokens": tokens, "ttft_ms": seconds * 1e3, "prompt_tokens_per_s": tokens / seconds,
+            "kernels": engine.prefill_kernels, "h2d_bytes": 8 * tokens, "d2h_bytes": 4,
+            "note": "median of 3, host-driven batch of dispatches, empty cache"}
+
+
 def tensor_parallel_check(args, whole_config, whole_weights, runtime, rank, world, group, timed_tokens) -> dict:
     """Correctness of the tensor-parallel run on real peers: (1) every rank produced the same token
     stream in the timed run; (2) a short decode from an empty cache gives, on every rank, the same
@@ -708,6 +727,8 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         result["tokens_match"] = result["tp_check"]["tokens_match"]
     del whole_weights, weights
 
+    if world == 1 and extra_legs:
+        result["prefill"] = time_prefill(engine, runtime, 512)
     if world == 1 and config.hidden >= 2048:
         result["prefill_gemm"] = time_prefill_gemm(runtime, peaks, m=2048, k=config.hidden, n=config.intermediate,
                                                    form="dual", weights=engine.layers[:4])

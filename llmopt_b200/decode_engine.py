@@ -281,6 +281,108 @@ class DecodeEngine:
             (self.cos_row.buffer, self.cos_table.buffer, row), (self.sin_row.buffer, self.sin_table.buffer, row),
             (self.new_slots.buffer, self.slot_table_by_position.buffer, 4 * self.batch)])
 
+    # ---- prefill ---------------------------------------------------------------------------------
+    def prefill(self, tokens: Sequence[int], sequence: int = 0) -> int:
+        """The whole prompt of one sequence in one pass — the reference's prefill path
+        (``Serving_engine.prefill``, lib/serving_engine.ml:435-570): every linear runs with one row
+        per prompt token (the tensor-memory GEMM from 64 rows on), attention is the dense causal
+        fp16 attention over the prompt's own keys and values, every token's K / V row is packed
+        into the Q8 cache (``Cache.with_batch_async``, lib/metal_cache.ml:93-116) and the
+        short-conv blocks leave their state behind.  Returns the first generated token; decode
+        continues with ``step(..., past_tokens=len(tokens))``.  A sequence is prefilled from an
+        empty cache (position 0)."""
+        config, runtime = self.config, self.runtime
+        if self.group is not None:
+            raise NotImplementedError("prefill of a tensor-parallel shard is not built: feed the prompt through step()")
+        count, hidden, dim = len(tokens), config.hidden, config.head_dim
+        if count == 0 or count > self.capacity:
+            raise ValueError("the prompt must hold 1 .. capacity tokens")
+        if not 0 <= sequence < self.batch:
+            raise ValueError("no such sequence")
+        commands = Batch(runtime)
+        context = dispatch.Context(runtime, batch=commands)
+        run = lambda name, buffers, params, grid=(256, 1, 1): commands.dispatch(
+            name=name, buffers=buffers, parameters=params, grid=grid, group=(256, 1, 1))
+        ids = self._tensor(np.asarray(tokens, np.int64), "int64")
+        current, other = self._empty((count, hidden)), self._empty((count, hidden))
+        normed = self._empty((count, hidden))
+        q = self._empty((count, config.query_heads * dim))
+        k = self._empty((count, config.kv_heads * dim))
+        v = self._empty((count, config.kv_heads * dim))
+        q_rot = self._empty((1, config.query_heads, count, dim))
+        k_rot = self._empty((1, config.kv_heads, count, dim))
+        attended = self._empty((1, count, config.query_heads * dim))
+        row = dim * 2
+        cosine = dispatch.Tensor(self.cos_table.buffer.view(0, count * row), (1, count, dim))
+        sine = dispatch.Tensor(self.sin_table.buffer.view(0, count * row), (1, count, dim))
+        slots = self.slot_table.buffer.view(sequence * self.capacity * 4, count * 4)
+        run("llmopt_embedding_f16", [ids.buffer, self.embedding.buffer, current.buffer],
+            parameters.embedding(tokens=count, vocabulary=self.full_vocabulary, width=hidden), (count * hidden, 1, 1))
+        attention_index = conv_index = 0
+        for kind, layer in zip(config.layers, self.layers):
+            run("llmopt_rms_norm_f16_simd", [current.buffer, layer["input_norm"].buffer, normed.buffer],
+                parameters.rms_norm(rows=count, width=hidden, epsilon=config.epsilon),
+                (dispatch.simd_rows_grid(count), 1, 1))
+            if kind == "attention":
+                dispatch.dispatch_w4a16_qkv_linear_command(
+                    context, input=normed, q_weight=layer["q"][0], q_scale=layer["q"][1], k_weight=layer["k"][0],
+                    k_scale=layer["k"][1], v_weight=layer["v"][0], v_scale=layer["v"][1], q_output=q, k_output=k,
+                    v_output=v)
+                run("llmopt_rotary_qk_f16_simd_h64",
+                    [q.buffer, k.buffer, cosine.buffer, sine.buffer, q_rot.buffer, k_rot.buffer],
+                    parameters.rotary_qk(batches=1, tokens=count, q_heads=config.query_heads, k_heads=config.kv_heads,
+                                         width=dim, half_dimension=dim // 2, trig_batches=1),
+                    (dispatch.simd_rows_grid(count * (config.query_heads + config.kv_heads)), 1, 1))
+                dispatch.dispatch_attention(
+                    context, causal=True, scale=float(np.float32(1.0 / math.sqrt(dim))), query=q_rot, key=k_rot,
+                    value=dispatch.Tensor(v.buffer, (1, count, config.kv_heads, dim)), output=attended)
+                region = self.layout.attentions[attention_index]
+                common = dict(items=count, group_size=self.layout.group_size, token_elements=self.layout.token_elements,
+                              token_groups=self.layout.token_groups, token_stride=self.layout.bytes_per_token,
+                              source_items=count, source_offset=0)
+                # K rows are head-major [kv_heads, T, D]; a V row is kv_heads * D contiguous halves per token
+                for source, segment, heads, width in ((k_rot, region.key_offset, config.kv_heads, dim),
+                                                      (v, region.value_offset, 1, config.kv_heads * dim)):
+                    groups = count * heads * width // self.layout.group_size
+                    run("llmopt_cache_pack_attention_q8_simd", [source.buffer, slots, self.cache.token_pool],
+                        parameters.cache_attention(segment_offset=segment, heads=heads, head_dim=width, **common),
+                        (dispatch.round_up(groups, 8) * 32, 1, 1))
+                dispatch.dispatch_w4a16_linear(
+                    context, input=dispatch.Tensor(attended.buffer, (count, config.query_heads * dim)),
+                    weight=layer["o"][0], scale=layer["o"][1], output=other, bias=current, bias_row_stride=hidden)
+                attention_index += 1
+            else:
+                in_proj = self._empty((1, count, 3 * hidden))
+                conv_out = self._empty((1, count, hidden))
+                dispatch.dispatch_w4a16_linear(context, input=normed, weight=layer["in_proj"][0],
+                                               scale=layer["in_proj"][1],
+                                               output=dispatch.Tensor(in_proj.buffer, (count, 3 * hidden)))
+                state = self.conv_states[conv_index]
+                dispatch.dispatch_short_conv_prefill(
+                    context, in_proj=in_proj, conv_weight=layer["conv"], output=conv_out,
+                    conv_state_out=dispatch.Tensor(state.buffer.view(sequence * 6 * hidden, 6 * hidden), (1, hidden, 3)))
+                dispatch.dispatch_w4a16_linear(
+                    context, input=dispatch.Tensor(conv_out.buffer, (count, hidden)), weight=layer["out_proj"][0],
+                    scale=layer["out_proj"][1], output=other, bias=current, bias_row_stride=hidden)
+                conv_index += 1
+            current, other = other, current
+            dispatch.dispatch_w4a16_swiglu_ffn_command(
+                context, m=count, n=config.intermediate, k=hidden, epsilon=config.epsilon, activation=current,
+                residual=current, gate_weight=layer["gate"][0], gate_scale=layer["gate"][1], up_weight=layer["up"][0],
+                up_scale=layer["up"][1], down_weight=layer["down"][0], down_scale=layer["down"][1],
+                norm_weight=layer["ffn_norm"], output=other, reference_guards=False)
+            current, other = other, current
+        picked = self._empty((1,), "int32", 4)
+        last = current.buffer.view((count - 1) * hidden * 2, hidden * 2)
+        dispatch.dispatch_w4a16_lm_head_argmax_command(
+            context, m=1, n=config.vocabulary, k=hidden, epsilon=config.epsilon, input=dispatch.Tensor(last, (1, hidden)),
+            norm_weight=self.final_norm, weight=self.lm_head[0], scale=self.lm_head[1], output=picked,
+            reference_guards=False, two_stage=False)
+        self.prefill_kernels = len(commands.pending)
+        self.prefill_hidden = current  # rows of the last block's output, one per prompt token
+        commands.commit()
+        return int(picked.buffer.to_numpy(np.int32)[0])
+
     # ---- stepping ------------------------------------------------------------------------------
     def step(self, tokens: Sequence[int], past_tokens: int) -> list:
         """One host-driven decode step: token ids in, next token ids out (the

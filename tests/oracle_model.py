@@ -103,6 +103,53 @@ class OracleDecoder:
                                                     *weights["lm_head"], config.epsilon, want_logits=want_logits)
         return [int(pick) for pick in picks], logits
 
+    def prefill_dense(self, tokens, want_logits=False, sequence=0):
+        """The reference's prefill path for one sequence starting at position 0: dense causal fp16
+        attention over the prompt's own rotated keys and values (nothing is read back from the Q8
+        cache), the K / V of every token packed into the cache afterwards, the short-conv blocks
+        through the prefill kernel's arithmetic.  Returns (pick after the last token, logits)."""
+        config, weights, layout = self.config, self.weights, self.layout
+        hidden, dim = config.hidden, config.head_dim
+        if self.pasts[sequence] != 0:
+            raise ValueError("dense prefill starts from an empty cache")
+        count = len(tokens)
+        h = orc.embedding_f16([int(t) for t in tokens], weights["embedding"])
+        attention_index = conv_index = 0
+        for index, kind in enumerate(config.layers):
+            layer = weights[f"layer{index}"]
+            xn = orc.rms_norm(h, layer["input_norm"], config.epsilon)
+            if kind == "attention":
+                q, k, v = orc.w4a16_qkv_linear(xn, *layer["q"], *layer["k"], *layer["v"])
+                q_rot, k_rot = orc.rotary_qk(q.reshape(1, count, config.query_heads, dim),
+                                             k.reshape(1, count, config.kv_heads, dim),
+                                             self.cos[:count][None], self.sin[:count][None], half_dimension=dim // 2)
+                v_heads = np.ascontiguousarray(v.reshape(1, count, config.kv_heads, dim).transpose(0, 2, 1, 3))
+                attended = orc.attention_dense(q_rot, k_rot, v_heads, None, causal=1,
+                                               scale=float(np.float32(1.0 / math.sqrt(dim))), kv_heads=config.kv_heads,
+                                               token_first_output=1)
+                region = layout.attentions[attention_index]
+                new_slots = np.arange(count, dtype=np.uint32)
+                for segment, source in ((region.key_offset, k_rot[0]), (region.value_offset, v_heads[0])):
+                    orc.cache_pack_attention_q8(np.ascontiguousarray(source), new_slots, self.pools[sequence],
+                                                segment_offset=segment, heads=config.kv_heads, head_dim=dim,
+                                                group_size=layout.group_size, token_elements=layout.token_elements,
+                                                token_stride=layout.bytes_per_token, source_items=count)
+                h = orc.w4a16_linear(attended.reshape(count, -1), *layer["o"], bias=h, bias_row_stride=hidden)
+                attention_index += 1
+            else:
+                in_proj = orc.w4a16_linear(xn, *layer["in_proj"])
+                out, self.conv_states[sequence][conv_index] = orc.short_conv_prefill(
+                    in_proj, layer["conv"].reshape(hidden, 3), None)
+                h = orc.w4a16_linear(out, *layer["out_proj"], bias=h, bias_row_stride=hidden)
+                conv_index += 1
+            h, _, _ = orc.w4a16_swiglu_ffn(h, h, *layer["gate"], *layer["up"], *layer["down"], layer["ffn_norm"],
+                                           config.epsilon)
+        self.pasts[sequence] = count
+        self.last_hidden = h
+        picks, logits, _ = orc.w4a16_lm_head_argmax(np.ascontiguousarray(h[-1:]), weights["final_norm"],
+                                                    *weights["lm_head"], config.epsilon, want_logits=want_logits)
+        return int(picks[0]), logits
+
     def prefill(self, tokens, want_logits=False, sequence=0):
         """A whole prompt of one sequence in one call; returns (pick after its last token, logits)."""
         picks, logits = self.forward([(sequence, token) for token in tokens], [len(tokens) - 1], want_logits)

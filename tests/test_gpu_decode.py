@@ -87,3 +87,62 @@ def test_hybrid_conv_attention_batched_teacher_forced(runtime):
                 mismatches += 1
         tokens = [prompts[b, position + 1] if position + 1 < prompt_length else results[b][0] for b in range(batch)]
     assert mismatches <= 3, f"{mismatches} near-tie picks differ"
+
+
+@pytest.mark.parametrize("layers,prompt_length", [(("attention",) * 3, 70), (("conv", "attention", "conv", "attention"), 130)])
+def test_prefill_path_then_decode_matches_oracle(runtime, layers, prompt_length):
+    """The prompt in one pass (one row per token through every linear — the tensor-memory GEMM from
+    64 rows on — dense causal attention, bulk cache pack, short-conv prefill), then greedy decode
+    over the cache the prefill left: the first token, the last prompt row's hidden state and the
+    following decode tokens equal the oracle's dense-prefill route."""
+    from llmopt_b200.decode_engine import DecodeEngine
+    from llmopt_b200.model import random_weights, tiny_config
+    from oracle_model import OracleDecoder
+
+    config = tiny_config(layers=layers, hidden=256, heads=4, kv_heads=2, head_dim=64, intermediate=512, vocabulary=2048)
+    weights = random_weights(config, seed=3, std=0.05)
+    prompt = np.random.default_rng(3).integers(0, config.vocabulary, size=prompt_length).tolist()
+    steps, capacity = 24, prompt_length + 25
+    engine = DecodeEngine(runtime, config, weights, batch=1, capacity=capacity)
+    cpu = OracleDecoder(config, weights, capacity)
+    want, _ = cpu.prefill_dense(prompt)
+    got = engine.prefill(prompt)
+    hidden = engine.prefill_hidden.buffer.to_numpy(np.float16, (prompt_length, config.hidden)).astype(np.float64)
+    reference = cpu.last_hidden.astype(np.float64)
+    drift = np.max(np.abs(hidden - reference)) / np.max(np.abs(reference))
+    assert drift <= 5e-3, f"prefill hidden rows differ by {drift:.3e} of their scale"
+    assert got == want
+    mismatches = 0
+    for step in range(steps):
+        got = engine.step([want], prompt_length + step)[0]
+        want_next, logits = cpu.step(want, want_logits=True)
+        if got != want_next:
+            row = logits[0].astype(np.float64)
+            gap = abs(row[want_next] - row[got]) / max(np.max(np.abs(row)), 1e-6)
+            assert gap <= 5e-3, f"step {step}: {got} != {want_next}, logit gap {gap:.3e}"
+            mismatches += 1
+        want = want_next
+    assert mismatches <= 1, f"{mismatches} near-tie picks differ"
+
+
+def test_prefill_path_on_the_smollm2_shape_gives_the_stream_of_the_stepped_route(runtime):
+    """SmolLM2-135M shape, 512-token prompt: prefill in one pass + 32 decode steps produce the token
+    stream the oracle produced feeding the prompt token by token (tests/golden/decode_streams.npz):
+    the two routes differ only in how the prompt's keys and values were read (fp16 versus the Q8
+    cache), which the picks of this stream tolerate (their smallest top-2 gap is 8.5e-2)."""
+    import os
+
+    from llmopt_b200 import model
+    from llmopt_b200.decode_engine import DecodeEngine
+
+    data = np.load(os.path.join(os.path.dirname(__file__), "golden", "decode_streams.npz"))
+    prompts, picks = data["smollm2_prompts"], data["smollm2_picks"]
+    config = model.SMOLLM2_135M
+    engine = DecodeEngine(runtime, config, model.random_weights(config, seed=0), batch=1, capacity=600)
+    token = engine.prefill(prompts[0].tolist())
+    stream = [token]
+    for step in range(32):
+        token = engine.step([token], 512 + step)[0]
+        stream.append(token)
+    assert stream == picks[0, :33].tolist()
+    assert engine.prefill_kernels < 16 * 30
