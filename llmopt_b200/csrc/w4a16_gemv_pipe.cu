@@ -627,6 +627,17 @@ uint32_t register_resident_limit() {
   return limit;
 }
 
+// Wide-batch forms (two and four batch tiles) compiled for two resident CTAs per SM (at most 112
+// registers, a few spilled words in the dual form) instead of one CTA with all the registers it
+// wants: LLMOPT_CUDA_GEMV_WIDE_RESIDENCY=2 selects it.
+inline bool wide_forms_at_two_ctas() {
+  static const bool two = []() {
+    const char* text = getenv("LLMOPT_CUDA_GEMV_WIDE_RESIDENCY");
+    return text != nullptr && text[0] == '2';
+  }();
+  return two;
+}
+
 template <int NT, int NMAT, int EPI, bool SMALLX, int GPW>
 bool plan_pipe(const KernelArgs& args, const GemvProblem& p, PipePlan* plan) {
   uint32_t total_tiles = 0;
@@ -644,8 +655,10 @@ bool plan_pipe(const KernelArgs& args, const GemvProblem& p, PipePlan* plan) {
   // Wide-batch forms on few, short tiles (QKV, o_proj): size grid and ring for the CTAs the registers really
   // let reside (batch 32: QKV 17.8 -> 14.6, o_proj 12.4 -> 10.9 us).  On many or long tiles the oversubscribed
   // grid measured faster (gate/up, down, LM head), so those keep it.
-  if (NT > 1 && total_tiles <= 3u * sms && chunks_per_tile <= 4u &&
-      register_resident_limit<NT, NMAT, EPI, SMALLX, GPW>() < most)
+  if (NT > 1 && wide_forms_at_two_ctas())
+    most = 2u;
+  else if (NT > 1 && total_tiles <= 3u * sms && chunks_per_tile <= 4u &&
+           register_resident_limit<NT, NMAT, EPI, SMALLX, GPW>() < most)
     most = register_resident_limit<NT, NMAT, EPI, SMALLX, GPW>();
   for (uint32_t resident = most; resident >= 1; --resident) {
     const size_t per_cta = kSharedPerSm / resident - 1024;
@@ -681,6 +694,8 @@ int run_pipe(const KernelArgs& args, const GemvProblem& p, const PipePlan& plan)
                     : w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX, GPW, kDense, kOneRow>;
   else if (sparse)
     kernel = w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX, GPW, kSparse>;
+  else if (NT > 1 && wide_forms_at_two_ctas())
+    kernel = w4a16_gemv_pipe_kernel<NT, NMAT, EPI, SMALLX, GPW, (NT > 1 ? 2 : kDense)>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.shared_bytes) != cudaSuccess) {
     cudaGetLastError();
     return -1;

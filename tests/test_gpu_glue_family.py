@@ -212,3 +212,22 @@ def test_triangular_recurrence_is_bit_exact(runtime, oracle):
                                                 output=out)
         want = oracle.triangular_recurrence(matrices, start=start, stop=stop)
         assert np.array_equal(out.buffer.to_numpy(np.float32, matrices.shape).view(np.uint32), want.view(np.uint32))
+
+
+def test_a_package_declaring_every_entry_validates_against_the_library(runtime):
+    """Package validation as the reference's loader does it (lib/metal_native.ml:271-285): every
+    kernel entry point a package declares must resolve in the loaded library.  The package here
+    declares the whole entry table, written and read back through the package.llmopt envelope."""
+    from llmopt_b200 import kernel_abi, serving_package as sp
+
+    tagged = [entry for entry in kernel_abi.ENTRIES
+              if entry.operation in sp._OPERATION_OF and entry.input_dtype in sp._DTYPE_OF and entry.output_dtype in sp._DTYPE_OF]
+    assert len(tagged) > 150
+    package = sp.of_bytes(sp.Package("compiled-graph", "model.metallib", tagged).to_bytes())
+    package.validate_declared_functions(runtime)
+    missing = [entry.name for entry in kernel_abi.ENTRIES if not runtime.has_function(entry.name)]
+    assert not missing, missing
+    with pytest.raises(sp.PackageError, match="does not define declared kernel"):
+        sp.Package("compiled-graph", "model.metallib",
+                   [kernel_abi.Entry("llmopt_no_such_kernel", kernel_abi.LINEAR, "float16", "float16")]
+                   ).validate_declared_functions(runtime)

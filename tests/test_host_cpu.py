@@ -300,3 +300,59 @@ def test_epilogue_digest_names_and_programs():
                        + bytes([3, 1, 1, 30]))
     with pytest.raises(ValueError):
         ep.tagged("bias")
+
+
+def test_serving_package_envelope_round_trip_and_errors():
+    """package.llmopt (lib/serving_package.ml:303-373): magic, version 27, stage, target, model,
+    kernel library, declared kernels with operation / dtype tags, tensor store, page size, two
+    length-prefixed blobs; the reader refuses what the reference's refuses, with its messages."""
+    from llmopt_b200 import kernel_abi, serving_package as sp
+
+    kernels = [kernel_abi.find_entry(name=name, operation=operation, input_dtype=i, output_dtype=o)
+               for name, operation, i, o in (
+                   ("llmopt_w4a16_qkv_linear_f16_g64", kernel_abi.W4A16_QKV_LINEAR, "float16", "float16"),
+                   ("llmopt_w4a16_lm_head_argmax_f16", kernel_abi.W4A16_LM_HEAD_ARGMAX, "float16", "int32"),
+                   ("llmopt_attention_q8_paged_simd_h64_gqa3", kernel_abi.ATTENTION, "float16", "float16"),
+                   ("llmopt_cache_pack_attention_q8_pair_simd", kernel_abi.CACHE, "float16", "uint8"),
+                   ("llmopt_rms_rope_qk_f16_simd_h64", kernel_abi.RMS_ROPE_QK, "float16", "float16"))]
+    package = sp.Package("serving", "kernels/model.metallib", kernels, schedule=b"\x01\x02\x03", memory_plan=b"\x09",
+                         model="smollm2-135m", tensor_store="weights/model.llmoptwt", page_size=16)
+    data = package.to_bytes()
+    # byte-level layout of the head: magic, u16 version, u8 stage (1 = serving), u8 target, option tag, u32 length
+    assert data[:8] == b"LLMOPTPK" and data[8:12] == bytes([27, 0, 1, 0]) and data[12] == 1
+    assert data[13:17] == (12).to_bytes(4, "little") and data[17:29] == b"smollm2-135m"
+    back = sp.of_bytes(data)
+    assert back == package and back.kernels[2].threadgroup == (256, 1, 1)
+    assert back.kernels[1].operation == "w4a16-lm-head-argmax" and back.kernels[1].output_dtype == "int32"
+    for mutate, message in (
+            (lambda b: b"XLMOPTPK" + b[8:], "invalid serving-package magic"),
+            (lambda b: b[:8] + bytes([26, 0]) + b[10:], "unsupported serving-package version: 26"),
+            (lambda b: b[:10] + bytes([2]) + b[11:], "unknown serving-package stage tag: 2"),
+            (lambda b: b[:11] + bytes([1]) + b[12:], "unsupported serving-package target tag: 1"),
+            (lambda b: b[:-1], "truncated binary input"),
+            (lambda b: b + b"\0", "trailing binary input")):
+        with pytest.raises(sp.PackageError, match=message):
+            sp.of_bytes(mutate(data))
+    with pytest.raises(sp.PackageError, match="must declare a tensor store"):
+        sp.of_bytes(sp.Package("serving", "a.metallib", kernels).to_bytes())
+    with pytest.raises(sp.PackageError, match="names must be unique"):
+        sp.of_bytes(sp.Package("compiled-graph", "a.metallib", kernels + kernels[:1]).to_bytes())
+    with pytest.raises(sp.PackageError, match="not canonical"):
+        sp.of_bytes(sp.Package("compiled-graph", "../a.metallib", kernels).to_bytes())
+
+    class FakeRuntime:  # has_function / preload_pipeline against a name set
+        def __init__(self, names):
+            self.names, self.preloaded = set(names), []
+
+        def has_function(self, name):
+            return name in self.names
+
+        def preload_pipeline(self, name):
+            self.preloaded.append(name)
+
+    runtime = FakeRuntime(entry.name for entry in kernels)
+    back.validate_declared_functions(runtime)
+    assert runtime.preloaded == [entry.name for entry in kernels]
+    runtime.names.discard("llmopt_rms_rope_qk_f16_simd_h64")
+    with pytest.raises(sp.PackageError, match="does not define declared kernel: llmopt_rms_rope_qk_f16_simd_h64"):
+        back.validate_declared_functions(runtime)
