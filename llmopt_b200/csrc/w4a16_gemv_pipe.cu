@@ -438,7 +438,41 @@ __global__ void __launch_bounds__(kThreads, RES) w4a16_gemv_pipe_kernel(const Ge
             acc[a][0][0] = fmaf(stage_scale_a[a][jg], sum[0], acc[a][0][0]);
             acc[a][0][2] = fmaf(stage_scale_b[a][jg], sum[2], acc[a][0][2]);
           }
-        } else if (SMALLX) {        } else {
+        } else if (SMALLX) {
+          const uint4 first = first_base[g * unit_stride];
+          const uint4 second = second_base[g * unit_stride];
+          const uint32_t frag[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
+          const float bias0 = bias_base0[g * bias_stride0];
+          const float bias1 = bias_base1[g * bias_stride1];
+#pragma unroll
+          for (int a = 0; a < NMAT; ++a) {
+            const unsigned char* base = stage + a * kStageBytes;
+            const uint2 word_a = *reinterpret_cast<const uint2*>(base + word_offset + jg * 32);
+            const uint2 word_b = *reinterpret_cast<const uint2*>(base + word_offset + jg * 32 + 8 * kRowBytes);
+            const float scale_a = __half2float(*reinterpret_cast<const __half*>(base + scale_offset + jg * 2));
+            const float scale_b =
+                __half2float(*reinterpret_cast<const __half*>(base + scale_offset + jg * 2 + 8 * kScaleRow));
+            // the group's bias term rides in as the accumulator's start value
+            float sum[4] = {bias0, bias1, bias0, bias1};  // the table holds the negated term
+            uint32_t a_even, a_odd, b_even, b_odd;
+            nibbles_biased(word_a.x, a_even, a_odd);
+            nibbles_biased(word_b.x, b_even, b_odd);
+            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[0], frag[1]);
+            nibbles_biased(word_a.x >> 8, a_even, a_odd);
+            nibbles_biased(word_b.x >> 8, b_even, b_odd);
+            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[2], frag[3]);
+            nibbles_biased(word_a.y, a_even, a_odd);
+            nibbles_biased(word_b.y, b_even, b_odd);
+            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[4], frag[5]);
+            nibbles_biased(word_a.y >> 8, a_even, a_odd);
+            nibbles_biased(word_b.y >> 8, b_even, b_odd);
+            mma_16816(sum, a_even, b_even, a_odd, b_odd, frag[6], frag[7]);
+            acc[a][0][0] = fmaf(scale_a, sum[0], acc[a][0][0]);
+            acc[a][0][1] = fmaf(scale_a, sum[1], acc[a][0][1]);
+            acc[a][0][2] = fmaf(scale_b, sum[2], acc[a][0][2]);
+            acc[a][0][3] = fmaf(scale_b, sum[3], acc[a][0][3]);
+          }
+        } else {
           uint32_t a_frag[NMAT][4][4];
           float scale_a[NMAT], scale_b[NMAT];
 #pragma unroll
