@@ -8,8 +8,8 @@ Everything is seeded: weights = ``model.random_weights(config, seed=0)`` (N(0, 0
 W4A16 group-64 by the numpy restatement of the reference quantiser, tied LM head), prompts are
 uniform random ids from ``numpy.random.default_rng(seed)``.  Per case the file holds the
 prompts, the oracle's pick after the prompt and after every further step (teacher-forced on its
-own picks = free-running greedy decode), the runner-up id of every pick and the gap between the
-two best logits relative to the largest |logit| of the step (what a near-tie analysis needs),
+own picks = free-running greedy decode), the eight best candidates of every pick with their
+logits relative to the largest |logit| of the step (what a near-tie analysis needs),
 and the hidden state that entered the LM head at the last step (the accumulated rounding
 difference of the whole stack shows there before any argmax hides it).
 
@@ -50,16 +50,20 @@ def run_case(name: str, case: dict) -> dict:
     oracle = OracleDecoder(config, weights, prompt_length + steps + 1, sequences=sequences)
     start = time.time()
     picks = np.zeros((sequences, steps + 1), np.int64)      # picks[:, 0]: after the prompt
-    runner_up = np.zeros((sequences, steps + 1), np.int64)
-    gap = np.zeros((sequences, steps + 1), np.float64)
+    top_ids = np.zeros((sequences, steps + 1, 8), np.int64)  # the eight largest logits, best first
+    top_gap = np.zeros((sequences, steps + 1, 8), np.float64)  # (logit of the pick - logit) / max |logit|
+    gap = np.zeros((sequences, steps + 1), np.float64)       # to the best candidate that is not the pick
 
     def record(column, chosen, logits):
         for s in range(sequences):
             row = logits[s].astype(np.float64)
-            order = np.argsort(row)[-2:]
+            scale = max(np.max(np.abs(row)), 1e-9)
+            order = np.argsort(-row, kind="stable")[:8]
             picks[s, column] = chosen[s]
-            runner_up[s, column] = order[0] if order[1] == chosen[s] else order[1]
-            gap[s, column] = (row[chosen[s]] - row[runner_up[s, column]]) / max(np.max(np.abs(row)), 1e-9)
+            top_ids[s, column] = order
+            top_gap[s, column] = (row[chosen[s]] - row[order]) / scale
+            others = [index for index in order if index != chosen[s]]
+            gap[s, column] = (row[chosen[s]] - row[others[0]]) / scale
 
     # the prompt: every sequence's rows in one call, picks wanted for each sequence's last row
     rows = [(s, int(prompts[s, t])) for s in range(sequences) for t in range(prompt_length)]
@@ -71,7 +75,8 @@ def run_case(name: str, case: dict) -> dict:
         chosen, logits = oracle.step_all(chosen, want_logits=True)
         record(step + 1, chosen, logits)
     print(f"{name}: {steps} steps done in {time.time() - start:.0f} s; smallest top-2 gap {gap.min():.3e}", flush=True)
-    return {f"{name}_prompts": prompts, f"{name}_picks": picks, f"{name}_runner_up": runner_up, f"{name}_gap": gap,
+    return {f"{name}_prompts": prompts, f"{name}_picks": picks, f"{name}_top_ids": top_ids, f"{name}_top_gap": top_gap,
+            f"{name}_gap": gap,
             f"{name}_last_hidden": oracle.last_hidden.copy()}
 
 

@@ -7,8 +7,8 @@ sequences side by side).
 
 The GPU consumes the oracle's stream (teacher forcing: prompt tokens, then the oracle's picks), so
 every step is compared on the same input and one disagreement cannot hide later ones.  A pick
-must equal the oracle's; the only excuse is a near-tie: the GPU choosing the oracle's runner-up
-while the oracle's two best logits are closer than the difference the stack has accumulated by
+must equal the oracle's; the only excuse is a near-tie: the GPU choosing one of the oracle's
+eight best candidates whose logit is closer to the pick's than the difference the stack has accumulated by
 then (5e-3 of the step's largest |logit|: every product and attention is within 2e-3 of its
 output scale, and a flipped Q8 code of a cached key or value moves that element by 1/127 of its
 group's range, so the last hidden state of these 16- to 30-block stacks differs by up to about
@@ -36,7 +36,7 @@ def _decode_against_stream(runtime, config_name, case):
     if f"{case}_picks" not in data:
         pytest.skip(f"tests/golden/decode_streams.npz holds no '{case}' stream (run tests/golden/make_decode_golden.py {case})")
     prompts, picks = data[f"{case}_prompts"], data[f"{case}_picks"]
-    runner_up, gap = data[f"{case}_runner_up"], data[f"{case}_gap"]
+    top_ids, top_gap, gap = data[f"{case}_top_ids"], data[f"{case}_top_gap"], data[f"{case}_gap"]
     sequences, prompt_length = prompts.shape
     steps = picks.shape[1] - 1
     config = getattr(model, config_name)
@@ -50,8 +50,10 @@ def _decode_against_stream(runtime, config_name, case):
     for step in range(steps + 1):
         for s in range(sequences):
             if got[s] != picks[s, step]:
-                record = (step, s, int(got[s]), int(picks[s, step]), int(runner_up[s, step]), float(gap[s, step]))
-                (near_ties if got[s] == runner_up[s, step] and gap[s, step] <= NEAR_TIE else wrong).append(record)
+                rank = np.flatnonzero(top_ids[s, step] == got[s])
+                distance = float(top_gap[s, step, rank[0]]) if rank.size else float("inf")
+                record = (step, s, int(got[s]), int(picks[s, step]), distance)
+                (near_ties if distance <= NEAR_TIE else wrong).append(record)
         if step < steps:
             got = engine.step(picks[:, step].tolist(), prompt_length + step)
     # accumulated difference of the whole stack: the hidden state that entered the LM head at the last step
@@ -66,7 +68,7 @@ def _decode_against_stream(runtime, config_name, case):
 
 def _report(case, near_ties, wrong, smallest_gap):
     return (f"{case}: {len(wrong)} wrong picks {wrong[:5]}, {len(near_ties)} near-tie picks {near_ties[:5]} "
-            f"(step, sequence, gpu, oracle, oracle runner-up, oracle top-2 gap); smallest top-2 gap of the stream {smallest_gap:.3e}")
+            f"(step, sequence, gpu, oracle, logit distance of the gpu pick from the oracle pick / max |logit|); smallest top-2 gap of the stream {smallest_gap:.3e}")
 
 
 def test_smollm2_135m_shape_512_prompt_128_steps(runtime):
