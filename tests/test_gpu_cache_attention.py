@@ -504,7 +504,7 @@ def test_slots_outside_the_pool_are_refused_on_the_device(runtime):
     config = dispatch.PagedAttentionConfig(token_elements=128, key_offset=0, value_offset=64, group_size=64,
                                            token_stride=132, scale=0.125)
     for window in (None, 64):
-        slots = np.array([0, 1, capacity + 5, 2] + [3] * 76, np.uint32)
+        slots = np.array([0, 1, 2] + [3] * 38 + [capacity + 5] + [4] * 38, np.uint32)  # the bad slot lies inside the window
         out = _tensor(runtime, np.full((1, 1, 2, 64), np.nan, np.float16))
         with pytest.raises(NativeError, match="outside its pool"):
             dispatch.dispatch_paged_attention_q8(
