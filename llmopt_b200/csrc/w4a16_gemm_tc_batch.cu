@@ -1,17 +1,22 @@
-// Decode batches (9..64 rows) of the W4A16 group-64 product on tcgen05, with the operands swapped
-// relative to the prefill kernel: the WEIGHT tile is the M side of the MMA (128 rows, converted to
-// fp16 in shared memory) and the activations are the N side (the batch, padded to 32 or 64), so
-// the tensor work is proportional to the batch and the kernel is bound by the weight stream from
-// HBM, like the single-row GEMV, instead of by a 128-row activation tile that is mostly padding.
+// Decode batches (9..128 rows) of the W4A16 group-64 product on tcgen05, with the operands swapped
+// relative to the prefill kernel: the WEIGHT tile is the M side of the MMA (128 rows) and the
+// activations are the N side (the batch, padded to 16, 32, 64 or 128), so the tensor work is
+// proportional to the batch and the kernel is bound by the weight stream from HBM, like the
+// single-row GEMV, instead of by a 128-row activation tile that is mostly padding.
 //   D^T[weight row, batch row] = W[weight row, :] . X[batch row, :]      per 64-wide k-block
+// The converted weights never touch shared memory: the A operand of the MMA is read from TENSOR
+// MEMORY, where lane = weight row and one 32-bit column = two consecutive k (K-major), which is
+// exactly what a thread that converts one weight row holds in registers (tcgen05.st, 32 columns per
+// k-block).  Shared memory carries only the packed bytes and the activation tiles.
 // Roles per CTA (one 128-row weight tile; gate and up tiles together in the dual form):
 //   warp 0        TMA: X tile [NB x 64] fp16, 128-byte swizzle, 4-deep ring
-//   warp 1        tcgen05.mma 128 x NB x 16, four per k-block and matrix; accumulators in tensor memory
-//   warps 2-9     each streams ITS rows' packed weights with cp.async in groups of four k-blocks (128
-//                 bytes per row, three groups deep, private to the warp: no barrier on the weight
-//                 stream) and converts them: int4 -> fp16 (q * scale) rows of the A tile, 128-byte
-//                 swizzled, 3-deep ring.  Eight warps issuing loads keep enough requests in flight
-//                 for HBM; one or two producer warps (or the TMA unit) reach about 10 GB/s per SM.
+//   warp 1        tcgen05.mma 128 x NB x 16 (A from tensor memory, B = X from shared memory), four per
+//                 k-block and matrix; accumulators in tensor memory
+//   warps 2-9     warp w owns tensor-memory lanes 32 (w % 4) .. +31, i.e. those 32 weight rows.  It
+//                 streams their packed bytes with cp.async in groups of four k-blocks (private to the
+//                 warp: no barrier on the weight stream, several groups deep) and converts them:
+//                 int4 -> fp16 (q * scale), 3-deep ring of A stages in tensor memory.  Dual form: the
+//                 two warps of a lane quarter take one matrix each; single form: alternate k-blocks.
 // K is split over CTAs when there are few weight tiles (narrow projections); the last CTA of a tile
 // adds the parked fp32 partials in split order and writes the result.  All waits are bounded.
 // Output is transposed on the way out: a thread owns one weight row = one output column.
@@ -31,7 +36,7 @@ namespace {
 
 constexpr int kRows = 128;  // weight rows per matrix and CTA
 constexpr int kBK = 64, kGroupBlocks = 4;
-constexpr int kXStages = 4, kWStages = 3, kRawStages = 3;
+constexpr int kXStages = 4, kAStages = 3;
 constexpr int kConvertWarps = 8;
 constexpr int kThreads = (2 + kConvertWarps) * 32;
 constexpr uint32_t kSplitCounterTiles = 1u << 14;
@@ -50,20 +55,56 @@ struct BatchProblem {
   uint32_t* counters;  // [tiles], zero between launches
 };
 
+constexpr uint32_t next_power_of_two(uint32_t value) {
+  uint32_t power = 32;
+  while (power < value) power *= 2;
+  return power;
+}
+
 template <int NMAT, int NB>
 struct Layout {
   static constexpr int kXTile = NB * 128;             // NB batch rows x 64 halves
-  static constexpr int kWTile = NMAT * kRows * 128;   // converted rows of one k-block
+  static constexpr int kXStride = (kXTile + 1023) / 1024 * 1024;
   static constexpr int kRawTile = NMAT * kRows * 128; // packed rows of one group (4 k-blocks)
+  // groups of packed bytes in flight per warp: what is left of shared memory beside the X ring
+  static constexpr int kRawStages = NMAT == 2 ? (NB > 64 ? 4 : 5) : 6;
   static constexpr int kOffsetX = 0;
-  static constexpr int kOffsetW = kOffsetX + kXStages * ((kXTile + 1023) / 1024 * 1024);
-  static constexpr int kOffsetRaw = kOffsetW + kWStages * kWTile;
+  static constexpr int kOffsetRaw = kOffsetX + kXStages * kXStride;
   static constexpr int kOffsetBarriers = kOffsetRaw + kRawStages * kRawTile;
-  static constexpr int kBarriers = 2 * kXStages + 2 * kWStages + 1;
+  static constexpr int kBarriers = 2 * kXStages + 2 * kAStages + 1;
   static constexpr int kOffsetHolder = kOffsetBarriers + kBarriers * 8;
   static constexpr int kBytes = kOffsetHolder + 16 + 1024;
-  static constexpr uint32_t kColumns = NMAT * NB < 32 ? 32 : NMAT * NB;  // tensor-memory columns (power of two)
+  // tensor memory: NMAT accumulators of NB fp32 columns, then kAStages stages of the converted k-block
+  // (64 k = 32 columns per matrix)
+  static constexpr uint32_t kAccumulatorColumns = (NMAT * NB + 31) / 32 * 32;  // the A ring starts on a 32-column boundary
+  static constexpr uint32_t kAColumns = NMAT * 32;
+  static constexpr uint32_t kColumns = next_power_of_two(kAccumulatorColumns + kAStages * kAColumns);
+  static_assert(kColumns <= 512, "tensor memory has 512 columns");
+  static_assert(kBytes <= 227 * 1024, "shared memory of one CTA");
 };
+
+// D[tmem] (+)= A[tmem] . B[smem descriptor]: the A operand (128 lanes x 8 columns per k16 step) comes from tensor memory.
+__device__ __forceinline__ void mma_f16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t accumulate,
+                                               uint32_t instruction) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(instruction), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// 32 consecutive columns of this thread's lane <- 32 registers.
+__device__ __forceinline__ void tmem_store_32(uint32_t address, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(address), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
 
 __device__ uint32_t g_abandoned_batch_launch = 0;
 
@@ -73,15 +114,15 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
                            uint32_t launch_id) {
   constexpr int NMAT = EPI == kBatchDualSwiglu ? 2 : 1;
   using L = Layout<NMAT, NB>;
-  constexpr int kXStride = (L::kXTile + 1023) / 1024 * 1024;
+  constexpr int kRawStages = L::kRawStages;
   extern __shared__ unsigned char shared_raw[];
   grid_chain_prologue();
   if (*reinterpret_cast<volatile uint32_t*>(&g_abandoned_batch_launch) == launch_id) return;
   const uint32_t base = (smem_u32(shared_raw) + 1023u) & ~1023u;
   unsigned char* base_pointer = shared_raw + (base - smem_u32(shared_raw));
   const uint32_t x_full = base + L::kOffsetBarriers, x_empty = x_full + kXStages * 8;
-  const uint32_t w_full = x_empty + kXStages * 8, w_empty = w_full + kWStages * 8;
-  const uint32_t accumulator_full = w_empty + kWStages * 8;
+  const uint32_t a_full = x_empty + kXStages * 8, a_empty = a_full + kAStages * 8;
+  const uint32_t accumulator_full = a_empty + kAStages * 8;
   volatile uint32_t* holder = reinterpret_cast<volatile uint32_t*>(base_pointer + L::kOffsetHolder);  // [tmem, abort, last]
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -91,15 +132,18 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
   const uint32_t group_end = (uint32_t)((uint64_t)all_groups * (split + 1u) / p.splits);
   const uint32_t kb_begin = group_begin * kGroupBlocks;
   const uint32_t k_blocks = min(group_end * kGroupBlocks, all_k_blocks) - kb_begin;
+  // single-matrix form: the two warps of a lane quarter convert alternate k-blocks, so a stage of A is
+  // completed by four warps; dual form: one matrix each, eight warps per stage
+  constexpr uint32_t kWarpsPerStage = NMAT == 2 ? kConvertWarps : kConvertWarps / 2;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kXStages; ++s) {
       barrier_init(x_full + s * 8, 1);
       barrier_init(x_empty + s * 8, 1);
     }
-    for (int s = 0; s < kWStages; ++s) {
-      barrier_init(w_full + s * 8, kConvertWarps);
-      barrier_init(w_empty + s * 8, 1);
+    for (int s = 0; s < kAStages; ++s) {
+      barrier_init(a_full + s * 8, kWarpsPerStage);
+      barrier_init(a_empty + s * 8, 1);
     }
     barrier_init(accumulator_full, 1);
     holder[1] = 0u;
@@ -115,6 +159,7 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = holder[0];
+  const uint32_t tmem_a_ring = tmem_base + L::kAccumulatorColumns;
   volatile uint32_t* abort_flag = holder + 1;
 
   auto give_up = [&]() {
@@ -134,7 +179,7 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
           break;
         }
         barrier_expect_tx(x_full + s * 8, L::kXTile);
-        tma_load_2d(base + L::kOffsetX + s * kXStride, &map_x, (int32_t)((kb_begin + kb) * kBK), 0, x_full + s * 8);
+        tma_load_2d(base + L::kOffsetX + s * L::kXStride, &map_x, (int32_t)((kb_begin + kb) * kBK), 0, x_full + s * 8);
         issued = kb + 1;
       }
       if (*abort_flag) {
@@ -148,58 +193,62 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
       constexpr uint32_t instruction = instruction_descriptor(kRows, NB);
       bool ok = true;
       for (uint32_t kb = 0; kb < k_blocks && ok; ++kb) {
-        const uint32_t s = kb % kXStages, t = kb % kWStages;
+        const uint32_t s = kb % kXStages, t = kb % kAStages;
         ok = !*abort_flag && barrier_wait(x_full + s * 8, (kb / kXStages) & 1u) &&
-             barrier_wait(w_full + t * 8, (kb / kWStages) & 1u);
+             barrier_wait(a_full + t * 8, (kb / kAStages) & 1u);
         if (!ok) {
           give_up();
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t x_tile = base + L::kOffsetX + s * kXStride, w_tile = base + L::kOffsetW + t * L::kWTile;
+        const uint32_t x_tile = base + L::kOffsetX + s * L::kXStride, a_stage = tmem_a_ring + t * L::kAColumns;
 #pragma unroll
         for (int a = 0; a < NMAT; ++a)
 #pragma unroll
           for (int j = 0; j < kBK / 16; ++j)
-            mma_f16(tmem_base + a * NB, operand_descriptor(w_tile + a * (kRows * 128) + j * 32),
-                    operand_descriptor(x_tile + j * 32), (kb > 0 || j > 0) ? 1u : 0u, instruction);
+            mma_f16_tmem_a(tmem_base + a * NB, a_stage + a * 32 + j * 8, operand_descriptor(x_tile + j * 32),
+                           (kb > 0 || j > 0) ? 1u : 0u, instruction);
         mma_commit(x_empty + s * 8);
-        mma_commit(w_empty + t * 8);
+        mma_commit(a_empty + t * 8);
       }
       if (ok) mma_commit(accumulator_full);
     }
   } else {
     // ------------------------------ conversion, then epilogue ------------------------------
-    constexpr uint32_t kThreadsPerRow = 256 / (NMAT * kRows);  // 1 (dual) or 2
-    constexpr uint32_t kWords = 8 / kThreadsPerRow;            // packed words (8 weights each) per thread and k-block
-    const uint32_t index = threadIdx.x - 64u;
-    const uint32_t row = index / kThreadsPerRow, part = index % kThreadsPerRow;  // row of the stacked tile
-    const uint32_t matrix = row / kRows, weight_row = n0 + row % kRows;
+    // a warp reaches the tensor-memory lanes 32 (warp % 4) .. +31 only: those are its weight rows
+    const uint32_t quarter = warp & 3u, pair = (warp - 2u) >> 2;
+    const uint32_t tile_row = quarter * 32u + lane;      // row of the weight tile = tensor-memory lane
+    const uint32_t matrix = NMAT == 2 ? pair : 0u;
+    const uint32_t weight_row = n0 + tile_row;
     const bool row_present = weight_row < p.n;
     const uint32_t groups = p.k / 64;
-    const __half* scale_row = p.scale[NMAT == 2 ? matrix : 0] + (size_t)(row_present ? weight_row : 0u) * groups;
-    const uint32_t swizzle = (row & 7u) * 16u;
+    const __half* scale_row = p.scale[matrix] + (size_t)(row_present ? weight_row : 0u) * groups;
+    const uint32_t swizzle = (tile_row & 7u) * 16u;
+    const uint32_t lane_base = (quarter * 32u) << 16;     // lane field of this warp's tensor-memory addresses
     bool ok = true;
     // scales of a whole group per load, fetched one group (four k-blocks) ahead
-    const bool vector_ok = groups % 4u == 0u && ((uintptr_t)p.scale[NMAT == 2 ? matrix : 0] & 7u) == 0;
+    const bool vector_ok = groups % 4u == 0u && ((uintptr_t)p.scale[matrix] & 7u) == 0;
     FourHalves group_scales, next_scales = load_four(scale_row, kb_begin, groups, vector_ok, row_present);
 
-    // this warp's private weight stream: its rows, 8 lanes per row (128 contiguous bytes), 4 rows per instruction
-    constexpr uint32_t kRowsPerWarp = NMAT * kRows / kConvertWarps;  // 32 (dual) or 16
-    const uint32_t first_row = (warp - 2u) * kRowsPerWarp, copy_chunk = lane & 7u, copy_row = lane >> 3;
+    // This warp's private weight stream: the packed bytes of ITS rows and ITS k-blocks.  Dual form: all
+    // 128 bytes of a row's group, 8 lanes per row; single form: the two 32-byte pieces of its k-blocks
+    // (k-blocks pair, pair + 2 of the group), 4 lanes per row.
+    constexpr uint32_t kLanesPerRow = NMAT == 2 ? 8 : 4, kRowsPerPass = 32 / kLanesPerRow;
+    const uint32_t copy_row = lane / kLanesPerRow, copy_piece = lane % kLanesPerRow;
+    const uint32_t copy_chunk = NMAT == 2 ? copy_piece : 2u * pair + (copy_piece & 1u) + 4u * (copy_piece >> 1);
     const uint32_t row_bytes = p.k / 2, my_groups = (k_blocks + kGroupBlocks - 1u) / kGroupBlocks;
+    const uint8_t* packed = p.packed[matrix];
     auto issue_group = [&](uint32_t group) {
       if (group < my_groups) {
-        const uint32_t stage = base + L::kOffsetRaw + (group % kRawStages) * L::kRawTile;
+        const uint32_t stage = base + L::kOffsetRaw + (group % kRawStages) * L::kRawTile + matrix * (kRows * 128u);
         const uint32_t byte_at = (group_begin + group) * (kGroupBlocks * kBK / 2) + copy_chunk * 16u;
         const uint32_t bytes = byte_at < row_bytes ? 16u : 0u;  // beyond the row end: zeros
 #pragma unroll
-        for (uint32_t pass = 0; pass < kRowsPerWarp / 4; ++pass) {
-          const uint32_t tile_row = first_row + pass * 4u + copy_row;
-          const uint32_t source_row = min(n0 + tile_row % kRows, p.n - 1u);  // absent rows re-read the last one
-          const uint8_t* source =
-              p.packed[NMAT == 2 ? tile_row / kRows : 0] + (size_t)source_row * row_bytes + (bytes ? byte_at : 0u);
-          const uint32_t target = stage + tile_row * 128u + ((copy_chunk ^ (tile_row & 7u)) * 16u);
+        for (uint32_t pass = 0; pass < 32 / kRowsPerPass; ++pass) {
+          const uint32_t row = quarter * 32u + pass * kRowsPerPass + copy_row;
+          const uint32_t source_row = min(n0 + row, p.n - 1u);  // absent rows re-read the last one
+          const uint8_t* source = packed + (size_t)source_row * row_bytes + (bytes ? byte_at : 0u);
+          const uint32_t target = stage + row * 128u + ((copy_chunk ^ (row & 7u)) * 16u);
           asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(target), "l"(source), "r"(bytes) : "memory");
         }
       }
@@ -209,7 +258,7 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
     for (uint32_t group = 0; group + 1u < kRawStages; ++group) issue_group(group);
 
     for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-      const uint32_t t = kb % kWStages, group = kb / kGroupBlocks, quarter_of_group = kb % kGroupBlocks;
+      const uint32_t t = kb % kAStages, group = kb / kGroupBlocks, quarter_of_group = kb % kGroupBlocks;
       const uint32_t rs = group % kRawStages;
       if (quarter_of_group == 0u) {
         __syncwarp();  // every lane is done with the stage the next copies overwrite
@@ -219,36 +268,34 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
         group_scales = next_scales;
         next_scales = load_four(scale_row, kb_begin + kb + kGroupBlocks, groups, vector_ok, row_present);
       }
+      if (NMAT == 1 && (quarter_of_group & 1u) != pair) continue;  // the other warp of this lane quarter converts it
       const __half scale = group_scales.value[quarter_of_group];
-      ok = !*abort_flag && barrier_wait(w_empty + t * 8, ((kb / kWStages) & 1u) ^ 1u);
+      ok = !*abort_flag && barrier_wait(a_empty + t * 8, ((kb / kAStages) & 1u) ^ 1u);
       if (!ok) {
         give_up();
         break;
       }
-      const unsigned char* raw = base_pointer + L::kOffsetRaw + rs * L::kRawTile + row * 128u;
-      uint32_t words[kWords];
-#pragma unroll
-      for (uint32_t i = 0; i < kWords / 4; ++i) {
-        const uint32_t raw_chunk = 2u * quarter_of_group + (kThreadsPerRow == 2 ? part : i);
-        const uint4 data = *reinterpret_cast<const uint4*>(raw + ((raw_chunk * 16u) ^ swizzle));
-        words[4 * i] = data.x, words[4 * i + 1] = data.y, words[4 * i + 2] = data.z, words[4 * i + 3] = data.w;
-      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const unsigned char* raw =
+          base_pointer + L::kOffsetRaw + rs * L::kRawTile + matrix * (kRows * 128u) + tile_row * 128u;
+      const uint4 first = *reinterpret_cast<const uint4*>(raw + (((2u * quarter_of_group) * 16u) ^ swizzle));
+      const uint4 second = *reinterpret_cast<const uint4*>(raw + (((2u * quarter_of_group + 1u) * 16u) ^ swizzle));
+      const uint32_t words[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
       const __half2 scale_pair = __halves2half2(scale, __hmul(scale, __float2half(0.0625f)));
       const uint32_t scales = *reinterpret_cast<const uint32_t*>(&scale_pair);
-      unsigned char* w_row = base_pointer + L::kOffsetW + t * L::kWTile + row * 128u;
+      uint32_t converted[32];  // column c of the stage = the halves (k = 2c, 2c + 1) of this row
 #pragma unroll
-      for (uint32_t i = 0; i < kWords; ++i) {  // packed word i -> k 8 i .. 8 i + 7 of this thread's part
-        uint4 chunk;
-        chunk.x = dequant_pair<false, 0>(words[i], scales, 0u);
-        chunk.y = dequant_pair<false, 1>(words[i], scales, 0u);
-        chunk.z = dequant_pair<false, 2>(words[i], scales, 0u);
-        chunk.w = dequant_pair<false, 3>(words[i], scales, 0u);
-        const uint32_t out_chunk = part * kWords + i;
-        *reinterpret_cast<uint4*>(w_row + ((out_chunk * 16u) ^ swizzle)) = chunk;
+      for (uint32_t i = 0; i < 8; ++i) {  // packed word i -> k 8 i .. 8 i + 7
+        converted[4 * i] = dequant_pair<false, 0>(words[i], scales, 0u);
+        converted[4 * i + 1] = dequant_pair<false, 1>(words[i], scales, 0u);
+        converted[4 * i + 2] = dequant_pair<false, 2>(words[i], scales, 0u);
+        converted[4 * i + 3] = dequant_pair<false, 3>(words[i], scales, 0u);
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tmem_store_32(lane_base + tmem_a_ring + t * L::kAColumns + matrix * 32u, converted);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) barrier_arrive(w_full + t * 8);
+      if (lane == 0) barrier_arrive(a_full + t * 8);
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
 
@@ -270,68 +317,36 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
     }
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      constexpr int kHalf = NB / 2;  // batch columns per thread: 16 or 32
-      const uint32_t quarter = warp & 3u, half_index = (warp - 2u) >> 2;
-      const uint32_t tile_row = quarter * 32u + lane, column = n0 + tile_row;  // output column
-      const uint32_t lane_address = tmem_base + ((quarter * 32u) << 16) + half_index * kHalf;
-      float values[NMAT][kHalf];
+      constexpr int kHalf = NB / 2;       // batch columns per thread
+      constexpr int kPiece = kHalf < 16 ? kHalf : 16;  // columns handled at a time
+      constexpr int kPieces = kHalf / kPiece;
+      const uint32_t half_index = pair;
+      const uint32_t column = weight_row;  // output column
+      const uint32_t lane_address = tmem_base + lane_base + half_index * kHalf;
+      constexpr int kPerTile = NMAT * kRows * NB;
+      auto load_piece = [&](int piece, float (&values)[NMAT][kPiece]) {
 #pragma unroll
-      for (int a = 0; a < NMAT; ++a) {
+        for (int a = 0; a < NMAT; ++a) {
+          if (kPiece == 16) {
+            uint32_t bits[16];
+            tmem_load_16(lane_address + a * NB + piece * 16, bits);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int piece = 0; piece < kHalf / 16; ++piece) {
-          uint32_t bits[16];
-          tmem_load_16(lane_address + a * NB + piece * 16, bits);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            for (int i = 0; i < kPiece; ++i) values[a][i] = __uint_as_float(bits[i % 16]);
+          } else {
+            uint32_t bits[8];
+            tmem_load_8(lane_address + a * NB, bits);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int i = 0; i < 16; ++i) values[a][piece * 16 + i] = __uint_as_float(bits[i]);
+            for (int i = 0; i < kPiece; ++i) values[a][i] = __uint_as_float(bits[i % 8]);
+          }
         }
-      }
-      bool finish = true;
-      if (p.splits > 1u) {
-        // park, count, and go on only as the last split of this tile
-        constexpr int kPerTile = NMAT * kRows * NB;
-        float* mine = p.partials + ((size_t)tile * p.splits + split) * kPerTile;
+      };
+      auto write_piece = [&](int piece, const float (&values)[NMAT][kPiece]) {
+        if (column >= p.n) return;
 #pragma unroll
-        for (int a = 0; a < NMAT; ++a)
-#pragma unroll
-          for (int i = 0; i < kHalf / 4; ++i)
-            *reinterpret_cast<float4*>(mine + ((size_t)a * kRows + tile_row) * NB + half_index * kHalf + 4 * i) =
-                make_float4(values[a][4 * i], values[a][4 * i + 1], values[a][4 * i + 2], values[a][4 * i + 3]);
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (threadIdx.x == 64u) {
-          __threadfence();
-          const uint32_t before = atomicAdd(p.counters + tile, 1u);
-          const bool last = before + 1u == p.splits;
-          if (last) p.counters[tile] = 0u;
-          holder[2] = last ? 1u : 0u;
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        finish = holder[2] != 0u;
-        if (finish) {
-          __threadfence();
-          const float* parts = p.partials + (size_t)tile * p.splits * kPerTile;
-#pragma unroll
-          for (int a = 0; a < NMAT; ++a)
-#pragma unroll
-            for (int i = 0; i < kHalf; ++i) values[a][i] = 0.0f;
-          for (uint32_t s = 0; s < p.splits; ++s)  // split order: the sum does not depend on who came last
-#pragma unroll
-            for (int a = 0; a < NMAT; ++a)
-#pragma unroll
-              for (int i = 0; i < kHalf / 4; ++i) {
-                const float4 part = __ldcg(reinterpret_cast<const float4*>(
-                    parts + (size_t)s * kPerTile + ((size_t)a * kRows + tile_row) * NB + half_index * kHalf + 4 * i));
-                values[a][4 * i] += part.x;
-                values[a][4 * i + 1] += part.y;
-                values[a][4 * i + 2] += part.z;
-                values[a][4 * i + 3] += part.w;
-              }
-        }
-      }
-      if (finish && column < p.n) {
-#pragma unroll
-        for (int i = 0; i < kHalf; ++i) {
-          const uint32_t batch_row = half_index * kHalf + i;
+        for (int i = 0; i < kPiece; ++i) {
+          const uint32_t batch_row = half_index * kHalf + piece * kPiece + i;
           if (batch_row >= p.m) break;
           float value;
           if (EPI == kBatchDualSwiglu) {
@@ -342,6 +357,64 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
             if (p.has_aux) value += __half2float(p.aux[(size_t)batch_row * p.aux_row_stride + column]);
           }
           p.out[(size_t)batch_row * p.n + column] = __float2half_rn(value);
+        }
+      };
+      if (p.splits == 1u) {
+#pragma unroll 1
+        for (int piece = 0; piece < kPieces; ++piece) {
+          float values[NMAT][kPiece];
+          load_piece(piece, values);
+          write_piece(piece, values);
+        }
+      } else {
+        // park, count, and go on only as the last split of this tile
+        float* mine = p.partials + ((size_t)tile * p.splits + split) * kPerTile;
+#pragma unroll 1
+        for (int piece = 0; piece < kPieces; ++piece) {
+          float values[NMAT][kPiece];
+          load_piece(piece, values);
+#pragma unroll
+          for (int a = 0; a < NMAT; ++a)
+#pragma unroll
+            for (int i = 0; i < kPiece / 4; ++i)
+              *reinterpret_cast<float4*>(mine + ((size_t)a * kRows + tile_row) * NB + half_index * kHalf + piece * kPiece +
+                                         4 * i) =
+                  make_float4(values[a][4 * i], values[a][4 * i + 1], values[a][4 * i + 2], values[a][4 * i + 3]);
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (threadIdx.x == 64u) {
+          __threadfence();
+          const uint32_t before = atomicAdd(p.counters + tile, 1u);
+          const bool last = before + 1u == p.splits;
+          if (last) p.counters[tile] = 0u;
+          holder[2] = last ? 1u : 0u;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (holder[2] != 0u) {
+          __threadfence();
+          const float* parts = p.partials + (size_t)tile * p.splits * kPerTile;
+#pragma unroll 1
+          for (int piece = 0; piece < kPieces; ++piece) {
+            float values[NMAT][kPiece];
+#pragma unroll
+            for (int a = 0; a < NMAT; ++a)
+#pragma unroll
+              for (int i = 0; i < kPiece; ++i) values[a][i] = 0.0f;
+            for (uint32_t s = 0; s < p.splits; ++s)  // split order: the sum does not depend on who came last
+#pragma unroll
+              for (int a = 0; a < NMAT; ++a)
+#pragma unroll
+                for (int i = 0; i < kPiece / 4; ++i) {
+                  const float4 part = __ldcg(reinterpret_cast<const float4*>(
+                      parts + (size_t)s * kPerTile + ((size_t)a * kRows + tile_row) * NB + half_index * kHalf +
+                      piece * kPiece + 4 * i));
+                  values[a][4 * i] += part.x;
+                  values[a][4 * i + 1] += part.y;
+                  values[a][4 * i + 2] += part.z;
+                  values[a][4 * i + 3] += part.w;
+                }
+            write_piece(piece, values);
+          }
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -417,9 +490,21 @@ uint32_t tensor_core_batch_min_rows() {
   return rows;
 }
 
-// Decode batches up to 64 rows; returns -1 outside its domain (the caller falls back).
+// Rows up to which this kernel is taken (at most 128); LLMOPT_CUDA_TC_BATCH_MAX_ROWS overrides it.
+uint32_t tensor_core_batch_max_rows() {
+  static const uint32_t rows = []() -> uint32_t {
+    const char* text = getenv("LLMOPT_CUDA_TC_BATCH_MAX_ROWS");
+    if (text == nullptr) return 64u;
+    const long value = strtol(text, nullptr, 10);
+    return value <= 0 ? 0u : (value > 128 ? 128u : (uint32_t)value);
+  }();
+  return rows;
+}
+
+// Decode batches up to 128 rows; returns -1 outside its domain (the caller falls back).
 int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& problem, int epilogue) {
-  if (args.ctx == nullptr || problem.m < tensor_core_batch_min_rows() || problem.m > 64 || problem.x_rows != problem.m ||
+  if (args.ctx == nullptr || problem.m < tensor_core_batch_min_rows() || problem.m > tensor_core_batch_max_rows() ||
+      problem.x_rows != problem.m ||
       problem.k % 64 != 0 || problem.norm_weight != nullptr)
     return -1;
   if (epilogue == kEpiQkv) {
@@ -442,7 +527,7 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
     if (((uintptr_t)problem.mat[i].packed & 15u) != 0 || problem.mat[i].n != problem.mat[0].n) return -1;
   EncodeTiled encode = encode_tiled();
   if (encode == nullptr) return -1;
-  const uint32_t padded = problem.m <= 32 ? 32u : 64u;
+  const uint32_t padded = problem.m <= 16 ? 16u : problem.m <= 32 ? 32u : problem.m <= 64 ? 64u : 128u;
   CUtensorMap map_x;
   const cuuint64_t dims[2] = {problem.k, problem.m};
   const cuuint64_t strides[1] = {(cuuint64_t)problem.k * 2};
@@ -464,9 +549,20 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
   p.aux = problem.aux0;
   p.aux_row_stride = problem.aux_row_stride;
   p.has_aux = problem.has_aux;
-  if (epilogue == kEpiDualSwiglu)
-    return padded == 32 ? run_batch<kBatchDualSwiglu, 32>(args, map_x, p) : run_batch<kBatchDualSwiglu, 64>(args, map_x, p);
-  return padded == 32 ? run_batch<kBatchLinear, 32>(args, map_x, p) : run_batch<kBatchLinear, 64>(args, map_x, p);
+  if (epilogue == kEpiDualSwiglu) {
+    switch (padded) {
+      case 16: return run_batch<kBatchDualSwiglu, 16>(args, map_x, p);
+      case 32: return run_batch<kBatchDualSwiglu, 32>(args, map_x, p);
+      case 64: return run_batch<kBatchDualSwiglu, 64>(args, map_x, p);
+      default: return run_batch<kBatchDualSwiglu, 128>(args, map_x, p);
+    }
+  }
+  switch (padded) {
+    case 16: return run_batch<kBatchLinear, 16>(args, map_x, p);
+    case 32: return run_batch<kBatchLinear, 32>(args, map_x, p);
+    case 64: return run_batch<kBatchLinear, 64>(args, map_x, p);
+    default: return run_batch<kBatchLinear, 128>(args, map_x, p);
+  }
 }
 
 }  // namespace llmopt

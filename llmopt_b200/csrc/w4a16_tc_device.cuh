@@ -150,5 +150,13 @@ __device__ __forceinline__ void tmem_load_16(uint32_t address, uint32_t (&v)[16]
       : "memory");
 }
 
+// 8 consecutive accumulator columns of this thread's lane.
+__device__ __forceinline__ void tmem_load_8(uint32_t address, uint32_t (&v)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(address)
+               : "memory");
+}
+
 }  // namespace tc
 }  // namespace llmopt

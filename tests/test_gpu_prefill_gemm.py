@@ -80,10 +80,13 @@ def test_prefill_swiglu_ffn_matches_oracle(runtime, oracle, m, k, n):
     assert_close_f16(out.buffer.to_numpy(np.float16, (m, k)), want, rel=3e-3, label="prefill swiglu ffn")
 
 
-# ---- decode batches (33..64 rows by default): the tensor-core kernel with the weights on the M side ----
+# ---- decode batches: the tensor-core kernel with the weights on the M side, converted into tensor memory.
+# Which rows take it is a library setting (LLMOPT_CUDA_TC_BATCH_MIN_ROWS / _MAX_ROWS); the cases cover
+# every padded batch width (16, 32, 64, 128) whichever kernel serves them. ----
 
 @pytest.mark.parametrize("m,k,n", [(33, 128, 128), (36, 64, 40), (40, 1024, 384), (33, 576, 192), (48, 2048, 1000),
-                                   (64, 4096, 512), (56, 14336, 256)])
+                                   (64, 4096, 512), (56, 14336, 256), (9, 1024, 384), (16, 4096, 512), (17, 576, 192),
+                                   (32, 4096, 1000), (24, 14336, 256), (100, 2048, 384), (128, 1024, 640)])
 def test_decode_batch_linear_matches_oracle(runtime, oracle, m, k, n):
     rng = np.random.default_rng(40)
     x = rng.standard_normal((m, k)).astype(np.float16)
@@ -105,7 +108,8 @@ def test_decode_batch_dyadic_inputs_are_bit_exact(runtime, oracle):
     assert np.array_equal(got.view(np.uint16), oracle.w4a16_linear(x, packed, scale).view(np.uint16))
 
 
-@pytest.mark.parametrize("m,k,n", [(33, 256, 256), (48, 576, 1536), (40, 1024, 192)])
+@pytest.mark.parametrize("m,k,n", [(33, 256, 256), (48, 576, 1536), (40, 1024, 192), (12, 1024, 192), (32, 576, 1536),
+                                   (96, 256, 256)])
 def test_decode_batch_swiglu_ffn_matches_oracle(runtime, oracle, m, k, n):
     from llmopt_b200 import dispatch
 
