@@ -1,6 +1,6 @@
-// Decode batches (9..128 rows) of the W4A16 group-64 product on tcgen05, with the operands swapped
+// Decode batches (9..64 rows) of the W4A16 group-64 product on tcgen05, with the operands swapped
 // relative to the prefill kernel: the WEIGHT tile is the M side of the MMA (128 rows) and the
-// activations are the N side (the batch, padded to 16, 32, 64 or 128), so the tensor work is
+// activations are the N side (the batch, padded to 16, 32 or 64), so the tensor work is
 // proportional to the batch and the kernel is bound by the weight stream from HBM, like the
 // single-row GEMV, instead of by a 128-row activation tile that is mostly padding.
 //   D^T[weight row, batch row] = W[weight row, :] . X[batch row, :]      per 64-wide k-block
@@ -12,11 +12,15 @@
 //   warp 0        TMA: X tile [NB x 64] fp16, 128-byte swizzle, 4-deep ring
 //   warp 1        tcgen05.mma 128 x NB x 16 (A from tensor memory, B = X from shared memory), four per
 //                 k-block and matrix; accumulators in tensor memory
-//   warps 2-9     warp w owns tensor-memory lanes 32 (w % 4) .. +31, i.e. those 32 weight rows.  It
-//                 streams their packed bytes with cp.async in groups of four k-blocks (private to the
-//                 warp: no barrier on the weight stream, several groups deep) and converts them:
-//                 int4 -> fp16 (q * scale), 3-deep ring of A stages in tensor memory.  Dual form: the
-//                 two warps of a lane quarter take one matrix each; single form: alternate k-blocks.
+//   warps 2-17    warp w owns tensor-memory lanes 32 (w % 4) .. +31, i.e. those 32 weight rows, and of
+//                 every group of k-blocks (eight; four per matrix in the dual form) it converts two
+//                 consecutive ones: it streams exactly those 64 packed bytes per row with cp.async
+//                 (private to the warp: no barrier on the weight stream, several groups deep) and
+//                 converts them, int4 -> fp16 (q * scale), one k-block = 32 columns per tcgen05.st,
+//                 into a ring of A stages in tensor memory.  The completion of a store is waited
+//                 for behind the next k-block's arithmetic: store, wait, publish per k-block made
+//                 every k-block cost ~0.7 us whatever else the kernel did (loads, MMAs, conversion
+//                 removed one at a time: no change), because every warp took part in every k-block.
 // K is split over CTAs when there are few weight tiles (narrow projections); the last CTA of a tile
 // adds the parked fp32 partials in split order and writes the result.  All waits are bounded.
 // Output is transposed on the way out: a thread owns one weight row = one output column.
@@ -35,9 +39,8 @@ void* context_split_scratch(Context* ctx, size_t zeroed_bytes, size_t bytes, cud
 namespace {
 
 constexpr int kRows = 128;  // weight rows per matrix and CTA
-constexpr int kBK = 64, kGroupBlocks = 4;
-constexpr int kXStages = 4, kAStages = 3;
-constexpr int kConvertWarps = 8;
+constexpr int kBK = 64;
+constexpr int kConvertWarps = 16;
 constexpr int kThreads = (2 + kConvertWarps) * 32;
 constexpr uint32_t kSplitCounterTiles = 1u << 14;
 
@@ -63,22 +66,32 @@ constexpr uint32_t next_power_of_two(uint32_t value) {
 
 template <int NMAT, int NB>
 struct Layout {
-  static constexpr int kXTile = NB * 128;             // NB batch rows x 64 halves
+  // A group is what the conversion warps of a lane quarter share out: every warp converts a PAIR of
+  // consecutive k-blocks of it (64 contiguous packed bytes per row).  Single form: four warps per lane
+  // quarter, eight k-blocks; dual form: two warps per lane quarter and matrix, four k-blocks.
+  // A ring stage (of X in shared memory, of A in tensor memory) is one such pair: the MMA thread pays
+  // its waits and its one commit per pair.
+  static constexpr int kGroupBlocks = NMAT == 2 ? 4 : 8;
+  static constexpr int kRowPitch = kGroupBlocks * 32;  // packed bytes of one row and group
+  static constexpr int kXTile = NB * 128;              // NB batch rows x 64 halves
   static constexpr int kXStride = (kXTile + 1023) / 1024 * 1024;
-  static constexpr int kRawTile = NMAT * kRows * 128; // packed rows of one group (4 k-blocks)
+  static constexpr int kXStage = 2 * kXStride;         // the pair's two X tiles
+  static constexpr int kRawTile = NMAT * kRows * kRowPitch;  // packed rows of one group
+  // ring depth: the pairs of a group are produced side by side and consumed in order, so a little more than a group
+  static constexpr int kStages = NMAT == 2 ? 3 : 6;
   // groups of packed bytes in flight per warp: what is left of shared memory beside the X ring
-  static constexpr int kRawStages = NMAT == 2 ? (NB > 64 ? 4 : 5) : 6;
+  static constexpr int kRawStages = (NMAT == 1 && NB > 32) ? 3 : 4;
   static constexpr int kOffsetX = 0;
-  static constexpr int kOffsetRaw = kOffsetX + kXStages * kXStride;
+  static constexpr int kOffsetRaw = kOffsetX + kStages * kXStage;
   static constexpr int kOffsetBarriers = kOffsetRaw + kRawStages * kRawTile;
-  static constexpr int kBarriers = 2 * kXStages + 2 * kAStages + 1;
+  static constexpr int kBarriers = 3 * kStages + 1;
   static constexpr int kOffsetHolder = kOffsetBarriers + kBarriers * 8;
   static constexpr int kBytes = kOffsetHolder + 16 + 1024;
-  // tensor memory: NMAT accumulators of NB fp32 columns, then kAStages stages of the converted k-block
-  // (64 k = 32 columns per matrix)
+  // tensor memory: NMAT accumulators of NB fp32 columns, then kStages stages of a converted pair:
+  // [k-block of the pair][matrix][32 columns = 64 k]
   static constexpr uint32_t kAccumulatorColumns = (NMAT * NB + 31) / 32 * 32;  // the A ring starts on a 32-column boundary
-  static constexpr uint32_t kAColumns = NMAT * 32;
-  static constexpr uint32_t kColumns = next_power_of_two(kAccumulatorColumns + kAStages * kAColumns);
+  static constexpr uint32_t kAColumns = 2 * NMAT * 32;
+  static constexpr uint32_t kColumns = next_power_of_two(kAccumulatorColumns + kStages * kAColumns);
   static_assert(kColumns <= 512, "tensor memory has 512 columns");
   static_assert(kBytes <= 227 * 1024, "shared memory of one CTA");
 };
@@ -114,15 +127,16 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
                            uint32_t launch_id) {
   constexpr int NMAT = EPI == kBatchDualSwiglu ? 2 : 1;
   using L = Layout<NMAT, NB>;
-  constexpr int kRawStages = L::kRawStages;
+  constexpr int kRawStages = L::kRawStages, kStages = L::kStages, kGroupBlocks = L::kGroupBlocks;
   extern __shared__ unsigned char shared_raw[];
   grid_chain_prologue();
   if (*reinterpret_cast<volatile uint32_t*>(&g_abandoned_batch_launch) == launch_id) return;
   const uint32_t base = (smem_u32(shared_raw) + 1023u) & ~1023u;
   unsigned char* base_pointer = shared_raw + (base - smem_u32(shared_raw));
-  const uint32_t x_full = base + L::kOffsetBarriers, x_empty = x_full + kXStages * 8;
-  const uint32_t a_full = x_empty + kXStages * 8, a_empty = a_full + kAStages * 8;
-  const uint32_t accumulator_full = a_empty + kAStages * 8;
+  // per ring stage: X landed (TMA bytes), A converted (one arrival per contributing warp), stage consumed
+  // (ONE tcgen05.commit, which both the TMA thread and the conversion warps wait for)
+  const uint32_t x_full = base + L::kOffsetBarriers, a_full = x_full + kStages * 8, empty = a_full + kStages * 8;
+  const uint32_t accumulator_full = empty + kStages * 8;
   volatile uint32_t* holder = reinterpret_cast<volatile uint32_t*>(base_pointer + L::kOffsetHolder);  // [tmem, abort, last]
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -132,18 +146,15 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
   const uint32_t group_end = (uint32_t)((uint64_t)all_groups * (split + 1u) / p.splits);
   const uint32_t kb_begin = group_begin * kGroupBlocks;
   const uint32_t k_blocks = min(group_end * kGroupBlocks, all_k_blocks) - kb_begin;
-  // single-matrix form: the two warps of a lane quarter convert alternate k-blocks, so a stage of A is
-  // completed by four warps; dual form: one matrix each, eight warps per stage
-  constexpr uint32_t kWarpsPerStage = NMAT == 2 ? kConvertWarps : kConvertWarps / 2;
+  const uint32_t pairs = (k_blocks + 1u) / 2u;  // ring stages this CTA goes through; the last may hold one k-block
+  // a pair of A is completed by one warp per lane quarter (and matrix)
+  constexpr uint32_t kWarpsPerStage = 4 * NMAT;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kXStages; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       barrier_init(x_full + s * 8, 1);
-      barrier_init(x_empty + s * 8, 1);
-    }
-    for (int s = 0; s < kAStages; ++s) {
       barrier_init(a_full + s * 8, kWarpsPerStage);
-      barrier_init(a_empty + s * 8, 1);
+      barrier_init(empty + s * 8, 1);
     }
     barrier_init(accumulator_full, 1);
     holder[1] = 0u;
@@ -172,53 +183,69 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
     // ------------------------------ X tiles by TMA ------------------------------
     if (lane == 0) {
       uint32_t issued = 0;
-      for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-        const uint32_t s = kb % kXStages;
-        if (*abort_flag || !barrier_wait(x_empty + s * 8, ((kb / kXStages) & 1u) ^ 1u)) {
+      for (uint32_t pair = 0; pair < pairs; ++pair) {
+        const uint32_t s = pair % kStages;
+        if (*abort_flag || !barrier_wait(empty + s * 8, ((pair / kStages) & 1u) ^ 1u)) {
           give_up();
           break;
         }
-        barrier_expect_tx(x_full + s * 8, L::kXTile);
-        tma_load_2d(base + L::kOffsetX + s * L::kXStride, &map_x, (int32_t)((kb_begin + kb) * kBK), 0, x_full + s * 8);
-        issued = kb + 1;
+        const bool both = 2u * pair + 1u < k_blocks;
+        barrier_expect_tx(x_full + s * 8, both ? 2 * L::kXTile : L::kXTile);
+        const uint32_t target = base + L::kOffsetX + s * L::kXStage;
+        tma_load_2d(target, &map_x, (int32_t)((kb_begin + 2u * pair) * kBK), 0, x_full + s * 8);
+        if (both) tma_load_2d(target + L::kXStride, &map_x, (int32_t)((kb_begin + 2u * pair + 1u) * kBK), 0, x_full + s * 8);
+        issued = pair + 1;
       }
       if (*abort_flag) {
-        const uint32_t first = issued > kXStages ? issued - kXStages : 0u;
-        for (uint32_t kb = first; kb < issued; ++kb) barrier_wait(x_full + (kb % kXStages) * 8, (kb / kXStages) & 1u);
+        const uint32_t first = issued > kStages ? issued - kStages : 0u;
+        for (uint32_t pair = first; pair < issued; ++pair) barrier_wait(x_full + (pair % kStages) * 8, (pair / kStages) & 1u);
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
+    // One thread issues everything, so its instruction stream is part of the critical path: descriptors
+    // are advanced by adding constants (never rebuilt), and the stage is released by a single commit.
     if (lane == 0) {
       constexpr uint32_t instruction = instruction_descriptor(kRows, NB);
+      const uint64_t x_descriptor_0 = operand_descriptor(base + L::kOffsetX);
       bool ok = true;
-      for (uint32_t kb = 0; kb < k_blocks && ok; ++kb) {
-        const uint32_t s = kb % kXStages, t = kb % kAStages;
-        ok = !*abort_flag && barrier_wait(x_full + s * 8, (kb / kXStages) & 1u) &&
-             barrier_wait(a_full + t * 8, (kb / kAStages) & 1u);
+      uint32_t accumulate = 0u;
+      for (uint32_t pair = 0; pair < pairs && ok; ++pair) {
+        const uint32_t s = pair % kStages, phase = (pair / kStages) & 1u;
+        ok = !*abort_flag && barrier_wait(x_full + s * 8, phase) && barrier_wait(a_full + s * 8, phase);
         if (!ok) {
           give_up();
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t x_tile = base + L::kOffsetX + s * L::kXStride, a_stage = tmem_a_ring + t * L::kAColumns;
+        const uint32_t a_stage = tmem_a_ring + s * L::kAColumns;
+        const uint64_t x_descriptor = x_descriptor_0 + (uint64_t)(s * (L::kXStage >> 4));
+        const uint32_t members = 2u * pair + 1u < k_blocks ? 2u : 1u;
 #pragma unroll
-        for (int a = 0; a < NMAT; ++a)
+        for (uint32_t which = 0; which < 2; ++which) {
+          if (which < members) {
 #pragma unroll
-          for (int j = 0; j < kBK / 16; ++j)
-            mma_f16_tmem_a(tmem_base + a * NB, a_stage + a * 32 + j * 8, operand_descriptor(x_tile + j * 32),
-                           (kb > 0 || j > 0) ? 1u : 0u, instruction);
-        mma_commit(x_empty + s * 8);
-        mma_commit(a_empty + t * 8);
+            for (int a = 0; a < NMAT; ++a)
+#pragma unroll
+              for (int j = 0; j < kBK / 16; ++j) {  // 16 k = 32 bytes further along the swizzled rows: + 2 in the address field
+                mma_f16_tmem_a(tmem_base + a * NB, a_stage + which * (NMAT * 32) + a * 32 + j * 8,
+                               x_descriptor + (uint64_t)(which * (L::kXStride >> 4) + 2 * j), j == 0 ? accumulate : 1u,
+                               instruction);
+              }
+            accumulate = 1u;
+          }
+        }
+        mma_commit(empty + s * 8);
       }
       if (ok) mma_commit(accumulator_full);
     }
   } else {
     // ------------------------------ conversion, then epilogue ------------------------------
     // a warp reaches the tensor-memory lanes 32 (warp % 4) .. +31 only: those are its weight rows
-    const uint32_t quarter = warp & 3u, pair = (warp - 2u) >> 2;
-    const uint32_t tile_row = quarter * 32u + lane;      // row of the weight tile = tensor-memory lane
-    const uint32_t matrix = NMAT == 2 ? pair : 0u;
+    const uint32_t quarter = warp & 3u, sub = (warp - 2u) >> 2;  // sub = 0..3: this warp among its lane quarter's four
+    const uint32_t tile_row = quarter * 32u + lane;               // row of the weight tile = tensor-memory lane
+    const uint32_t matrix = NMAT == 2 ? sub >> 1 : 0u;
+    const uint32_t duo = NMAT == 2 ? (sub & 1u) : sub;  // this warp converts k-blocks 2 duo and 2 duo + 1 of every group
     const uint32_t weight_row = n0 + tile_row;
     const bool row_present = weight_row < p.n;
     const uint32_t groups = p.k / 64;
@@ -226,29 +253,32 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
     const uint32_t swizzle = (tile_row & 7u) * 16u;
     const uint32_t lane_base = (quarter * 32u) << 16;     // lane field of this warp's tensor-memory addresses
     bool ok = true;
-    // scales of a whole group per load, fetched one group (four k-blocks) ahead
-    const bool vector_ok = groups % 4u == 0u && ((uintptr_t)p.scale[matrix] & 7u) == 0;
-    FourHalves group_scales, next_scales = load_four(scale_row, kb_begin, groups, vector_ok, row_present);
+    // the two group scales of this warp's k-blocks, fetched one group ahead (one 4-byte load where aligned)
+    const bool pair_ok = groups % 2u == 0u && ((uintptr_t)p.scale[matrix] & 3u) == 0;
+    auto load_scales = [&](uint32_t group) -> __half2 {
+      const uint32_t first = kb_begin + group * kGroupBlocks + 2u * duo;
+      if (!row_present || first >= groups) return __float2half2_rn(0.0f);
+      if (pair_ok) return __ldg(reinterpret_cast<const __half2*>(scale_row + first));
+      return __halves2half2(__ldg(scale_row + first), first + 1u < groups ? __ldg(scale_row + first + 1u) : __float2half(0.0f));
+    };
+    __half2 group_scales = __float2half2_rn(0.0f), next_scales = load_scales(0);
 
-    // This warp's private weight stream: the packed bytes of ITS rows and ITS k-blocks.  Dual form: all
-    // 128 bytes of a row's group, 8 lanes per row; single form: the two 32-byte pieces of its k-blocks
-    // (k-blocks pair, pair + 2 of the group), 4 lanes per row.
-    constexpr uint32_t kLanesPerRow = NMAT == 2 ? 8 : 4, kRowsPerPass = 32 / kLanesPerRow;
-    const uint32_t copy_row = lane / kLanesPerRow, copy_piece = lane % kLanesPerRow;
-    const uint32_t copy_chunk = NMAT == 2 ? copy_piece : 2u * pair + (copy_piece & 1u) + 4u * (copy_piece >> 1);
+    // This warp's private weight stream: the 64 contiguous bytes per row (chunks 4 duo .. 4 duo + 3 of the
+    // row's group) that it converts, four lanes per row, eight rows per instruction.
+    const uint32_t copy_row = lane >> 2, copy_chunk = 4u * duo + (lane & 3u);
     const uint32_t row_bytes = p.k / 2, my_groups = (k_blocks + kGroupBlocks - 1u) / kGroupBlocks;
     const uint8_t* packed = p.packed[matrix];
     auto issue_group = [&](uint32_t group) {
       if (group < my_groups) {
-        const uint32_t stage = base + L::kOffsetRaw + (group % kRawStages) * L::kRawTile + matrix * (kRows * 128u);
-        const uint32_t byte_at = (group_begin + group) * (kGroupBlocks * kBK / 2) + copy_chunk * 16u;
+        const uint32_t stage = base + L::kOffsetRaw + (group % kRawStages) * L::kRawTile + matrix * (kRows * L::kRowPitch);
+        const uint32_t byte_at = (group_begin + group) * L::kRowPitch + copy_chunk * 16u;
         const uint32_t bytes = byte_at < row_bytes ? 16u : 0u;  // beyond the row end: zeros
 #pragma unroll
-        for (uint32_t pass = 0; pass < 32 / kRowsPerPass; ++pass) {
-          const uint32_t row = quarter * 32u + pass * kRowsPerPass + copy_row;
+        for (uint32_t pass = 0; pass < 4; ++pass) {
+          const uint32_t row = quarter * 32u + pass * 8u + copy_row;
           const uint32_t source_row = min(n0 + row, p.n - 1u);  // absent rows re-read the last one
           const uint8_t* source = packed + (size_t)source_row * row_bytes + (bytes ? byte_at : 0u);
-          const uint32_t target = stage + row * 128u + ((copy_chunk ^ (row & 7u)) * 16u);
+          const uint32_t target = stage + row * L::kRowPitch + ((copy_chunk ^ (row & 7u)) * 16u);
           asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(target), "l"(source), "r"(bytes) : "memory");
         }
       }
@@ -257,45 +287,53 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
 #pragma unroll 1
     for (uint32_t group = 0; group + 1u < kRawStages; ++group) issue_group(group);
 
-    for (uint32_t kb = 0; kb < k_blocks; ++kb) {
-      const uint32_t t = kb % kAStages, group = kb / kGroupBlocks, quarter_of_group = kb % kGroupBlocks;
+    for (uint32_t group = 0; group < my_groups && ok; ++group) {
       const uint32_t rs = group % kRawStages;
-      if (quarter_of_group == 0u) {
-        __syncwarp();  // every lane is done with the stage the next copies overwrite
-        issue_group(group + kRawStages - 1u);
-        asm volatile("cp.async.wait_group %0;" ::"n"(kRawStages - 1) : "memory");  // this group has landed
-        __syncwarp();
-        group_scales = next_scales;
-        next_scales = load_four(scale_row, kb_begin + kb + kGroupBlocks, groups, vector_ok, row_present);
-      }
-      if (NMAT == 1 && (quarter_of_group & 1u) != pair) continue;  // the other warp of this lane quarter converts it
-      const __half scale = group_scales.value[quarter_of_group];
-      ok = !*abort_flag && barrier_wait(a_empty + t * 8, ((kb / kAStages) & 1u) ^ 1u);
-      if (!ok) {
-        give_up();
-        break;
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      __syncwarp();  // every lane is done with the stage the next copies overwrite
+      issue_group(group + kRawStages - 1u);
+      asm volatile("cp.async.wait_group %0;" ::"n"(kRawStages - 1) : "memory");  // this group has landed
+      __syncwarp();
+      group_scales = next_scales;
+      next_scales = load_scales(group + 1u);
+      const uint32_t pair = group * (kGroupBlocks / 2) + duo;  // this warp's pair of the group = one ring stage
+      if (2u * pair >= k_blocks) continue;
+      const uint32_t s = pair % kStages;
       const unsigned char* raw =
-          base_pointer + L::kOffsetRaw + rs * L::kRawTile + matrix * (kRows * 128u) + tile_row * 128u;
-      const uint4 first = *reinterpret_cast<const uint4*>(raw + (((2u * quarter_of_group) * 16u) ^ swizzle));
-      const uint4 second = *reinterpret_cast<const uint4*>(raw + (((2u * quarter_of_group + 1u) * 16u) ^ swizzle));
-      const uint32_t words[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
-      const __half2 scale_pair = __halves2half2(scale, __hmul(scale, __float2half(0.0625f)));
-      const uint32_t scales = *reinterpret_cast<const uint32_t*>(&scale_pair);
-      uint32_t converted[32];  // column c of the stage = the halves (k = 2c, 2c + 1) of this row
+          base_pointer + L::kOffsetRaw + rs * L::kRawTile + matrix * (kRows * L::kRowPitch) + tile_row * L::kRowPitch;
 #pragma unroll
-      for (uint32_t i = 0; i < 8; ++i) {  // packed word i -> k 8 i .. 8 i + 7
-        converted[4 * i] = dequant_pair<false, 0>(words[i], scales, 0u);
-        converted[4 * i + 1] = dequant_pair<false, 1>(words[i], scales, 0u);
-        converted[4 * i + 2] = dequant_pair<false, 2>(words[i], scales, 0u);
-        converted[4 * i + 3] = dequant_pair<false, 3>(words[i], scales, 0u);
+      for (uint32_t which = 0; which < 2; ++which) {
+        if (2u * pair + which >= k_blocks) break;
+        const uint32_t in_group = 2u * duo + which;
+        const uint4 first = *reinterpret_cast<const uint4*>(raw + (((2u * in_group) * 16u) ^ swizzle));
+        const uint4 second = *reinterpret_cast<const uint4*>(raw + (((2u * in_group + 1u) * 16u) ^ swizzle));
+        const uint32_t words[8] = {first.x, first.y, first.z, first.w, second.x, second.y, second.z, second.w};
+        const __half scale = which == 0 ? __low2half(group_scales) : __high2half(group_scales);
+        const __half2 scale_pair = __halves2half2(scale, __hmul(scale, __float2half(0.0625f)));
+        const uint32_t scales = *reinterpret_cast<const uint32_t*>(&scale_pair);
+        uint32_t converted[32];  // column c of the k-block = the halves (k = 2c, 2c + 1) of this row
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) {  // packed word i -> k 8 i .. 8 i + 7
+          converted[4 * i] = dequant_pair<false, 0>(words[i], scales, 0u);
+          converted[4 * i + 1] = dequant_pair<false, 1>(words[i], scales, 0u);
+          converted[4 * i + 2] = dequant_pair<false, 2>(words[i], scales, 0u);
+          converted[4 * i + 3] = dequant_pair<false, 3>(words[i], scales, 0u);
+        }
+        if (which == 0) {  // the stage must have been consumed (arithmetic first: the wait is usually over by now)
+          ok = !*abort_flag && barrier_wait(empty + s * 8, ((pair / kStages) & 1u) ^ 1u);
+          if (!ok) {
+            give_up();
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        tmem_store_32(lane_base + tmem_a_ring + s * L::kAColumns + which * (NMAT * 32u) + matrix * 32u, converted);
       }
-      tmem_store_32(lane_base + tmem_a_ring + t * L::kAColumns + matrix * 32u, converted);
+      if (!ok) break;
+      // one completion wait and one arrival per pair (per k-block they cost more than the conversion)
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) barrier_arrive(a_full + t * 8);
+      if (lane == 0) barrier_arrive(a_full + s * 8);
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
 
@@ -308,7 +346,7 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
       asm volatile(
           "{\n\t.reg .pred p, q;\n\t"
           "setp.ne.u32 q, %1, 0;\n\t"
-          "bar.red.and.pred p, 1, 256, q;\n\t"
+          "bar.red.and.pred p, 1, 512, q;\n\t"
           "selp.u32 %0, 1, 0, p;\n\t}"
           : "=r"(all_ok)
           : "r"(ok ? 1u : 0u)
@@ -317,29 +355,33 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
     }
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      constexpr int kHalf = NB / 2;       // batch columns per thread
+      constexpr int kHalf = NB / 4;       // batch columns per thread (the four warps of a lane quarter split them)
       constexpr int kPiece = kHalf < 16 ? kHalf : 16;  // columns handled at a time
       constexpr int kPieces = kHalf / kPiece;
-      const uint32_t half_index = pair;
+      const uint32_t half_index = sub;
       const uint32_t column = weight_row;  // output column
       const uint32_t lane_address = tmem_base + lane_base + half_index * kHalf;
       constexpr int kPerTile = NMAT * kRows * NB;
       auto load_piece = [&](int piece, float (&values)[NMAT][kPiece]) {
 #pragma unroll
         for (int a = 0; a < NMAT; ++a) {
+          uint32_t bits[16];
           if (kPiece == 16) {
-            uint32_t bits[16];
             tmem_load_16(lane_address + a * NB + piece * 16, bits);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          } else if (kPiece == 8) {
+            uint32_t eight[8];
+            tmem_load_8(lane_address + a * NB, eight);
 #pragma unroll
-            for (int i = 0; i < kPiece; ++i) values[a][i] = __uint_as_float(bits[i % 16]);
+            for (int i = 0; i < 8; ++i) bits[i] = eight[i];
           } else {
-            uint32_t bits[8];
-            tmem_load_8(lane_address + a * NB, bits);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            uint32_t four[4];
+            tmem_load_4(lane_address + a * NB, four);
 #pragma unroll
-            for (int i = 0; i < kPiece; ++i) values[a][i] = __uint_as_float(bits[i % 8]);
+            for (int i = 0; i < 4; ++i) bits[i] = four[i];
           }
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int i = 0; i < kPiece; ++i) values[a][i] = __uint_as_float(bits[i]);
         }
       };
       auto write_piece = [&](int piece, const float (&values)[NMAT][kPiece]) {
@@ -381,7 +423,7 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
                                          4 * i) =
                   make_float4(values[a][4 * i], values[a][4 * i + 1], values[a][4 * i + 2], values[a][4 * i + 3]);
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, 512;" ::: "memory");
         if (threadIdx.x == 64u) {
           __threadfence();
           const uint32_t before = atomicAdd(p.counters + tile, 1u);
@@ -389,7 +431,7 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
           if (last) p.counters[tile] = 0u;
           holder[2] = last ? 1u : 0u;
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, 512;" ::: "memory");
         if (holder[2] != 0u) {
           __threadfence();
           const float* parts = p.partials + (size_t)tile * p.splits * kPerTile;
@@ -454,7 +496,7 @@ int run_batch(const KernelArgs& args, const CUtensorMap& map_x, BatchProblem p) 
     return -1;
   }
   const uint32_t tiles = (p.n + kRows - 1) / kRows, sms = (uint32_t)context_sm_count(args.ctx);
-  const uint32_t groups = (p.k / kBK + kGroupBlocks - 1u) / kGroupBlocks;
+  const uint32_t groups = (p.k / kBK + L::kGroupBlocks - 1u) / L::kGroupBlocks;
   // one CTA per SM at most (a second wave would double the time); each split keeps at least two groups
   uint32_t splits = sms / tiles;
   if (splits > groups / 2u) splits = groups / 2u;
@@ -479,33 +521,41 @@ int run_batch(const KernelArgs& args, const CUtensorMap& map_x, BatchProblem p) 
 }  // namespace
 
 // Rows from which decode batches take this kernel (below it the small-M GEMV wins);
-// LLMOPT_CUDA_TC_BATCH_MIN_ROWS overrides it, 0 disables the kernel.
+// LLMOPT_CUDA_TC_BATCH_MIN_ROWS overrides it, 0 disables the kernel.  Measured at the Llama-8B shapes
+// (us in a back-to-back run over 32 operand sets, pipelined GEMV -> this kernel): 32 rows: gate/up 54.1 ->
+// 36.7, down 35.2 -> 30.4, o_proj 11.2 -> 14.7, QKV (three launches here) 15.4 -> 42; 16 rows: gate/up
+// 36.0 -> 35.4, down 17.2 -> 26.6.  So from 17 rows the large matrices take it, the small ones from 33.
 uint32_t tensor_core_batch_min_rows() {
   static const uint32_t rows = []() -> uint32_t {
     const char* text = getenv("LLMOPT_CUDA_TC_BATCH_MIN_ROWS");
-    if (text == nullptr) return 33u;
+    if (text == nullptr) return 17u;
     const long value = strtol(text, nullptr, 10);
     return value <= 0 ? 0xffffffffu : (uint32_t)value;
   }();
   return rows;
 }
 
-// Rows up to which this kernel is taken (at most 128); LLMOPT_CUDA_TC_BATCH_MAX_ROWS overrides it.
+// Rows up to which this kernel is taken (at most 64); LLMOPT_CUDA_TC_BATCH_MAX_ROWS overrides it.
 uint32_t tensor_core_batch_max_rows() {
   static const uint32_t rows = []() -> uint32_t {
     const char* text = getenv("LLMOPT_CUDA_TC_BATCH_MAX_ROWS");
     if (text == nullptr) return 64u;
     const long value = strtol(text, nullptr, 10);
-    return value <= 0 ? 0u : (value > 128 ? 128u : (uint32_t)value);
+    return value <= 0 ? 0u : (value > 64 ? 64u : (uint32_t)value);
   }();
   return rows;
 }
 
-// Decode batches up to 128 rows; returns -1 outside its domain (the caller falls back).
+// Decode batches up to 64 rows; returns -1 outside its domain (the caller falls back).
 int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& problem, int epilogue) {
   if (args.ctx == nullptr || problem.m < tensor_core_batch_min_rows() || problem.m > tensor_core_batch_max_rows() ||
       problem.x_rows != problem.m ||
       problem.k % 64 != 0 || problem.norm_weight != nullptr)
+    return -1;
+  // up to 32 rows only matrices of 32 M weights and more gain (see tensor_core_batch_min_rows)
+  static const bool forced = getenv("LLMOPT_CUDA_TC_BATCH_MIN_ROWS") != nullptr;
+  if (problem.m <= 32 && !forced &&
+      (epilogue == kEpiQkv || (uint64_t)problem.mat[0].n * problem.k < (32ull << 20)))
     return -1;
   if (epilogue == kEpiQkv) {
     for (uint32_t i = 0; i < problem.matrices; ++i) {
@@ -527,7 +577,7 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
     if (((uintptr_t)problem.mat[i].packed & 15u) != 0 || problem.mat[i].n != problem.mat[0].n) return -1;
   EncodeTiled encode = encode_tiled();
   if (encode == nullptr) return -1;
-  const uint32_t padded = problem.m <= 16 ? 16u : problem.m <= 32 ? 32u : problem.m <= 64 ? 64u : 128u;
+  const uint32_t padded = problem.m <= 16 ? 16u : problem.m <= 32 ? 32u : 64u;
   CUtensorMap map_x;
   const cuuint64_t dims[2] = {problem.k, problem.m};
   const cuuint64_t strides[1] = {(cuuint64_t)problem.k * 2};
@@ -553,15 +603,13 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
     switch (padded) {
       case 16: return run_batch<kBatchDualSwiglu, 16>(args, map_x, p);
       case 32: return run_batch<kBatchDualSwiglu, 32>(args, map_x, p);
-      case 64: return run_batch<kBatchDualSwiglu, 64>(args, map_x, p);
-      default: return run_batch<kBatchDualSwiglu, 128>(args, map_x, p);
+      default: return run_batch<kBatchDualSwiglu, 64>(args, map_x, p);
     }
   }
   switch (padded) {
     case 16: return run_batch<kBatchLinear, 16>(args, map_x, p);
     case 32: return run_batch<kBatchLinear, 32>(args, map_x, p);
-    case 64: return run_batch<kBatchLinear, 64>(args, map_x, p);
-    default: return run_batch<kBatchLinear, 128>(args, map_x, p);
+    default: return run_batch<kBatchLinear, 64>(args, map_x, p);
   }
 }
 

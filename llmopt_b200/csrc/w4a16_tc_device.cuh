@@ -158,5 +158,13 @@ __device__ __forceinline__ void tmem_load_8(uint32_t address, uint32_t (&v)[8]) 
                : "memory");
 }
 
+// 4 consecutive accumulator columns of this thread's lane.
+__device__ __forceinline__ void tmem_load_4(uint32_t address, uint32_t (&v)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+               : "r"(address)
+               : "memory");
+}
+
 }  // namespace tc
 }  // namespace llmopt
