@@ -44,7 +44,10 @@ constexpr int kConvertWarps = 16;
 constexpr int kThreads = (2 + kConvertWarps) * 32;
 constexpr uint32_t kSplitCounterTiles = 1u << 14;
 
-enum BatchEpilogue { kBatchLinear = 0, kBatchDualSwiglu = 1 };
+// kBatchLinear: one 128-row weight tile per CTA; kBatchDualSwiglu: the gate and the up tile of the same rows;
+// kBatchLinearPair: two neighbouring 128-row tiles of ONE matrix (the prompt form: the activation tile is
+// read once for 256 output columns).
+enum BatchEpilogue { kBatchLinear = 0, kBatchDualSwiglu = 1, kBatchLinearPair = 2 };
 
 struct BatchProblem {
   uint32_t m, n, k;
@@ -78,9 +81,9 @@ struct Layout {
   static constexpr int kXStage = 2 * kXStride;         // the pair's two X tiles
   static constexpr int kRawTile = NMAT * kRows * kRowPitch;  // packed rows of one group
   // ring depth: the pairs of a group are produced side by side and consumed in order, so a little more than a group
-  static constexpr int kStages = NMAT == 2 ? 3 : 6;
+  static constexpr int kStages = NMAT == 2 ? (NB > 64 ? 2 : 3) : (NB > 64 ? 3 : 6);
   // groups of packed bytes in flight per warp: what is left of shared memory beside the X ring
-  static constexpr int kRawStages = (NMAT == 1 && NB > 32) ? 3 : 4;
+  static constexpr int kRawStages = (NMAT == 1 && NB > 32) ? 3 : 4;  // 32 KB each
   static constexpr int kOffsetX = 0;
   static constexpr int kOffsetRaw = kOffsetX + kStages * kXStage;
   static constexpr int kOffsetBarriers = kOffsetRaw + kRawStages * kRawTile;
@@ -125,7 +128,8 @@ template <int EPI, int NB>
 __global__ void __launch_bounds__(kThreads, 1)
 w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const BatchProblem p, uint32_t* error_word,
                            uint32_t launch_id) {
-  constexpr int NMAT = EPI == kBatchDualSwiglu ? 2 : 1;
+  constexpr int NMAT = EPI == kBatchLinear ? 1 : 2;
+  constexpr uint32_t kTileRows = EPI == kBatchLinearPair ? 2 * kRows : kRows;  // output columns of one CTA
   using L = Layout<NMAT, NB>;
   constexpr int kRawStages = L::kRawStages, kStages = L::kStages, kGroupBlocks = L::kGroupBlocks;
   extern __shared__ unsigned char shared_raw[];
@@ -140,7 +144,9 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
   volatile uint32_t* holder = reinterpret_cast<volatile uint32_t*>(base_pointer + L::kOffsetHolder);  // [tmem, abort, last]
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-  const uint32_t tile = blockIdx.x, split = blockIdx.y, n0 = tile * kRows;
+  const uint32_t tile = blockIdx.x, split = blockIdx.y, n0 = tile * kTileRows;
+  const uint32_t token0 = blockIdx.z * NB;           // first activation row of this CTA (prompts: several row tiles)
+  const uint32_t tile_id = blockIdx.z * gridDim.x + tile;  // index of the output tile for the K-split bookkeeping
   const uint32_t all_k_blocks = p.k / kBK, all_groups = (all_k_blocks + kGroupBlocks - 1u) / kGroupBlocks;
   const uint32_t group_begin = (uint32_t)((uint64_t)all_groups * split / p.splits);
   const uint32_t group_end = (uint32_t)((uint64_t)all_groups * (split + 1u) / p.splits);
@@ -192,8 +198,8 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
         const bool both = 2u * pair + 1u < k_blocks;
         barrier_expect_tx(x_full + s * 8, both ? 2 * L::kXTile : L::kXTile);
         const uint32_t target = base + L::kOffsetX + s * L::kXStage;
-        tma_load_2d(target, &map_x, (int32_t)((kb_begin + 2u * pair) * kBK), 0, x_full + s * 8);
-        if (both) tma_load_2d(target + L::kXStride, &map_x, (int32_t)((kb_begin + 2u * pair + 1u) * kBK), 0, x_full + s * 8);
+        tma_load_2d(target, &map_x, (int32_t)((kb_begin + 2u * pair) * kBK), (int32_t)token0, x_full + s * 8);
+        if (both) tma_load_2d(target + L::kXStride, &map_x, (int32_t)((kb_begin + 2u * pair + 1u) * kBK), (int32_t)token0, x_full + s * 8);
         issued = pair + 1;
       }
       if (*abort_flag) {
@@ -244,17 +250,19 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
     // a warp reaches the tensor-memory lanes 32 (warp % 4) .. +31 only: those are its weight rows
     const uint32_t quarter = warp & 3u, sub = (warp - 2u) >> 2;  // sub = 0..3: this warp among its lane quarter's four
     const uint32_t tile_row = quarter * 32u + lane;               // row of the weight tile = tensor-memory lane
-    const uint32_t matrix = NMAT == 2 ? sub >> 1 : 0u;
+    const uint32_t matrix = NMAT == 2 ? sub >> 1 : 0u;  // which of the CTA's two weight tiles
     const uint32_t duo = NMAT == 2 ? (sub & 1u) : sub;  // this warp converts k-blocks 2 duo and 2 duo + 1 of every group
-    const uint32_t weight_row = n0 + tile_row;
+    const uint32_t source = EPI == kBatchDualSwiglu ? matrix : 0u;                       // the matrix the tile comes from
+    const uint32_t tile_first_row = n0 + (EPI == kBatchLinearPair ? matrix * kRows : 0u);  // and its first row there
+    const uint32_t weight_row = tile_first_row + tile_row;
     const bool row_present = weight_row < p.n;
     const uint32_t groups = p.k / 64;
-    const __half* scale_row = p.scale[matrix] + (size_t)(row_present ? weight_row : 0u) * groups;
+    const __half* scale_row = p.scale[source] + (size_t)(row_present ? weight_row : 0u) * groups;
     const uint32_t swizzle = (tile_row & 7u) * 16u;
     const uint32_t lane_base = (quarter * 32u) << 16;     // lane field of this warp's tensor-memory addresses
     bool ok = true;
     // the two group scales of this warp's k-blocks, fetched one group ahead (one 4-byte load where aligned)
-    const bool pair_ok = groups % 2u == 0u && ((uintptr_t)p.scale[matrix] & 3u) == 0;
+    const bool pair_ok = groups % 2u == 0u && ((uintptr_t)p.scale[source] & 3u) == 0;
     auto load_scales = [&](uint32_t group) -> __half2 {
       const uint32_t first = kb_begin + group * kGroupBlocks + 2u * duo;
       if (!row_present || first >= groups) return __float2half2_rn(0.0f);
@@ -267,7 +275,7 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
     // row's group) that it converts, four lanes per row, eight rows per instruction.
     const uint32_t copy_row = lane >> 2, copy_chunk = 4u * duo + (lane & 3u);
     const uint32_t row_bytes = p.k / 2, my_groups = (k_blocks + kGroupBlocks - 1u) / kGroupBlocks;
-    const uint8_t* packed = p.packed[matrix];
+    const uint8_t* packed = p.packed[source];
     auto issue_group = [&](uint32_t group) {
       if (group < my_groups) {
         const uint32_t stage = base + L::kOffsetRaw + (group % kRawStages) * L::kRawTile + matrix * (kRows * L::kRowPitch);
@@ -276,10 +284,10 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
 #pragma unroll
         for (uint32_t pass = 0; pass < 4; ++pass) {
           const uint32_t row = quarter * 32u + pass * 8u + copy_row;
-          const uint32_t source_row = min(n0 + row, p.n - 1u);  // absent rows re-read the last one
-          const uint8_t* source = packed + (size_t)source_row * row_bytes + (bytes ? byte_at : 0u);
+          const uint32_t source_row = min(tile_first_row + row, p.n - 1u);  // absent rows re-read the last one
+          const uint8_t* from = packed + (size_t)source_row * row_bytes + (bytes ? byte_at : 0u);
           const uint32_t target = stage + row * L::kRowPitch + ((copy_chunk ^ (row & 7u)) * 16u);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(target), "l"(source), "r"(bytes) : "memory");
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(target), "l"(from), "r"(bytes) : "memory");
         }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
@@ -359,7 +367,6 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
       constexpr int kPiece = kHalf < 16 ? kHalf : 16;  // columns handled at a time
       constexpr int kPieces = kHalf / kPiece;
       const uint32_t half_index = sub;
-      const uint32_t column = weight_row;  // output column
       const uint32_t lane_address = tmem_base + lane_base + half_index * kHalf;
       constexpr int kPerTile = NMAT * kRows * NB;
       auto load_piece = [&](int piece, float (&values)[NMAT][kPiece]) {
@@ -385,20 +392,24 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
         }
       };
       auto write_piece = [&](int piece, const float (&values)[NMAT][kPiece]) {
-        if (column >= p.n) return;
 #pragma unroll
-        for (int i = 0; i < kPiece; ++i) {
-          const uint32_t batch_row = half_index * kHalf + piece * kPiece + i;
-          if (batch_row >= p.m) break;
-          float value;
-          if (EPI == kBatchDualSwiglu) {
-            const float g = values[0][i];
-            value = (g / (1.0f + __expf(-g))) * values[NMAT - 1][i];  // lib/metal_w4a16_source.ml:571-575
-          } else {
-            value = values[0][i];
-            if (p.has_aux) value += __half2float(p.aux[(size_t)batch_row * p.aux_row_stride + column]);
+        for (int a = 0; a < (EPI == kBatchLinearPair ? 2 : 1); ++a) {  // the pair form writes both of its tiles
+          const uint32_t column = n0 + a * kRows + tile_row;           // output column
+          if (column >= p.n) continue;
+#pragma unroll
+          for (int i = 0; i < kPiece; ++i) {
+            const uint32_t batch_row = token0 + half_index * kHalf + piece * kPiece + i;
+            if (batch_row >= p.m) break;
+            float value;
+            if (EPI == kBatchDualSwiglu) {
+              const float g = values[0][i];
+              value = (g / (1.0f + __expf(-g))) * values[NMAT - 1][i];  // lib/metal_w4a16_source.ml:571-575
+            } else {
+              value = values[a][i];
+              if (p.has_aux) value += __half2float(p.aux[(size_t)batch_row * p.aux_row_stride + column]);
+            }
+            p.out[(size_t)batch_row * p.n + column] = __float2half_rn(value);
           }
-          p.out[(size_t)batch_row * p.n + column] = __float2half_rn(value);
         }
       };
       if (p.splits == 1u) {
@@ -410,7 +421,7 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
         }
       } else {
         // park, count, and go on only as the last split of this tile
-        float* mine = p.partials + ((size_t)tile * p.splits + split) * kPerTile;
+        float* mine = p.partials + ((size_t)tile_id * p.splits + split) * kPerTile;
 #pragma unroll 1
         for (int piece = 0; piece < kPieces; ++piece) {
           float values[NMAT][kPiece];
@@ -426,15 +437,15 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
         asm volatile("bar.sync 1, 512;" ::: "memory");
         if (threadIdx.x == 64u) {
           __threadfence();
-          const uint32_t before = atomicAdd(p.counters + tile, 1u);
+          const uint32_t before = atomicAdd(p.counters + tile_id, 1u);
           const bool last = before + 1u == p.splits;
-          if (last) p.counters[tile] = 0u;
+          if (last) p.counters[tile_id] = 0u;
           holder[2] = last ? 1u : 0u;
         }
         asm volatile("bar.sync 1, 512;" ::: "memory");
         if (holder[2] != 0u) {
           __threadfence();
-          const float* parts = p.partials + (size_t)tile * p.splits * kPerTile;
+          const float* parts = p.partials + (size_t)tile_id * p.splits * kPerTile;
 #pragma unroll 1
           for (int piece = 0; piece < kPieces; ++piece) {
             float values[NMAT][kPiece];
@@ -488,24 +499,26 @@ EncodeTiled encode_tiled() {
 
 template <int EPI, int NB>
 int run_batch(const KernelArgs& args, const CUtensorMap& map_x, BatchProblem p) {
-  constexpr int NMAT = EPI == kBatchDualSwiglu ? 2 : 1;
+  constexpr int NMAT = EPI == kBatchLinear ? 1 : 2;
+  constexpr uint32_t kTileRows = EPI == kBatchLinearPair ? 2 * kRows : kRows;
   using L = Layout<NMAT, NB>;
   auto kernel = w4a16_gemm_tc_batch_kernel<EPI, NB>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess) {
     cudaGetLastError();
     return -1;
   }
-  const uint32_t tiles = (p.n + kRows - 1) / kRows, sms = (uint32_t)context_sm_count(args.ctx);
+  const uint32_t tiles = (p.n + kTileRows - 1) / kTileRows, row_tiles = (p.m + NB - 1) / NB;
+  const uint32_t sms = (uint32_t)context_sm_count(args.ctx);
   const uint32_t groups = (p.k / kBK + L::kGroupBlocks - 1u) / L::kGroupBlocks;
   // one CTA per SM at most (a second wave would double the time); each split keeps at least two groups
-  uint32_t splits = sms / tiles;
+  uint32_t splits = sms / (tiles * row_tiles);
   if (splits > groups / 2u) splits = groups / 2u;
   if (splits > 16u) splits = 16u;
-  if (splits < 1u || tiles > kSplitCounterTiles) splits = 1u;
+  if (splits < 1u || tiles * row_tiles > kSplitCounterTiles) splits = 1u;
   p.splits = splits;
   if (splits > 1u) {
     constexpr size_t counter_bytes = kSplitCounterTiles * sizeof(uint32_t);
-    const size_t partial_bytes = (size_t)tiles * splits * NMAT * kRows * NB * sizeof(float);
+    const size_t partial_bytes = (size_t)tiles * row_tiles * splits * NMAT * kRows * NB * sizeof(float);
     uint8_t* scratch =
         (uint8_t*)context_split_scratch(args.ctx, counter_bytes, counter_bytes + partial_bytes, args.stream, args.error);
     if (scratch == nullptr) return 1;
@@ -513,7 +526,7 @@ int run_batch(const KernelArgs& args, const CUtensorMap& map_x, BatchProblem p) 
     p.partials = reinterpret_cast<float*>(scratch + counter_bytes);
   }
   static std::atomic<uint32_t> launches{0};
-  launch_kernel(args, kernel, dim3(tiles, splits), dim3(kThreads), L::kBytes, map_x, p,
+  launch_kernel(args, kernel, dim3(tiles, splits, row_tiles), dim3(kThreads), L::kBytes, map_x, p,
                 context_device_error(args.ctx), launches.fetch_add(1) + 1u);
   return check_launch(args);
 }
@@ -546,12 +559,23 @@ uint32_t tensor_core_batch_max_rows() {
   return rows;
 }
 
-// Decode batches up to 64 rows; returns -1 outside its domain (the caller falls back).
+// Prompts (more than 64 rows) on this kernel: 128-row activation tiles, two weight tiles per CTA.
+// LLMOPT_CUDA_TC_PROMPT_TMEM=0 sends them to the shared-memory-operand GEMM instead.
+static bool prompt_rows_enabled() {
+  static const bool enabled = []() {
+    const char* text = getenv("LLMOPT_CUDA_TC_PROMPT_TMEM");
+    return text == nullptr || text[0] != '0';
+  }();
+  return enabled;
+}
+
+// Decode batches (up to 64 rows) and prompts; returns -1 outside its domain (the caller falls back).
 int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& problem, int epilogue) {
-  if (args.ctx == nullptr || problem.m < tensor_core_batch_min_rows() || problem.m > tensor_core_batch_max_rows() ||
-      problem.x_rows != problem.m ||
+  if (args.ctx == nullptr || problem.m < tensor_core_batch_min_rows() || problem.x_rows != problem.m ||
       problem.k % 64 != 0 || problem.norm_weight != nullptr)
     return -1;
+  const bool prompt = problem.m > tensor_core_batch_max_rows();
+  if (prompt && (!prompt_rows_enabled() || problem.m <= 64)) return -1;
   // up to 32 rows only matrices of 32 M weights and more gain (see tensor_core_batch_min_rows)
   static const bool forced = getenv("LLMOPT_CUDA_TC_BATCH_MIN_ROWS") != nullptr;
   if (problem.m <= 32 && !forced &&
@@ -577,7 +601,7 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
     if (((uintptr_t)problem.mat[i].packed & 15u) != 0 || problem.mat[i].n != problem.mat[0].n) return -1;
   EncodeTiled encode = encode_tiled();
   if (encode == nullptr) return -1;
-  const uint32_t padded = problem.m <= 16 ? 16u : problem.m <= 32 ? 32u : 64u;
+  const uint32_t padded = prompt ? 128u : problem.m <= 16 ? 16u : problem.m <= 32 ? 32u : 64u;
   CUtensorMap map_x;
   const cuuint64_t dims[2] = {problem.k, problem.m};
   const cuuint64_t strides[1] = {(cuuint64_t)problem.k * 2};
@@ -599,6 +623,10 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
   p.aux = problem.aux0;
   p.aux_row_stride = problem.aux_row_stride;
   p.has_aux = problem.has_aux;
+  if (prompt) {
+    if (epilogue == kEpiDualSwiglu) return run_batch<kBatchDualSwiglu, 128>(args, map_x, p);
+    return p.n > kRows ? run_batch<kBatchLinearPair, 128>(args, map_x, p) : run_batch<kBatchLinear, 128>(args, map_x, p);
+  }
   if (epilogue == kEpiDualSwiglu) {
     switch (padded) {
       case 16: return run_batch<kBatchDualSwiglu, 16>(args, map_x, p);
