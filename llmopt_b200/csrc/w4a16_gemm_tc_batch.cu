@@ -46,8 +46,10 @@ constexpr uint32_t kSplitCounterTiles = 1u << 14;
 
 // kBatchLinear: one 128-row weight tile per CTA; kBatchDualSwiglu: the gate and the up tile of the same rows;
 // kBatchLinearPair: two neighbouring 128-row tiles of ONE matrix (the prompt form: the activation tile is
-// read once for 256 output columns).
-enum BatchEpilogue { kBatchLinear = 0, kBatchDualSwiglu = 1, kBatchLinearPair = 2 };
+// read once for 256 output columns); kBatchDualStacked: ONE tile whose lanes 0..63 are 64 gate rows and
+// lanes 64..127 the same 64 up rows, so that gate/up prompts also run 256 tokens wide with one accumulator
+// (the halves meet in shared memory for silu(gate) * up).
+enum BatchEpilogue { kBatchLinear = 0, kBatchDualSwiglu = 1, kBatchLinearPair = 2, kBatchDualStacked = 3 };
 
 struct BatchProblem {
   uint32_t m, n, k;
@@ -80,14 +82,20 @@ struct Layout {
   static constexpr int kXStride = (kXTile + 1023) / 1024 * 1024;
   static constexpr int kXStage = 2 * kXStride;         // the pair's two X tiles
   static constexpr int kRawTile = NMAT * kRows * kRowPitch;  // packed rows of one group
-  // ring depth: the pairs of a group are produced side by side and consumed in order, so a little more than a group
-  static constexpr int kStages = NMAT == 2 ? (NB > 64 ? 2 : 3) : (NB > 64 ? 3 : 6);
+  // Depth of the A ring (tensor memory).  The pairs of a group are produced side by side by different warps
+  // and consumed in order, and the waits tell ring phases apart by parity alone: a warp must never be two
+  // uses of a stage ahead of the commits, which holds when the ring has at least as many stages as a group
+  // has pairs (a warp's previous pair then vouches for the commit two uses back).
+  static constexpr int kStages = NMAT == 2 ? (NB > 64 ? 2 : 3) : (NB > 64 ? 4 : 6);
+  static_assert(kStages >= kGroupBlocks / 2, "ring phases would alias");
+  // Depth of the X ring (shared memory): the same, with the same barrier, unless the tiles are too large
+  static constexpr int kXStages = (NMAT == 1 && NB > 128) ? 2 : kStages;
   // groups of packed bytes in flight per warp: what is left of shared memory beside the X ring
-  static constexpr int kRawStages = (NMAT == 1 && NB > 32) ? 3 : 4;  // 32 KB each
+  static constexpr int kRawStages = NB > 64 && NMAT == 1 ? 2 : (NMAT == 1 && NB > 32) ? 3 : 4;  // 32 KB each
   static constexpr int kOffsetX = 0;
-  static constexpr int kOffsetRaw = kOffsetX + kStages * kXStage;
+  static constexpr int kOffsetRaw = kOffsetX + kXStages * kXStage;
   static constexpr int kOffsetBarriers = kOffsetRaw + kRawStages * kRawTile;
-  static constexpr int kBarriers = 3 * kStages + 1;
+  static constexpr int kBarriers = 2 * kStages + 2 * kXStages + 1;
   static constexpr int kOffsetHolder = kOffsetBarriers + kBarriers * 8;
   static constexpr int kBytes = kOffsetHolder + 16 + 1024;
   // tensor memory: NMAT accumulators of NB fp32 columns, then kStages stages of a converted pair:
@@ -128,10 +136,11 @@ template <int EPI, int NB>
 __global__ void __launch_bounds__(kThreads, 1)
 w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const BatchProblem p, uint32_t* error_word,
                            uint32_t launch_id) {
-  constexpr int NMAT = EPI == kBatchLinear ? 1 : 2;
-  constexpr uint32_t kTileRows = EPI == kBatchLinearPair ? 2 * kRows : kRows;  // output columns of one CTA
+  constexpr bool kStacked = EPI == kBatchDualStacked;
+  constexpr int NMAT = (EPI == kBatchLinear || kStacked) ? 1 : 2;
+  constexpr uint32_t kTileRows = EPI == kBatchLinearPair ? 2 * kRows : kStacked ? kRows / 2 : kRows;  // output columns of one CTA
   using L = Layout<NMAT, NB>;
-  constexpr int kRawStages = L::kRawStages, kStages = L::kStages, kGroupBlocks = L::kGroupBlocks;
+  constexpr int kRawStages = L::kRawStages, kStages = L::kStages, kXStages = L::kXStages, kGroupBlocks = L::kGroupBlocks;
   extern __shared__ unsigned char shared_raw[];
   grid_chain_prologue();
   if (*reinterpret_cast<volatile uint32_t*>(&g_abandoned_batch_launch) == launch_id) return;
@@ -139,8 +148,10 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
   unsigned char* base_pointer = shared_raw + (base - smem_u32(shared_raw));
   // per ring stage: X landed (TMA bytes), A converted (one arrival per contributing warp), stage consumed
   // (ONE tcgen05.commit, which both the TMA thread and the conversion warps wait for)
-  const uint32_t x_full = base + L::kOffsetBarriers, a_full = x_full + kStages * 8, empty = a_full + kStages * 8;
-  const uint32_t accumulator_full = empty + kStages * 8;
+  // (a separate X ring has its own release barrier and costs a second commit per pair)
+  const uint32_t x_full = base + L::kOffsetBarriers, a_full = x_full + kXStages * 8, empty = a_full + kStages * 8;
+  const uint32_t x_empty = empty + kStages * 8, accumulator_full = x_empty + kXStages * 8;
+  constexpr bool kSharedRelease = kXStages == kStages;
   volatile uint32_t* holder = reinterpret_cast<volatile uint32_t*>(base_pointer + L::kOffsetHolder);  // [tmem, abort, last]
 
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -158,9 +169,12 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      barrier_init(x_full + s * 8, 1);
       barrier_init(a_full + s * 8, kWarpsPerStage);
       barrier_init(empty + s * 8, 1);
+    }
+    for (int s = 0; s < kXStages; ++s) {
+      barrier_init(x_full + s * 8, 1);
+      barrier_init(x_empty + s * 8, 1);
     }
     barrier_init(accumulator_full, 1);
     holder[1] = 0u;
@@ -190,21 +204,21 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
     if (lane == 0) {
       uint32_t issued = 0;
       for (uint32_t pair = 0; pair < pairs; ++pair) {
-        const uint32_t s = pair % kStages;
-        if (*abort_flag || !barrier_wait(empty + s * 8, ((pair / kStages) & 1u) ^ 1u)) {
+        const uint32_t s = pair % kXStages;
+        if (*abort_flag || !barrier_wait((kSharedRelease ? empty : x_empty) + s * 8, ((pair / kXStages) & 1u) ^ 1u)) {
           give_up();
           break;
         }
         const bool both = 2u * pair + 1u < k_blocks;
         barrier_expect_tx(x_full + s * 8, both ? 2 * L::kXTile : L::kXTile);
-        const uint32_t target = base + L::kOffsetX + s * L::kXStage;
+        const uint32_t target = base + L::kOffsetX + s * L::kXStage;  // s: stage of the X ring
         tma_load_2d(target, &map_x, (int32_t)((kb_begin + 2u * pair) * kBK), (int32_t)token0, x_full + s * 8);
         if (both) tma_load_2d(target + L::kXStride, &map_x, (int32_t)((kb_begin + 2u * pair + 1u) * kBK), (int32_t)token0, x_full + s * 8);
         issued = pair + 1;
       }
       if (*abort_flag) {
-        const uint32_t first = issued > kStages ? issued - kStages : 0u;
-        for (uint32_t pair = first; pair < issued; ++pair) barrier_wait(x_full + (pair % kStages) * 8, (pair / kStages) & 1u);
+        const uint32_t first = issued > kXStages ? issued - kXStages : 0u;
+        for (uint32_t pair = first; pair < issued; ++pair) barrier_wait(x_full + (pair % kXStages) * 8, (pair / kXStages) & 1u);
       }
     }
   } else if (warp == 1) {
@@ -217,15 +231,15 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
       bool ok = true;
       uint32_t accumulate = 0u;
       for (uint32_t pair = 0; pair < pairs && ok; ++pair) {
-        const uint32_t s = pair % kStages, phase = (pair / kStages) & 1u;
-        ok = !*abort_flag && barrier_wait(x_full + s * 8, phase) && barrier_wait(a_full + s * 8, phase);
+        const uint32_t s = pair % kStages, phase = (pair / kStages) & 1u, sx = pair % kXStages;
+        ok = !*abort_flag && barrier_wait(x_full + sx * 8, (pair / kXStages) & 1u) && barrier_wait(a_full + s * 8, phase);
         if (!ok) {
           give_up();
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_stage = tmem_a_ring + s * L::kAColumns;
-        const uint64_t x_descriptor = x_descriptor_0 + (uint64_t)(s * (L::kXStage >> 4));
+        const uint64_t x_descriptor = x_descriptor_0 + (uint64_t)(sx * (L::kXStage >> 4));
         const uint32_t members = 2u * pair + 1u < k_blocks ? 2u : 1u;
 #pragma unroll
         for (uint32_t which = 0; which < 2; ++which) {
@@ -242,6 +256,7 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
           }
         }
         mma_commit(empty + s * 8);
+        if (!kSharedRelease) mma_commit(x_empty + sx * 8);
       }
       if (ok) mma_commit(accumulator_full);
     }
@@ -252,9 +267,11 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
     const uint32_t tile_row = quarter * 32u + lane;               // row of the weight tile = tensor-memory lane
     const uint32_t matrix = NMAT == 2 ? sub >> 1 : 0u;  // which of the CTA's two weight tiles
     const uint32_t duo = NMAT == 2 ? (sub & 1u) : sub;  // this warp converts k-blocks 2 duo and 2 duo + 1 of every group
-    const uint32_t source = EPI == kBatchDualSwiglu ? matrix : 0u;                       // the matrix the tile comes from
-    const uint32_t tile_first_row = n0 + (EPI == kBatchLinearPair ? matrix * kRows : 0u);  // and its first row there
-    const uint32_t weight_row = tile_first_row + tile_row;
+    // the matrix this warp's rows come from, the tile's first row there, and the row of a tile row
+    const uint32_t source = EPI == kBatchDualSwiglu ? matrix : kStacked ? quarter >> 1 : 0u;
+    const uint32_t tile_first_row = n0 + (EPI == kBatchLinearPair ? matrix * kRows : 0u);
+    auto row_in_source = [&](uint32_t row) { return kStacked ? (row & (kRows / 2 - 1u)) : row; };
+    const uint32_t weight_row = tile_first_row + row_in_source(tile_row);
     const bool row_present = weight_row < p.n;
     const uint32_t groups = p.k / 64;
     const __half* scale_row = p.scale[source] + (size_t)(row_present ? weight_row : 0u) * groups;
@@ -284,7 +301,7 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
 #pragma unroll
         for (uint32_t pass = 0; pass < 4; ++pass) {
           const uint32_t row = quarter * 32u + pass * 8u + copy_row;
-          const uint32_t source_row = min(tile_first_row + row, p.n - 1u);  // absent rows re-read the last one
+          const uint32_t source_row = min(tile_first_row + row_in_source(row), p.n - 1u);  // absent rows re-read the last one
           const uint8_t* from = packed + (size_t)source_row * row_bytes + (bytes ? byte_at : 0u);
           const uint32_t target = stage + row * L::kRowPitch + ((copy_chunk ^ (row & 7u)) * 16u);
           asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(target), "l"(from), "r"(bytes) : "memory");
@@ -412,12 +429,24 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
           }
         }
       };
+      // stacked gate/up form: the finished values meet in shared memory ([token][tile row], the rings are idle by now)
+      float* stash = reinterpret_cast<float*>(base_pointer + L::kOffsetX);
+      static_assert(!kStacked || NB * kRows * 4 <= L::kXStages * L::kXStage, "the stash must fit the X ring");
+      auto emit = [&](int piece, const float (&values)[NMAT][kPiece]) {
+        if (kStacked) {
+#pragma unroll
+          for (int i = 0; i < kPiece; ++i) stash[(half_index * kHalf + piece * kPiece + i) * kRows + tile_row] = values[0][i];
+        } else {
+          write_piece(piece, values);
+        }
+      };
+      bool finished = true;
       if (p.splits == 1u) {
 #pragma unroll 1
         for (int piece = 0; piece < kPieces; ++piece) {
           float values[NMAT][kPiece];
           load_piece(piece, values);
-          write_piece(piece, values);
+          emit(piece, values);
         }
       } else {
         // park, count, and go on only as the last split of this tile
@@ -443,7 +472,8 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
           holder[2] = last ? 1u : 0u;
         }
         asm volatile("bar.sync 1, 512;" ::: "memory");
-        if (holder[2] != 0u) {
+        finished = holder[2] != 0u;
+        if (finished) {
           __threadfence();
           const float* parts = p.partials + (size_t)tile_id * p.splits * kPerTile;
 #pragma unroll 1
@@ -466,8 +496,20 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
                   values[a][4 * i + 2] += part.z;
                   values[a][4 * i + 3] += part.w;
                 }
-            write_piece(piece, values);
+            emit(piece, values);
           }
+        }
+      }
+      if (kStacked && finished) {
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        // silu(gate) * up for the tile's 64 output columns: consecutive threads = consecutive columns
+        const uint32_t first = threadIdx.x - 64u;
+        for (uint32_t index = first; index < (kRows / 2) * NB; index += kConvertWarps * 32) {
+          const uint32_t token = index / (kRows / 2), local = index % (kRows / 2);
+          const uint32_t batch_row = token0 + token, column = n0 + local;
+          if (batch_row >= p.m || column >= p.n) continue;
+          const float g = stash[token * kRows + local], u = stash[token * kRows + kRows / 2 + local];
+          p.out[(size_t)batch_row * p.n + column] = __float2half_rn((g / (1.0f + __expf(-g))) * u);  // lib/metal_w4a16_source.ml:571-575
         }
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -499,8 +541,8 @@ EncodeTiled encode_tiled() {
 
 template <int EPI, int NB>
 int run_batch(const KernelArgs& args, const CUtensorMap& map_x, BatchProblem p) {
-  constexpr int NMAT = EPI == kBatchLinear ? 1 : 2;
-  constexpr uint32_t kTileRows = EPI == kBatchLinearPair ? 2 * kRows : kRows;
+  constexpr int NMAT = (EPI == kBatchLinear || EPI == kBatchDualStacked) ? 1 : 2;
+  constexpr uint32_t kTileRows = EPI == kBatchLinearPair ? 2 * kRows : EPI == kBatchDualStacked ? kRows / 2 : kRows;
   using L = Layout<NMAT, NB>;
   auto kernel = w4a16_gemm_tc_batch_kernel<EPI, NB>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess) {
@@ -601,7 +643,11 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
     if (((uintptr_t)problem.mat[i].packed & 15u) != 0 || problem.mat[i].n != problem.mat[0].n) return -1;
   EncodeTiled encode = encode_tiled();
   if (encode == nullptr) return -1;
-  const uint32_t padded = prompt ? 128u : problem.m <= 16 ? 16u : problem.m <= 32 ? 32u : 64u;
+  // prompts of 256 rows and more: 256-token tiles (an MMA with N = 256 runs at the tensor pipe's full rate,
+  // narrower ones cost three quarters of that for half the work); LLMOPT_CUDA_TC_PROMPT_WIDE=0 keeps 128
+  static const bool wide_prompts = getenv("LLMOPT_CUDA_TC_PROMPT_WIDE") == nullptr || getenv("LLMOPT_CUDA_TC_PROMPT_WIDE")[0] != '0';
+  const bool wide = prompt && wide_prompts && problem.m >= 256;
+  const uint32_t padded = wide ? 256u : prompt ? 128u : problem.m <= 16 ? 16u : problem.m <= 32 ? 32u : 64u;
   CUtensorMap map_x;
   const cuuint64_t dims[2] = {problem.k, problem.m};
   const cuuint64_t strides[1] = {(cuuint64_t)problem.k * 2};
@@ -624,7 +670,9 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
   p.aux_row_stride = problem.aux_row_stride;
   p.has_aux = problem.has_aux;
   if (prompt) {
-    if (epilogue == kEpiDualSwiglu) return run_batch<kBatchDualSwiglu, 128>(args, map_x, p);
+    if (epilogue == kEpiDualSwiglu)
+      return padded == 256 ? run_batch<kBatchDualStacked, 256>(args, map_x, p) : run_batch<kBatchDualSwiglu, 128>(args, map_x, p);
+    if (padded == 256) return run_batch<kBatchLinear, 256>(args, map_x, p);
     return p.n > kRows ? run_batch<kBatchLinearPair, 128>(args, map_x, p) : run_batch<kBatchLinear, 128>(args, map_x, p);
   }
   if (epilogue == kEpiDualSwiglu) {
