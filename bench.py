@@ -595,11 +595,13 @@ def time_prefill(engine, runtime, tokens: int) -> dict:
     for _ in range(3):
         start = time.perf_counter()
         engine.prefill(prompt)
-        samples.append(time.perf_counter() - start)
-    seconds = statistics.median(samples)
+        samples.append((time.perf_counter() - start, *engine.prefill_seconds))
+    seconds, record, execute = sorted(samples)[1]
     return {"prompt_tokens": tokens, "ttft_ms": seconds * 1e3, "prompt_tokens_per_s": tokens / seconds,
+            "record_ms": record * 1e3, "execute_ms": execute * 1e3, "execute_tokens_per_s": tokens / execute,
             "kernels": engine.prefill_kernels, "h2d_bytes": 8 * tokens, "d2h_bytes": 4,
-            "note": "median of 3, host-driven batch of dispatches, empty cache"}
+            "note": "median of 3, empty cache; record = the host side building the list of dispatches (Python), "
+                    "execute = commit of that list until the first token is back on the host"}
 
 
 def tensor_parallel_check(args, whole_config, whole_weights, runtime, rank, world, group, timed_tokens) -> dict:

@@ -55,6 +55,7 @@ struct BatchProblem {
   uint32_t m, n, k;
   const uint8_t* packed[2];
   const __half* scale[2];
+  const __half* zero[2];  // zero points of the unsigned-nibble form (AFFINE), else unused
   __half* out;
   const __half* aux;  // bias (row stride 0) or residual (row stride n)
   uint32_t aux_row_stride, has_aux;
@@ -132,7 +133,7 @@ __device__ __forceinline__ void tmem_store_32(uint32_t address, const uint32_t (
 
 __device__ uint32_t g_abandoned_batch_launch = 0;
 
-template <int EPI, int NB>
+template <int EPI, int NB, bool AFFINE = false>
 __global__ void __launch_bounds__(kThreads, 1)
 w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const BatchProblem p, uint32_t* error_word,
                            uint32_t launch_id) {
@@ -287,6 +288,16 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
       return __halves2half2(__ldg(scale_row + first), first + 1u < groups ? __ldg(scale_row + first + 1u) : __float2half(0.0f));
     };
     __half2 group_scales = __float2half2_rn(0.0f), next_scales = load_scales(0);
+    // zero points of the unsigned-nibble form, fetched like the scales
+    const __half* zero_row = AFFINE ? p.zero[source] + (size_t)(row_present ? weight_row : 0u) * groups : nullptr;
+    const bool zero_pair_ok = AFFINE && groups % 2u == 0u && ((uintptr_t)p.zero[source] & 3u) == 0;
+    auto load_zeros = [&](uint32_t group) -> __half2 {
+      const uint32_t first = kb_begin + group * kGroupBlocks + 2u * duo;
+      if (!AFFINE || !row_present || first >= groups) return __float2half2_rn(0.0f);
+      if (zero_pair_ok) return __ldg(reinterpret_cast<const __half2*>(zero_row + first));
+      return __halves2half2(__ldg(zero_row + first), first + 1u < groups ? __ldg(zero_row + first + 1u) : __float2half(0.0f));
+    };
+    __half2 group_zeros = __float2half2_rn(0.0f), next_zeros = load_zeros(0);
 
     // This warp's private weight stream: the 64 contiguous bytes per row (chunks 4 duo .. 4 duo + 3 of the
     // row's group) that it converts, four lanes per row, eight rows per instruction.
@@ -320,6 +331,10 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
       __syncwarp();
       group_scales = next_scales;
       next_scales = load_scales(group + 1u);
+      if (AFFINE) {
+        group_zeros = next_zeros;
+        next_zeros = load_zeros(group + 1u);
+      }
       const uint32_t pair = group * (kGroupBlocks / 2) + duo;  // this warp's pair of the group = one ring stage
       if (2u * pair >= k_blocks) continue;
       const uint32_t s = pair % kStages;
@@ -335,13 +350,16 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
         const __half scale = which == 0 ? __low2half(group_scales) : __high2half(group_scales);
         const __half2 scale_pair = __halves2half2(scale, __hmul(scale, __float2half(0.0625f)));
         const uint32_t scales = *reinterpret_cast<const uint32_t*>(&scale_pair);
+        const __half zero = which == 0 ? __low2half(group_zeros) : __high2half(group_zeros);
+        const __half2 zero_pair = __halves2half2(zero, __hmul(zero, __float2half(16.0f)));
+        const uint32_t zeros = *reinterpret_cast<const uint32_t*>(&zero_pair);
         uint32_t converted[32];  // column c of the k-block = the halves (k = 2c, 2c + 1) of this row
 #pragma unroll
         for (uint32_t i = 0; i < 8; ++i) {  // packed word i -> k 8 i .. 8 i + 7
-          converted[4 * i] = dequant_pair<false, 0>(words[i], scales, 0u);
-          converted[4 * i + 1] = dequant_pair<false, 1>(words[i], scales, 0u);
-          converted[4 * i + 2] = dequant_pair<false, 2>(words[i], scales, 0u);
-          converted[4 * i + 3] = dequant_pair<false, 3>(words[i], scales, 0u);
+          converted[4 * i] = dequant_pair<AFFINE, 0>(words[i], scales, zeros);
+          converted[4 * i + 1] = dequant_pair<AFFINE, 1>(words[i], scales, zeros);
+          converted[4 * i + 2] = dequant_pair<AFFINE, 2>(words[i], scales, zeros);
+          converted[4 * i + 3] = dequant_pair<AFFINE, 3>(words[i], scales, zeros);
         }
         if (which == 0) {  // the stage must have been consumed (arithmetic first: the wait is usually over by now)
           ok = !*abort_flag && barrier_wait(empty + s * 8, ((pair / kStages) & 1u) ^ 1u);
@@ -539,12 +557,12 @@ EncodeTiled encode_tiled() {
   return function;
 }
 
-template <int EPI, int NB>
+template <int EPI, int NB, bool AFFINE = false>
 int run_batch(const KernelArgs& args, const CUtensorMap& map_x, BatchProblem p) {
   constexpr int NMAT = (EPI == kBatchLinear || EPI == kBatchDualStacked) ? 1 : 2;
   constexpr uint32_t kTileRows = EPI == kBatchLinearPair ? 2 * kRows : EPI == kBatchDualStacked ? kRows / 2 : kRows;
   using L = Layout<NMAT, NB>;
-  auto kernel = w4a16_gemm_tc_batch_kernel<EPI, NB>;
+  auto kernel = w4a16_gemm_tc_batch_kernel<EPI, NB, AFFINE>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kBytes) != cudaSuccess) {
     cudaGetLastError();
     return -1;
@@ -612,16 +630,17 @@ static bool prompt_rows_enabled() {
 }
 
 // Decode batches (up to 64 rows) and prompts; returns -1 outside its domain (the caller falls back).
-int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& problem, int epilogue) {
+int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& problem, int epilogue, bool affine) {
   if (args.ctx == nullptr || problem.m < tensor_core_batch_min_rows() || problem.x_rows != problem.m ||
       problem.k % 64 != 0 || problem.norm_weight != nullptr)
     return -1;
   const bool prompt = problem.m > tensor_core_batch_max_rows();
   if (prompt && (!prompt_rows_enabled() || problem.m <= 64)) return -1;
-  // up to 32 rows only matrices of 32 M weights and more gain (see tensor_core_batch_min_rows)
+  // up to 32 rows only large matrices gain (measured: 58 M weights yes, 17 M no; the line is drawn at 24 M, which
+  // keeps the halves of a two-way tensor-parallel split on this kernel)
   static const bool forced = getenv("LLMOPT_CUDA_TC_BATCH_MIN_ROWS") != nullptr;
   if (problem.m <= 32 && !forced &&
-      (epilogue == kEpiQkv || (uint64_t)problem.mat[0].n * problem.k < (32ull << 20)))
+      (epilogue == kEpiQkv || (uint64_t)problem.mat[0].n * problem.k < (24ull << 20)))
     return -1;
   if (epilogue == kEpiQkv) {
     for (uint32_t i = 0; i < problem.matrices; ++i) {
@@ -630,13 +649,15 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
       one.matrices = 1;
       one.out[0] = problem.out[i];
       one.has_aux = 0;
-      const int status = launch_w4a16_gemm_tc_batch(args, one, kEpiLinear);
+      const int status = launch_w4a16_gemm_tc_batch(args, one, kEpiLinear, false);
       if (status != 0) return i == 0 ? status : (status < 0 ? 1 : status);
     }
     return 0;
   }
   if (epilogue != kEpiLinear && epilogue != kEpiDualSwiglu) return -1;
   if (problem.out_f32 != nullptr) return -1;
+  // the zero-point form: plain products of prompts only (what the shared-memory-operand GEMM covered)
+  if (affine && (epilogue != kEpiLinear || !prompt || problem.mat[0].zero == nullptr)) return -1;
   const uint32_t matrices = epilogue == kEpiDualSwiglu ? 2u : 1u;
   if (((uintptr_t)problem.x & 15u) != 0 || (problem.k / 2) % 16 != 0) return -1;
   for (uint32_t i = 0; i < matrices; ++i)
@@ -664,6 +685,7 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
   for (uint32_t i = 0; i < 2; ++i) {
     p.packed[i] = problem.mat[i < matrices ? i : 0].packed;
     p.scale[i] = problem.mat[i < matrices ? i : 0].scale;
+    p.zero[i] = problem.mat[i < matrices ? i : 0].zero;
   }
   p.out = problem.out[0];
   p.aux = problem.aux0;
@@ -672,6 +694,10 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
   if (prompt) {
     if (epilogue == kEpiDualSwiglu)
       return padded == 256 ? run_batch<kBatchDualStacked, 256>(args, map_x, p) : run_batch<kBatchDualSwiglu, 128>(args, map_x, p);
+    if (affine) {
+      if (padded == 256) return run_batch<kBatchLinear, 256, true>(args, map_x, p);
+      return p.n > kRows ? run_batch<kBatchLinearPair, 128, true>(args, map_x, p) : run_batch<kBatchLinear, 128, true>(args, map_x, p);
+    }
     if (padded == 256) return run_batch<kBatchLinear, 256>(args, map_x, p);
     return p.n > kRows ? run_batch<kBatchLinearPair, 128>(args, map_x, p) : run_batch<kBatchLinear, 128>(args, map_x, p);
   }

@@ -315,9 +315,9 @@ int launch_w4a16_gemv(const KernelArgs& args, GemvProblem problem, int epilogue,
     problem.norm_out = nullptr;
   }
 
-  // decode batches (9..64 rows): weights as the M side of the tensor-core product, bound by HBM
-  if (!affine) {
-    const int status = launch_w4a16_gemm_tc_batch(args, problem, epilogue);
+  // decode batches from 17 rows and prompts: weights as the M side of the tensor-core product, converted into tensor memory
+  {
+    const int status = launch_w4a16_gemm_tc_batch(args, problem, epilogue, affine);
     if (status >= 0) return status;
   }
 

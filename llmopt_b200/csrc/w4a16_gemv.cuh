@@ -50,9 +50,9 @@ int launch_w4a16_gemv(const KernelArgs& args, GemvProblem problem, int epilogue,
 int launch_w4a16_gemm_tc(const KernelArgs& args, const GemvProblem& problem, int epilogue, bool affine);
 uint32_t tensor_core_min_rows();
 
-// Tensor-core kernel for decode batches (weights on the M side, batch on the N side, up to 64 rows);
-// returns -1 outside its domain.
-int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& problem, int epilogue);
+// Tensor-core kernel with the converted weights in tensor memory (weights on the M side, rows on the N side):
+// decode batches from 17 rows and prompts; returns -1 outside its domain.
+int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& problem, int epilogue, bool affine);
 
 // Pipelined fast path (K % 512 == 0, <= 32 rows); returns -1 if the shape is outside its domain.
 int launch_w4a16_gemv_pipe(const KernelArgs& args, const GemvProblem& problem, int epilogue);

@@ -20,6 +20,7 @@ ranks' vocabulary shards.  Every rank computes the same hidden state and token.
 from __future__ import annotations
 
 import math
+import time
 from typing import Optional, Sequence
 
 import numpy as np
@@ -294,6 +295,7 @@ class DecodeEngine:
         config, runtime = self.config, self.runtime
         if self.group is not None:
             raise NotImplementedError("prefill of a tensor-parallel shard is not built: feed the prompt through step()")
+        started = time.perf_counter()
         count, hidden, dim = len(tokens), config.hidden, config.head_dim
         if count == 0 or count > self.capacity:
             raise ValueError("the prompt must hold 1 .. capacity tokens")
@@ -380,8 +382,12 @@ class DecodeEngine:
             reference_guards=False, two_stage=False)
         self.prefill_kernels = len(commands.pending)
         self.prefill_hidden = current  # rows of the last block's output, one per prompt token
+        recorded = time.perf_counter()
         commands.commit()
-        return int(picked.buffer.to_numpy(np.int32)[0])
+        token = int(picked.buffer.to_numpy(np.int32)[0])
+        # host seconds spent recording the dispatches / executing them (commit until the token is back)
+        self.prefill_seconds = (recorded - started, time.perf_counter() - recorded)
+        return token
 
     # ---- stepping ------------------------------------------------------------------------------
     def step(self, tokens: Sequence[int], past_tokens: int) -> list:

@@ -46,11 +46,13 @@ def test_prefill_bias_and_row_residual(runtime, oracle):
     assert_close_f16(_linear(runtime, x, packed, scale, residual, n), oracle.w4a16_linear(x, packed, scale, residual, n))
 
 
-def test_prefill_affine_zero_points(runtime, oracle):
+@pytest.mark.parametrize("m,k,n", [(256, 576, 1536), (100, 1024, 384), (300, 512, 100), (64, 576, 1536)])
+def test_prefill_affine_zero_points(runtime, oracle, m, k, n):
+    """Unsigned nibbles with fp16 zero points at prompt rows: 256-token tiles, 128-token pairs of weight
+    tiles, a single narrow tile, and 64 rows (the shared-memory-operand GEMM)."""
     from llmopt_b200 import dispatch
 
     rng = np.random.default_rng(13)
-    m, k, n = 256, 576, 1536
     x = rng.standard_normal((m, k)).astype(np.float16)
     packed, scale = random_w4(rng, n, k)
     zero = rng.uniform(6, 9, size=(n, k // 64)).astype(np.float16)
@@ -86,7 +88,8 @@ def test_prefill_swiglu_ffn_matches_oracle(runtime, oracle, m, k, n):
 
 @pytest.mark.parametrize("m,k,n", [(33, 128, 128), (36, 64, 40), (40, 1024, 384), (33, 576, 192), (48, 2048, 1000),
                                    (64, 4096, 512), (56, 14336, 256), (9, 1024, 384), (16, 4096, 512), (17, 576, 192),
-                                   (32, 4096, 1000), (24, 14336, 256), (100, 2048, 384), (128, 1024, 640)])
+                                   (32, 4096, 1000), (24, 14336, 256), (100, 2048, 384), (128, 1024, 640),
+                                   (32, 4096, 8192), (20, 8192, 4096)])  # 32 M weights: the tensor-core kernel from 17 rows
 def test_decode_batch_linear_matches_oracle(runtime, oracle, m, k, n):
     rng = np.random.default_rng(40)
     x = rng.standard_normal((m, k)).astype(np.float16)
@@ -109,7 +112,7 @@ def test_decode_batch_dyadic_inputs_are_bit_exact(runtime, oracle):
 
 
 @pytest.mark.parametrize("m,k,n", [(33, 256, 256), (48, 576, 1536), (40, 1024, 192), (12, 1024, 192), (32, 576, 1536),
-                                   (96, 256, 256)])
+                                   (96, 256, 256), (24, 4096, 8192), (300, 512, 1024)])
 def test_decode_batch_swiglu_ffn_matches_oracle(runtime, oracle, m, k, n):
     from llmopt_b200 import dispatch
 
