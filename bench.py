@@ -467,6 +467,37 @@ def time_baseline_mode(runtime, peaks) -> dict:
     return out
 
 
+def time_other_kernels(runtime, peaks) -> dict:
+    """Kernels of the path that no leg above times: the Q4_0-block GEMV (GGUF blocks, 18 bytes per 32
+    weights) at the gate shape against the HBM peak, and the dense causal prefill attention
+    (mma.sync flash-attention forward) at 2048 tokens of the Llama-8B head geometry against the
+    tensor peak."""
+    from llmopt_b200 import kernel_bench
+
+    out = {}
+    options = types.SimpleNamespace(op="q4_0", m=1, k=4096, n=14336, heads=32, kv_heads=8, dim=128, group=64, layers=2,
+                                    past=8192)
+    item, nbytes, keep = kernel_bench.build_item(runtime, options)
+    milliseconds = runtime.time_dispatch(item, warmup=3, iterations=20, flush_l2=True)
+    out["q4_0_gemv_m1"] = {"kernel": item.name, "ms": round(milliseconds, 5), "bytes": nbytes, "bound": "hbm",
+                           "gbs": round(nbytes / milliseconds / 1e6, 1),
+                           "frac": round(nbytes / milliseconds / 1e6 / peaks["hbm_gbs"], 3),
+                           "mode": "isolated launch, L2 flushed before each"}
+    del keep
+    tokens = 2048
+    options = types.SimpleNamespace(op="dense_attention", m=tokens, k=0, n=0, heads=32, kv_heads=8, dim=128, group=64,
+                                    layers=2, past=0)
+    item, nbytes, keep = kernel_bench.build_item(runtime, options)
+    milliseconds = runtime.time_dispatch(item, warmup=3, iterations=10, flush_l2=True)
+    flops = 2.0 * tokens * tokens * 128 * 32  # causal: half of the square, two products per head
+    out["dense_attention_causal_2048"] = {
+        "kernel": item.name, "ms": round(milliseconds, 5), "bound": "tensor", "tflops": round(flops / milliseconds / 1e9, 1),
+        "frac": round(flops / milliseconds / 1e9 / peaks["bf16_tflops"], 3),
+        "note": "legacy tensor path (mma.sync), fp16, 32 query / 8 KV heads of 128", "mode": "isolated launch"}
+    del keep
+    return out
+
+
 # ---- decode measurement ---------------------------------------------------------------------------
 
 def measure_decode(engine, runtime, args, group, *, context: int, jobs: int, device_index: int, peaks: dict) -> dict:
@@ -743,6 +774,7 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         sweep.append(time_prefill_gemm(runtime, peaks, m=2048, k=8192, n=28672, form="linear"))
         result["prefill_gemm_c5"] = sweep
         result["baseline_mode"] = time_baseline_mode(runtime, peaks)
+        result["other_kernels"] = time_other_kernels(runtime, peaks)
         result["smollm2_135m"] = small_model_leg(runtime, args, "smollm2-135m", peaks)
         result["lfm25_350m"] = small_model_leg(runtime, args, "lfm2.5-350m", peaks)
         result["lfm25_350m_batch16"] = small_model_leg(runtime, args, "lfm2.5-350m", peaks, batch=16)

@@ -4,7 +4,7 @@ as achieved GB/s over the algorithmic bytes.  The counterpart of the reference's
 stand-alone Metal tile probes (bench/metal_q4_tile_probe.swift); also the small,
 self-terminating command used for profiler captures.
 
-  python -m llmopt_b200.kernel_bench --op linear|linear_affine|qkv|gate_up|down|lm_head|attention \\
+  python -m llmopt_b200.kernel_bench --op linear|linear_affine|qkv|gate_up|down|lm_head|attention|q4_0|dense_attention \\
          --m 1 --k 4096 --n 14336 [--heads 32 --kv-heads 8 --dim 128 --past 8192] [--iters 20]
 """
 
@@ -112,6 +112,25 @@ def build_item(runtime, args):
             output=_f16(runtime, rng, (m, 1, args.heads, args.dim)), slot_batch_stride=args.past)
         per_key = 2 * args.kv_heads * args.dim + 4 * args.kv_heads * args.dim // args.group + 4
         nbytes = m * (args.past * per_key + 2 * args.heads * args.dim * 2 + 2 * args.kv_heads * args.dim * 2)
+    elif args.op == "q4_0":
+        # GGUF Q4_0 blocks: 18 bytes per 32 weights
+        blocks = rng.integers(0, 256, size=(n, (k // 32) * 18), dtype=np.uint8)
+        blocks.reshape(n, k // 32, 18)[:, :, 0:2] = rng.uniform(0.005, 0.02, size=(n, k // 32, 1)).astype(np.float16).view(
+            np.uint8).reshape(n, k // 32, 2)
+        dispatch.dispatch_quant_linear(
+            context, m=m, n=n, k=k, input=_f16(runtime, rng, (m, k)),
+            weight=dispatch.Tensor(Buffer.of_array(runtime, blocks), (n, (k // 32) * 18), "uint8"),
+            output=_f16(runtime, rng, (m, n)))
+        nbytes = n * (k // 32) * 18 + m * k * 2 + m * n * 2
+    elif args.op == "dense_attention":
+        # causal prefill attention over m query = key rows: query / key head-major, value and output token-first
+        tokens = m
+        dispatch.dispatch_attention(
+            context, causal=True, scale=float(np.float32(1 / math.sqrt(args.dim))),
+            query=_f16(runtime, rng, (1, args.heads, tokens, args.dim)), key=_f16(runtime, rng, (1, args.kv_heads, tokens, args.dim)),
+            value=_f16(runtime, rng, (1, tokens, args.kv_heads, args.dim)),
+            output=_f16(runtime, rng, (1, tokens, args.heads * args.dim)))
+        nbytes = (2 * args.heads + 2 * args.kv_heads) * tokens * args.dim * 2
     else:
         raise SystemExit(f"unknown op {args.op}")
     item = commands.pending[0]
@@ -140,8 +159,10 @@ def main() -> None:
     runtime = cuda_native.Runtime()
     item, nbytes, _keep = build_item(runtime, args)
     result = {"op": args.op, "kernel": item.name, "m": args.m, "k": args.k, "n": args.n, "algorithmic_bytes": nbytes}
-    products = {"linear": 1, "linear_affine": 1, "gate_up": 2, "down": 1, "lm_head": 1}.get(args.op)
+    products = {"linear": 1, "linear_affine": 1, "gate_up": 2, "down": 1, "lm_head": 1, "q4_0": 1}.get(args.op)
     flops = 2.0 * args.m * args.k * args.n * products if products else None
+    if args.op == "dense_attention":  # causal: half of the q x k square, two products of 2 q k D flops per head
+        flops = 2.0 * args.m * args.m * args.dim * args.heads
     if args.copies > 1:
         # distinct operands per launch, launched back to back: in-plan conditions (cold
         # operands because the set exceeds the L2, launch gaps as in a replayed plan)
