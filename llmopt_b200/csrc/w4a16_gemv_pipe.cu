@@ -44,15 +44,13 @@ namespace {
 // 512*GPW k of 16 weight rows (+32 bytes of padding per row) and their scales.
 // More groups per warp and stage = more independent work per wait (the math of
 // one group is a dependent chain) and less per-stage overhead.
-template <int GPW, int CW = 8> struct Stage {
-  static constexpr int kChunkK = 64 * CW * GPW;
+template <int GPW> struct Stage {
+  static constexpr int kChunkK = 512 * GPW;
   static constexpr int kRowBytes = kChunkK / 2 + 32;
   static constexpr int kWeights = 16 * kRowBytes;
-  static constexpr int kScaleRow = 2 * CW * GPW;  // CW*GPW fp16 scales per row
+  static constexpr int kScaleRow = 16 * GPW;  // 8*GPW fp16 scales per row
   static constexpr int kBytes = kWeights + 16 * kScaleRow;
 };
-// Consumer warps per CTA: eight, or sixteen (the CW template argument) for single-row launches with few
-// tiles, where two CTAs of eight per SM leave most schedulers idle and each warp a long chain of groups.
 constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr uint32_t kSpinLimit = 1u << 18;    // polls of ~0.1 us: tens of milliseconds at most
@@ -90,8 +88,7 @@ __device__ __forceinline__ void copy_16(uint32_t destination, const void* source
 __device__ __forceinline__ void arrive_when_copied(uint32_t barrier) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(barrier) : "memory");
 }
-template <int CW = 8>
-__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory"); }
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // (word & mask) ^ constant with the exponent of 1024 (even nibbles) or 64 (odd
 // nibbles) and bit 3 of the nibble flipped: the halves read 1032 + q and 72 + q.
@@ -150,21 +147,19 @@ template <int NT, int EPI> constexpr int kDenseResidency = NT == 1 ? (EPI == kEp
 // is a real output then, so the kernel keeps two accumulators per matrix instead of four, applies two
 // scale FMAs per group instead of four, reads one bias term per group instead of two, and hands
 // the bias to the first MMA of a group as its C operand (no register moves to seed the sum).
-template <int NT, int NMAT, int EPI, bool SMALLX, int GPW, int RES = kDenseResidency<NT, EPI>, bool ONE = false, int CW = 8>
-__global__ void __launch_bounds__((CW + 1) * 32, RES) w4a16_gemv_pipe_kernel(const GemvProblem p, const uint32_t stage_count,
-                                                                        uint32_t* error_word) {
+template <int NT, int NMAT, int EPI, bool SMALLX, int GPW, int RES = kDenseResidency<NT, EPI>, bool ONE = false>
+__global__ void __launch_bounds__(kThreads, RES) w4a16_gemv_pipe_kernel(const GemvProblem p, const uint32_t stage_count,
+                                                                   uint32_t* error_word) {
   static_assert(!ONE || (SMALLX && NT == 1), "the one-row form is a staged-activation, one-batch-tile form");
-  static_assert(CW == 8 || (CW == 16 && ONE), "sixteen consumer warps exist for the one-row form only");
-  constexpr int kConsumerWarps = CW;  // shadows the namespace constant inside this kernel
   extern __shared__ __align__(16) unsigned char shared[];
   // The next kernel of the stream may start its launch now; the producer warp below
   // streams weights (which no kernel writes) without waiting for the previous kernel,
   // the consumer warps wait for it before they read the activations.
   grid_launch_dependents();
   constexpr int kAcc = NMAT * NT * 4;
-  constexpr int kChunkK = Stage<GPW, CW>::kChunkK, kRowBytes = Stage<GPW, CW>::kRowBytes;
-  constexpr int kStageWeights = Stage<GPW, CW>::kWeights, kScaleRow = Stage<GPW, CW>::kScaleRow;
-  constexpr int kStageBytes = Stage<GPW, CW>::kBytes;
+  constexpr int kChunkK = Stage<GPW>::kChunkK, kRowBytes = Stage<GPW>::kRowBytes;
+  constexpr int kStageWeights = Stage<GPW>::kWeights, kScaleRow = Stage<GPW>::kScaleRow;
+  constexpr int kStageBytes = Stage<GPW>::kBytes;
   const uint32_t groups = p.k >> 6;
   // [full barriers | empty barriers | reduction words] [ring] [reduce] [x fragments] [x bias]
   uint64_t* barriers = reinterpret_cast<uint64_t*>(shared);
@@ -249,13 +244,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, RES) w4a16_gemv_pipe_kernel(con
                         mat.packed + (size_t)row * half_k + (size_t)chunk * (kChunkK / 2) + (lane & 15u) * 16);
               }
             }
-            // scales: 16 rows x kScaleRow bytes in sixteen-byte pieces
-            constexpr uint32_t kPiecesPerRow = kScaleRow / 16, kPieces = 16 * kPiecesPerRow;
+            // scales: 16 rows x kScaleRow bytes = 16*GPW sixteen-byte pieces
 #pragma unroll
-            for (int i = 0; i < (int)(kPieces + 31) / 32; ++i) {
+            for (int i = 0; i < (16 * GPW + 31) / 32; ++i) {
               const uint32_t piece = i * 32 + lane;
-              if (piece < kPieces) {
-                const uint32_t row_in_tile = piece / kPiecesPerRow, part = piece % kPiecesPerRow;
+              if (piece < 16u * GPW) {
+                const uint32_t row_in_tile = piece / GPW, part = piece % GPW;
                 const uint32_t row = min(local_tile * 16u + row_in_tile, mat.n - 1u);
                 copy_16(target + a * kStageBytes + kStageWeights + row_in_tile * kScaleRow + part * 16,
                         reinterpret_cast<const unsigned char*>(mat.scale + (size_t)row * groups) +
@@ -302,7 +296,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, RES) w4a16_gemv_pipe_kernel(con
         squares = warp_sum(squares);
         if (lane == 0) inverse_rms[warp] = rsqrtf(squares / (float)p.k + p.norm_epsilon);
       }
-      consumer_barrier<CW>();
+      consumer_barrier();
     }
     for (uint32_t unit = threadIdx.x; unit < units; unit += kConsumerWarps * 32) {
       const uint32_t cc = unit & 3u, row = (unit >> 2) % p.x_rows, gh = (unit >> 2) / p.x_rows;
@@ -349,7 +343,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, RES) w4a16_gemv_pipe_kernel(con
         if ((unit & 7u) == 0u) x_bias[unit >> 3] = -(1032.0f * even + 72.0f * odd);  // stored negated
       }
     }
-    if (!single_row) consumer_barrier<CW>();
+    if (!single_row) consumer_barrier();
     // several rows: per (row, group) 1032 * sum of the even-k activations + 72 * sum of the odd-k
     // ones, read back from the fragment units (words x, z hold even k, words y, w odd k), fixed order
     for (uint32_t index = threadIdx.x; !single_row && index < p.x_rows * groups; index += kConsumerWarps * 32) {
@@ -373,7 +367,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, RES) w4a16_gemv_pipe_kernel(con
       x_fragments[units] = make_uint4(0u, 0u, 0u, 0u);
       x_bias[p.x_rows * groups] = 0.0f;
     }
-    consumer_barrier<CW>();
+    consumer_barrier();
   }
 
   float acc[NMAT][NT][4];
@@ -432,21 +426,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, RES) w4a16_gemv_pipe_kernel(con
             nibbles_biased(word_a.x, a_even, a_odd);
             nibbles_biased(word_b.x, b_even, b_odd);
             mma_16816_from(sum, a_even, b_even, a_odd, b_odd, first.x, first.y, bias0, 0.0f, bias0, 0.0f);
-#ifdef LLMOPT_GEMV_TWO_CHAINS
-            // two chains of two MMAs instead of one of four (the group sum is then a + b: one more rounding)
-            float other[4];
-            nibbles_biased(word_a.x >> 8, a_even, a_odd);
-            nibbles_biased(word_b.x >> 8, b_even, b_odd);
-            mma_16816_from(other, a_even, b_even, a_odd, b_odd, first.z, first.w, 0.0f, 0.0f, 0.0f, 0.0f);
-            nibbles_biased(word_a.y, a_even, a_odd);
-            nibbles_biased(word_b.y, b_even, b_odd);
-            mma_16816(sum, a_even, b_even, a_odd, b_odd, second.x, second.y);
-            nibbles_biased(word_a.y >> 8, a_even, a_odd);
-            nibbles_biased(word_b.y >> 8, b_even, b_odd);
-            mma_16816(other, a_even, b_even, a_odd, b_odd, second.z, second.w);
-            acc[a][0][0] = fmaf(stage_scale_a[a][jg], sum[0] + other[0], acc[a][0][0]);
-            acc[a][0][2] = fmaf(stage_scale_b[a][jg], sum[2] + other[2], acc[a][0][2]);
-#else
             nibbles_biased(word_a.x >> 8, a_even, a_odd);
             nibbles_biased(word_b.x >> 8, b_even, b_odd);
             mma_16816(sum, a_even, b_even, a_odd, b_odd, first.z, first.w);
@@ -458,7 +437,6 @@ __global__ void __launch_bounds__((CW + 1) * 32, RES) w4a16_gemv_pipe_kernel(con
             mma_16816(sum, a_even, b_even, a_odd, b_odd, second.z, second.w);
             acc[a][0][0] = fmaf(stage_scale_a[a][jg], sum[0], acc[a][0][0]);
             acc[a][0][2] = fmaf(stage_scale_b[a][jg], sum[2], acc[a][0][2]);
-#endif
           }
         } else if (SMALLX) {
           const uint4 first = first_base[g * unit_stride];
@@ -622,7 +600,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, RES) w4a16_gemv_pipe_kernel(con
         }
       }
     } else {
-      consumer_barrier<CW>();  // the previous tile's reader is done with the buffer
+      consumer_barrier();  // the previous tile's reader is done with the buffer
 #pragma unroll
       for (int a = 0; a < NMAT; ++a)
 #pragma unroll
@@ -632,7 +610,7 @@ __global__ void __launch_bounds__((CW + 1) * 32, RES) w4a16_gemv_pipe_kernel(con
             reduce[(warp * kAcc + (a * NT + t) * 4 + j) * 32 + lane] = acc[a][t][j];
             acc[a][t][j] = 0.0f;
           }
-      consumer_barrier<CW>();
+      consumer_barrier();
       // every consumer thread finishes some accumulator positions: fixed-order sum over the
       // eight warps' partials, then the writeback of that position
       for (uint32_t position = threadIdx.x; position < NT * 4 * 32; position += kConsumerWarps * 32) {
@@ -694,21 +672,20 @@ inline bool wide_forms_at_two_ctas() {
   return two;
 }
 
-template <int NT, int NMAT, int EPI, bool SMALLX, int GPW, int CW = 8>
+template <int NT, int NMAT, int EPI, bool SMALLX, int GPW>
 bool plan_pipe(const KernelArgs& args, const GemvProblem& p, PipePlan* plan) {
   uint32_t total_tiles = 0;
   const uint32_t matrices = EPI == kEpiQkv ? p.matrices : 1u;
   for (uint32_t i = 0; i < matrices; ++i) total_tiles += (p.mat[i].n + 15u) / 16u;
   const uint32_t groups = p.k / 64;
-  size_t fixed_bytes = (size_t)CW * NMAT * NT * 4 * 32 * sizeof(float) + 64;
+  size_t fixed_bytes = (size_t)kConsumerWarps * NMAT * NT * 4 * 32 * sizeof(float) + 64;
   if (SMALLX) fixed_bytes += (size_t)groups * 2 * p.x_rows * 4 * 16 + 16 + (size_t)(p.x_rows * groups + 4) * sizeof(float);
-  const size_t stage_bytes = (size_t)NMAT * Stage<GPW, CW>::kBytes + 16;
+  const size_t stage_bytes = (size_t)NMAT * Stage<GPW>::kBytes + 16;
   const uint32_t sms = (uint32_t)context_sm_count(args.ctx);
   constexpr size_t kSharedPerSm = 220 * 1024;  // usable shared memory of one SM
-  const uint32_t chunks_per_tile = p.k / Stage<GPW, CW>::kChunkK;
+  const uint32_t chunks_per_tile = p.k / Stage<GPW>::kChunkK;
   // a fourth resident CTA only where the kernel was compiled for it and every CTA still gets four tiles
   uint32_t most = kDenseResidency<NT, EPI> == 4 && total_tiles >= 16u * sms ? 4u : 3u;
-  if (CW == 16) most = 2u;  // seventeen warps per CTA: two CTAs fill an SM
   // Wide-batch forms on few, short tiles (QKV, o_proj): size grid and ring for the CTAs the registers really
   // let reside (batch 32: QKV 17.8 -> 14.6, o_proj 12.4 -> 10.9 us).  On many or long tiles the oversubscribed
   // grid measured faster (gate/up, down, LM head), so those keep it.
@@ -761,34 +738,6 @@ int run_pipe(const KernelArgs& args, const GemvProblem& p, const PipePlan& plan)
   return check_launch(args);
 }
 
-// Single-row launches whose tiles fill at most two CTA slots per SM (the narrow projections: 256 to 384
-// tiles for 444 slots of the eight-warp CTAs) take sixteen consumer warps per CTA and two CTAs per SM: every
-// tile's K is split sixteen ways, so each warp's chain of dependent groups is half as long and all four
-// schedulers of an SM have eight warps.  LLMOPT_CUDA_GEMV_SIXTEEN=0 keeps eight.
-template <int NMAT, int EPI>
-int launch_pipe_sixteen(const KernelArgs& args, const GemvProblem& p) {
-  static const bool enabled = getenv("LLMOPT_CUDA_GEMV_SIXTEEN") == nullptr || getenv("LLMOPT_CUDA_GEMV_SIXTEEN")[0] != '0';
-  if (!enabled || p.x_rows != 1u) return -1;
-  uint32_t total_tiles = 0;
-  const uint32_t matrices = EPI == kEpiQkv ? p.matrices : 1u;
-  for (uint32_t i = 0; i < matrices; ++i) total_tiles += (p.mat[i].n + 15u) / 16u;
-  if (total_tiles > 2u * (uint32_t)context_sm_count(args.ctx)) return -1;
-  PipePlan plan = {};
-  auto run = [&](auto kernel) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.shared_bytes) != cudaSuccess) {
-      cudaGetLastError();
-      return -1;
-    }
-    launch_kernel(args, kernel, dim3(plan.ctas), dim3(17 * 32), plan.shared_bytes, p, plan.stages, context_device_error(args.ctx));
-    return check_launch(args);
-  };
-  if (p.k % 2048 == 0 && plan_pipe<1, NMAT, EPI, true, 2, 16>(args, p, &plan) && plan.resident >= 2)
-    return run(w4a16_gemv_pipe_kernel<1, NMAT, EPI, true, 2, 2, true, 16>);
-  if (p.k % 1024 == 0 && plan_pipe<1, NMAT, EPI, true, 1, 16>(args, p, &plan) && plan.resident >= 2)
-    return run(w4a16_gemv_pipe_kernel<1, NMAT, EPI, true, 1, 2, true, 16>);
-  return -1;
-}
-
 // Groups per warp and stage: the most (4, 2, 1) that K allows and that still leaves at
 // least two CTAs (18 warps) resident per SM; a fat stage that forces one CTA per SM
 // loses more to idle issue slots than it gains from amortised waits.  Four groups only for
@@ -817,12 +766,6 @@ int launch_pipe_by_rows(const KernelArgs& args, const GemvProblem& p) {
   const bool small = (size_t)rows * p.k <= 16384 && rows <= 8 && EPI != kEpiSplitF32;
   if (p.norm_weight != nullptr && !small) return -1;  // only the staged-activation form absorbs a norm
   if (rows <= 8) {
-    if constexpr (EPI != kEpiSplitF32) {
-      if (small && rows == 1) {
-        const int status = launch_pipe_sixteen<NMAT, EPI>(args, p);
-        if (status >= 0) return status;
-      }
-    }
     if (small) return launch_pipe<1, NMAT, EPI, true>(args, p);
     return launch_pipe<1, NMAT, EPI, false>(args, p);
   }
