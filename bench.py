@@ -754,6 +754,19 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         result["batch32"] = leg
         result["gpu_launches"] += leg["gpu_launches"]
         del wide
+        if world == 1:
+            # the stated configuration's other batch sizes, in short: same weights, same process
+            for other_batch in (8, 64):
+                other = make_engine(other_batch, share=engine)
+                other.fill_cache_random(args.context, seed=0)
+                other.build(args.context)
+                leg = measure_decode(other, runtime, args, group, context=args.context, jobs=jobs, device_index=local,
+                                     peaks=peaks)
+                result[f"batch{other_batch}"] = {key: leg[key] for key in (
+                    "value", "unit", "ms_per_step", "e2e", "kernels_per_step", "gpu_launches", "repetitions_ms",
+                    "tokens_identical_across_repetitions", "clocks") if key in leg}
+                result["gpu_launches"] += leg["gpu_launches"]
+                del other
 
     if tensor_parallel_mode:
         result["tp_check"] = tensor_parallel_check(args, whole_config, whole_weights, runtime, rank, world, group, timed_tokens)

@@ -1,4 +1,4 @@
-// Decode batches (9..64 rows) of the W4A16 group-64 product on tcgen05, with the operands swapped
+// Decode batches (17..64 rows) and prompts of the W4A16 group-64 product on tcgen05, with the operands swapped
 // relative to the prefill kernel: the WEIGHT tile is the M side of the MMA (128 rows) and the
 // activations are the N side (the batch, padded to 16, 32 or 64), so the tensor work is
 // proportional to the batch and the kernel is bound by the weight stream from HBM, like the
@@ -49,7 +49,10 @@ constexpr uint32_t kSplitCounterTiles = 1u << 14;
 // read once for 256 output columns); kBatchDualStacked: ONE tile whose lanes 0..63 are 64 gate rows and
 // lanes 64..127 the same 64 up rows, so that gate/up prompts also run 256 tokens wide with one accumulator
 // (the halves meet in shared memory for silu(gate) * up).
-enum BatchEpilogue { kBatchLinear = 0, kBatchDualSwiglu = 1, kBatchLinearPair = 2, kBatchDualStacked = 3 };
+// kBatchSplitF32: one weight tile; the activation rows are fp32 values given as exact hi/lo half pairs in
+// 8-row slot tiles [hi0..hi3, lo0..lo3] (the LM head's normalised rows) and the output is the fp32 sum of the
+// pair's two accumulator columns.
+enum BatchEpilogue { kBatchLinear = 0, kBatchDualSwiglu = 1, kBatchLinearPair = 2, kBatchDualStacked = 3, kBatchSplitF32 = 4 };
 
 struct BatchProblem {
   uint32_t m, n, k;
@@ -57,6 +60,7 @@ struct BatchProblem {
   const __half* scale[2];
   const __half* zero[2];  // zero points of the unsigned-nibble form (AFFINE), else unused
   __half* out;
+  float* out_f32;     // kBatchSplitF32: [m, n] fp32
   const __half* aux;  // bias (row stride 0) or residual (row stride n)
   uint32_t aux_row_stride, has_aux;
   uint32_t splits;
@@ -138,7 +142,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const BatchProblem p, uint32_t* error_word,
                            uint32_t launch_id) {
   constexpr bool kStacked = EPI == kBatchDualStacked;
-  constexpr int NMAT = (EPI == kBatchLinear || kStacked) ? 1 : 2;
+  constexpr int NMAT = (EPI == kBatchLinear || kStacked || EPI == kBatchSplitF32) ? 1 : 2;
   constexpr uint32_t kTileRows = EPI == kBatchLinearPair ? 2 * kRows : kStacked ? kRows / 2 : kRows;  // output columns of one CTA
   using L = Layout<NMAT, NB>;
   constexpr int kRawStages = L::kRawStages, kStages = L::kStages, kXStages = L::kXStages, kGroupBlocks = L::kGroupBlocks;
@@ -451,7 +455,20 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
       float* stash = reinterpret_cast<float*>(base_pointer + L::kOffsetX);
       static_assert(!kStacked || NB * kRows * 4 <= L::kXStages * L::kXStage, "the stash must fit the X ring");
       auto emit = [&](int piece, const float (&values)[NMAT][kPiece]) {
-        if (kStacked) {
+        if (EPI == kBatchSplitF32) {
+          // this thread's 16 columns are two slot tiles: token 4 t + w = column 8 t + w (hi) + column 8 t + 4 + w (lo)
+          static_assert(EPI != kBatchSplitF32 || kPiece == 16, "hi and lo of a token must sit in one thread's piece");
+          const uint32_t column = n0 + tile_row;
+          if (column < p.n) {
+#pragma unroll
+            for (int t = 0; t < kPiece / 8; ++t)
+#pragma unroll
+              for (int w = 0; w < 4; ++w) {
+                const uint32_t token = (half_index * kHalf + piece * kPiece) / 2 + 4 * t + w;
+                if (token < p.m) p.out_f32[(size_t)token * p.n + column] = values[0][8 * t + w] + values[0][8 * t + 4 + w];
+              }
+          }
+        } else if (kStacked) {
 #pragma unroll
           for (int i = 0; i < kPiece; ++i) stash[(half_index * kHalf + piece * kPiece + i) * kRows + tile_row] = values[0][i];
         } else {
@@ -559,7 +576,7 @@ EncodeTiled encode_tiled() {
 
 template <int EPI, int NB, bool AFFINE = false>
 int run_batch(const KernelArgs& args, const CUtensorMap& map_x, BatchProblem p) {
-  constexpr int NMAT = (EPI == kBatchLinear || EPI == kBatchDualStacked) ? 1 : 2;
+  constexpr int NMAT = (EPI == kBatchLinear || EPI == kBatchDualStacked || EPI == kBatchSplitF32) ? 1 : 2;
   constexpr uint32_t kTileRows = EPI == kBatchLinearPair ? 2 * kRows : EPI == kBatchDualStacked ? kRows / 2 : kRows;
   using L = Layout<NMAT, NB>;
   auto kernel = w4a16_gemm_tc_batch_kernel<EPI, NB, AFFINE>;
@@ -631,8 +648,8 @@ static bool prompt_rows_enabled() {
 
 // Decode batches (up to 64 rows) and prompts; returns -1 outside its domain (the caller falls back).
 int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& problem, int epilogue, bool affine) {
-  if (args.ctx == nullptr || problem.m < tensor_core_batch_min_rows() || problem.x_rows != problem.m ||
-      problem.k % 64 != 0 || problem.norm_weight != nullptr)
+  if (args.ctx == nullptr || problem.m < tensor_core_batch_min_rows() ||
+      (problem.x_rows != problem.m && epilogue != kEpiSplitF32) || problem.k % 64 != 0 || problem.norm_weight != nullptr)
     return -1;
   const bool prompt = problem.m > tensor_core_batch_max_rows();
   if (prompt && (!prompt_rows_enabled() || problem.m <= 64)) return -1;
@@ -653,6 +670,31 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
       if (status != 0) return i == 0 ? status : (status < 0 ? 1 : status);
     }
     return 0;
+  }
+  if (epilogue == kEpiSplitF32) {
+    // the LM head's hi/lo rows: 17..32 rows = up to 64 slot rows, one launch instead of two 16-row passes
+    if (affine || prompt || problem.m > 32 || problem.x_rows > 64 || problem.x_rows % 8 != 0 || problem.out_f32 == nullptr ||
+        ((uintptr_t)problem.x & 15u) != 0 || (problem.k / 2) % 16 != 0 || ((uintptr_t)problem.mat[0].packed & 15u) != 0)
+      return -1;
+    EncodeTiled encode = encode_tiled();
+    if (encode == nullptr) return -1;
+    CUtensorMap map_x;
+    const cuuint64_t dims[2] = {problem.k, problem.x_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)problem.k * 2};
+    const cuuint32_t box[2] = {kBK, 64};
+    const cuuint32_t element_strides[2] = {1, 1};
+    if (encode(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(problem.x), dims, strides, box,
+               element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return -1;
+    BatchProblem p = {};
+    p.m = problem.m;
+    p.n = problem.mat[0].n;
+    p.k = problem.k;
+    p.packed[0] = p.packed[1] = problem.mat[0].packed;
+    p.scale[0] = p.scale[1] = problem.mat[0].scale;
+    p.out_f32 = problem.out_f32;
+    return run_batch<kBatchSplitF32, 64>(args, map_x, p);
   }
   if (epilogue != kEpiLinear && epilogue != kEpiDualSwiglu) return -1;
   if (problem.out_f32 != nullptr) return -1;

@@ -162,6 +162,17 @@ int lm_head_stage(const KernelArgs& args, bool input_f32, const void* input, con
   problem.out_f32 = logits_f32;
   // At most 16 rows (32 hi/lo slot rows) per launch: that is what the pipelined kernel takes, and two
   // passes over the weights through it beat one pass through the direct-load kernel (batch 32: 583 -> ~500 us).
+  if (m > 16u) {
+    // 17..32 rows: one pass over the weights on the tensor-core kernel (weights converted into tensor memory)
+    problem.x_rows = tiles * 8;
+    problem.m = m;
+    const int status = launch_w4a16_gemm_tc_batch(args, problem, kEpiSplitF32, false);
+    if (status > 0) return status;
+    if (status == 0) {
+      launch_kernel(args, argmax_partial_kernel, dim3(kCandidateParts, m), dim3(256), 0, logits_f32, candidates, logits, n);
+      return check_launch(args);
+    }
+  }
   for (uint32_t first = 0; first < m; first += 16u) {
     const uint32_t rows = m - first < 16u ? m - first : 16u;
     problem.x = slots + (size_t)(first / 4u) * 8u * k;

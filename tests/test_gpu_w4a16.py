@@ -193,7 +193,8 @@ def test_tagged_epilogues(runtime, oracle, tag):
 
 
 @pytest.mark.parametrize("m,k,n,f32,two_stage,logits", [(1, 576, 4096, False, True, False), (2, 1024, 3000, False, False, True),
-                                                         (1, 576, 49152, True, True, True), (5, 128, 777, False, True, False)])
+                                                         (1, 576, 49152, True, True, True), (5, 128, 777, False, True, False),
+                                                         (32, 1024, 32768, False, True, True), (20, 576, 49152, True, True, False)])  # 17..32 rows: one tensor-core pass
 def test_lm_head_argmax(runtime, oracle, m, k, n, f32, two_stage, logits):
     from llmopt_b200 import dispatch
 
