@@ -321,7 +321,8 @@ int launch_w4a16_gemv(const KernelArgs& args, GemvProblem problem, int epilogue,
     if (status >= 0) return status;
   }
 
-  // 64 rows and more: the tensor-memory GEMM
+  // 64 rows and more that the kernel above does not cover (tagged epilogues): the GEMM with the converted
+  // weights as the shared-memory B operand
   if (problem.m >= tensor_core_min_rows() && problem.x_rows == problem.m) {
     const int status = launch_w4a16_gemm_tc(args, problem, epilogue, affine);
     if (status >= 0) return status;

@@ -286,7 +286,7 @@ class DecodeEngine:
     def prefill(self, tokens: Sequence[int], sequence: int = 0) -> int:
         """The whole prompt of one sequence in one pass — the reference's prefill path
         (``Serving_engine.prefill``, lib/serving_engine.ml:435-570): every linear runs with one row
-        per prompt token (the tensor-memory GEMM from 64 rows on), attention is the dense causal
+        per prompt token (the tcgen05 kernels from 17 rows on), attention is the dense causal
         fp16 attention over the prompt's own keys and values, every token's K / V row is packed
         into the Q8 cache (``Cache.with_batch_async``, lib/metal_cache.ml:93-116) and the
         short-conv blocks leave their state behind.  Returns the first generated token; decode

@@ -91,8 +91,8 @@ def test_hybrid_conv_attention_batched_teacher_forced(runtime):
 
 @pytest.mark.parametrize("layers,prompt_length", [(("attention",) * 3, 70), (("conv", "attention", "conv", "attention"), 130)])
 def test_prefill_path_then_decode_matches_oracle(runtime, layers, prompt_length):
-    """The prompt in one pass (one row per token through every linear — the tensor-memory GEMM from
-    64 rows on — dense causal attention, bulk cache pack, short-conv prefill), then greedy decode
+    """The prompt in one pass (one row per token through every linear — the tcgen05 kernels from
+    17 rows on — dense causal attention, bulk cache pack, short-conv prefill), then greedy decode
     over the cache the prefill left: the first token, the last prompt row's hidden state and the
     following decode tokens equal the oracle's dense-prefill route."""
     from llmopt_b200.decode_engine import DecodeEngine
