@@ -79,7 +79,16 @@ __device__ __forceinline__ float exp2_fast(float x) {
 constexpr int kQueryTile = 64;
 constexpr float kLowest = -1.0e30f;
 
-// KT keys per tile: 64 for D = 64, 32 for D = 128 (static shared memory stays under 48 KiB).
+// 16-byte asynchronous copy global -> shared; `bytes` = 0 writes zeros (rows past the end)
+__device__ __forceinline__ void copy_async_16(void* shared_target, const void* source, uint32_t bytes) {
+  const uint32_t address = (uint32_t)__cvta_generic_to_shared(shared_target);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(address), "l"(source), "r"(bytes) : "memory");
+}
+
+// 64 query rows per CTA (16 per warp), KT keys per tile.  K and V tiles are double-buffered in dynamic
+// shared memory and fetched with cp.async one tile ahead of the arithmetic; a tile every key of which
+// every query row of the warp may see (no mask, inside the causal triangle, inside k_len) skips the
+// per-element visibility test.
 template <int D, int KT>
 __global__ void __launch_bounds__(128) dense_attention_mma_kernel(const __half* __restrict__ query,
                                                                   const __half* __restrict__ key,
@@ -88,13 +97,41 @@ __global__ void __launch_bounds__(128) dense_attention_mma_kernel(const __half* 
                                                                   __half* __restrict__ output, DenseParams p) {
   grid_chain_prologue();
   constexpr int kStride = D + 8;  // halves per shared row: 16 bytes of padding against bank conflicts
-  __shared__ __align__(16) __half q_tile[kQueryTile][kStride];
-  __shared__ __align__(16) __half k_tile[KT][kStride];
-  __shared__ __align__(16) __half v_tile[KT][kStride];
-  const uint32_t q0 = blockIdx.x * kQueryTile, head = blockIdx.y, batch = blockIdx.z;
+  extern __shared__ __align__(16) unsigned char dense_shared[];
+  typedef __half Row[kStride];
+  Row* q_tile = reinterpret_cast<Row*>(dense_shared);                 // [kQueryTile]
+  Row* k_tiles = q_tile + kQueryTile;                                  // [2][KT]
+  Row* v_tiles = k_tiles + 2 * KT;                                     // [2][KT]
+  // the last query tiles see the most keys under a causal mask: they are scheduled first
+  const uint32_t q0 = (gridDim.x - 1u - blockIdx.x) * kQueryTile, head = blockIdx.y, batch = blockIdx.z;
   const uint32_t kv_head = head / (p.heads / p.kv_heads);
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, r = lane >> 2, c = lane & 3u;
   constexpr int kChunks = D / 8;  // 16-byte chunks per row
+
+  // keys beyond the last visible one of this query tile are never touched
+  uint32_t key_end = p.k_len;
+  if (p.causal) {
+    const uint32_t last_query = min(q0 + kQueryTile, p.q_len) - 1u;
+    key_end = min(p.k_len, last_query + p.past_length + 1u);
+  }
+  const uint32_t tiles = (key_end + KT - 1) / KT;
+  auto fetch_tile = [&](uint32_t tile) {
+    if (tile < tiles) {
+      const uint32_t k0 = tile * KT;
+      Row* k_tile = k_tiles + (tile & 1u) * KT;
+      Row* v_tile = v_tiles + (tile & 1u) * KT;
+      for (uint32_t index = threadIdx.x; index < KT * kChunks; index += 128) {
+        const uint32_t row = index / kChunks, chunk = index % kChunks;
+        const bool present = k0 + row < p.k_len;
+        const uint32_t ki = present ? k0 + row : 0u;
+        copy_async_16(&k_tile[row][chunk * 8],
+                      key + (((size_t)batch * p.kv_heads + kv_head) * p.k_len + ki) * D + chunk * 8, present ? 16u : 0u);
+        copy_async_16(&v_tile[row][chunk * 8], value + value_index(p, batch, kv_head, ki) + chunk * 8, present ? 16u : 0u);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch_tile(0);
 
   for (uint32_t index = threadIdx.x; index < kQueryTile * kChunks; index += 128) {
     const uint32_t row = index / kChunks, chunk = index % kChunks;
@@ -119,25 +156,13 @@ __global__ void __launch_bounds__(128) dense_attention_mma_kernel(const __half* 
 #pragma unroll
     for (int j = 0; j < 4; ++j) out[t][j] = 0.0f;
 
-  // keys beyond the last visible one of this query tile are never touched
-  uint32_t key_end = p.k_len;
-  if (p.causal) {
-    const uint32_t last_query = min(q0 + kQueryTile, p.q_len) - 1u;
-    key_end = min(p.k_len, last_query + p.past_length + 1u);
-  }
-  for (uint32_t k0 = 0; k0 < key_end; k0 += KT) {
-    __syncthreads();  // the previous tile has been consumed
-    for (uint32_t index = threadIdx.x; index < KT * kChunks; index += 128) {
-      const uint32_t row = index / kChunks, chunk = index % kChunks;
-      uint4 key_data = make_uint4(0u, 0u, 0u, 0u), value_data = key_data;
-      if (k0 + row < p.k_len) {
-        key_data = *reinterpret_cast<const uint4*>(key + (((size_t)batch * p.kv_heads + kv_head) * p.k_len + k0 + row) * D + chunk * 8);
-        value_data = *reinterpret_cast<const uint4*>(value + value_index(p, batch, kv_head, k0 + row) + chunk * 8);
-      }
-      *reinterpret_cast<uint4*>(&k_tile[row][chunk * 8]) = key_data;
-      *reinterpret_cast<uint4*>(&v_tile[row][chunk * 8]) = value_data;
-    }
+  for (uint32_t tile = 0; tile < tiles; ++tile) {
+    const uint32_t k0 = tile * KT;
+    fetch_tile(tile + 1);  // into the other buffer, which the previous iteration's last barrier released
+    asm volatile("cp.async.wait_group 1;" ::: "memory");  // this tile has landed (the next one may be in flight)
     __syncthreads();
+    Row* k_tile = k_tiles + (tile & 1u) * KT;
+    Row* v_tile = v_tiles + (tile & 1u) * KT;
 
     // S[16 x KT] = Q K^T: n-tile j covers keys 8j .. 8j+7
     float score[KT / 8][4];
@@ -157,15 +182,27 @@ __global__ void __launch_bounds__(128) dense_attention_mma_kernel(const __half* 
 
     // visibility and the tile maximum of the two rows
     float tile_max[2] = {kLowest, kLowest};
+    const bool all_visible = mask == nullptr && k0 + KT <= p.k_len && q0 + warp * 16 + 15u < p.q_len &&
+                             (!p.causal || k0 + KT - 1u <= q0 + warp * 16 + p.past_length);
+    if (all_visible) {
 #pragma unroll
-    for (int j = 0; j < KT / 8; ++j)
+      for (int j = 0; j < KT / 8; ++j)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t qi = (i & 2) ? row_high : row_low, ki = k0 + 8 * j + 2 * c + (i & 1);
-        const bool visible = qi < p.q_len && ki < p.k_len && key_allowed(p, mask, batch, head, qi, ki);
-        score[j][i] = visible ? score[j][i] * score_scale : -INFINITY;
-        tile_max[i >> 1] = fmaxf(tile_max[i >> 1], score[j][i]);
-      }
+        for (int i = 0; i < 4; ++i) {
+          score[j][i] *= score_scale;
+          tile_max[i >> 1] = fmaxf(tile_max[i >> 1], score[j][i]);
+        }
+    } else {
+#pragma unroll
+      for (int j = 0; j < KT / 8; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t qi = (i & 2) ? row_high : row_low, ki = k0 + 8 * j + 2 * c + (i & 1);
+          const bool visible = qi < p.q_len && ki < p.k_len && key_allowed(p, mask, batch, head, qi, ki);
+          score[j][i] = visible ? score[j][i] * score_scale : -INFINITY;
+          tile_max[i >> 1] = fmaxf(tile_max[i >> 1], score[j][i]);
+        }
+    }
     float rescale[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -208,7 +245,9 @@ __global__ void __launch_bounds__(128) dense_attention_mma_kernel(const __half* 
         mma_16816(out[2 * t], p_frag[s], b[0], b[1]);
         mma_16816(out[2 * t + 1], p_frag[s], b[2], b[3]);
       }
+    __syncthreads();  // every warp is done with this buffer before the next iteration's fetch refills it
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
 
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -307,11 +346,16 @@ int launch_attention_dense(const KernelArgs& args) {
   const bool aligned = (((uintptr_t)args.buffers[0] | (uintptr_t)args.buffers[1] | (uintptr_t)args.buffers[2]) & 15u) == 0 &&
                        ((uintptr_t)args.buffers[4] & 3u) == 0;
   const dim3 grid((p.q_len + kQueryTile - 1) / kQueryTile, p.heads, p.batches);
+  auto shared_bytes = [](uint32_t dim, uint32_t keys) { return (size_t)(kQueryTile + 4 * keys) * (dim + 8) * sizeof(__half); };
   if (aligned && p.dim == 64) {
-    launch_kernel(args, dense_attention_mma_kernel<64, 64>, grid, dim3(128), 0, (const __half*)args.buffers[0],
+    auto kernel = dense_attention_mma_kernel<64, 64>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared_bytes(64, 64));
+    launch_kernel(args, kernel, grid, dim3(128), shared_bytes(64, 64), (const __half*)args.buffers[0],
                   (const __half*)args.buffers[1], (const __half*)args.buffers[2], mask, (__half*)args.buffers[4], p);
   } else if (aligned && p.dim == 128) {
-    launch_kernel(args, dense_attention_mma_kernel<128, 32>, grid, dim3(128), 0, (const __half*)args.buffers[0],
+    auto kernel = dense_attention_mma_kernel<128, 64>;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared_bytes(128, 64));
+    launch_kernel(args, kernel, grid, dim3(128), shared_bytes(128, 64), (const __half*)args.buffers[0],
                   (const __half*)args.buffers[1], (const __half*)args.buffers[2], mask, (__half*)args.buffers[4], p);
   } else {
     const size_t rows = (size_t)p.batches * p.heads * p.q_len;
