@@ -44,6 +44,8 @@ struct KernelArgs {
   const char* name;
   std::string* error;
   const FusedNorm* fused_norm;  // null unless the plan builder folded a norm into this dispatch
+  // null unless the plan builder handed the rotary + cache pack of the new token to this (attention) dispatch
+  const struct RotaryPackFusion* rotary_fusion;
 };
 
 typedef int (*Launcher)(const KernelArgs&);

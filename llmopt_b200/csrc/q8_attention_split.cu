@@ -32,6 +32,7 @@
 // paged_merge_kernel merges the records of all splits and the current token.
 #include <cstdlib>
 #include "q8_attention.cuh"
+#include "q8_codec.cuh"
 
 namespace llmopt {
 uint32_t* context_device_error(Context* ctx);
@@ -126,12 +127,18 @@ struct SplitShape {
   static constexpr int kRingBytes = kWarps * kStages * kStageBytes;
 };
 
-template <int D, int GROUP, int CP>
+// FUSED: the launch also does the rotary embedding and the cache pack of the new token (`fusion`), which
+// otherwise are a kernel of their own right before this one.  Every CTA rotates the query rows of its KV
+// group in registers on the way into the MMA fragments (same rounding sequence as rotary_element); the
+// writes of the rotated query / key rows (the merge kernel reads them) and the Q8 pack of the new key and
+// value rows are warp tasks handed out over the CTAs of a (batch, KV head), done while the first tiles are
+// in flight.
+template <int D, int GROUP, int CP, bool FUSED = false>
 __global__ void __launch_bounds__(kWarps * 32, kResidentCtas)
 paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__ pool,
                    const uint32_t* __restrict__ slots, float* __restrict__ scratch, PagedParams p,
                    uint32_t slot_batch_stride, uint32_t splits, const uint32_t* __restrict__ past_cell,
-                   uint32_t pool_tokens, uint32_t* error_word) {
+                   uint32_t pool_tokens, uint32_t* error_word, RotaryPackFusion fusion) {
   grid_chain_prologue();
   using Shape = SplitShape<D, CP>;
   constexpr int kSteps = D / 16;  // k-steps of QK^T, m-tiles of PV
@@ -171,7 +178,7 @@ paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__
 
   // Query fragments: B operand, n = head r of this KV group, k = dims 16 s + 4 c .. + 3.
   uint32_t q_frag[kSteps][2];
-  {
+  if (!FUSED) {
     const uint32_t head = kv_head * heads_per_kv + r;
     const __half* source = query + ((size_t)batch * p.query_heads + head) * D;  // q_len == 1
 #pragma unroll
@@ -369,6 +376,62 @@ paged_split_kernel(const __half* __restrict__ query, const uint8_t* __restrict__
 #pragma unroll 1
   for (uint32_t index = 0; index < (uint32_t)(kStages - 1); ++index) issue(index, index);
   uint32_t consume_stage = 0, issue_stage = kStages - 1;
+  if (FUSED) {
+    // this lane's query dims 16 s + 4 c + j pair with 16 (s + kSteps / 2) + 4 c + j: both halves of a
+    // rotation sit in the same lane
+    const uint32_t head = kv_head * heads_per_kv + r;
+    const size_t row = ((size_t)batch * p.query_heads + head) * D;
+    const size_t trig = (size_t)(fusion.rotary.trig_batches == 1 ? 0 : batch) * D;
+#pragma unroll
+    for (int s = 0; s < kSteps; ++s) {
+      q_frag[s][0] = 0u;
+      q_frag[s][1] = 0u;
+    }
+    if (r < heads_per_kv) {
+      const __half* raw = fusion.q_input + row;
+      const __half* cosine = fusion.cosine + trig;
+      const __half* sine = fusion.sine + trig;
+      // the four halves at dims `first` .. + 3 as two 32-bit loads
+      auto four = [](const __half* base, uint32_t first, __half (&out)[4]) {
+        const uint32_t low = *reinterpret_cast<const uint32_t*>(base + first);
+        const uint32_t high = *reinterpret_cast<const uint32_t*>(base + first + 2);
+        out[0] = __ushort_as_half((unsigned short)(low & 0xffffu));
+        out[1] = __ushort_as_half((unsigned short)(low >> 16));
+        out[2] = __ushort_as_half((unsigned short)(high & 0xffffu));
+        out[3] = __ushort_as_half((unsigned short)(high >> 16));
+      };
+      auto pack = [](const __half (&v)[4], uint32_t (&words)[2]) {
+        words[0] = (uint32_t)__half_as_ushort(v[0]) | ((uint32_t)__half_as_ushort(v[1]) << 16);
+        words[1] = (uint32_t)__half_as_ushort(v[2]) | ((uint32_t)__half_as_ushort(v[3]) << 16);
+      };
+#pragma unroll
+      for (int s = 0; s < kSteps / 2; ++s) {
+        const uint32_t low_dim = 16 * s + 4 * c, high_dim = low_dim + D / 2;
+        __half x_low[4], x_high[4], cos_low[4], cos_high[4], sin_low[4], sin_high[4], out_low[4], out_high[4];
+        four(raw, low_dim, x_low);
+        four(raw, high_dim, x_high);
+        four(cosine, low_dim, cos_low);
+        four(cosine, high_dim, cos_high);
+        four(sine, low_dim, sin_low);
+        four(sine, high_dim, sin_high);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // rotary_element for col < D / 2 and for col >= D / 2
+          out_low[j] = __hadd_rn(__hmul_rn(x_low[j], cos_low[j]), __hmul_rn(__hneg(x_high[j]), sin_low[j]));
+          out_high[j] = __hadd_rn(__hmul_rn(x_high[j], cos_high[j]), __hmul_rn(x_low[j], sin_high[j]));
+        }
+        pack(out_low, q_frag[s]);
+        pack(out_high, q_frag[s + kSteps / 2]);
+      }
+    }
+    // warp tasks of this (batch, KV head): its query rows, its key row, its value row
+    const uint32_t tasks = heads_per_kv + 2u;
+    for (uint32_t task = split + warp * splits; task < tasks; task += splits * kWarps) {
+      if (task < heads_per_kv)
+        rotary_pack_row(fusion, 0u, batch, kv_head * heads_per_kv + task, lane);
+      else
+        rotary_pack_row(fusion, task == heads_per_kv ? 1u : 2u, batch, kv_head, lane);
+    }
+  }
 #pragma unroll 1
   for (uint32_t index = 0; index < my_tiles; ++index) {
     issue(index + kStages - 1, issue_stage);
@@ -514,16 +577,17 @@ paged_merge_kernel(const __half* __restrict__ query, const __half* __restrict__ 
 template <int D, int GROUP, int CP>
 int launch_split_copy(const KernelArgs& args, const PagedParams& p, uint32_t slot_batch_stride, float* scratch,
                       uint32_t splits, uint32_t pool_tokens) {
-  auto kernel = paged_split_kernel<D, GROUP, CP>;
+  auto kernel = args.rotary_fusion ? paged_split_kernel<D, GROUP, CP, true> : paged_split_kernel<D, GROUP, CP, false>;
   constexpr int ring_bytes = SplitShape<D, CP>::kRingBytes;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ring_bytes) != cudaSuccess) {
     cudaGetLastError();
     return fail(args, "paged attention: the device cannot give one CTA its tile ring");
   }
+  const RotaryPackFusion fusion = args.rotary_fusion ? *args.rotary_fusion : RotaryPackFusion{};
   launch_kernel(args, kernel, dim3(splits, p.kv_heads, p.batches), dim3(kWarps * 32), ring_bytes,
       (const __half*)args.buffers[0], (const uint8_t*)args.buffers[3], (const uint32_t*)args.buffers[4], scratch, p,
       slot_batch_stride, splits, args.past_tokens_cell, pool_tokens,
-      args.ctx ? context_device_error(args.ctx) : nullptr);
+      args.ctx ? context_device_error(args.ctx) : nullptr, fusion);
   return check_launch(args);
 }
 

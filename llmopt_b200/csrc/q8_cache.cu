@@ -10,53 +10,20 @@
 // One warp owns one quantisation group (the reference's *_simd mapping); lanes
 // stride the group so any group size works.  HBM-bound and tiny: 2 bytes read,
 // 1 + 2/G written per element.
-#include "common.cuh"
+#include "q8_codec.cuh"
 
 namespace llmopt {
 uint32_t* context_device_error(Context* ctx);
 namespace {
 
-// Token rows the pool buffer holds; slot values at or beyond it are refused on the device
-// (the access is skipped and the context's error word raised).
-struct PoolBound {
-  uint32_t tokens;
-  uint32_t* error_word;
-};
-__device__ __forceinline__ bool slot_in_pool(uint32_t slot, const PoolBound& bound, uint32_t lane) {
-  if (slot < bound.tokens) return true;
-  if (lane == 0 && bound.error_word) atomicExch(bound.error_word, 1u);
-  return false;
-}
-
 struct AttentionCacheParams {  // lib/metal_cache_source.ml:9-20
   uint32_t items, segment_offset, heads, head_dim, group_size, token_elements, token_groups,
       token_stride, source_items, source_offset;
-};
-struct AttentionCachePairParams {  // lib/metal_cache_source.ml:22-34
-  uint32_t items, key_segment_offset, value_segment_offset, heads, head_dim, group_size,
-      token_elements, token_groups, token_stride, source_items, source_offset;
 };
 struct CheckpointCacheParams {  // lib/metal_cache_source.ml:36-44
   uint32_t checkpoint, layer, layer_elements, group_size, checkpoint_elements, checkpoint_groups,
       checkpoint_stride;
 };
-
-__device__ __forceinline__ void quantize_group(const __half* __restrict__ source, uint32_t group_size,
-                                               int8_t* __restrict__ values, __half* __restrict__ scale_out,
-                                               uint32_t lane) {
-  float maximum = 0.0f;
-  for (uint32_t index = lane; index < group_size; index += 32)
-    maximum = fmaxf(maximum, fabsf(__half2float(source[index])));
-  maximum = warp_max(maximum);
-  const __half stored = __float2half_rn(maximum == 0.0f ? 1.0f : __fdiv_rn(maximum, 127.0f));
-  const float scale = __half2float(stored);
-  for (uint32_t index = lane; index < group_size; index += 32) {
-    int quantized = (int)rintf(__fdiv_rn(__half2float(source[index]), scale));
-    quantized = max(-127, min(127, quantized));
-    values[index] = (int8_t)quantized;
-  }
-  if (lane == 0) *scale_out = stored;
-}
 
 __global__ void pack_attention_kernel(const __half* __restrict__ source, const uint32_t* __restrict__ slots,
                                       uint8_t* __restrict__ pool, AttentionCacheParams p, PoolBound bound) {
@@ -108,57 +75,22 @@ __global__ void pack_attention_pair_kernel(const __half* __restrict__ key_source
                  scales + p.value_segment_offset / p.group_size + local_group, lane);
 }
 
-struct RotaryQkParams {  // lib/metal_normalization_source.ml:760-763
-  uint32_t batches, tokens, q_heads, k_heads, width, half_dimension, trig_batches;
-};
-
 // One decode token per sequence: the rotary embedding of Q and K (llmopt_rotary_qk_f16_simd_h64,
 // lib/metal_normalization_source.ml:765-802) and the Q8 pack of the rotated K row and the V row
 // into the new cache slot (llmopt_cache_pack_attention_q8_pair_simd) as one launch; a prebaked
 // plan takes it when the two records are adjacent and the pack reads what the rotary wrote.
-// One warp per head row; every lane quantises the columns it rotated itself, with the same
-// half-precision operation sequence and the same codec as the two kernels, so all bytes are equal.
-__global__ void rotary_pack_kernel(const __half* __restrict__ q_input, const __half* __restrict__ k_input,
-                                   const __half* __restrict__ v_input, const __half* __restrict__ cosine,
-                                   const __half* __restrict__ sine, __half* __restrict__ q_output, __half* k_output,
-                                   const uint32_t* __restrict__ slots, uint8_t* __restrict__ pool, RotaryQkParams r,
-                                   AttentionCachePairParams c, PoolBound bound) {
+// One warp per head row (rotary_pack_row); every lane quantises the columns it rotated itself, with the
+// same half-precision operation sequence and the same codec as the two kernels, so all bytes are equal.
+__global__ void rotary_pack_kernel(RotaryPackFusion f) {
   grid_chain_prologue();
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const uint32_t q_rows = r.batches * r.q_heads, k_rows = r.batches * r.k_heads;
+  const uint32_t q_rows = f.rotary.batches * f.rotary.q_heads, k_rows = f.rotary.batches * f.rotary.k_heads;
   if (row >= q_rows + 2u * k_rows) return;
-  const bool is_q = row < q_rows, is_v = row >= q_rows + k_rows;
-  const uint32_t local_row = is_q ? row : (is_v ? row - q_rows - k_rows : row - q_rows);
-  const uint32_t heads = is_q ? r.q_heads : r.k_heads;
-  const uint32_t batch = local_row / heads, head = local_row % heads;
-  const size_t base = (size_t)local_row * r.width;  // one token: token-first and head-major rows coincide
-  if (!is_v) {
-    const __half* input = is_q ? q_input : k_input;
-    __half* output = is_q ? q_output : k_output;
-    const size_t trig_base = (size_t)(r.trig_batches == 1 ? 0 : batch) * r.width;
-    for (uint32_t col = lane; col < r.width; col += 32) {
-      const uint32_t rotated_col = col < r.half_dimension ? col + r.half_dimension : col - r.half_dimension;
-      __half rotated = input[base + rotated_col];
-      if (col < r.half_dimension) rotated = __hneg(rotated);
-      const __half direct = __hmul_rn(input[base + col], cosine[trig_base + col]);
-      const __half turned = __hmul_rn(rotated, sine[trig_base + col]);
-      output[base + col] = __hadd_rn(direct, turned);
-    }
-    if (is_q) return;
-    __syncwarp();
-  }
-  const __half* source = is_v ? v_input + base : k_output + base;
-  if (!slot_in_pool(slots[batch], bound, lane)) return;
-  const size_t slot_base = (size_t)slots[batch] * c.token_stride;
-  int8_t* values = reinterpret_cast<int8_t*>(pool + slot_base);
-  __half* scales = reinterpret_cast<__half*>(pool + slot_base + c.token_elements);
-  const uint32_t segment = is_v ? c.value_segment_offset : c.key_segment_offset;
-  for (uint32_t group = 0; group < r.width / c.group_size; ++group) {
-    const uint32_t local = head * r.width + group * c.group_size;
-    quantize_group(source + group * c.group_size, c.group_size, values + segment + local,
-                   scales + (segment + local) / c.group_size, lane);
-  }
+  const uint32_t kind = row < q_rows ? 0u : (row < q_rows + k_rows ? 1u : 2u);
+  const uint32_t local_row = kind == 0 ? row : (kind == 1 ? row - q_rows : row - q_rows - k_rows);
+  const uint32_t heads = kind == 0 ? f.rotary.q_heads : f.rotary.k_heads;
+  rotary_pack_row(f, kind, local_row / heads, local_row % heads, lane);
 }
 
 __global__ void unpack_attention_kernel(const uint8_t* __restrict__ pool, const uint32_t* __restrict__ slots,
@@ -404,35 +336,52 @@ int launch_cache_pack_attention_q8_pair(const KernelArgs& args) {
   return check_launch(args);
 }
 
-// The fused form of a rotary record followed by the pair-pack record of the same token.  Returns -1
-// when the two do not fit it (the caller then runs them one after the other), 0 on success, 1 on a
-// launch failure.  rotary: [q_in, k_in, cosine, sine, q_out, k_out]; pack: [key, value, slots, pool].
-int launch_rotary_pack_fused(const KernelArgs& rotary, const KernelArgs& pack) {
+// The fused form of a rotary record followed by the pair-pack record of the same token, or false when
+// the two do not fit it.  rotary: [q_in, k_in, cosine, sine, q_out, k_out]; pack: [key, value, slots, pool].
+bool make_rotary_pack_fusion(const KernelArgs& rotary, const KernelArgs& pack, RotaryPackFusion* fusion) {
   RotaryQkParams r;
   AttentionCachePairParams c;
   if (rotary.buffer_count != 6 || rotary.param_bytes != sizeof(r) || pack.buffer_count != 4 || !read_params(pack, &c))
-    return -1;
+    return false;
   memcpy(&r, rotary.params, sizeof(r));
-  if (r.tokens != 1 || r.width == 0 || r.half_dimension * 2 > r.width || r.batches == 0 || r.k_heads == 0) return -1;
+  if (r.tokens != 1 || r.width == 0 || r.half_dimension * 2 > r.width || r.batches == 0 || r.k_heads == 0) return false;
   if (pack.buffers[0] != rotary.buffers[5] || c.items != r.batches || c.source_items != c.items || c.source_offset != 0)
-    return -1;
-  if (c.group_size == 0 || r.width % c.group_size != 0 || !valid_geometry(c.head_dim, c.group_size)) return -1;
-  if ((size_t)c.heads * c.head_dim != (size_t)r.k_heads * r.width || (c.heads != 1 && c.items != 1)) return -1;
-  if ((c.key_segment_offset | c.value_segment_offset) % c.group_size != 0) return -1;
+    return false;
+  if (c.group_size == 0 || r.width % c.group_size != 0 || !valid_geometry(c.head_dim, c.group_size)) return false;
+  if ((size_t)c.heads * c.head_dim != (size_t)r.k_heads * r.width || (c.heads != 1 && c.items != 1)) return false;
+  if ((c.key_segment_offset | c.value_segment_offset) % c.group_size != 0) return false;
   if (!segment_in_token(c.key_segment_offset, c.heads, c.head_dim, c.group_size, c.token_elements, c.token_stride) ||
       !segment_in_token(c.value_segment_offset, c.heads, c.head_dim, c.group_size, c.token_elements, c.token_stride))
-    return -1;  // the stand-alone pack launcher reports it
+    return false;  // the stand-alone pack launcher reports it
   const size_t q_bytes = (size_t)r.batches * r.q_heads * r.width * 2, k_bytes = (size_t)r.batches * r.k_heads * r.width * 2;
   const size_t trig_bytes = (size_t)(r.trig_batches == 1 ? 1 : r.batches) * r.width * 2;
   if (rotary.lengths[0] < q_bytes || rotary.lengths[4] < q_bytes || rotary.lengths[1] < k_bytes ||
       rotary.lengths[5] < k_bytes || rotary.lengths[2] < trig_bytes || rotary.lengths[3] < trig_bytes ||
       pack.lengths[1] < k_bytes || pack.lengths[2] < (size_t)c.items * 4)
-    return -1;
-  const uint32_t rows = r.batches * (r.q_heads + 2u * r.k_heads);
-  launch_kernel(rotary, rotary_pack_kernel, dim3((rows + 7) / 8), dim3(256), 0, (const __half*)rotary.buffers[0],
-                (const __half*)rotary.buffers[1], (const __half*)pack.buffers[1], (const __half*)rotary.buffers[2],
-                (const __half*)rotary.buffers[3], (__half*)rotary.buffers[4], (__half*)rotary.buffers[5],
-                (const uint32_t*)pack.buffers[2], (uint8_t*)pack.buffers[3], r, c, pool_bound(pack, 3, c.token_stride));
+    return false;
+  fusion->q_input = (const __half*)rotary.buffers[0];
+  fusion->k_input = (const __half*)rotary.buffers[1];
+  fusion->v_input = (const __half*)pack.buffers[1];
+  fusion->cosine = (const __half*)rotary.buffers[2];
+  fusion->sine = (const __half*)rotary.buffers[3];
+  fusion->q_output = (__half*)rotary.buffers[4];
+  fusion->k_output = (__half*)rotary.buffers[5];
+  fusion->slots = (const uint32_t*)pack.buffers[2];
+  fusion->pool = (uint8_t*)pack.buffers[3];
+  fusion->rotary = r;
+  fusion->cache = c;
+  const PoolBound bound = pool_bound(pack, 3, c.token_stride);
+  fusion->bound = bound;
+  return true;
+}
+
+// Returns -1 when the two records do not fit the fused form (the caller then runs them one after the
+// other), 0 on success, 1 on a launch failure.
+int launch_rotary_pack_fused(const KernelArgs& rotary, const KernelArgs& pack) {
+  RotaryPackFusion fusion;
+  if (!make_rotary_pack_fusion(rotary, pack, &fusion)) return -1;
+  const uint32_t rows = fusion.rotary.batches * (fusion.rotary.q_heads + 2u * fusion.rotary.k_heads);
+  launch_kernel(rotary, rotary_pack_kernel, dim3((rows + 7) / 8), dim3(256), 0, fusion);
   return check_launch(rotary);
 }
 

@@ -22,6 +22,7 @@
 
 #include "../../include/llmopt_cuda.h"
 #include "common.cuh"
+#include "q8_codec.cuh"
 
 namespace llmopt {
 
@@ -65,6 +66,7 @@ int launch_short_conv_prefill(const KernelArgs&);
 template <bool INPUT_F32> int launch_rms_norm(const KernelArgs&);
 int launch_rotary_qk(const KernelArgs&);
 int launch_rotary_pack_fused(const KernelArgs& rotary, const KernelArgs& pack);
+bool paged_attention_takes_rotary_pack(const KernelArgs& attention, const RotaryPackFusion& fusion);
 int launch_embedding_f16(const KernelArgs&);
 int launch_chain_token_id(const KernelArgs&);
 int launch_chain_token_ids(const KernelArgs&);
@@ -581,6 +583,30 @@ static int run_rotary_pack(Context* context, const OwnedRecord& rotary, const Ow
   const int status = launch_rotary_pack_fused(rotary_args, pack_args);
   if (status > 0) return set_error(LLMOPT_CUDA_FAILURE, message);
   return status < 0 ? -1 : LLMOPT_CUDA_OK;
+}
+
+// Plan-capture peephole: rotary record, pair-pack record and the paged attention of the same decode token as
+// ONE attention launch that rotates its query rows itself and hands the rotated rows and the new slot's Q8
+// bytes out as warp tasks.  Returns -1 when the three do not fit that form.
+static int run_rotary_pack_attention(Context* context, const OwnedRecord& rotary, const OwnedRecord& pack,
+                                     const OwnedRecord& attention, const uint32_t* past_cell,
+                                     const uint32_t* checkpoint_cell) {
+  if (rotary.is_copy || pack.is_copy || attention.is_copy || rotary.name != "llmopt_rotary_qk_f16_simd_h64" ||
+      pack.name != "llmopt_cache_pack_attention_q8_pair_simd" ||
+      attention.name.rfind("llmopt_attention_q8_paged_", 0) != 0)
+    return -1;
+  KernelArgs rotary_args = {}, pack_args = {}, attention_args = {};
+  fill_args(context, rotary, nullptr, nullptr, &rotary_args);
+  fill_args(context, pack, nullptr, nullptr, &pack_args);
+  fill_args(context, attention, past_cell, checkpoint_cell, &attention_args);
+  RotaryPackFusion fusion;
+  if (!make_rotary_pack_fusion(rotary_args, pack_args, &fusion) || !paged_attention_takes_rotary_pack(attention_args, fusion))
+    return -1;
+  attention_args.rotary_fusion = &fusion;
+  std::string message;
+  attention_args.error = &message;
+  if (attention.launcher(attention_args) != 0) return set_error(LLMOPT_CUDA_FAILURE, message);
+  return LLMOPT_CUDA_OK;
 }
 
 static int wait_stream(Context* context, const char* what) {
@@ -1212,8 +1238,21 @@ int llmopt_cuda_prebaked_create_bound(llmopt_cuda_library* library, const llmopt
   int failure = LLMOPT_CUDA_OK;
   const bool fold = getenv("LLMOPT_CUDA_FOLD_NORMS") == nullptr || getenv("LLMOPT_CUDA_FOLD_NORMS")[0] != '0';
   const bool fuse_pack = getenv("LLMOPT_CUDA_FUSE_ROTARY_PACK") == nullptr || getenv("LLMOPT_CUDA_FUSE_ROTARY_PACK")[0] != '0';
+  const bool fuse_attention = fuse_pack && (getenv("LLMOPT_CUDA_FUSE_ROTARY_ATTENTION") == nullptr ||
+                                            getenv("LLMOPT_CUDA_FUSE_ROTARY_ATTENTION")[0] != '0');
   for (size_t index = 0; index < plan->records.size(); ++index) {
     FusedNorm fused;
+    if (fuse_attention && index + 2 < plan->records.size()) {
+      const int fused_status =
+          run_rotary_pack_attention(context, plan->records[index], plan->records[index + 1], plan->records[index + 2],
+                                    &plan->cells->past_tokens, &plan->cells->checkpoint);
+      if (fused_status >= 0) {
+        failure = fused_status;
+        index += 2;
+        if (failure != LLMOPT_CUDA_OK) break;
+        continue;
+      }
+    }
     if (fuse_pack && index + 1 < plan->records.size()) {
       const int fused_status = run_rotary_pack(context, plan->records[index], plan->records[index + 1]);
       if (fused_status >= 0) {

@@ -423,6 +423,81 @@ def test_plan_fuses_rotary_and_pair_pack_byte_for_byte(runtime, monkeypatch, bat
     assert not np.array_equal(plain_pool, np.full_like(plain_pool, 0x55))
 
 
+@pytest.mark.parametrize("batch,q_heads,k_heads,dim,group,past", [(1, 32, 8, 128, 64, 700), (3, 8, 2, 128, 64, 90),
+                                                                  (2, 16, 8, 64, 32, 333), (1, 4, 1, 64, 64, 0)])
+def test_plan_hands_rotary_and_pack_to_the_attention_byte_for_byte(runtime, monkeypatch, batch, q_heads, k_heads, dim, group, past):
+    """Rotary record, pair-pack record and the paged attention of the same token run as one attention launch
+    (+ merge): rotated Q and K, the new slot's bytes and scales and the attention output equal what the
+    separate kernels write, bit for bit, and the plan is one kernel shorter."""
+    from llmopt_b200 import dispatch, parameters
+    from llmopt_b200.cuda_native import Batch, Buffer, DispatchItem, Prebaked
+    from llmopt_b200.kv_cache import AttentionLayer, Layout
+
+    rng = np.random.default_rng(80 + batch)
+    layout = Layout([AttentionLayer(k_heads, dim)] * 2, group_size=group)
+    region = layout.attentions[1]
+    capacity = past + 5
+    q = rng.standard_normal((batch, 1, q_heads, dim)).astype(np.float16)
+    k = rng.standard_normal((batch, 1, k_heads, dim)).astype(np.float16)
+    v = rng.standard_normal((batch, k_heads, 1, dim)).astype(np.float16)
+    angle = rng.uniform(0, 6.28, size=(1, 1, dim))
+    cos, sin = np.cos(angle).astype(np.float16), np.sin(angle).astype(np.float16)
+    pool_bytes = random_pool(rng, batch * capacity, layout.bytes_per_token, layout.token_elements, group)
+    slot_table = np.stack([b * capacity + rng.permutation(capacity) for b in range(batch)]).astype(np.uint32)
+    new_slots = np.ascontiguousarray(slot_table[:, past])
+    segment = k_heads * dim
+
+    def run(fuse: bool):
+        monkeypatch.setenv("LLMOPT_CUDA_FUSE_ROTARY_ATTENTION", "1" if fuse else "0")
+        pool = Buffer.of_array(runtime, pool_bytes)
+        q_out = Buffer.of_array(runtime, np.full(q.shape, np.nan, np.float16))
+        k_out = Buffer.of_array(runtime, np.full(k.shape, np.nan, np.float16))
+        v_in = Buffer.of_array(runtime, v)
+        out = Buffer.of_array(runtime, np.full((batch, 1, q_heads, dim), np.nan, np.float16))
+        commands = Batch(runtime)
+        dispatch.dispatch_paged_attention_q8(
+            dispatch.Context(runtime, batch=commands),
+            config=dispatch.PagedAttentionConfig(token_elements=layout.token_elements, key_offset=region.key_offset,
+                                                 value_offset=region.value_offset, group_size=group,
+                                                 token_stride=layout.bytes_per_token, scale=1.0 / np.sqrt(dim)),
+            query=dispatch.Tensor(q_out, (batch, q_heads, 1, dim)), current_key=dispatch.Tensor(k_out, (batch, k_heads, 1, dim)),
+            current_value=dispatch.Tensor(v_in, (batch, k_heads, 1, dim)),
+            pool=dispatch.Tensor(pool, (pool_bytes.size,), "uint8"),
+            slots=dispatch.Tensor(Buffer.of_array(runtime, np.ascontiguousarray(slot_table[:, :max(past, 1)])),
+                                  (batch, past), "uint32"),
+            output=dispatch.Tensor(out, (batch, 1, q_heads, dim)), slot_batch_stride=max(past, 1))
+        attention = commands.pending[0]
+        commands.abort()
+        records = [
+            DispatchItem("llmopt_rotary_qk_f16_simd_h64",
+                         [Buffer.of_array(runtime, q), Buffer.of_array(runtime, k), Buffer.of_array(runtime, cos),
+                          Buffer.of_array(runtime, sin), q_out, k_out],
+                         parameters.rotary_qk(batches=batch, tokens=1, q_heads=q_heads, k_heads=k_heads, width=dim,
+                                              half_dimension=dim // 2, trig_batches=1),
+                         (32 * batch * (q_heads + k_heads), 1, 1), (256, 1, 1)),
+            DispatchItem("llmopt_cache_pack_attention_q8_pair_simd",
+                         [k_out, v_in, Buffer.of_array(runtime, new_slots), pool],
+                         parameters.cache_attention_pair(
+                             items=batch, key_segment_offset=region.key_offset, value_segment_offset=region.value_offset,
+                             heads=1, head_dim=segment, group_size=group, token_elements=layout.token_elements,
+                             token_groups=layout.token_groups, token_stride=layout.bytes_per_token, source_items=batch,
+                             source_offset=0),
+                         (32 * batch * segment // group, 1, 1), (256, 1, 1)),
+            attention,
+        ]
+        plan = Prebaked(runtime, records, None, None)
+        plan.execute(token=0, past_tokens=past)
+        return (plan.kernel_count(), q_out.to_numpy(np.uint16), k_out.to_numpy(np.uint16), pool.to_numpy(np.uint8),
+                out.to_numpy(np.uint16))
+
+    fused, plain = run(True), run(False)
+    assert fused[0] == plain[0] - 1
+    for index, label in ((1, "rotated query"), (2, "rotated key"), (3, "pool"), (4, "attention output")):
+        assert np.array_equal(fused[index], plain[index]), label
+    assert not np.array_equal(plain[3], pool_bytes)
+    assert not np.any(np.isnan(plain[4].view(np.float16)))
+
+
 def test_plan_refuses_tokens_beyond_its_tables(runtime):
     """A replayed plan indexes device tables with the per-token values it is given: a row binding
     reads row ``past_tokens``, paged attention reads ``past_tokens`` slot entries.  Values beyond
