@@ -614,7 +614,10 @@ def small_model_leg(runtime, args, name: str, peaks: dict, batch: int = 1) -> di
     }
 
 
-def time_prefill(engine, runtime, tokens: int) -> dict:
+PREFILL_TOKENS = 512
+
+
+def time_prefill(engine, runtime, tokens: int, group=None) -> dict:
     """Time to first token through the prefill path: the whole prompt in one pass (one row per
     token through every linear, dense causal attention, bulk cache pack), wall clock around the
     call that returns the first generated token; the prompt ids go host to device, the token comes back."""
@@ -624,6 +627,8 @@ def time_prefill(engine, runtime, tokens: int) -> dict:
     runtime.synchronize()
     samples = []
     for _ in range(3):
+        if group is not None:
+            group.barrier()  # every rank has finished the previous prompt's exchanges
         start = time.perf_counter()
         engine.prefill(prompt)
         samples.append((time.perf_counter() - start, *engine.prefill_seconds))
@@ -716,8 +721,10 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         if tensor_parallel_mode:
             from llmopt_b200 import tensor_parallel
 
+            # slots of the first engine also hold the fp32 partial sums of a 512-token prompt (the prefill leg)
+            rows = max(batch, PREFILL_TOKENS if share is None and extra_legs else batch)
             exchange_group = tensor_parallel.ExchangeGroup.create(
-                runtime, rank, world, max(batch * whole_config.hidden * 4, min(batch, 32) * 256 * 8), 7,
+                runtime, rank, world, max(rows * whole_config.hidden * 4, min(batch, 32) * 256 * 8), 7,
                 tensor_parallel.torch_all_gather())
             local_weights = None if share is not None else tensor_parallel.shard_weights(whole_config, whole_weights, rank, world)
             return DecodeEngine(runtime, tensor_parallel.local_config(whole_config, world), local_weights, batch=batch,
@@ -773,8 +780,12 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         result["tokens_match"] = result["tp_check"]["tokens_match"]
     del whole_weights, weights
 
-    if world == 1 and extra_legs:
-        result["prefill"] = time_prefill(engine, runtime, 512)
+    if extra_legs:
+        if group is not None:
+            group.barrier()  # no exchange of the decode legs is in flight on any rank when the prompt starts
+        result["prefill"] = time_prefill(engine, runtime, PREFILL_TOKENS, group)
+        if tensor_parallel_mode:
+            result["prefill"]["parallelism"] = f"tp{world}: the same pass on every rank's heads and columns, o_proj and down as row splits with their fp32 partial sums added over peer memory"
     if world == 1 and config.hidden >= 2048:
         result["prefill_gemm"] = time_prefill_gemm(runtime, peaks, m=2048, k=config.hidden, n=config.intermediate,
                                                    form="dual", weights=engine.layers[:4])

@@ -310,8 +310,10 @@ int launch_tp_exchange_sum(const KernelArgs& args) {
                  "a region is too short or misaligned");
   LLMOPT_REQUIRE(args.lengths[p.ranks + 1] >= elements * 2 && (!p.has_residual || args.lengths[p.ranks] >= elements * 2),
                  "residual or output buffer is too short");
+  // decode rows: a few CTAs; prompt rows (megabytes per rank): enough CTAs to keep NVLink busy
   uint32_t ctas = (uint32_t)((elements + 1023) / 1024);
-  if (ctas > 32) ctas = 32;
+  const uint32_t most = elements > (1u << 18) ? 4u * (uint32_t)context_sm_count(args.ctx) : 32u;
+  if (ctas > most) ctas = most;
   launch_kernel(args, exchange_sum_kernel, dim3(ctas), dim3(256), 0, regions, (const __half*)args.buffers[p.ranks],
                 (__half*)args.buffers[p.ranks + 1], p, context_device_error(args.ctx));
   return check_launch(args);

@@ -447,7 +447,10 @@ w4a16_gemm_tc_batch_kernel(const __grid_constant__ CUtensorMap map_x, const Batc
               value = values[a][i];
               if (p.has_aux) value += __half2float(p.aux[(size_t)batch_row * p.aux_row_stride + column]);
             }
-            p.out[(size_t)batch_row * p.n + column] = __float2half_rn(value);
+            if (EPI != kBatchDualSwiglu && p.out_f32 != nullptr)
+              p.out_f32[(size_t)batch_row * p.n + column] = value;  // unrounded partial sum of a row-split product
+            else
+              p.out[(size_t)batch_row * p.n + column] = __float2half_rn(value);
           }
         }
       };
@@ -697,7 +700,7 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
     return run_batch<kBatchSplitF32, 64>(args, map_x, p);
   }
   if (epilogue != kEpiLinear && epilogue != kEpiDualSwiglu) return -1;
-  if (problem.out_f32 != nullptr) return -1;
+  if (problem.out_f32 != nullptr && (epilogue != kEpiLinear || problem.has_aux)) return -1;
   // the zero-point form: plain products of prompts only (what the shared-memory-operand GEMM covered)
   if (affine && (epilogue != kEpiLinear || !prompt || problem.mat[0].zero == nullptr)) return -1;
   const uint32_t matrices = epilogue == kEpiDualSwiglu ? 2u : 1u;
@@ -730,6 +733,7 @@ int launch_w4a16_gemm_tc_batch(const KernelArgs& args, const GemvProblem& proble
     p.zero[i] = problem.mat[i < matrices ? i : 0].zero;
   }
   p.out = problem.out[0];
+  p.out_f32 = problem.out_f32;
   p.aux = problem.aux0;
   p.aux_row_stride = problem.aux_row_stride;
   p.has_aux = problem.has_aux;

@@ -236,7 +236,7 @@ int launch_w4a16_linear(const KernelArgs& args) {
 int launch_w4a16_linear_partial_f32(const KernelArgs& args) {
   LLMOPT_REQUIRE(args.buffer_count == 4 && args.param_bytes == 12, "expects 4 buffers and 12 parameter bytes");
   const uint32_t m = param_u32(args, 0), n = param_u32(args, 1), k = param_u32(args, 2);
-  LLMOPT_REQUIRE(m > 0 && m <= 32 && n > 0 && k > 0 && k % 64 == 0, "needs 0 < m <= 32, n > 0 and k a multiple of 64");
+  LLMOPT_REQUIRE(m > 0 && n > 0 && k > 0 && k % 64 == 0, "needs m > 0, n > 0 and k a multiple of 64");
   LLMOPT_REQUIRE(args.lengths[0] >= (size_t)m * k * 2, "input buffer is too short");
   LLMOPT_REQUIRE(weight_sizes_ok(args, 1, 2, n, k), "weight or scale buffer is too short");
   LLMOPT_REQUIRE(args.lengths[3] >= (size_t)m * n * 4, "output buffer is too short");
@@ -248,6 +248,12 @@ int launch_w4a16_linear_partial_f32(const KernelArgs& args) {
   problem.mat[0] = {(const uint8_t*)args.buffers[1], (const __half*)args.buffers[2], nullptr, n};
   problem.matrices = 1;
   problem.out_f32 = (float*)args.buffers[3];
+  if (m > 32) {
+    // prompt rows: the tensor-core kernel with the weights in tensor memory writes the fp32 accumulator
+    const int status = launch_w4a16_gemm_tc_batch(args, problem, kEpiLinear, false);
+    LLMOPT_REQUIRE(status >= 0, "more than 32 rows need K a multiple of 64 and 16-byte aligned operands");
+    return status;
+  }
   return launch_w4a16_gemv(args, problem, kEpiLinear, false);
 }
 

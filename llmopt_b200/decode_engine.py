@@ -130,6 +130,7 @@ class DecodeEngine:
 
             exchanges = 2 * len(config.layers) + (batch + 31) // 32
             slot_count, slot_of = plan_slots(exchanges)
+            self._decode_slots = list(slot_of)
             if slot_count > group.slot_count or max(batch * hidden * 4, min(batch, 32) * CANDIDATE_PARTS * 8) > group.slot_bytes:
                 raise ValueError("the exchange group's slots are too few or too small for this plan")
 
@@ -293,14 +294,34 @@ class DecodeEngine:
         continues with ``step(..., past_tokens=len(tokens))``.  A sequence is prefilled from an
         empty cache (position 0)."""
         config, runtime = self.config, self.runtime
-        if self.group is not None:
-            raise NotImplementedError("prefill of a tensor-parallel shard is not built: feed the prompt through step()")
+        group = self.group
         started = time.perf_counter()
         count, hidden, dim = len(tokens), config.hidden, config.head_dim
         if count == 0 or count > self.capacity:
             raise ValueError("the prompt must hold 1 .. capacity tokens")
         if not 0 <= sequence < self.batch:
             raise ValueError("no such sequence")
+        if group is not None:
+            # Tensor-parallel shard: the same pass over this rank's heads and columns; o_proj and down are
+            # row splits whose fp32 partial sums (one slot of rows x hidden floats each) every rank adds in rank
+            # order.  Slots alternate like a decode step's: never the same in adjacent exchanges, the first not
+            # the decode step's last, the last not its first.  No exchange of an earlier step may still be in
+            # flight on any rank when the prompt starts (true once every rank has read that step's token).
+            if count * hidden * 4 > group.slot_bytes:
+                raise ValueError("the exchange slots are smaller than rows x hidden fp32 partial sums of this prompt")
+            if group.slot_count < 3:
+                raise ValueError("a tensor-parallel prompt needs at least three exchange slots")
+            exchanges = 2 * len(config.layers) + 1
+            decode = getattr(self, "_decode_slots", None) or [0]
+            slot_sequence = None
+            for start in range(group.slot_count):
+                candidate = [(start + index) % group.slot_count for index in range(exchanges)]
+                if candidate[0] != decode[-1] and candidate[-1] != decode[0]:
+                    slot_sequence = candidate
+                    break
+            if slot_sequence is None:
+                raise ValueError("no slot order fits between the decode steps' exchanges")
+        exchange = 0
         commands = Batch(runtime)
         context = dispatch.Context(runtime, batch=commands)
         run = lambda name, buffers, params, grid=(256, 1, 1): commands.dispatch(
@@ -349,9 +370,18 @@ class DecodeEngine:
                     run("llmopt_cache_pack_attention_q8_simd", [source.buffer, slots, self.cache.token_pool],
                         parameters.cache_attention(segment_offset=segment, heads=heads, head_dim=width, **common),
                         (dispatch.round_up(groups, 8) * 32, 1, 1))
-                dispatch.dispatch_w4a16_linear(
-                    context, input=dispatch.Tensor(attended.buffer, (count, config.query_heads * dim)),
-                    weight=layer["o"][0], scale=layer["o"][1], output=other, bias=current, bias_row_stride=hidden)
+                if group is None:
+                    dispatch.dispatch_w4a16_linear(
+                        context, input=dispatch.Tensor(attended.buffer, (count, config.query_heads * dim)),
+                        weight=layer["o"][0], scale=layer["o"][1], output=other, bias=current, bias_row_stride=hidden)
+                else:
+                    slot = slot_sequence[exchange]
+                    exchange += 1
+                    run("llmopt_w4a16_linear_partial_f32_g64",
+                        [attended.buffer, layer["o"][0].buffer, layer["o"][1].buffer, group.slot_view(slot, count * hidden * 4)],
+                        parameters.u32s([count, hidden, config.query_heads * dim]))
+                    group.sum_record(commands.dispatch, slot=slot, rows=count, width=hidden, residual=current.buffer,
+                                     output=other.buffer)
                 attention_index += 1
             else:
                 in_proj = self._empty((1, count, 3 * hidden))
@@ -368,18 +398,46 @@ class DecodeEngine:
                     scale=layer["out_proj"][1], output=other, bias=current, bias_row_stride=hidden)
                 conv_index += 1
             current, other = other, current
-            dispatch.dispatch_w4a16_swiglu_ffn_command(
-                context, m=count, n=config.intermediate, k=hidden, epsilon=config.epsilon, activation=current,
-                residual=current, gate_weight=layer["gate"][0], gate_scale=layer["gate"][1], up_weight=layer["up"][0],
-                up_scale=layer["up"][1], down_weight=layer["down"][0], down_scale=layer["down"][1],
-                norm_weight=layer["ffn_norm"], output=other, reference_guards=False)
+            if group is None:
+                dispatch.dispatch_w4a16_swiglu_ffn_command(
+                    context, m=count, n=config.intermediate, k=hidden, epsilon=config.epsilon, activation=current,
+                    residual=current, gate_weight=layer["gate"][0], gate_scale=layer["gate"][1], up_weight=layer["up"][0],
+                    up_scale=layer["up"][1], down_weight=layer["down"][0], down_scale=layer["down"][1],
+                    norm_weight=layer["ffn_norm"], output=other, reference_guards=False)
+            else:
+                # the same three kernels on this rank's intermediate columns; the down projection is the row split
+                ffn = parameters.w4a16_swiglu_ffn(m=count, n=config.intermediate, k=hidden, epsilon=config.epsilon)
+                product = self._empty((count, config.intermediate))
+                run("llmopt_w4a16_swiglu_rms_f16_g64", [current.buffer, layer["ffn_norm"].buffer, normed.buffer], ffn,
+                    (count * 256, 1, 1))
+                run("llmopt_w4a16_dual_swiglu_f16_g64_m4",
+                    [normed.buffer, layer["gate"][0].buffer, layer["gate"][1].buffer, layer["up"][0].buffer,
+                     layer["up"][1].buffer, product.buffer], ffn)
+                slot = slot_sequence[exchange]
+                exchange += 1
+                run("llmopt_w4a16_linear_partial_f32_g64",
+                    [product.buffer, layer["down"][0].buffer, layer["down"][1].buffer, group.slot_view(slot, count * hidden * 4)],
+                    parameters.u32s([count, hidden, config.intermediate]))
+                group.sum_record(commands.dispatch, slot=slot, rows=count, width=hidden, residual=current.buffer,
+                                 output=other.buffer)
             current, other = other, current
         picked = self._empty((1,), "int32", 4)
         last = current.buffer.view((count - 1) * hidden * 2, hidden * 2)
-        dispatch.dispatch_w4a16_lm_head_argmax_command(
-            context, m=1, n=config.vocabulary, k=hidden, epsilon=config.epsilon, input=dispatch.Tensor(last, (1, hidden)),
-            norm_weight=self.final_norm, weight=self.lm_head[0], scale=self.lm_head[1], output=picked,
-            reference_guards=False, two_stage=False)
+        if group is None:
+            dispatch.dispatch_w4a16_lm_head_argmax_command(
+                context, m=1, n=config.vocabulary, k=hidden, epsilon=config.epsilon, input=dispatch.Tensor(last, (1, hidden)),
+                norm_weight=self.final_norm, weight=self.lm_head[0], scale=self.lm_head[1], output=picked,
+                reference_guards=False, two_stage=False)
+        else:
+            from .tensor_parallel import CANDIDATE_PARTS
+
+            slot = slot_sequence[exchange]
+            exchange += 1
+            run("llmopt_w4a16_lm_head_argmax_stage1_f16",
+                [last, self.final_norm.buffer, self.lm_head[0].buffer, self.lm_head[1].buffer,
+                 group.slot_view(slot, CANDIDATE_PARTS * 8)],
+                parameters.w4a16_lm_head_argmax(m=1, n=config.vocabulary, k=hidden, epsilon=config.epsilon), (256 * 256, 1, 1))
+            group.argmax_record(commands.dispatch, slot=slot, rows=1, shard_columns=config.vocabulary, output=picked.buffer)
         self.prefill_kernels = len(commands.pending)
         self.prefill_hidden = current  # rows of the last block's output, one per prompt token
         recorded = time.perf_counter()

@@ -151,6 +151,36 @@ def test_single_rank_plan_through_the_exchange_kernels(runtime):
     assert any(record.name == "llmopt_tp_exchange_sum_f16" for record in engine.records)
 
 
+def test_single_rank_prefill_through_the_exchange_kernels(runtime):
+    """The tensor-parallel prompt pass with a group of one: fp32 partial products of all prompt rows,
+    exchange sums over rows x hidden slots and the exchange argmax, then decode over the cache the prompt left:
+    the oracle's dense-prefill route."""
+    from llmopt_b200.decode_engine import DecodeEngine
+    from llmopt_b200.model import random_weights, tiny_config
+    from llmopt_b200.tensor_parallel import CANDIDATE_PARTS, ExchangeGroup
+    from oracle_model import OracleDecoder
+
+    config = tiny_config(layers=("attention",) * 2, hidden=256, heads=4, kv_heads=2, head_dim=64, intermediate=512,
+                         vocabulary=1024)
+    weights = random_weights(config, seed=4, std=0.05)
+    prompt = np.random.default_rng(9).integers(0, config.vocabulary, size=70).tolist()
+    steps, capacity = 16, len(prompt) + 17
+    group = ExchangeGroup.create(runtime, 0, 1, max(len(prompt) * config.hidden * 4, CANDIDATE_PARTS * 8), 7)
+    engine = DecodeEngine(runtime, config, weights, batch=1, capacity=capacity, group=group)
+    cpu = OracleDecoder(config, weights, capacity)
+    want, _ = cpu.prefill_dense(prompt)
+    got = engine.prefill(prompt)
+    assert got == want
+    for step in range(steps):
+        got = engine.step([want], len(prompt) + step)[0]
+        want_next, logits = cpu.step(want, want_logits=True)
+        if got != want_next:
+            row = logits[0].astype(np.float64)
+            gap = abs(row[want_next] - row[got]) / max(np.max(np.abs(row)), 1e-6)
+            assert gap <= 5e-3, f"step {step}: {got} != {want_next}, logit gap {gap:.3e}"
+        want = want_next
+
+
 def _free_port() -> int:
     with socket.socket() as probe:
         probe.bind(("127.0.0.1", 0))
@@ -180,3 +210,6 @@ def test_two_ranks_on_two_gpus_match_the_single_gpu_tokens(tmp_path):
     assert all(p.returncode == 0 for p in processes), "\n".join(outputs)
     results = [np.load(tmp_path / f"rank{rank}.npz") for rank in range(2)]
     assert results[0]["tokens"].tolist() == results[1]["tokens"].tolist() == results[0]["want"].tolist()
+    # the sharded prompt pass (rows x hidden partial sums exchanged) and the decode after it
+    assert results[0]["prompt_tokens"].tolist() == results[1]["prompt_tokens"].tolist()
+    assert results[0]["prompt_tokens"].tolist() == results[0]["prompt_want"].tolist()

@@ -23,8 +23,9 @@ def main() -> None:
                          vocabulary=1024)
     weights = random_weights(config, seed=4, std=0.05)
     steps, prompt = 24, [5, 77, 301, 12]
+    long_prompt = np.random.default_rng(9).integers(0, config.vocabulary, size=70).tolist()
     group = tensor_parallel.ExchangeGroup.create(
-        runtime, rank, world, max(config.hidden * 4, tensor_parallel.CANDIDATE_PARTS * 8), 7,
+        runtime, rank, world, max(len(long_prompt) * config.hidden * 4, tensor_parallel.CANDIDATE_PARTS * 8), 7,
         tensor_parallel.torch_all_gather())
     engine = DecodeEngine(runtime, tensor_parallel.local_config(config, world),
                           tensor_parallel.shard_weights(config, weights, rank, world), batch=1,
@@ -46,7 +47,26 @@ def main() -> None:
         for _ in range(steps):
             want.append(reference)
             reference, _ = cpu.step(reference)
-    np.savez(os.environ["TP_OUT"], tokens=np.array(tokens), want=np.array(want))
+    # second part: the prompt in one sharded pass, then decode over the cache it left
+    dist.barrier()  # no exchange of the stepped part is in flight on any rank
+    second = DecodeEngine(runtime, tensor_parallel.local_config(config, world),
+                          tensor_parallel.shard_weights(config, weights, rank, world), batch=1,
+                          capacity=len(long_prompt) + steps + 1, group=group)
+    token = second.prefill(long_prompt)
+    prompt_tokens = [token]
+    for step in range(steps):
+        token = second.step([token], len(long_prompt) + step)[0]
+        prompt_tokens.append(token)
+    prompt_want = []
+    if rank == 0:
+        cpu = OracleDecoder(config, weights, len(long_prompt) + steps + 1)
+        reference, _ = cpu.prefill_dense(long_prompt)
+        prompt_want.append(reference)
+        for _ in range(steps):
+            reference, _ = cpu.step(reference)
+            prompt_want.append(reference)
+    np.savez(os.environ["TP_OUT"], tokens=np.array(tokens), want=np.array(want), prompt_tokens=np.array(prompt_tokens),
+             prompt_want=np.array(prompt_want))
     dist.barrier()  # no rank unmaps its region while a peer may still read it
     runtime.synchronize()
     dist.destroy_process_group()
