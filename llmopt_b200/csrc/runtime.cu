@@ -42,6 +42,8 @@ int launch_w4a16_linear_partial_f32(const KernelArgs&);
 int launch_tp_exchange_sum(const KernelArgs&);
 int launch_tp_exchange_argmax(const KernelArgs&);
 int launch_tp_exchange_sum_norm(const KernelArgs&);
+int launch_tp_exchange_reduce_rows(const KernelArgs&);
+int launch_tp_exchange_gather_rows(const KernelArgs&);
 int launch_attention_dense(const KernelArgs&);
 int launch_q4_0_linear(const KernelArgs&);
 int launch_q4_0_gated_linear(const KernelArgs&);
@@ -277,6 +279,8 @@ static void register_kernels(llmopt_cuda_library* library) {
   add("llmopt_tp_exchange_sum_f16", launch_tp_exchange_sum);
   add("llmopt_tp_exchange_argmax", launch_tp_exchange_argmax);
   add("llmopt_tp_exchange_sum_rms_f16", launch_tp_exchange_sum_norm);
+  add("llmopt_tp_exchange_reduce_rows_f16", launch_tp_exchange_reduce_rows);
+  add("llmopt_tp_exchange_gather_rows_f16", launch_tp_exchange_gather_rows);
   add("llmopt_w4a16_qkv_linear_f16_g64", launch_w4a16_qkv_linear);
   add("llmopt_w4a16_qkv_linear_f16_g64_m4", launch_w4a16_qkv_linear);
   add("llmopt_w4a16_qkv_linear_f16_g64_m8", launch_w4a16_qkv_linear);

@@ -18,6 +18,8 @@
 // A wait that runs out raises the context's error word; the kernel returns without output.
 #include <float.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace llmopt {
@@ -133,6 +135,88 @@ __global__ void __launch_bounds__(256) exchange_sum_kernel(Regions regions, cons
       __half2* target = reinterpret_cast<__half2*>(output + index);
       target[0] = __floats2half2_rn(sum.x, sum.y);
       target[1] = __floats2half2_rn(sum.z, sum.w);
+    }
+  }
+  complete_exchange(regions.base[p.rank], epoch != 0u ? epoch : *reinterpret_cast<volatile uint32_t*>(regions.base[p.rank]) + 1u);
+}
+
+struct RowsParams {
+  uint32_t ranks, rank, rows, width, slot_offset, has_residual, slice_offset;
+};
+__device__ __forceinline__ void rows_of_rank(const RowsParams& p, uint32_t rank, uint32_t& first, uint32_t& last) {
+  const uint32_t share = (p.rows + p.ranks - 1u) / p.ranks;
+  first = min(rank * share, p.rows);
+  last = min(first + share, p.rows);
+}
+
+// Prompt rows (many rows per exchange): the sum is a reduce-scatter followed by an all-gather, so that a rank
+// reads every partial once for ITS rows only instead of all rows of all ranks.
+// Step 1: this rank's share of the rows = half(residual + sum over ranks, in rank order, of the fp32 partials);
+// written to `output` and, for the peers, into this rank's own region at `slice_offset` (fp16, same row layout).
+__global__ void __launch_bounds__(256) exchange_reduce_rows_kernel(Regions regions, const __half* __restrict__ residual,
+                                                                   __half* __restrict__ output, RowsParams p,
+                                                                   uint32_t* error_word) {
+  grid_chain_prologue();
+  const uint32_t epoch = announce_and_wait(regions, p.ranks, p.rank, error_word);
+  if (epoch != 0u) {
+    uint32_t first, last;
+    rows_of_rank(p, p.rank, first, last);
+    __half* slice = reinterpret_cast<__half*>(regions.base[p.rank] + p.slice_offset);
+    const uint32_t begin = first * p.width, end = last * p.width;
+    for (uint32_t index = begin + (blockIdx.x * 256u + threadIdx.x) * 4u; index < end; index += gridDim.x * 1024u) {
+      float4 parts[kMaxRanks];
+#pragma unroll
+      for (uint32_t r = 0; r < kMaxRanks; ++r)
+        if (r < p.ranks)
+          parts[r] = *reinterpret_cast<const float4*>(regions.base[r] + p.slot_offset + (size_t)index * 4u);
+      float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+      for (uint32_t r = 0; r < kMaxRanks; ++r)
+        if (r < p.ranks) {
+          sum.x += parts[r].x;
+          sum.y += parts[r].y;
+          sum.z += parts[r].z;
+          sum.w += parts[r].w;
+        }
+      if (p.has_residual) {
+        const __half2* add = reinterpret_cast<const __half2*>(residual + index);
+        const float2 low = __half22float2(add[0]), high = __half22float2(add[1]);
+        sum.x += low.x;
+        sum.y += low.y;
+        sum.z += high.x;
+        sum.w += high.y;
+      }
+      const __half2 low = __floats2half2_rn(sum.x, sum.y), high = __floats2half2_rn(sum.z, sum.w);
+      uint2 packed;
+      packed.x = *reinterpret_cast<const uint32_t*>(&low);
+      packed.y = *reinterpret_cast<const uint32_t*>(&high);
+      *reinterpret_cast<uint2*>(output + index) = packed;
+      *reinterpret_cast<uint2*>(slice + index) = packed;
+    }
+  }
+  complete_exchange(regions.base[p.rank], epoch != 0u ? epoch : *reinterpret_cast<volatile uint32_t*>(regions.base[p.rank]) + 1u);
+}
+
+// Step 2 (its own exchange: the announcement says "my share is written"): the other ranks' shares of the rows,
+// copied from their regions into `output`.
+__global__ void __launch_bounds__(256) exchange_gather_rows_kernel(Regions regions, __half* __restrict__ output,
+                                                                   RowsParams p, uint32_t* error_word) {
+  grid_chain_prologue();
+  const uint32_t epoch = announce_and_wait(regions, p.ranks, p.rank, error_word);
+  if (epoch != 0u) {
+    for (uint32_t r = 0; r < p.ranks; ++r) {
+      if (r == p.rank) continue;
+      uint32_t first, last;
+      rows_of_rank(p, r, first, last);
+      const __half* slice = reinterpret_cast<const __half*>(regions.base[r] + p.slice_offset);
+      const uint32_t begin = first * p.width, end = last * p.width;
+      for (uint32_t index = begin + (blockIdx.x * 256u + threadIdx.x) * 8u; index < end; index += gridDim.x * 2048u) {
+        if (index + 8u <= end) {
+          *reinterpret_cast<uint4*>(output + index) = *reinterpret_cast<const uint4*>(slice + index);
+        } else {
+          for (uint32_t i = index; i < end; ++i) output[i] = slice[i];
+        }
+      }
     }
   }
   complete_exchange(regions.base[p.rank], epoch != 0u ? epoch : *reinterpret_cast<volatile uint32_t*>(regions.base[p.rank]) + 1u);
@@ -316,6 +400,61 @@ int launch_tp_exchange_sum(const KernelArgs& args) {
   if (ctas > most) ctas = most;
   launch_kernel(args, exchange_sum_kernel, dim3(ctas), dim3(256), 0, regions, (const __half*)args.buffers[p.ranks],
                 (__half*)args.buffers[p.ranks + 1], p, context_device_error(args.ctx));
+  return check_launch(args);
+}
+
+// Prompt rows, step 1.  Buffers [region_0 .. region_{ranks-1}, residual, output]; params u32 {ranks, rank, rows,
+// width, slot_offset (fp32 partials), has_residual, slice_offset (fp16 shares, a different slot)}.
+int launch_tp_exchange_reduce_rows(const KernelArgs& args) {
+  RowsParams p;
+  LLMOPT_REQUIRE(args.param_bytes == sizeof(p), "expects 28 parameter bytes");
+  memcpy(&p, args.params, sizeof(p));
+  LLMOPT_REQUIRE(p.ranks >= 1 && p.ranks <= kMaxRanks && p.rank < p.ranks, "needs 1 <= ranks <= 8 and rank < ranks");
+  LLMOPT_REQUIRE((uint32_t)args.buffer_count == p.ranks + 2, "expects one region per rank, a residual and an output");
+  LLMOPT_REQUIRE(p.rows > 0 && p.width > 0 && p.width % 8 == 0 && p.slot_offset >= 256 && p.slot_offset % 16 == 0 &&
+                     p.slice_offset >= 256 && p.slice_offset % 16 == 0,
+                 "needs rows > 0, width a multiple of 8 and 16-byte aligned slots behind the header");
+  const size_t elements = (size_t)p.rows * p.width;
+  const bool apart = (size_t)p.slice_offset >= (size_t)p.slot_offset + elements * 4 ||
+                     (size_t)p.slot_offset >= (size_t)p.slice_offset + elements * 2;
+  LLMOPT_REQUIRE(apart, "the fp32 partials and the fp16 shares must be different slots");
+  Regions regions;
+  const size_t needed = std::max((size_t)p.slot_offset + elements * 4, (size_t)p.slice_offset + elements * 2);
+  LLMOPT_REQUIRE(collect_regions(args, p.ranks, needed, &regions), "a region is too short or misaligned");
+  LLMOPT_REQUIRE(args.lengths[p.ranks + 1] >= elements * 2 && (!p.has_residual || args.lengths[p.ranks] >= elements * 2),
+                 "residual or output buffer is too short");
+  const size_t share = ((size_t)(p.rows + p.ranks - 1) / p.ranks) * p.width;
+  uint32_t ctas = (uint32_t)((share + 1023) / 1024);
+  const uint32_t most = 4u * (uint32_t)context_sm_count(args.ctx);
+  if (ctas > most) ctas = most;
+  if (ctas == 0) ctas = 1;
+  launch_kernel(args, exchange_reduce_rows_kernel, dim3(ctas), dim3(256), 0, regions, (const __half*)args.buffers[p.ranks],
+                (__half*)args.buffers[p.ranks + 1], p, context_device_error(args.ctx));
+  return check_launch(args);
+}
+
+// Prompt rows, step 2.  Buffers [region_0 .. region_{ranks-1}, output]; the same 28 parameter bytes.
+int launch_tp_exchange_gather_rows(const KernelArgs& args) {
+  RowsParams p;
+  LLMOPT_REQUIRE(args.param_bytes == sizeof(p), "expects 28 parameter bytes");
+  memcpy(&p, args.params, sizeof(p));
+  LLMOPT_REQUIRE(p.ranks >= 1 && p.ranks <= kMaxRanks && p.rank < p.ranks, "needs 1 <= ranks <= 8 and rank < ranks");
+  LLMOPT_REQUIRE((uint32_t)args.buffer_count == p.ranks + 1, "expects one region per rank and an output");
+  LLMOPT_REQUIRE(p.rows > 0 && p.width > 0 && p.width % 8 == 0 && p.slice_offset >= 256 && p.slice_offset % 16 == 0,
+                 "needs rows > 0, width a multiple of 8 and a 16-byte aligned slot behind the header");
+  const size_t elements = (size_t)p.rows * p.width;
+  Regions regions;
+  LLMOPT_REQUIRE(collect_regions(args, p.ranks, (size_t)p.slice_offset + elements * 2, &regions),
+                 "a region is too short or misaligned");
+  LLMOPT_REQUIRE(args.lengths[p.ranks] >= elements * 2 && ((uintptr_t)args.buffers[p.ranks] & 15u) == 0,
+                 "output buffer is too short or misaligned");
+  const size_t share = ((size_t)(p.rows + p.ranks - 1) / p.ranks) * p.width;
+  uint32_t ctas = (uint32_t)((share + 2047) / 2048);
+  const uint32_t most = 4u * (uint32_t)context_sm_count(args.ctx);
+  if (ctas > most) ctas = most;
+  if (ctas == 0) ctas = 1;
+  launch_kernel(args, exchange_gather_rows_kernel, dim3(ctas), dim3(256), 0, regions, (__half*)args.buffers[p.ranks], p,
+                context_device_error(args.ctx));
   return check_launch(args);
 }
 

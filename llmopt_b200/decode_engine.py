@@ -303,15 +303,16 @@ class DecodeEngine:
             raise ValueError("no such sequence")
         if group is not None:
             # Tensor-parallel shard: the same pass over this rank's heads and columns; o_proj and down are
-            # row splits whose fp32 partial sums (one slot of rows x hidden floats each) every rank adds in rank
-            # order.  Slots alternate like a decode step's: never the same in adjacent exchanges, the first not
+            # row splits whose fp32 partial sums (one slot of rows x hidden floats each) are added in rank order by a
+            # reduce-scatter exchange and an all-gather exchange (a second slot carries the fp16 shares).
+            # Slots alternate like a decode step's: never the same in adjacent exchanges, the first not
             # the decode step's last, the last not its first.  No exchange of an earlier step may still be in
             # flight on any rank when the prompt starts (true once every rank has read that step's token).
             if count * hidden * 4 > group.slot_bytes:
                 raise ValueError("the exchange slots are smaller than rows x hidden fp32 partial sums of this prompt")
             if group.slot_count < 3:
                 raise ValueError("a tensor-parallel prompt needs at least three exchange slots")
-            exchanges = 2 * len(config.layers) + 1
+            exchanges = 4 * len(config.layers) + 1  # a reduce and a gather exchange per row split, the argmax
             decode = getattr(self, "_decode_slots", None) or [0]
             slot_sequence = None
             for start in range(group.slot_count):
@@ -375,13 +376,13 @@ class DecodeEngine:
                         context, input=dispatch.Tensor(attended.buffer, (count, config.query_heads * dim)),
                         weight=layer["o"][0], scale=layer["o"][1], output=other, bias=current, bias_row_stride=hidden)
                 else:
-                    slot = slot_sequence[exchange]
-                    exchange += 1
+                    slot, slice_slot = slot_sequence[exchange], slot_sequence[exchange + 1]
+                    exchange += 2
                     run("llmopt_w4a16_linear_partial_f32_g64",
                         [attended.buffer, layer["o"][0].buffer, layer["o"][1].buffer, group.slot_view(slot, count * hidden * 4)],
                         parameters.u32s([count, hidden, config.query_heads * dim]))
-                    group.sum_record(commands.dispatch, slot=slot, rows=count, width=hidden, residual=current.buffer,
-                                     output=other.buffer)
+                    group.sum_rows_records(commands.dispatch, slot=slot, slice_slot=slice_slot, rows=count, width=hidden,
+                                           residual=current.buffer, output=other.buffer)
                 attention_index += 1
             else:
                 in_proj = self._empty((1, count, 3 * hidden))
@@ -413,13 +414,13 @@ class DecodeEngine:
                 run("llmopt_w4a16_dual_swiglu_f16_g64_m4",
                     [normed.buffer, layer["gate"][0].buffer, layer["gate"][1].buffer, layer["up"][0].buffer,
                      layer["up"][1].buffer, product.buffer], ffn)
-                slot = slot_sequence[exchange]
-                exchange += 1
+                slot, slice_slot = slot_sequence[exchange], slot_sequence[exchange + 1]
+                exchange += 2
                 run("llmopt_w4a16_linear_partial_f32_g64",
                     [product.buffer, layer["down"][0].buffer, layer["down"][1].buffer, group.slot_view(slot, count * hidden * 4)],
                     parameters.u32s([count, hidden, config.intermediate]))
-                group.sum_record(commands.dispatch, slot=slot, rows=count, width=hidden, residual=current.buffer,
-                                 output=other.buffer)
+                group.sum_rows_records(commands.dispatch, slot=slot, slice_slot=slice_slot, rows=count, width=hidden,
+                                       residual=current.buffer, output=other.buffer)
             current, other = other, current
         picked = self._empty((1,), "int32", 4)
         last = current.buffer.view((count - 1) * hidden * 2, hidden * 2)

@@ -167,6 +167,26 @@ class ExchangeGroup:
         return dispatch_item(name="llmopt_tp_exchange_sum_rms_f16", buffers=buffers, parameters=params,
                              grid=(256 * rows, 1, 1), group=(256, 1, 1))
 
+    def sum_rows_records(self, dispatch_item, *, slot: int, slice_slot: int, rows: int, width: int, residual, output):
+        """Prompt rows: the exchange sum as a reduce-scatter and an all-gather, two exchanges on two slots
+        (``llmopt_tp_exchange_reduce_rows_f16``: this rank's share of the rows from every rank's fp32 partial in
+        ``slot``, written to ``output`` and, as fp16, to its own ``slice_slot``; ``llmopt_tp_exchange_gather_rows_f16``:
+        the other ranks' shares).  A rank reads each partial once for its own rows only."""
+        from . import parameters
+
+        if slot == slice_slot:
+            raise ValueError("the fp32 partials and the fp16 shares need different slots")
+        if rows * width * 4 > self.slot_bytes:
+            raise ValueError("contribution larger than a slot")
+        params = parameters.u32s([self.world, self.rank, rows, width, self.slot_offset(slot), 1 if residual else 0,
+                                  self.slot_offset(slice_slot)])
+        buffers = list(self.regions) + [residual if residual is not None else output, output]
+        first = dispatch_item(name="llmopt_tp_exchange_reduce_rows_f16", buffers=buffers, parameters=params,
+                              grid=(256, 1, 1), group=(256, 1, 1))
+        second = dispatch_item(name="llmopt_tp_exchange_gather_rows_f16", buffers=list(self.regions) + [output],
+                               parameters=params, grid=(256, 1, 1), group=(256, 1, 1))
+        return [first, second]
+
     def argmax_record(self, dispatch_item, *, slot: int, rows: int, shard_columns: int, output):
         """``llmopt_tp_exchange_argmax``: best of every rank's stage-1 candidates, global indices."""
         from . import parameters

@@ -56,6 +56,43 @@ def test_exchange_sum_two_ranks_staged_peer(runtime):
         assert header0[FLAGS // 4] == epoch and header1[FLAGS // 4] == epoch  # rank 0 announced to both regions
 
 
+def test_exchange_rows_reduce_then_gather_staged_peer(runtime):
+    """Prompt rows: rank 0 of two reduces ITS rows from both partials (reduce-scatter), then copies the
+    peer's rows from the peer's fp16 share (all-gather); the peer's contribution, share and flags are staged."""
+    from llmopt_b200 import parameters
+    from llmopt_b200.cuda_native import Buffer
+
+    rng = np.random.default_rng(5)
+    rows, width = 7, 256  # shares: rows 0..3 (rank 0), 4..6 (rank 1)
+    slot_bytes = rows * width * 4
+    regions = [Buffer.create(runtime, HEADER + 2 * slot_bytes) for _ in range(2)]
+    residual = rng.standard_normal((rows, width)).astype(np.float16)
+    mine = rng.standard_normal((rows, width)).astype(np.float32)
+    theirs = rng.standard_normal((rows, width)).astype(np.float32)
+    total = ((mine + theirs) + residual.astype(np.float32)).astype(np.float16)
+    partial_offset, share_offset = HEADER, HEADER + slot_bytes
+    regions[0].write(partial_offset, mine)
+    regions[1].write(partial_offset, theirs)
+    peer_share = np.zeros((rows, width), np.float16)
+    peer_share[4:] = total[4:]  # what rank 1's reduce step leaves in its own region
+    regions[1].write(share_offset, peer_share)
+    output = Buffer.of_array(runtime, np.full((rows, width), np.nan, np.float16))
+    params = parameters.u32s([2, 0, rows, width, partial_offset, 1, share_offset])
+    regions[0].write(FLAGS + 4, np.array([1], np.uint32))  # the peer has announced exchange 1 (partials written)
+    _dispatch(runtime, "llmopt_tp_exchange_reduce_rows_f16", regions + [Buffer.of_array(runtime, residual), output], params)
+    got = output.to_numpy(np.float16, (rows, width))
+    assert np.array_equal(got[:4].view(np.uint16), total[:4].view(np.uint16))
+    assert np.all(np.isnan(got[4:]))  # the peer's rows are not this step's
+    own_share = regions[0].view(share_offset, rows * width * 2).to_numpy(np.float16, (rows, width))
+    assert np.array_equal(own_share[:4].view(np.uint16), total[:4].view(np.uint16))
+    regions[0].write(FLAGS + 4, np.array([2], np.uint32))  # the peer has announced exchange 2 (its share written)
+    _dispatch(runtime, "llmopt_tp_exchange_gather_rows_f16", regions + [output], params)
+    got = output.to_numpy(np.float16, (rows, width))
+    assert np.array_equal(got.view(np.uint16), total.view(np.uint16))
+    header0 = regions[0].view(0, HEADER).to_numpy(np.uint32)
+    assert header0[0] == 2 and header0[1] == 0
+
+
 def test_exchange_argmax_two_ranks_staged_peer(runtime):
     from llmopt_b200 import parameters
     from llmopt_b200.cuda_native import Buffer
