@@ -442,6 +442,66 @@ def time_prefill_gemm(runtime, peaks, *, m, k, n, form, weights=None) -> dict:
             "frac_of_sustained": tflops / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"]}
 
 
+def time_ffn_tensor_parallel(runtime, peaks, rank: int, world: int, group) -> list:
+    """The 70B-shape SwiGLU FFN (hidden 8192, intermediate 28672) of a prompt, split over the ranks: every rank runs
+    the RMS norm, gate and up with the SwiGLU epilogue on its 28672 / N intermediate columns and the down projection
+    on the matching rows of K as an fp32 partial of all prompt rows, then the partials are added over peer memory
+    (reduce-scatter + all-gather of the rows).  Device-timed back to back on every rank, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from llmopt_b200 import dispatch, parameters, tensor_parallel
+    from llmopt_b200.cuda_native import Batch, Buffer
+
+    hidden, intermediate = 8192, 28672
+    columns = intermediate // world
+    rows_most = 8192
+    rng = np.random.default_rng(11 + rank)
+    exchange = tensor_parallel.ExchangeGroup.create(runtime, rank, world, rows_most * hidden * 4, 2,
+                                                    tensor_parallel.torch_all_gather())
+
+    def w4(rows, cols):
+        packed = Buffer.of_array(runtime, rng.integers(0, 256, size=(rows, cols // 2), dtype=np.uint8))
+        scale = Buffer.of_array(runtime, rng.uniform(0.002, 0.01, size=(rows, cols // 64)).astype(np.float16))
+        return packed, scale
+
+    gate, up, down = w4(columns, hidden), w4(columns, hidden), w4(hidden, columns)
+    norm = Buffer.of_array(runtime, np.ones(hidden, np.float16))
+    out = []
+    for m in (512, 2048, 8192):
+        x = Buffer.of_array(runtime, np.random.default_rng(5).standard_normal((m, hidden)).astype(np.float16))
+        normed, result = Buffer.create(runtime, m * hidden * 2), Buffer.create(runtime, m * hidden * 2)
+        product = Buffer.create(runtime, m * columns * 2)
+        commands = Batch(runtime)
+        ffn = parameters.w4a16_swiglu_ffn(m=m, n=columns, k=hidden, epsilon=1e-5)
+        commands.dispatch(name="llmopt_w4a16_swiglu_rms_f16_g64", buffers=[x, norm, normed], parameters=ffn,
+                          grid=(m * 256, 1, 1), group=(256, 1, 1))
+        commands.dispatch(name="llmopt_w4a16_dual_swiglu_f16_g64_m4",
+                          buffers=[normed, gate[0], gate[1], up[0], up[1], product], parameters=ffn,
+                          grid=(1, 1, 1), group=(256, 1, 1))
+        commands.dispatch(name="llmopt_w4a16_linear_partial_f32_g64",
+                          buffers=[product, down[0], down[1], exchange.slot_view(0, m * hidden * 4)],
+                          parameters=parameters.u32s([m, hidden, columns]), grid=(1, 1, 1), group=(256, 1, 1))
+        exchange.sum_rows_records(commands.dispatch, slot=0, slice_slot=1, rows=m, width=hidden, residual=x, output=result)
+        items = list(commands.pending)
+        dist.barrier()
+        milliseconds = runtime.time_dispatches(items, warmup=2, iterations=5) * len(items)  # per FFN, not per launch
+        commands.abort()
+        worst = torch.tensor([milliseconds], dtype=torch.float64)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        milliseconds = float(worst.item())
+        tflops = 3 * 2.0 * m * hidden * intermediate / milliseconds / 1e9
+        out.append({"m": m, "k": hidden, "n": intermediate, "parallelism": f"tp{world}", "ms": round(milliseconds, 4),
+                    "tflops": round(tflops, 1), "tflops_per_gpu": round(tflops / world, 1),
+                    "frac_of_measured_bf16_per_gpu": round(tflops / world / peaks["bf16_tflops"], 3),
+                    "launches": len(items), "exchange_bytes_per_gpu": m * hidden * (4 + 2) * (world - 1) // world,
+                    "data": "synthetic"})
+        del x, normed, result, product
+    dist.barrier()  # no rank unmaps its region while a peer may still read it
+    runtime.synchronize()
+    return out
+
+
 def time_baseline_mode(runtime, peaks) -> dict:
     """The zero-point / group-32 input mode of the stated configurations, timed alone: the decode
     GEMV on unsigned nibbles with fp16 zero points (w = (u - z) s) at the gate shape, and the
@@ -786,6 +846,8 @@ def run_native(args, config, rank: int, world: int, local: int, group) -> dict:
         result["prefill"] = time_prefill(engine, runtime, PREFILL_TOKENS, group)
         if tensor_parallel_mode:
             result["prefill"]["parallelism"] = f"tp{world}: the same pass on every rank's heads and columns, o_proj and down as row splits with their fp32 partial sums added over peer memory"
+    if tensor_parallel_mode and extra_legs:
+        result["prefill_ffn_c5"] = time_ffn_tensor_parallel(runtime, peaks, rank, world, group)
     if world == 1 and config.hidden >= 2048:
         result["prefill_gemm"] = time_prefill_gemm(runtime, peaks, m=2048, k=config.hidden, n=config.intermediate,
                                                    form="dual", weights=engine.layers[:4])
