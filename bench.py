@@ -456,18 +456,26 @@ def time_ffn_tensor_parallel(runtime, peaks, rank: int, world: int, group) -> li
     hidden, intermediate = 8192, 28672
     columns = intermediate // world
     rows_most = 8192
-    rng = np.random.default_rng(11 + rank)
+    rng = np.random.default_rng(11)  # the same whole matrices on every rank; a rank uploads its share
     exchange = tensor_parallel.ExchangeGroup.create(runtime, rank, world, rows_most * hidden * 4, 2,
                                                     tensor_parallel.torch_all_gather())
 
-    def w4(rows, cols):
-        packed = Buffer.of_array(runtime, rng.integers(0, 256, size=(rows, cols // 2), dtype=np.uint8))
-        scale = Buffer.of_array(runtime, rng.uniform(0.002, 0.01, size=(rows, cols // 64)).astype(np.float16))
-        return packed, scale
+    def whole(rows, cols):
+        return (rng.integers(0, 256, size=(rows, cols // 2), dtype=np.uint8),
+                rng.uniform(0.002, 0.01, size=(rows, cols // 64)).astype(np.float16))
 
-    gate, up, down = w4(columns, hidden), w4(columns, hidden), w4(hidden, columns)
+    def upload(pair):
+        return tuple(Buffer.of_array(runtime, np.ascontiguousarray(part)) for part in pair)
+
+    whole_gate, whole_up, whole_down = whole(intermediate, hidden), whole(intermediate, hidden), whole(hidden, intermediate)
+    mine = slice(rank * columns, (rank + 1) * columns)
+    gate = upload((whole_gate[0][mine], whole_gate[1][mine]))   # this rank's intermediate columns: rows of gate / up
+    up = upload((whole_up[0][mine], whole_up[1][mine]))
+    down = upload((whole_down[0][:, rank * columns // 2:(rank + 1) * columns // 2],  # the matching stretch of K
+                   whole_down[1][:, rank * columns // 64:(rank + 1) * columns // 64]))
     norm = Buffer.of_array(runtime, np.ones(hidden, np.float16))
     out = []
+    check = None
     for m in (512, 2048, 8192):
         x = Buffer.of_array(runtime, np.random.default_rng(5).standard_normal((m, hidden)).astype(np.float16))
         normed, result = Buffer.create(runtime, m * hidden * 2), Buffer.create(runtime, m * hidden * 2)
@@ -487,6 +495,30 @@ def time_ffn_tensor_parallel(runtime, peaks, rank: int, world: int, group) -> li
         dist.barrier()
         milliseconds = runtime.time_dispatches(items, warmup=2, iterations=5) * len(items)  # per FFN, not per launch
         commands.abort()
+        if check is None:
+            # the same layer unsplit, on rank 0 alone, against the exchanged result (every rank holds the same one)
+            check = {"m": m, "bound": 2e-3}
+            if rank == 0:
+                single = Batch(runtime)
+                context = dispatch.Context(runtime, batch=single)
+                tensors = []
+                for pair in (whole_gate, whole_up, whole_down):
+                    packed, scale = upload(pair)
+                    tensors.append((dispatch.Tensor(packed, pair[0].shape, "uint8"), dispatch.Tensor(scale, pair[1].shape)))
+                expected = dispatch.Tensor(Buffer.create(runtime, m * hidden * 2), (m, hidden))
+                activation = dispatch.Tensor(x, (m, hidden))
+                dispatch.dispatch_w4a16_swiglu_ffn_command(
+                    context, m=m, n=intermediate, k=hidden, epsilon=1e-5, activation=activation, residual=activation,
+                    gate_weight=tensors[0][0], gate_scale=tensors[0][1], up_weight=tensors[1][0], up_scale=tensors[1][1],
+                    down_weight=tensors[2][0], down_scale=tensors[2][1],
+                    norm_weight=dispatch.Tensor(norm, (hidden,)), output=expected, reference_guards=False)
+                single.commit()
+                want = expected.buffer.to_numpy(np.float16, (m, hidden)).astype(np.float32)
+                got = result.to_numpy(np.float16, (m, hidden)).astype(np.float32)
+                check["max_error_over_scale"] = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
+                check["equal_to_one_gpu"] = bool(check["max_error_over_scale"] <= check["bound"])
+                del tensors, expected
+            dist.barrier()
         worst = torch.tensor([milliseconds], dtype=torch.float64)
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
         milliseconds = float(worst.item())
@@ -499,6 +531,8 @@ def time_ffn_tensor_parallel(runtime, peaks, rank: int, world: int, group) -> li
         del x, normed, result, product
     dist.barrier()  # no rank unmaps its region while a peer may still read it
     runtime.synchronize()
+    if check is not None:
+        out[0]["check_against_one_gpu"] = check
     return out
 
 
