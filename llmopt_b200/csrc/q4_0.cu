@@ -14,12 +14,22 @@
 // w = scale * code + minimum; the block's contribution is scale * sum(x code) + minimum * sum(x),
 // the association the reference kernels use (:108-143).
 //
-// One warp per output column: the lanes take the row's blocks round-robin (a warp reads 32 x 18
-// contiguous bytes per step), each lane multiplies its block with the 32 matching activations of up
-// to four batch rows, fp32 accumulation, one warp reduction per (row, column).  More rows are
-// served in tiles of four over the same weight row (which stays in L1).  HBM-bound at M = 1:
-// 0.5625 bytes per weight.
-#include "common.cuh"
+// Two forms.  The general one: one warp per output column, the lanes take the row's blocks round-robin
+// (a warp reads 32 x 18 contiguous bytes per step), each lane multiplies its block with the 32 matching
+// activations of up to four batch rows, fp32 accumulation, one warp reduction per (row, column); more rows
+// are served in tiles of four over the same weight row (which stays in L1).
+// The tensor-core one (Q4_0 rows that are a whole number of 16-byte vectors, i.e. K a multiple of 256, up to
+// 32 batch rows): a CTA owns 16 weight rows, copies them to shared memory in K chunks of 4096 with 16-byte
+// cp.async (the first chunk before it waits for its predecessor: weights do not depend on it), and its eight
+// warps share out the blocks of a chunk.  A block is two mma.sync.m16n8k16: the low nibbles (elements 0..15)
+// as halves 1024 + u, the high nibbles (16..31), read in place, as 64 + u, one LOP3 per pair of weights; the
+// offsets 1032 and 72 (u - 8 is the weight) leave as a per-block term -(1032 sum(x low) + 72 sum(x high)) that
+// seeds the accumulator, and the block's fp32 sum is scaled by d.  The activations are staged once per CTA in
+// the order of the B fragments.  HBM-bound at M = 1: 0.5625 bytes per weight.
+#include <cstdlib>
+#include <initializer_list>
+
+#include "w4a16_gemv_device.cuh"
 
 namespace llmopt {
 namespace {
@@ -268,6 +278,288 @@ __global__ void __launch_bounds__(256) q4_0_dequant_kernel(const uint8_t* __rest
   out[(size_t)block * 32u + i] = __float2half_rn(d * (float)q);
 }
 
+// ---- tensor-core form ----------------------------------------------------------------------------
+constexpr int kMmaRows = 16;                // weight rows (output columns) of a CTA
+constexpr int kMmaWarps = 8;
+constexpr uint32_t kChunkBlocks = 128;      // blocks of a K chunk: 4096 elements, 2304 bytes of a row
+constexpr uint32_t kChunkPitch = kChunkBlocks * 18u + 16u;  // 145 vectors: rows 0..7 start 4 banks apart
+constexpr int kCopyParts = 4;               // commit groups of a chunk: the first blocks are used while the rest lands
+constexpr int kMaxRowTiles = 4;             // batch rows of a launch: 8 per tile
+
+struct MmaProblem {
+  uint32_t m, k, mode;          // mode: epilogue (linear), activation (gated)
+  uint32_t matrices;            // 1, or 3 for the fused QKV (NMAT == 1); gate and up are one "matrix" of NMAT == 2
+  const uint8_t* weight[3];     // gated: {gate, up}
+  __half* out[3];
+  uint32_t n[3], first_tile[3];  // columns and first CTA of every matrix
+  const __half* additive;
+  uint32_t chunk_buffers;       // 1 or 2
+  uint32_t staged_rows;         // batch rows the activation staging is sized for (1..8)
+};
+
+__device__ __forceinline__ uint32_t shared_load_32(uint32_t address) {
+  uint32_t value;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(value) : "r"(address) : "memory");
+  return value;
+}
+__device__ __forceinline__ uint4 shared_load_128(uint32_t address) {
+  uint4 value;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(value.x), "=r"(value.y), "=r"(value.z), "=r"(value.w) : "r"(address) : "memory");
+  return value;
+}
+__device__ __forceinline__ float2 shared_load_float2(uint32_t address) {
+  float2 value;
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(value.x), "=f"(value.y) : "r"(address) : "memory");
+  return value;
+}
+__device__ __forceinline__ void copy_wait(int pending) {  // cp.async.wait_group takes an immediate
+  switch (pending) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+  }
+}
+
+// Shared memory: [chunk buffers][NMAT][16 rows][kChunkPitch] | fragments [128 blocks][staged_rows][4] uint4 |
+// bias [128 blocks][8] float | (the reduction reuses the fragments).
+template <int NMAT>
+__host__ __device__ inline size_t mma_shared_bytes(uint32_t chunk_buffers, uint32_t staged_rows) {
+  const size_t fragments = (size_t)kChunkBlocks * staged_rows * 64u;
+  const size_t reduction = (size_t)NMAT * kMmaWarps * kMmaRows * 8u * 4u;
+  return (size_t)chunk_buffers * NMAT * kMmaRows * kChunkPitch + (fragments > reduction ? fragments : reduction) +
+         (size_t)kChunkBlocks * 8u * 4u;
+}
+
+// TILES: batch-row tiles of eight the accumulators are built for (1: up to 8 rows, 4: up to 32)
+template <int NMAT, int TILES>
+__global__ void __launch_bounds__(kMmaWarps * 32, NMAT == 1 ? 4 : 2) q4_0_mma_kernel(const __half* __restrict__ x, MmaProblem p) {
+  using namespace gemv;
+  extern __shared__ __align__(16) uint8_t shared[];
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, r = lane >> 2, c = lane & 3u;
+  // which matrix and which 16 of its rows
+  uint32_t which = 0;
+  if (NMAT == 1 && p.matrices == 3) which = blockIdx.x >= p.first_tile[2] ? 2u : (blockIdx.x >= p.first_tile[1] ? 1u : 0u);
+  // (selected with constant indices: a dynamic index would put the parameter block on the stack)
+  const uint32_t n = which == 0u ? p.n[0] : which == 1u ? p.n[1] : p.n[2];
+  const uint32_t n0 = (blockIdx.x - (which == 0u ? p.first_tile[0] : which == 1u ? p.first_tile[1] : p.first_tile[2])) * kMmaRows;
+  const uint8_t* const own_weight = which == 0u ? p.weight[0] : which == 1u ? p.weight[1] : p.weight[2];
+  __half* const own_out = which == 0u ? p.out[0] : which == 1u ? p.out[1] : p.out[2];
+  const uint32_t blocks = p.k >> 5, chunks = (blocks + kChunkBlocks - 1) / kChunkBlocks;
+  const size_t row_bytes = (size_t)blocks * 18u;
+  uint8_t* const weights = shared;
+  uint4* const fragments = reinterpret_cast<uint4*>(shared + (size_t)p.chunk_buffers * NMAT * kMmaRows * kChunkPitch);
+  const size_t fragment_bytes = (size_t)kChunkBlocks * p.staged_rows * 64u, reduction_bytes = (size_t)NMAT * kMmaWarps * kMmaRows * 32u;
+  float* const bias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fragments) +
+                                                (fragment_bytes > reduction_bytes ? fragment_bytes : reduction_bytes));
+  float* const reduction = reinterpret_cast<float*>(fragments);
+
+  // one chunk of the CTA's rows -> buffer, as kCopyParts commit groups (rows past n re-read the last row):
+  // sixteen consecutive threads copy consecutive vectors of one row
+  const uint32_t copy_row = threadIdx.x >> 4, copy_lane = threadIdx.x & 15u;
+  const uint8_t* copy_from[NMAT];
+#pragma unroll
+  for (int a = 0; a < NMAT; ++a)
+    copy_from[a] = (NMAT == 2 ? p.weight[a] : own_weight) + (size_t)min(n0 + copy_row, n - 1u) * row_bytes + copy_lane * 16u;
+  auto copy_chunk = [&](uint32_t chunk) {
+    const uint32_t chunk_blocks = min(kChunkBlocks, blocks - chunk * kChunkBlocks);
+    const uint32_t vectors = (chunk_blocks * 18u) >> 4, share = (vectors + kCopyParts - 1) / kCopyParts;
+    const uint32_t buffer = (uint32_t)__cvta_generic_to_shared(weights) + (chunk % p.chunk_buffers) * (NMAT * kMmaRows * kChunkPitch) +
+                            copy_row * kChunkPitch + copy_lane * 16u;
+#pragma unroll
+    for (int part = 0; part < kCopyParts; ++part) {
+      const uint32_t end = min(vectors, (part + 1) * share);
+      for (uint32_t vector = part * share + copy_lane; vector < end; vector += 16) {
+#pragma unroll
+        for (int a = 0; a < NMAT; ++a)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(buffer + a * (kMmaRows * kChunkPitch) + (vector - copy_lane) * 16u),
+                       "l"(copy_from[a] + (size_t)chunk * (kChunkBlocks * 18u) + (size_t)(vector - copy_lane) * 16u)
+                       : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+  };
+  copy_chunk(0);  // ahead of the predecessor's results
+  grid_chain_prologue();
+
+  const uint32_t row_tiles = (p.m + 7u) / 8u;
+  float acc[NMAT][TILES][4];
+#pragma unroll
+  for (int a = 0; a < NMAT; ++a)
+#pragma unroll
+    for (int t = 0; t < TILES; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[a][t][i] = 0.0f;
+
+  for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+    const bool ahead = chunk + 1u < chunks && p.chunk_buffers == 2u;
+    if (ahead) copy_chunk(chunk + 1u);  // its buffer was released by the barrier that ended chunk - 1
+    const uint32_t chunk_blocks = min(kChunkBlocks, blocks - chunk * kChunkBlocks);
+    const uint32_t vectors = (chunk_blocks * 18u) >> 4, share = (vectors + kCopyParts - 1) / kCopyParts;
+    // shared-window addresses: the loads of the block loop are ld.shared with 32-bit address arithmetic
+    const uint32_t buffer_at = (uint32_t)__cvta_generic_to_shared(weights) + (chunk % p.chunk_buffers) * (NMAT * kMmaRows * kChunkPitch);
+    const uint32_t fragments_at = (uint32_t)__cvta_generic_to_shared(fragments), bias_at = (uint32_t)__cvta_generic_to_shared(bias);
+#pragma unroll
+    for (int t = 0; t < TILES; ++t) {
+      if ((uint32_t)t >= row_tiles) break;
+      const uint32_t rows = min(8u, p.m - 8u * t);
+      // the tile's activations of this chunk in B-fragment order, and the per-block offset term
+      // (only the rows that exist: with one row every thread stages two quads of it, all loads at once)
+#pragma unroll 2
+      for (uint32_t item = threadIdx.x; item < chunk_blocks * rows * 4u; item += kMmaWarps * 32) {
+        const uint32_t block = rows == 1u ? item >> 2 : (item >> 2) / rows, row = (item >> 2) - block * rows, quad = item & 3u;
+        float low_sum = 0.0f, high_sum = 0.0f;
+        {
+          const __half* source = x + (size_t)(8u * t + row) * p.k + (size_t)(chunk * kChunkBlocks + block) * 32u + 4u * quad;
+          const uint2 low = *reinterpret_cast<const uint2*>(source), high = *reinterpret_cast<const uint2*>(source + 16);
+          // k slots (2 quad, 2 quad + 1) hold elements (4 quad, 4 quad + 2), slots (+8, +9) elements (4 quad + 1, 4 quad + 3)
+          fragments[(block * p.staged_rows + row) * 4u + quad] =
+              make_uint4(prmt(low.x, low.y, 0x5410u), prmt(low.x, low.y, 0x7632u), prmt(high.x, high.y, 0x5410u),
+                         prmt(high.x, high.y, 0x7632u));
+          const float2 l0 = __half22float2(*reinterpret_cast<const __half2*>(&low.x));
+          const float2 l1 = __half22float2(*reinterpret_cast<const __half2*>(&low.y));
+          const float2 h0 = __half22float2(*reinterpret_cast<const __half2*>(&high.x));
+          const float2 h1 = __half22float2(*reinterpret_cast<const __half2*>(&high.y));
+          low_sum = (l0.x + l0.y) + (l1.x + l1.y);
+          high_sum = (h0.x + h0.y) + (h1.x + h1.y);
+        }
+        low_sum += __shfl_xor_sync(0xffffffffu, low_sum, 1);
+        low_sum += __shfl_xor_sync(0xffffffffu, low_sum, 2);
+        high_sum += __shfl_xor_sync(0xffffffffu, high_sum, 1);
+        high_sum += __shfl_xor_sync(0xffffffffu, high_sum, 2);
+        if (quad == 0u) bias[block * 8u + row] = -(1032.0f * low_sum + 72.0f * high_sum);
+      }
+      uint32_t begin = 0;
+#pragma unroll
+      for (int part = 0; part < kCopyParts; ++part) {
+        // the chunk's copies up to this part have landed (on the first tile; later tiles find them there)
+        copy_wait((ahead ? kCopyParts : 0) + kCopyParts - 1 - part);
+        __syncthreads();  // everybody's copies, and (part 0) the fragments
+        // whole PAIRS of blocks (36 bytes, word aligned) inside the bytes landed so far; a warp takes every eighth pair
+        const uint32_t end = (part == kCopyParts - 1 ? chunk_blocks : min(chunk_blocks, (min(vectors, (part + 1) * share) * 16u) / 18u)) & ~1u;
+        for (uint32_t pair = begin / 2u + ((warp + kMmaWarps - (begin / 2u) % kMmaWarps) % kMmaWarps); 2u * pair < end; pair += kMmaWarps) {
+          const uint32_t fragment_at = fragments_at + ((2u * pair * p.staged_rows + r) * 4u + c) * 16u;
+          uint4 b_even = make_uint4(0u, 0u, 0u, 0u), b_odd = b_even;
+          if (r < rows) {
+            b_even = shared_load_128(fragment_at);
+            b_odd = shared_load_128(fragment_at + p.staged_rows * 64u);
+          }
+          const float2 offset_even = shared_load_float2(bias_at + (2u * pair * 8u + 2u * c) * 4u);
+          const float2 offset_odd = shared_load_float2(bias_at + ((2u * pair + 1u) * 8u + 2u * c) * 4u);
+#pragma unroll
+          for (int a = 0; a < NMAT; ++a) {
+            // the pair of one row: {d, 16 quant bytes} {d, 16 quant bytes} = nine words
+            const uint32_t first_row = buffer_at + (a * kMmaRows + r) * kChunkPitch + 36u * pair, second_row = first_row + 8u * kChunkPitch;
+            const uint32_t head_a = shared_load_32(first_row), tail_a = shared_load_32(first_row + 16u);
+            const uint32_t head_b = shared_load_32(second_row), tail_b = shared_load_32(second_row + 16u);
+            // even block: its quant word c starts two bytes into word c; odd block: quant word c is word 5 + c
+            const uint32_t even_a = __funnelshift_r(shared_load_32(first_row + 4u * c), shared_load_32(first_row + 4u * c + 4u), 16);
+            const uint32_t even_b = __funnelshift_r(shared_load_32(second_row + 4u * c), shared_load_32(second_row + 4u * c + 4u), 16);
+            const uint32_t odd_a = shared_load_32(first_row + 20u + 4u * c), odd_b = shared_load_32(second_row + 20u + 4u * c);
+            const float d_even_a = __half2float(__ushort_as_half((unsigned short)(head_a & 0xffffu)));
+            const float d_even_b = __half2float(__ushort_as_half((unsigned short)(head_b & 0xffffu)));
+            const float d_odd_a = __half2float(__ushort_as_half((unsigned short)(tail_a >> 16)));
+            const float d_odd_b = __half2float(__ushort_as_half((unsigned short)(tail_b >> 16)));
+            float sum[4] = {offset_even.x, offset_even.y, offset_even.x, offset_even.y};
+            // low nibbles of bytes (0, 2) and (1, 3): elements (4c, 4c + 2), (4c + 1, 4c + 3) as 1024 + u
+            mma_16816(sum, lop3_and_xor(even_a, 0x000F000Fu, 0x64006400u), lop3_and_xor(even_b, 0x000F000Fu, 0x64006400u),
+                      lop3_and_xor(even_a >> 8, 0x000F000Fu, 0x64006400u), lop3_and_xor(even_b >> 8, 0x000F000Fu, 0x64006400u),
+                      b_even.x, b_even.y);
+            // high nibbles in place: elements 16 + the same, as 64 + u
+            mma_16816(sum, lop3_and_xor(even_a, 0x00F000F0u, 0x54005400u), lop3_and_xor(even_b, 0x00F000F0u, 0x54005400u),
+                      lop3_and_xor(even_a >> 8, 0x00F000F0u, 0x54005400u), lop3_and_xor(even_b >> 8, 0x00F000F0u, 0x54005400u),
+                      b_even.z, b_even.w);
+            float next[4] = {offset_odd.x, offset_odd.y, offset_odd.x, offset_odd.y};
+            mma_16816(next, lop3_and_xor(odd_a, 0x000F000Fu, 0x64006400u), lop3_and_xor(odd_b, 0x000F000Fu, 0x64006400u),
+                      lop3_and_xor(odd_a >> 8, 0x000F000Fu, 0x64006400u), lop3_and_xor(odd_b >> 8, 0x000F000Fu, 0x64006400u),
+                      b_odd.x, b_odd.y);
+            mma_16816(next, lop3_and_xor(odd_a, 0x00F000F0u, 0x54005400u), lop3_and_xor(odd_b, 0x00F000F0u, 0x54005400u),
+                      lop3_and_xor(odd_a >> 8, 0x00F000F0u, 0x54005400u), lop3_and_xor(odd_b >> 8, 0x00F000F0u, 0x54005400u),
+                      b_odd.z, b_odd.w);
+            acc[a][t][0] = fmaf(d_odd_a, next[0], fmaf(d_even_a, sum[0], acc[a][t][0]));
+            acc[a][t][1] = fmaf(d_odd_a, next[1], fmaf(d_even_a, sum[1], acc[a][t][1]));
+            acc[a][t][2] = fmaf(d_odd_b, next[2], fmaf(d_even_b, sum[2], acc[a][t][2]));
+            acc[a][t][3] = fmaf(d_odd_b, next[3], fmaf(d_even_b, sum[3], acc[a][t][3]));
+          }
+        }
+        begin = end;
+      }
+      __syncthreads();  // the fragments (and, after the last tile, the chunk buffer) may be overwritten
+    }
+  }
+
+  // the eight warps' sums meet in shared memory; thread (row, column) adds them in warp order and writes
+#pragma unroll
+  for (int t = 0; t < TILES; ++t) {
+    if ((uint32_t)t >= row_tiles) break;
+#pragma unroll
+    for (int a = 0; a < NMAT; ++a) {
+      float* mine = reduction + ((a * kMmaWarps + warp) * kMmaRows) * 8u;
+      *reinterpret_cast<float2*>(mine + r * 8u + 2u * c) = make_float2(acc[a][t][0], acc[a][t][1]);
+      *reinterpret_cast<float2*>(mine + (r + 8u) * 8u + 2u * c) = make_float2(acc[a][t][2], acc[a][t][3]);
+    }
+    __syncthreads();
+    if (threadIdx.x < kMmaRows * 8) {
+      const uint32_t row = threadIdx.x >> 3, batch_row = 8u * t + (threadIdx.x & 7u), column = n0 + row;
+      float value[NMAT];
+#pragma unroll
+      for (int a = 0; a < NMAT; ++a) {
+        value[a] = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; ++w) value[a] += reduction[((a * kMmaWarps + w) * kMmaRows + row) * 8u + (threadIdx.x & 7u)];
+      }
+      if (batch_row < p.m && column < n) {
+        if (NMAT == 2) {
+          p.out[0][(size_t)batch_row * n + column] = gated_product(value[0], value[NMAT - 1], p.mode);
+        } else {
+          if (p.mode == 1) value[0] += __half2float(p.additive[column]);
+          if (p.mode == 2) value[0] += __half2float(p.additive[(size_t)batch_row * n + column]);
+          own_out[(size_t)batch_row * n + column] = __float2half_rn(value[0]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// The tensor-core form takes rows of whole 16-byte vectors (K a multiple of 256) on 16-byte boundaries.
+// LLMOPT_CUDA_Q4_0_MMA=0 keeps every launch on the general kernels.
+bool mma_form_ok(uint32_t k, std::initializer_list<const void*> weights) {
+  static const bool allowed = getenv("LLMOPT_CUDA_Q4_0_MMA") == nullptr || getenv("LLMOPT_CUDA_Q4_0_MMA")[0] != '0';
+  if (!allowed || k % 256u != 0u) return false;
+  for (const void* weight : weights)
+    if (((uintptr_t)weight & 15u) != 0) return false;
+  return true;
+}
+
+// Launches the tensor-core form over all rows (passes of up to 32); false when the device refuses the shared memory.
+template <int NMAT>
+bool launch_mma_form(const KernelArgs& args, const __half* x, MmaProblem p, uint32_t tiles) {
+  const uint32_t m = p.m;
+  p.chunk_buffers = (p.k >> 5) > kChunkBlocks ? 2u : 1u;
+  p.staged_rows = m < 8u ? m : 8u;
+  const size_t shared = mma_shared_bytes<NMAT>(p.chunk_buffers, p.staged_rows);
+  auto kernel = m <= 8u ? q4_0_mma_kernel<NMAT, 1> : q4_0_mma_kernel<NMAT, kMaxRowTiles>;
+  if (shared > (48u << 10) &&
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_shared_bytes<NMAT>(2, 8)) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  for (uint32_t row0 = 0; row0 < m; row0 += 8u * kMaxRowTiles) {
+    MmaProblem pass = p;
+    pass.m = min(m - row0, 8u * (uint32_t)kMaxRowTiles);
+    for (uint32_t i = 0; i < 3; ++i)
+      if (pass.out[i] != nullptr) pass.out[i] += (size_t)row0 * p.n[i];
+    if (NMAT == 1 && p.mode == 2) pass.additive += (size_t)row0 * p.n[0];
+    launch_kernel(args, kernel, dim3(tiles), dim3(kMmaWarps * 32), shared, x + (size_t)row0 * p.k, pass);
+  }
+  return true;
+}
+
 bool shape_ok(uint32_t k, const void* x) { return k > 0 && k % 32 == 0 && ((uintptr_t)x & 15u) == 0 && k % 8 == 0; }
 
 }  // namespace
@@ -285,6 +577,15 @@ static int launch_quant_linear(const KernelArgs& args) {
                      args.lengths[3] >= (size_t)p.m * p.n * 2, "buffer is too short");
   if (p.mode == 1) LLMOPT_REQUIRE(args.lengths[2] >= (size_t)p.n * 2, "bias buffer is too short");
   if (p.mode == 2) LLMOPT_REQUIRE(args.lengths[2] >= (size_t)p.m * p.n * 2, "residual buffer is too short");
+  if (FORMAT == kQ4_0 && mma_form_ok(p.k, {args.buffers[1]})) {
+    MmaProblem problem = {};
+    problem.m = p.m, problem.k = p.k, problem.mode = p.mode, problem.matrices = 1;
+    problem.weight[0] = (const uint8_t*)args.buffers[1];
+    problem.out[0] = (__half*)args.buffers[3];
+    problem.n[0] = p.n;
+    problem.additive = (const __half*)args.buffers[2];
+    if (launch_mma_form<1>(args, (const __half*)args.buffers[0], problem, (p.n + kMmaRows - 1) / kMmaRows)) return check_launch(args);
+  }
   launch_kernel(args, quant_linear_kernel<FORMAT>, dim3((p.n + 7) / 8), dim3(256), 0, (const __half*)args.buffers[0],
                 (const uint8_t*)args.buffers[1], (const __half*)args.buffers[2], (__half*)args.buffers[3], p);
   return check_launch(args);
@@ -302,6 +603,15 @@ int launch_q4_0_gated_linear(const KernelArgs& args) {
   const size_t weight_bytes = (size_t)p.n * (p.k / 32) * 18;
   LLMOPT_REQUIRE(args.lengths[0] >= (size_t)p.m * p.k * 2 && args.lengths[1] >= weight_bytes &&
                      args.lengths[2] >= weight_bytes && args.lengths[3] >= (size_t)p.m * p.n * 2, "buffer is too short");
+  if (mma_form_ok(p.k, {args.buffers[1], args.buffers[2]})) {
+    MmaProblem problem = {};
+    problem.m = p.m, problem.k = p.k, problem.mode = p.mode, problem.matrices = 1;
+    problem.weight[0] = (const uint8_t*)args.buffers[1];
+    problem.weight[1] = (const uint8_t*)args.buffers[2];
+    problem.out[0] = (__half*)args.buffers[3];
+    problem.n[0] = p.n;
+    if (launch_mma_form<2>(args, (const __half*)args.buffers[0], problem, (p.n + kMmaRows - 1) / kMmaRows)) return check_launch(args);
+  }
   launch_kernel(args, q4_0_gated_kernel, dim3((p.n + 7) / 8), dim3(256), 0, (const __half*)args.buffers[0],
                 (const uint8_t*)args.buffers[1], (const uint8_t*)args.buffers[2], (__half*)args.buffers[3], p);
   return check_launch(args);
@@ -320,6 +630,20 @@ int launch_q4_0_qkv_linear(const KernelArgs& args) {
   LLMOPT_REQUIRE(args.lengths[4] >= (size_t)p.m * p.n_q * 2 && args.lengths[5] >= (size_t)p.m * p.n_k * 2 &&
                      args.lengths[6] >= (size_t)p.m * p.n_v * 2, "output buffer is too short");
   const uint32_t columns = p.n_q + p.n_k + p.n_v;
+  if (mma_form_ok(p.k, {args.buffers[1], args.buffers[2], args.buffers[3]})) {
+    MmaProblem problem = {};
+    problem.m = p.m, problem.k = p.k, problem.mode = 0, problem.matrices = 3;
+    const uint32_t widths[3] = {p.n_q, p.n_k, p.n_v};
+    uint32_t tiles = 0;
+    for (uint32_t i = 0; i < 3; ++i) {
+      problem.weight[i] = (const uint8_t*)args.buffers[1 + i];
+      problem.out[i] = (__half*)args.buffers[4 + i];
+      problem.n[i] = widths[i];
+      problem.first_tile[i] = tiles;
+      tiles += (widths[i] + kMmaRows - 1) / kMmaRows;
+    }
+    if (launch_mma_form<1>(args, (const __half*)args.buffers[0], problem, tiles)) return check_launch(args);
+  }
   launch_kernel(args, q4_0_qkv_kernel, dim3((columns + 7) / 8), dim3(256), 0, (const __half*)args.buffers[0],
                 (const uint8_t*)args.buffers[1], (const uint8_t*)args.buffers[2], (const uint8_t*)args.buffers[3],
                 (__half*)args.buffers[4], (__half*)args.buffers[5], (__half*)args.buffers[6], p);

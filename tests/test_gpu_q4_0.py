@@ -50,7 +50,9 @@ def test_reference_fixture_block_layout(runtime, oracle):
 
 
 @pytest.mark.parametrize("m,k,n,mode", [(1, 576, 1536, 0), (1, 4096, 512, 2), (2, 1024, 96, 1), (5, 1536, 333, 2),
-                                        (16, 256, 40, 0), (37, 96, 17, 2)])
+                                        (16, 256, 40, 0), (37, 96, 17, 2),
+                                        # the tensor-core form: two K chunks, a short last chunk, more than 32 rows
+                                        (1, 8192, 48, 0), (9, 4352, 32, 1), (33, 512, 64, 2), (8, 14336, 24, 0)])
 def test_linear_matches_oracle(runtime, oracle, m, k, n, mode):
     from llmopt_b200 import dispatch
 
