@@ -18,10 +18,11 @@
 // (a warp reads 32 x 18 contiguous bytes per step), each lane multiplies its block with the 32 matching
 // activations of up to four batch rows, fp32 accumulation, one warp reduction per (row, column); more rows
 // are served in tiles of four over the same weight row (which stays in L1).
-// The tensor-core one (Q4_0 rows that are a whole number of 16-byte vectors, i.e. K a multiple of 256, up to
-// 32 batch rows): a CTA owns 16 weight rows, copies them to shared memory in K chunks of 4096 with 16-byte
-// cp.async (the first chunk before it waits for its predecessor: weights do not depend on it), and its eight
-// warps share out the blocks of a chunk.  A block is two mma.sync.m16n8k16: the low nibbles (elements 0..15)
+// The tensor-core one (Q4_0 rows that are a whole number of 16-byte vectors, i.e. K a multiple of 256): a CTA
+// works on 16 weight rows at a time, copied to shared memory with 16-byte cp.async (the first copies before it
+// waits for its predecessor: weights do not depend on it), and its eight warps share out the blocks.  Up to 8
+// batch rows it is a stream (a few CTAs per SM walk over the tiles, every warp with a private two-deep ring of
+// its own K slices), beyond that a CTA per tile with K chunks of 4096 (up to 32 rows per pass).  A block is two mma.sync.m16n8k16: the low nibbles (elements 0..15)
 // as halves 1024 + u, the high nibbles (16..31), read in place, as 64 + u, one LOP3 per pair of weights; the
 // offsets 1032 and 72 (u - 8 is the weight) leave as a per-block term -(1032 sum(x low) + 72 sum(x high)) that
 // seeds the accumulator, and the block's fp32 sum is scaled by d.  The activations are staged once per CTA in
@@ -295,21 +296,33 @@ struct MmaProblem {
   const __half* additive;
   uint32_t chunk_buffers;       // 1 or 2
   uint32_t staged_rows;         // batch rows the activation staging is sized for (1..8)
+  uint32_t tiles_total;         // 16-row tiles of all matrices
 };
 
-__device__ __forceinline__ uint32_t shared_load_32(uint32_t address) {
+// [address + OFFSET] with the offset in the instruction (an address operand of inline PTX costs a register and an add)
+template <uint32_t OFFSET>
+__device__ __forceinline__ uint32_t shared_load_32_at(uint32_t address) {
   uint32_t value;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(value) : "r"(address) : "memory");
+  asm volatile("ld.shared.b32 %0, [%1+%2];" : "=r"(value) : "r"(address), "n"(OFFSET) : "memory");
   return value;
+}
+// D = A B + C with C in registers of its own: the first MMA of a block takes the offset term without seeding moves
+__device__ __forceinline__ void mma_16816_seeded(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                                 uint32_t b1, float c0, float c1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1));
 }
 __device__ __forceinline__ uint4 shared_load_128(uint32_t address) {
   uint4 value;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(value.x), "=r"(value.y), "=r"(value.z), "=r"(value.w) : "r"(address) : "memory");
   return value;
 }
-__device__ __forceinline__ float2 shared_load_float2(uint32_t address) {
-  float2 value;
+// two float2 that lie 32 bytes apart: the offset terms of a lane's two columns, for a block and for the next one
+__device__ __forceinline__ float4 shared_load_float2_pair(uint32_t address) {
+  float4 value;
   asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(value.x), "=f"(value.y) : "r"(address) : "memory");
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2+32];" : "=f"(value.z), "=f"(value.w) : "r"(address) : "memory");
   return value;
 }
 __device__ __forceinline__ void copy_wait(int pending) {  // cp.async.wait_group takes an immediate
@@ -323,6 +336,68 @@ __device__ __forceinline__ void copy_wait(int pending) {  // cp.async.wait_group
     case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
     default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
   }
+}
+
+// One pair of blocks (36 bytes of every row, word aligned) of a staged chunk against one batch-row tile: four MMAs per
+// weight tile.  `fragment_at`: this lane's B fragment of the pair's first block (the second `fragment_stride` further);
+// `offsets_at`: the offset terms of columns 2c, 2c + 1 of the first block (the second block's 32 bytes further).
+template <int NMAT, uint32_t PITCH>
+__device__ __forceinline__ void block_pair_step(uint32_t buffer_at, uint32_t pair, uint32_t fragment_at, uint32_t fragment_stride,
+                                                uint32_t offsets_at, bool has_row, uint32_t r, uint32_t c, float (&acc)[NMAT][4]) {
+  using namespace gemv;
+  uint4 b_even = make_uint4(0u, 0u, 0u, 0u), b_odd = b_even;
+  if (has_row) {
+    b_even = shared_load_128(fragment_at);
+    b_odd = shared_load_128(fragment_at + fragment_stride);
+  }
+  const float4 offsets = shared_load_float2_pair(offsets_at);  // {even block: columns 2c, 2c + 1; odd block: the same}
+#pragma unroll
+  for (int a = 0; a < NMAT; ++a) {
+    // the pair of one row: {d, 16 quant bytes} {d, 16 quant bytes} = nine words; rows r and r + 8
+    const uint32_t row_at = buffer_at + (a * kMmaRows + r) * PITCH + 36u * pair, quad_at = row_at + 4u * c;
+    const uint32_t head_a = shared_load_32_at<0>(row_at), tail_a = shared_load_32_at<16>(row_at);
+    const uint32_t head_b = shared_load_32_at<8 * PITCH>(row_at), tail_b = shared_load_32_at<8 * PITCH + 16>(row_at);
+    // even block: its quant word c starts two bytes into word c; odd block: quant word c is word 5 + c
+    const uint32_t even_a = __funnelshift_r(shared_load_32_at<0>(quad_at), shared_load_32_at<4>(quad_at), 16);
+    const uint32_t even_b = __funnelshift_r(shared_load_32_at<8 * PITCH>(quad_at), shared_load_32_at<8 * PITCH + 4>(quad_at), 16);
+    const uint32_t odd_a = shared_load_32_at<20>(quad_at), odd_b = shared_load_32_at<8 * PITCH + 20>(quad_at);
+    // d of the even block is the low half of the pair's first word, d of the odd block the high half of its fifth
+    const float d_even_a = __low2float(*reinterpret_cast<const __half2*>(&head_a)), d_odd_a = __high2float(*reinterpret_cast<const __half2*>(&tail_a));
+    const float d_even_b = __low2float(*reinterpret_cast<const __half2*>(&head_b)), d_odd_b = __high2float(*reinterpret_cast<const __half2*>(&tail_b));
+    float sum[4], next[4];
+    // low nibbles of bytes (0, 2) and (1, 3): elements (4c, 4c + 2), (4c + 1, 4c + 3) as 1024 + u
+    mma_16816_seeded(sum, lop3_and_xor(even_a, 0x000F000Fu, 0x64006400u), lop3_and_xor(even_b, 0x000F000Fu, 0x64006400u),
+                     lop3_and_xor(even_a >> 8, 0x000F000Fu, 0x64006400u), lop3_and_xor(even_b >> 8, 0x000F000Fu, 0x64006400u),
+                     b_even.x, b_even.y, offsets.x, offsets.y);
+    // high nibbles in place: elements 16 + the same, as 64 + u
+    mma_16816(sum, lop3_and_xor(even_a, 0x00F000F0u, 0x54005400u), lop3_and_xor(even_b, 0x00F000F0u, 0x54005400u),
+              lop3_and_xor(even_a >> 8, 0x00F000F0u, 0x54005400u), lop3_and_xor(even_b >> 8, 0x00F000F0u, 0x54005400u),
+              b_even.z, b_even.w);
+    mma_16816_seeded(next, lop3_and_xor(odd_a, 0x000F000Fu, 0x64006400u), lop3_and_xor(odd_b, 0x000F000Fu, 0x64006400u),
+                     lop3_and_xor(odd_a >> 8, 0x000F000Fu, 0x64006400u), lop3_and_xor(odd_b >> 8, 0x000F000Fu, 0x64006400u),
+                     b_odd.x, b_odd.y, offsets.z, offsets.w);
+    mma_16816(next, lop3_and_xor(odd_a, 0x00F000F0u, 0x54005400u), lop3_and_xor(odd_b, 0x00F000F0u, 0x54005400u),
+              lop3_and_xor(odd_a >> 8, 0x00F000F0u, 0x54005400u), lop3_and_xor(odd_b >> 8, 0x00F000F0u, 0x54005400u),
+              b_odd.z, b_odd.w);
+    acc[a][0] = fmaf(d_odd_a, next[0], fmaf(d_even_a, sum[0], acc[a][0]));
+    acc[a][1] = fmaf(d_odd_a, next[1], fmaf(d_even_a, sum[1], acc[a][1]));
+    acc[a][2] = fmaf(d_odd_b, next[2], fmaf(d_even_b, sum[2], acc[a][2]));
+    acc[a][3] = fmaf(d_odd_b, next[3], fmaf(d_even_b, sum[3], acc[a][3]));
+  }
+}
+
+// One quad of a batch row's block in B-fragment order (k slots (2 quad, 2 quad + 1) hold elements (4 quad, 4 quad + 2),
+// slots (+8, +9) elements (4 quad + 1, 4 quad + 3); the same for the upper sixteen), and its sums of x.
+__device__ __forceinline__ uint4 fragment_of(const __half* source, float& low_sum, float& high_sum) {
+  using namespace gemv;
+  const uint2 low = *reinterpret_cast<const uint2*>(source), high = *reinterpret_cast<const uint2*>(source + 16);
+  const float2 l0 = __half22float2(*reinterpret_cast<const __half2*>(&low.x));
+  const float2 l1 = __half22float2(*reinterpret_cast<const __half2*>(&low.y));
+  const float2 h0 = __half22float2(*reinterpret_cast<const __half2*>(&high.x));
+  const float2 h1 = __half22float2(*reinterpret_cast<const __half2*>(&high.y));
+  low_sum = (l0.x + l0.y) + (l1.x + l1.y);
+  high_sum = (h0.x + h0.y) + (h1.x + h1.y);
+  return make_uint4(prmt(low.x, low.y, 0x5410u), prmt(low.x, low.y, 0x7632u), prmt(high.x, high.y, 0x5410u), prmt(high.x, high.y, 0x7632u));
 }
 
 // Shared memory: [chunk buffers][NMAT][16 rows][kChunkPitch] | fragments [128 blocks][staged_rows][4] uint4 |
@@ -387,13 +462,13 @@ __global__ void __launch_bounds__(kMmaWarps * 32, NMAT == 1 ? 4 : 2) q4_0_mma_ke
   grid_chain_prologue();
 
   const uint32_t row_tiles = (p.m + 7u) / 8u;
-  float acc[NMAT][TILES][4];
+  float acc[TILES][NMAT][4];
 #pragma unroll
-  for (int a = 0; a < NMAT; ++a)
+  for (int t = 0; t < TILES; ++t)
 #pragma unroll
-    for (int t = 0; t < TILES; ++t)
+    for (int a = 0; a < NMAT; ++a)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[a][t][i] = 0.0f;
+      for (int i = 0; i < 4; ++i) acc[t][a][i] = 0.0f;
 
   for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
     const bool ahead = chunk + 1u < chunks && p.chunk_buffers == 2u;
@@ -412,21 +487,9 @@ __global__ void __launch_bounds__(kMmaWarps * 32, NMAT == 1 ? 4 : 2) q4_0_mma_ke
 #pragma unroll 2
       for (uint32_t item = threadIdx.x; item < chunk_blocks * rows * 4u; item += kMmaWarps * 32) {
         const uint32_t block = rows == 1u ? item >> 2 : (item >> 2) / rows, row = (item >> 2) - block * rows, quad = item & 3u;
-        float low_sum = 0.0f, high_sum = 0.0f;
-        {
-          const __half* source = x + (size_t)(8u * t + row) * p.k + (size_t)(chunk * kChunkBlocks + block) * 32u + 4u * quad;
-          const uint2 low = *reinterpret_cast<const uint2*>(source), high = *reinterpret_cast<const uint2*>(source + 16);
-          // k slots (2 quad, 2 quad + 1) hold elements (4 quad, 4 quad + 2), slots (+8, +9) elements (4 quad + 1, 4 quad + 3)
-          fragments[(block * p.staged_rows + row) * 4u + quad] =
-              make_uint4(prmt(low.x, low.y, 0x5410u), prmt(low.x, low.y, 0x7632u), prmt(high.x, high.y, 0x5410u),
-                         prmt(high.x, high.y, 0x7632u));
-          const float2 l0 = __half22float2(*reinterpret_cast<const __half2*>(&low.x));
-          const float2 l1 = __half22float2(*reinterpret_cast<const __half2*>(&low.y));
-          const float2 h0 = __half22float2(*reinterpret_cast<const __half2*>(&high.x));
-          const float2 h1 = __half22float2(*reinterpret_cast<const __half2*>(&high.y));
-          low_sum = (l0.x + l0.y) + (l1.x + l1.y);
-          high_sum = (h0.x + h0.y) + (h1.x + h1.y);
-        }
+        float low_sum, high_sum;
+        fragments[(block * p.staged_rows + row) * 4u + quad] =
+            fragment_of(x + (size_t)(8u * t + row) * p.k + (size_t)(chunk * kChunkBlocks + block) * 32u + 4u * quad, low_sum, high_sum);
         low_sum += __shfl_xor_sync(0xffffffffu, low_sum, 1);
         low_sum += __shfl_xor_sync(0xffffffffu, low_sum, 2);
         high_sum += __shfl_xor_sync(0xffffffffu, high_sum, 1);
@@ -442,49 +505,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, NMAT == 1 ? 4 : 2) q4_0_mma_ke
         // whole PAIRS of blocks (36 bytes, word aligned) inside the bytes landed so far; a warp takes every eighth pair
         const uint32_t end = (part == kCopyParts - 1 ? chunk_blocks : min(chunk_blocks, (min(vectors, (part + 1) * share) * 16u) / 18u)) & ~1u;
         for (uint32_t pair = begin / 2u + ((warp + kMmaWarps - (begin / 2u) % kMmaWarps) % kMmaWarps); 2u * pair < end; pair += kMmaWarps) {
-          const uint32_t fragment_at = fragments_at + ((2u * pair * p.staged_rows + r) * 4u + c) * 16u;
-          uint4 b_even = make_uint4(0u, 0u, 0u, 0u), b_odd = b_even;
-          if (r < rows) {
-            b_even = shared_load_128(fragment_at);
-            b_odd = shared_load_128(fragment_at + p.staged_rows * 64u);
-          }
-          const float2 offset_even = shared_load_float2(bias_at + (2u * pair * 8u + 2u * c) * 4u);
-          const float2 offset_odd = shared_load_float2(bias_at + ((2u * pair + 1u) * 8u + 2u * c) * 4u);
-#pragma unroll
-          for (int a = 0; a < NMAT; ++a) {
-            // the pair of one row: {d, 16 quant bytes} {d, 16 quant bytes} = nine words
-            const uint32_t first_row = buffer_at + (a * kMmaRows + r) * kChunkPitch + 36u * pair, second_row = first_row + 8u * kChunkPitch;
-            const uint32_t head_a = shared_load_32(first_row), tail_a = shared_load_32(first_row + 16u);
-            const uint32_t head_b = shared_load_32(second_row), tail_b = shared_load_32(second_row + 16u);
-            // even block: its quant word c starts two bytes into word c; odd block: quant word c is word 5 + c
-            const uint32_t even_a = __funnelshift_r(shared_load_32(first_row + 4u * c), shared_load_32(first_row + 4u * c + 4u), 16);
-            const uint32_t even_b = __funnelshift_r(shared_load_32(second_row + 4u * c), shared_load_32(second_row + 4u * c + 4u), 16);
-            const uint32_t odd_a = shared_load_32(first_row + 20u + 4u * c), odd_b = shared_load_32(second_row + 20u + 4u * c);
-            const float d_even_a = __half2float(__ushort_as_half((unsigned short)(head_a & 0xffffu)));
-            const float d_even_b = __half2float(__ushort_as_half((unsigned short)(head_b & 0xffffu)));
-            const float d_odd_a = __half2float(__ushort_as_half((unsigned short)(tail_a >> 16)));
-            const float d_odd_b = __half2float(__ushort_as_half((unsigned short)(tail_b >> 16)));
-            float sum[4] = {offset_even.x, offset_even.y, offset_even.x, offset_even.y};
-            // low nibbles of bytes (0, 2) and (1, 3): elements (4c, 4c + 2), (4c + 1, 4c + 3) as 1024 + u
-            mma_16816(sum, lop3_and_xor(even_a, 0x000F000Fu, 0x64006400u), lop3_and_xor(even_b, 0x000F000Fu, 0x64006400u),
-                      lop3_and_xor(even_a >> 8, 0x000F000Fu, 0x64006400u), lop3_and_xor(even_b >> 8, 0x000F000Fu, 0x64006400u),
-                      b_even.x, b_even.y);
-            // high nibbles in place: elements 16 + the same, as 64 + u
-            mma_16816(sum, lop3_and_xor(even_a, 0x00F000F0u, 0x54005400u), lop3_and_xor(even_b, 0x00F000F0u, 0x54005400u),
-                      lop3_and_xor(even_a >> 8, 0x00F000F0u, 0x54005400u), lop3_and_xor(even_b >> 8, 0x00F000F0u, 0x54005400u),
-                      b_even.z, b_even.w);
-            float next[4] = {offset_odd.x, offset_odd.y, offset_odd.x, offset_odd.y};
-            mma_16816(next, lop3_and_xor(odd_a, 0x000F000Fu, 0x64006400u), lop3_and_xor(odd_b, 0x000F000Fu, 0x64006400u),
-                      lop3_and_xor(odd_a >> 8, 0x000F000Fu, 0x64006400u), lop3_and_xor(odd_b >> 8, 0x000F000Fu, 0x64006400u),
-                      b_odd.x, b_odd.y);
-            mma_16816(next, lop3_and_xor(odd_a, 0x00F000F0u, 0x54005400u), lop3_and_xor(odd_b, 0x00F000F0u, 0x54005400u),
-                      lop3_and_xor(odd_a >> 8, 0x00F000F0u, 0x54005400u), lop3_and_xor(odd_b >> 8, 0x00F000F0u, 0x54005400u),
-                      b_odd.z, b_odd.w);
-            acc[a][t][0] = fmaf(d_odd_a, next[0], fmaf(d_even_a, sum[0], acc[a][t][0]));
-            acc[a][t][1] = fmaf(d_odd_a, next[1], fmaf(d_even_a, sum[1], acc[a][t][1]));
-            acc[a][t][2] = fmaf(d_odd_b, next[2], fmaf(d_even_b, sum[2], acc[a][t][2]));
-            acc[a][t][3] = fmaf(d_odd_b, next[3], fmaf(d_even_b, sum[3], acc[a][t][3]));
-          }
+          block_pair_step<NMAT, kChunkPitch>(buffer_at, pair, fragments_at + ((2u * pair * p.staged_rows + r) * 4u + c) * 16u,
+                                p.staged_rows * 64u, bias_at + (2u * pair * 8u + 2u * c) * 4u, r < rows, r, c, acc[t]);
         }
         begin = end;
       }
@@ -499,8 +521,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, NMAT == 1 ? 4 : 2) q4_0_mma_ke
 #pragma unroll
     for (int a = 0; a < NMAT; ++a) {
       float* mine = reduction + ((a * kMmaWarps + warp) * kMmaRows) * 8u;
-      *reinterpret_cast<float2*>(mine + r * 8u + 2u * c) = make_float2(acc[a][t][0], acc[a][t][1]);
-      *reinterpret_cast<float2*>(mine + (r + 8u) * 8u + 2u * c) = make_float2(acc[a][t][2], acc[a][t][3]);
+      *reinterpret_cast<float2*>(mine + r * 8u + 2u * c) = make_float2(acc[t][a][0], acc[t][a][1]);
+      *reinterpret_cast<float2*>(mine + (r + 8u) * 8u + 2u * c) = make_float2(acc[t][a][2], acc[t][a][3]);
     }
     __syncthreads();
     if (threadIdx.x < kMmaRows * 8) {
@@ -526,6 +548,154 @@ __global__ void __launch_bounds__(kMmaWarps * 32, NMAT == 1 ? 4 : 2) q4_0_mma_ke
   }
 }
 
+// The same arithmetic as a STREAM: up to 8 batch rows whose fragments of ALL of K fit shared memory.  A CTA stages the
+// activations once, then walks over weight tiles blockIdx.x, + gridDim.x, ...  Every warp has a weight stream of its
+// own: of each 128 blocks of K it owns 16 consecutive ones (288 contiguous bytes of each of the tile's rows), copies
+// them with its own cp.async groups into a two-deep private ring and waits for nothing but its own copies, so the
+// weight stream of an SM does not stop for a tile's reduction or a CTA's prologue; the CTA meets only to add the eight
+// warps' sums of a tile.
+constexpr uint32_t kSliceBlocks = 16, kSlicePitch = kSliceBlocks * 18u + 16u;  // 19 vectors: rows 0..7 start 4 banks apart
+constexpr uint32_t kSliceSpan = kMmaWarps * kSliceBlocks;                      // blocks of K the eight slices cover
+template <int NMAT>
+__host__ __device__ inline size_t stream_shared_bytes(uint32_t blocks, uint32_t staged_rows) {
+  return (size_t)kMmaWarps * 2u * NMAT * kMmaRows * kSlicePitch + (size_t)blocks * staged_rows * 64u + (size_t)blocks * 32u +
+         (size_t)NMAT * kMmaWarps * kMmaRows * 32u;
+}
+
+template <int NMAT>
+__global__ void __launch_bounds__(kMmaWarps * 32, 2) q4_0_mma_stream_kernel(const __half* __restrict__ x, MmaProblem p) {
+  using namespace gemv;
+  extern __shared__ __align__(16) uint8_t shared[];
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, r = lane >> 2, c = lane & 3u;
+  const uint32_t blocks = p.k >> 5;
+  constexpr uint32_t kStageBytes = NMAT * kMmaRows * kSlicePitch;
+  const size_t row_bytes = (size_t)blocks * 18u;
+  uint4* const fragments = reinterpret_cast<uint4*>(shared + kMmaWarps * 2u * kStageBytes);
+  float* const bias = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(fragments) + (size_t)blocks * p.staged_rows * 64u);
+  float* const reduction = bias + (size_t)blocks * 8u;
+  const uint32_t ring_at = (uint32_t)__cvta_generic_to_shared(shared) + warp * 2u * kStageBytes;
+  const uint32_t fragments_at = (uint32_t)__cvta_generic_to_shared(fragments), bias_at = (uint32_t)__cvta_generic_to_shared(bias);
+
+  const uint32_t my_tiles = blockIdx.x < p.tiles_total ? (p.tiles_total - blockIdx.x + gridDim.x - 1u) / gridDim.x : 0u;
+  // this warp's slices of one row: blocks [span * kSliceSpan + warp * kSliceBlocks, + kSliceBlocks) while inside K
+  const uint32_t first_slice = warp * kSliceBlocks;
+  const uint32_t slices = blocks > first_slice ? (blocks - first_slice + kSliceSpan - 1u) / kSliceSpan : 0u;
+  const uint32_t total = my_tiles * slices;
+  // the matrix, its width and the first row of a tile
+  auto locate = [&](uint32_t tile, uint32_t& which, uint32_t& n, uint32_t& n0) {
+    which = 0;
+    if (NMAT == 1 && p.matrices == 3) which = tile >= p.first_tile[2] ? 2u : (tile >= p.first_tile[1] ? 1u : 0u);
+    n = which == 0u ? p.n[0] : which == 1u ? p.n[1] : p.n[2];
+    n0 = (tile - (which == 0u ? p.first_tile[0] : which == 1u ? p.first_tile[1] : p.first_tile[2])) * kMmaRows;
+  };
+  // slice `sequence` of this warp (tile sequence / slices, span sequence % slices) -> ring stage sequence % 2: one commit group
+  auto copy_slice = [&](uint32_t sequence) {
+    if (sequence < total) {
+      const uint32_t tile = blockIdx.x + (sequence / slices) * gridDim.x, start = (sequence % slices) * kSliceSpan + first_slice;
+      uint32_t which, n, n0;
+      locate(tile, which, n, n0);
+      const uint32_t vectors = (min(kSliceBlocks, blocks - start) * 18u) >> 4;  // of one row: 18, or 9 for a last half slice
+      const uint32_t target = ring_at + (sequence & 1u) * kStageBytes;
+      const uint8_t* matrix = which == 0u ? p.weight[0] : which == 1u ? p.weight[1] : p.weight[2];
+      uint32_t row = lane / vectors, vector = lane % vectors;
+      const uint32_t row_step = 32u / vectors, vector_step = 32u % vectors;
+      while (row < kMmaRows) {
+        const size_t source = (size_t)min(n0 + row, n - 1u) * row_bytes + (size_t)start * 18u + vector * 16u;  // rows past n re-read the last
+#pragma unroll
+        for (int a = 0; a < NMAT; ++a)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(target + (a * kMmaRows + row) * kSlicePitch + vector * 16u),
+                       "l"((NMAT == 2 ? p.weight[a] : matrix) + source)
+                       : "memory");
+        row += row_step;
+        vector += vector_step;
+        if (vector >= vectors) {
+          vector -= vectors;
+          ++row;
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  copy_slice(0);  // ahead of the predecessor's results
+  copy_slice(1);
+  grid_chain_prologue();
+  if (my_tiles == 0u) return;
+
+  // the activations of all of K, once
+  const uint32_t rows = p.m;
+#pragma unroll 2
+  for (uint32_t item = threadIdx.x; item < blocks * rows * 4u; item += kMmaWarps * 32) {
+    const uint32_t block = rows == 1u ? item >> 2 : (item >> 2) / rows, row = (item >> 2) - block * rows, quad = item & 3u;
+    float low_sum, high_sum;
+    fragments[(block * p.staged_rows + row) * 4u + quad] = fragment_of(x + (size_t)row * p.k + (size_t)block * 32u + 4u * quad, low_sum, high_sum);
+    low_sum += __shfl_xor_sync(0xffffffffu, low_sum, 1);
+    low_sum += __shfl_xor_sync(0xffffffffu, low_sum, 2);
+    high_sum += __shfl_xor_sync(0xffffffffu, high_sum, 1);
+    high_sum += __shfl_xor_sync(0xffffffffu, high_sum, 2);
+    if (quad == 0u) bias[block * 8u + row] = -(1032.0f * low_sum + 72.0f * high_sum);
+  }
+  __syncthreads();
+
+  uint32_t sequence = 0;
+  for (uint32_t mine = 0; mine < my_tiles; ++mine) {
+    float acc[NMAT][4];
+#pragma unroll
+    for (int a = 0; a < NMAT; ++a)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[a][i] = 0.0f;
+    for (uint32_t span = 0; span < slices; ++span, ++sequence) {
+      // this slice has landed: all of this lane's groups but the one after it
+      if (sequence + 1u < total) {
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+      } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+      }
+      __syncwarp();
+      const uint32_t start = span * kSliceSpan + first_slice, count = min(kSliceBlocks, blocks - start);
+      const uint32_t stage_at = ring_at + (sequence & 1u) * kStageBytes;
+      for (uint32_t pair = 0; 2u * pair < count; ++pair) {
+        const uint32_t block = start + 2u * pair;  // of the row: what the fragments are indexed by
+        block_pair_step<NMAT, kSlicePitch>(stage_at, pair, fragments_at + ((block * p.staged_rows + r) * 4u + c) * 16u, p.staged_rows * 64u,
+                              bias_at + (block * 8u + 2u * c) * 4u, r < rows, r, c, acc);
+      }
+      __syncwarp();  // every lane is done with the stage
+      copy_slice(sequence + 2u);
+    }
+    // the tile is summed: the eight warps' parts meet in shared memory, thread (row, column) adds them in warp order
+    uint32_t which, n, n0;
+    locate(blockIdx.x + mine * gridDim.x, which, n, n0);
+#pragma unroll
+    for (int a = 0; a < NMAT; ++a) {
+      float* part = reduction + ((a * kMmaWarps + warp) * kMmaRows) * 8u;
+      *reinterpret_cast<float2*>(part + r * 8u + 2u * c) = make_float2(acc[a][0], acc[a][1]);
+      *reinterpret_cast<float2*>(part + (r + 8u) * 8u + 2u * c) = make_float2(acc[a][2], acc[a][3]);
+    }
+    __syncthreads();
+    if (threadIdx.x < kMmaRows * 8) {
+      const uint32_t row = threadIdx.x >> 3, batch_row = threadIdx.x & 7u, column = n0 + row;
+      float value[NMAT];
+#pragma unroll
+      for (int a = 0; a < NMAT; ++a) {
+        value[a] = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; ++w) value[a] += reduction[((a * kMmaWarps + w) * kMmaRows + row) * 8u + batch_row];
+      }
+      if (batch_row < p.m && column < n) {
+        if (NMAT == 2) {
+          p.out[0][(size_t)batch_row * n + column] = gated_product(value[0], value[NMAT - 1], p.mode);
+        } else {
+          __half* out = which == 0u ? p.out[0] : which == 1u ? p.out[1] : p.out[2];
+          if (p.mode == 1) value[0] += __half2float(p.additive[column]);
+          if (p.mode == 2) value[0] += __half2float(p.additive[(size_t)batch_row * n + column]);
+          out[(size_t)batch_row * n + column] = __float2half_rn(value[0]);
+        }
+      }
+    }
+    __syncthreads();  // the reduction area may be overwritten
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
 // The tensor-core form takes rows of whole 16-byte vectors (K a multiple of 256) on 16-byte boundaries.
 // LLMOPT_CUDA_Q4_0_MMA=0 keeps every launch on the general kernels.
 bool mma_form_ok(uint32_t k, std::initializer_list<const void*> weights) {
@@ -540,6 +710,24 @@ bool mma_form_ok(uint32_t k, std::initializer_list<const void*> weights) {
 template <int NMAT>
 bool launch_mma_form(const KernelArgs& args, const __half* x, MmaProblem p, uint32_t tiles) {
   const uint32_t m = p.m;
+  p.tiles_total = tiles;
+  // up to 8 rows whose fragments of all of K fit beside the copy buffers: the stream form, a few CTAs per SM
+  static const bool stream_allowed = getenv("LLMOPT_CUDA_Q4_0_STREAM") == nullptr || getenv("LLMOPT_CUDA_Q4_0_STREAM")[0] != '0';
+  if (stream_allowed && m <= 8u && args.ctx != nullptr) {
+    p.staged_rows = m;
+    const size_t shared = stream_shared_bytes<NMAT>(p.k >> 5, p.staged_rows);
+    // two CTAs per SM where they fit, else one (still ahead of the one-shot form at 4 and 8 rows, level with it at K = 14336)
+    const uint32_t resident = shared * 2u <= (size_t)(220u << 10) ? 2u : 1u;
+    if (shared <= (size_t)(200u << 10)) {
+      auto kernel = q4_0_mma_stream_kernel<NMAT>;
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200u << 10)) == cudaSuccess) {
+        const uint32_t ctas = min(tiles, resident * (uint32_t)context_sm_count(args.ctx));
+        launch_kernel(args, kernel, dim3(ctas), dim3(kMmaWarps * 32), shared, x, p);
+        return true;
+      }
+      cudaGetLastError();
+    }
+  }
   p.chunk_buffers = (p.k >> 5) > kChunkBlocks ? 2u : 1u;
   p.staged_rows = m < 8u ? m : 8u;
   const size_t shared = mma_shared_bytes<NMAT>(p.chunk_buffers, p.staged_rows);
