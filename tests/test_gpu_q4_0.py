@@ -52,7 +52,9 @@ def test_reference_fixture_block_layout(runtime, oracle):
 @pytest.mark.parametrize("m,k,n,mode", [(1, 576, 1536, 0), (1, 4096, 512, 2), (2, 1024, 96, 1), (5, 1536, 333, 2),
                                         (16, 256, 40, 0), (37, 96, 17, 2),
                                         # the tensor-core form: two K chunks, a short last chunk, more than 32 rows
-                                        (1, 8192, 48, 0), (9, 4352, 32, 1), (33, 512, 64, 2), (8, 14336, 24, 0)])
+                                        (1, 8192, 48, 0), (9, 4352, 32, 1), (33, 512, 64, 2), (8, 14336, 24, 0),
+                                        # the stream form with a single half slice of K, and seven rows
+                                        (3, 256, 24, 1), (7, 2304, 50, 2)])
 def test_linear_matches_oracle(runtime, oracle, m, k, n, mode):
     from llmopt_b200 import dispatch
 
@@ -69,7 +71,7 @@ def test_linear_matches_oracle(runtime, oracle, m, k, n, mode):
                      label=f"q4_0 linear m={m} k={k} n={n} mode={mode}")
 
 
-@pytest.mark.parametrize("m,k,nq,nk,nv", [(1, 576, 576, 192, 192), (3, 1024, 256, 64, 64)])
+@pytest.mark.parametrize("m,k,nq,nk,nv", [(1, 576, 576, 192, 192), (3, 1024, 256, 64, 64), (2, 512, 40, 24, 8), (12, 768, 48, 16, 40)])
 def test_qkv_matches_oracle(runtime, oracle, m, k, nq, nk, nv):
     from llmopt_b200 import dispatch
 
