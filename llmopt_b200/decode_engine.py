@@ -310,18 +310,10 @@ class DecodeEngine:
             # flight on any rank when the prompt starts (true once every rank has read that step's token).
             if count * hidden * 4 > group.slot_bytes:
                 raise ValueError("the exchange slots are smaller than rows x hidden fp32 partial sums of this prompt")
-            if group.slot_count < 3:
-                raise ValueError("a tensor-parallel prompt needs at least three exchange slots")
+            from .tensor_parallel import plan_prompt_slots
+
             exchanges = 4 * len(config.layers) + 1  # a reduce and a gather exchange per row split, the argmax
-            decode = getattr(self, "_decode_slots", None) or [0]
-            slot_sequence = None
-            for start in range(group.slot_count):
-                candidate = [(start + index) % group.slot_count for index in range(exchanges)]
-                if candidate[0] != decode[-1] and candidate[-1] != decode[0]:
-                    slot_sequence = candidate
-                    break
-            if slot_sequence is None:
-                raise ValueError("no slot order fits between the decode steps' exchanges")
+            slot_sequence = plan_prompt_slots(group.slot_count, exchanges, getattr(self, "_decode_slots", None) or [0])
         exchange = 0
         commands = Batch(runtime)
         context = dispatch.Context(runtime, batch=commands)

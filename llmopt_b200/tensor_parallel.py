@@ -100,6 +100,21 @@ def plan_slots(exchanges: int) -> tuple:
     raise ValueError("no slot count up to 7 fits this number of exchanges")  # first at 421 exchanges
 
 
+def plan_prompt_slots(slot_count: int, exchanges: int, decode_slots: Sequence[int]) -> list:
+    """Slot of each exchange of a prompt pass that runs between decode steps whose exchanges use
+    ``decode_slots``: round-robin from a start chosen so that the first is not the decode step's last
+    slot and the last is not its first (adjacent exchanges then never share a slot, across the
+    border either).  Needs at least three slots."""
+    if slot_count < 3:
+        raise ValueError("a tensor-parallel prompt needs at least three exchange slots")
+    decode = list(decode_slots) or [0]
+    for start in range(slot_count):
+        candidate = [(start + index) % slot_count for index in range(exchanges)]
+        if not candidate or (candidate[0] != decode[-1] and candidate[-1] != decode[0]):
+            return candidate
+    raise ValueError("no slot order fits between the decode steps' exchanges")
+
+
 def check_slot_plan(slots: Sequence[int]) -> bool:
     """True when, replaying the step forever, two uses of a slot are never adjacent exchanges."""
     doubled = list(slots) + list(slots)

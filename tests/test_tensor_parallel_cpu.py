@@ -27,6 +27,47 @@ def test_slot_plan_never_reuses_a_slot_in_adjacent_exchanges():
     assert not tensor_parallel.check_slot_plan([0, 1, 2, 0])  # wraps 0 -> 0
 
 
+def test_prompt_slot_order_fits_between_decode_steps():
+    for slot_count in (3, 4, 5, 7):
+        for layers in (1, 2, 16, 32):
+            decode_count, decode = tensor_parallel.plan_slots(2 * layers + 1)
+            if decode_count > slot_count:
+                continue
+            slots = tensor_parallel.plan_prompt_slots(slot_count, 4 * layers + 1, decode)
+            assert len(slots) == 4 * layers + 1 and max(slots) < slot_count
+            sequence = list(decode) + slots + list(decode)  # a step, the prompt, a step
+            assert all(a != b for a, b in zip(sequence, sequence[1:])), (slot_count, layers)
+    with pytest.raises(ValueError):
+        tensor_parallel.plan_prompt_slots(2, 9, [0, 1])
+
+
+class _FakeBuffer:
+    pass
+
+
+def test_prompt_row_exchange_records():
+    import struct
+
+    regions = [_FakeBuffer() for _ in range(4)]
+    group = tensor_parallel.ExchangeGroup(1, 4, 8 * 4096 * 4, 3, regions)
+    seen = []
+    record = lambda **item: seen.append(item) or item
+    residual, output = _FakeBuffer(), _FakeBuffer()
+    first, second = group.sum_rows_records(record, slot=2, slice_slot=0, rows=8, width=4096, residual=residual, output=output)
+    assert [item["name"] for item in seen] == ["llmopt_tp_exchange_reduce_rows_f16", "llmopt_tp_exchange_gather_rows_f16"]
+    assert first["buffers"] == regions + [residual, output] and second["buffers"] == regions + [output]
+    assert first["parameters"] == second["parameters"] and len(first["parameters"]) == 28
+    assert struct.unpack("<7I", first["parameters"]) == (4, 1, 8, 4096, group.slot_offset(2), 1, group.slot_offset(0))
+    without = group.sum_rows_records(record, slot=1, slice_slot=2, rows=3, width=64, residual=None, output=output)[0]
+    assert struct.unpack("<7I", without["parameters"])[5] == 0 and without["buffers"][-2:] == [output, output]
+    with pytest.raises(ValueError):
+        group.sum_rows_records(record, slot=1, slice_slot=1, rows=8, width=4096, residual=None, output=output)
+    with pytest.raises(ValueError):
+        group.sum_rows_records(record, slot=0, slice_slot=1, rows=9, width=4096, residual=None, output=output)
+    with pytest.raises(ValueError):
+        group.slot_offset(3)
+
+
 def test_which_models_shard():
     assert all(tensor_parallel.shards(LLAMA3_8B, world) for world in (1, 2, 4, 8))
     assert not tensor_parallel.shards(LLAMA3_8B, 3) and not tensor_parallel.shards(LLAMA3_8B, 16)
