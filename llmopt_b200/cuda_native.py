@@ -297,6 +297,11 @@ class _RecordArray:
         return len(self.items)
 
 
+def pack_records(items: Sequence[DispatchItem]) -> _RecordArray:
+    """The C array of a dispatch list, for ``Batch.dispatch_recorded``; it keeps the list's buffers alive."""
+    return _RecordArray(items)
+
+
 class Runtime:
     """``Metal_native.t``: one context + the kernel library (lib/metal_native.mli:10-17)."""
 
@@ -422,6 +427,14 @@ class Batch:
         records = _RecordArray(self.pending)
         self._keep.append(records)
         self.pending = []
+        _check(load_library().llmopt_cuda_batch_dispatch_all(
+            self._handle, self.runtime._library, records.array, len(records)))
+
+    def dispatch_recorded(self, records: "_RecordArray") -> None:
+        """Appends a list packed earlier with ``pack_records`` (a dispatch list recorded once and
+        replayed, e.g. the prompt pass of a known length): no per-dispatch host work."""
+        self.flush()
+        self._keep.append(records)
         _check(load_library().llmopt_cuda_batch_dispatch_all(
             self._handle, self.runtime._library, records.array, len(records)))
 

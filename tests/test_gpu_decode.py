@@ -125,6 +125,39 @@ def test_prefill_path_then_decode_matches_oracle(runtime, layers, prompt_length)
     assert mismatches <= 1, f"{mismatches} near-tie picks differ"
 
 
+def test_a_replayed_prompt_plan_equals_a_fresh_pass(runtime):
+    """A second prompt of a length seen before replays the recorded dispatch list with new ids: first
+    token, hidden rows and the decode that follows are bit-identical to a fresh engine's pass over that
+    prompt (every buffer of the pass is fully rewritten)."""
+    from llmopt_b200.decode_engine import DecodeEngine
+    from llmopt_b200.model import random_weights, tiny_config
+
+    config = tiny_config(layers=("conv", "attention", "attention"), hidden=256, heads=4, kv_heads=2, head_dim=64,
+                         intermediate=512, vocabulary=2048)
+    weights = random_weights(config, seed=8, std=0.05)
+    length, steps = 90, 12
+    rng = np.random.default_rng(8)
+    first, second = (rng.integers(0, config.vocabulary, size=length).tolist() for _ in range(2))
+
+    def run(engine, prompt):
+        token = engine.prefill(prompt)
+        hidden = engine.prefill_hidden.buffer.to_numpy(np.float16, (length, config.hidden)).copy()
+        stream = [token]
+        for step in range(steps):
+            stream.append(engine.step([stream[-1]], length + step)[0])
+        return stream, hidden
+
+    reused = DecodeEngine(runtime, config, weights, batch=1, capacity=length + steps + 1)
+    run(reused, first)
+    recorded = reused.prefill_seconds[0]
+    stream, hidden = run(reused, second)  # the plan of `first`, the ids of `second`
+    assert reused.prefill_seconds[0] < recorded, "the second pass recorded its dispatches again"
+    fresh = DecodeEngine(runtime, config, weights, batch=1, capacity=length + steps + 1)
+    want_stream, want_hidden = run(fresh, second)
+    assert stream == want_stream
+    assert np.array_equal(hidden.view(np.uint16), want_hidden.view(np.uint16))
+
+
 def test_prefill_path_on_the_smollm2_shape_gives_the_stream_of_the_stepped_route(runtime):
     """SmolLM2-135M shape, 512-token prompt: prefill in one pass + 32 decode steps produce the token
     stream the oracle produced feeding the prompt token by token (tests/golden/decode_streams.npz):
