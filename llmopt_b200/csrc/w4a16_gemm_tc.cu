@@ -302,7 +302,7 @@ w4a16_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     ok = ok && !*abort_flag && barrier_wait(accumulator_full, 0u);
     if (!ok) give_up();
     {
-      // one verdict for all eight epilogue warps: the steps below synchronise among them
+      // one decision for all eight epilogue warps: the steps below synchronise among them
       uint32_t all_ok;
       asm volatile(
           "{\n\t.reg .pred p, q;\n\t"

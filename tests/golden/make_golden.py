@@ -21,7 +21,7 @@ def main(reference_root: str) -> None:
 
     torch.manual_seed(0)
     out = {}
-    # pack / unpack on random-init weights at the first BASELINE shape and a ragged one
+    # pack / unpack on random-init weights at the reference runtime test's own shape and a ragged one
     for tag, (n, k) in {"c1": (1536, 576), "small": (29, 128)}.items():
         weight = torch.randn(n, k) * 0.02
         packed, scale = q.pack_int4_weight(weight)
