@@ -115,6 +115,15 @@ def plan_prompt_slots(slot_count: int, exchanges: int, decode_slots: Sequence[in
     raise ValueError("no slot order fits between the decode steps' exchanges")
 
 
+def prompt_row_share(rows: int, world: int, rank: int) -> tuple:
+    """[first, last) of the prompt rows rank ``rank`` sums in the reduce-scatter exchange and hands
+    out in the all-gather exchange: ceil(rows / world) consecutive rows per rank, the last ranks
+    fewer or none (the partition ``llmopt_tp_exchange_reduce_rows_f16`` uses)."""
+    share = (rows + world - 1) // world
+    first = min(rank * share, rows)
+    return first, min(first + share, rows)
+
+
 def check_slot_plan(slots: Sequence[int]) -> bool:
     """True when, replaying the step forever, two uses of a slot are never adjacent exchanges."""
     doubled = list(slots) + list(slots)

@@ -45,6 +45,15 @@ class _FakeBuffer:
     pass
 
 
+def test_prompt_row_shares_cover_the_rows_once():
+    for rows in (1, 2, 5, 8, 70, 512):
+        for world in (1, 2, 4, 8):
+            shares = [tensor_parallel.prompt_row_share(rows, world, rank) for rank in range(world)]
+            assert shares[0][0] == 0 and shares[-1][1] == rows
+            assert all(a[1] == b[0] for a, b in zip(shares, shares[1:]))
+            assert max(hi - lo for lo, hi in shares) == (rows + world - 1) // world
+
+
 def test_prompt_row_exchange_records():
     import struct
 
@@ -138,5 +147,8 @@ def test_two_gloo_ranks_reproduce_the_unsharded_layer(tmp_path):
     results = [np.load(tmp_path / f"rank{rank}.npz") for rank in range(2)]
     assert np.array_equal(results[0]["hidden"], results[1]["hidden"])  # same bits on every rank
     assert int(results[0]["token"]) == int(results[1]["token"]) == int(results[0]["want_token"])
+    # prompt rows through the reduce-scatter / all-gather form of the exchange: same bits on both ranks, oracle's result
+    assert np.array_equal(results[0]["rows"].view(np.uint16), results[1]["rows"].view(np.uint16))
+    assert float(results[0]["rows_error"]) <= 2e-3
     error = float(results[0]["error"])
     assert error <= 2e-3, error

@@ -56,7 +56,36 @@ def main() -> None:
     best = max(gathered, key=lambda c: (float(c[0]), -float(c[1])))
     want_token, _, _ = oracle.w4a16_lm_head_argmax(out[:1], weights["final_norm"], weights["lm_head"][0],
                                                    weights["lm_head"][1], config.epsilon)
-    np.savez(os.environ["TP_OUT"], hidden=out, token=int(best[1]), want_token=int(want_token[0]), error=error)
+    # Prompt rows: the same row split as a reduce-scatter (this rank sums ITS share of the rows over every
+    # rank's fp32 partial, rank order, residual, one rounding) and an all-gather of the fp16 shares
+    rows = 5
+    prompt = rng.standard_normal((rows, config.hidden)).astype(np.float16)
+    want_rows, normed_rows, _ = oracle.w4a16_swiglu_ffn(prompt, prompt, whole["gate"][0], whole["gate"][1], whole["up"][0],
+                                                        whole["up"][1], whole["down"][0], whole["down"][1],
+                                                        whole["ffn_norm"], config.epsilon)
+    product_rows = oracle.w4a16_dual_swiglu(normed_rows, layer["gate"][0], layer["gate"][1], layer["up"][0], layer["up"][1])
+    partial_rows = torch.from_numpy(np.ascontiguousarray(
+        oracle.w4a16_linear_f64(product_rows, layer["down"][0], layer["down"][1]).astype(np.float32)))
+    partials = [torch.empty_like(partial_rows) for _ in range(world)]
+    dist.all_gather(partials, partial_rows)  # stands for the peer reads of the slot
+    first, last = tensor_parallel.prompt_row_share(rows, world, rank)
+    total = np.zeros((last - first, config.hidden), np.float32)
+    for part in partials:
+        total += part.numpy()[first:last]
+    # (the fp16 bits travel as int32: gloo has no 16-bit integer)
+    share = torch.from_numpy((total + prompt[first:last].astype(np.float32)).astype(np.float16).view(np.uint16).astype(np.int32))
+    padded = torch.zeros(((rows + world - 1) // world, config.hidden), dtype=torch.int32)
+    padded[:last - first] = share
+    shares = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(shares, padded)  # the gather exchange
+    out_rows = np.zeros((rows, config.hidden), np.float16)
+    for peer, piece in enumerate(shares):
+        lo, hi = tensor_parallel.prompt_row_share(rows, world, peer)
+        out_rows[lo:hi] = piece.numpy().astype(np.uint16).view(np.float16)[:hi - lo]
+    rows_error = (np.max(np.abs(out_rows.astype(np.float64) - want_rows.astype(np.float64))) /
+                  np.max(np.abs(want_rows.astype(np.float64))))
+    np.savez(os.environ["TP_OUT"], hidden=out, token=int(best[1]), want_token=int(want_token[0]), error=error,
+             rows=out_rows, rows_error=rows_error)
     dist.barrier()
     dist.destroy_process_group()
 
