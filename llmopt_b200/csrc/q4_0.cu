@@ -22,7 +22,8 @@
 // works on 16 weight rows at a time, copied to shared memory with 16-byte cp.async (the first copies before it
 // waits for its predecessor: weights do not depend on it), and its eight warps share out the blocks.  Up to 8
 // batch rows it is a stream (a few CTAs per SM walk over the tiles, every warp with a private two-deep ring of
-// its own K slices), beyond that a CTA per tile with K chunks of 4096 (up to 32 rows per pass).  A block is two mma.sync.m16n8k16: the low nibbles (elements 0..15)
+// its own K slices), beyond that a CTA per tile with K chunks of 4096 (up to 32 rows per pass).
+// A block is two mma.sync.m16n8k16: the low nibbles (elements 0..15)
 // as halves 1024 + u, the high nibbles (16..31), read in place, as 64 + u, one LOP3 per pair of weights; the
 // offsets 1032 and 72 (u - 8 is the weight) leave as a per-block term -(1032 sum(x low) + 72 sum(x high)) that
 // seeds the accumulator, and the block's fp32 sum is scaled by d.  The activations are staged once per CTA in
