@@ -96,7 +96,9 @@ int llmopt_cuda_register_alias(llmopt_cuda_library* library, const char* alias, 
  * operands, 12 stack slots.  A dispatch of `name` binds [input, weight, scale, bias_or_scale,
  * output, operand 0 ...] with the 20-byte linear parameter block and computes
  * half(expression) in fp32, like the generated kernel.  llmopt_b200/epilogue.py derives names
- * and programs from expression trees. */
+ * and programs from expression trees.  A name that extends llmopt_q4_0_linear_f16* binds the same program over the
+ * Q4_0-block product instead, with the buffer order of lib/metal_q4_0_epilogue_codegen.ml:7-31 ([input, weight,
+ * operand 0 .., output], the 16-byte quant-linear parameter block). */
 int llmopt_cuda_register_expr_epilogue(llmopt_cuda_library* library, const char* name, const void* program,
                                        size_t program_bytes, int operand_count);
 

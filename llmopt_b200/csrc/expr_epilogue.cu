@@ -169,4 +169,44 @@ int launch_w4a16_linear_expr(const KernelArgs& args) {
   return check_launch(args);
 }
 
+// The same over a Q4_0-block weight, with the buffer order of the reference's Q4_0 epilogue kernels
+// (Writeback.Epilogue, lib/metal_q4_0_epilogue_codegen.ml:7-31): [input, weight, operand 0 .., output] and the
+// 16-byte quant-linear parameter block {m, n, k, has_bias}; the flat bias does not exist in this form.
+int launch_q4_0_product_f32(const KernelArgs& args, const __half* x, const uint8_t* weight, float* out, uint32_t m, uint32_t n,
+                            uint32_t k);
+int launch_q4_0_linear_expr(const KernelArgs& args) {
+  const ExprProgram* program = args.ctx ? context_expr_program(args.ctx, args.name) : nullptr;
+  LLMOPT_REQUIRE(program != nullptr, "no expression program is registered under this name");
+  LLMOPT_REQUIRE(args.buffer_count == 3 + (int)program->operands, "unexpected buffer count for this expression epilogue");
+  LLMOPT_REQUIRE(args.param_bytes == 16, "expects 16 parameter bytes");
+  const uint32_t m = param_u32(args, 0), n = param_u32(args, 1), k = param_u32(args, 2);
+  LLMOPT_REQUIRE(m > 0 && n > 0 && k > 0 && k % 32 == 0 && ((uintptr_t)args.buffers[0] & 15u) == 0,
+                 "needs m, n > 0, k a positive multiple of 32 and a 16-byte aligned input");
+  const int output = 2 + (int)program->operands;
+  LLMOPT_REQUIRE(args.lengths[0] >= (size_t)m * k * 2 && args.lengths[1] >= (size_t)n * (k / 32) * 18 &&
+                     args.lengths[output] >= (size_t)m * n * 2,
+                 "input, weight or output buffer is too short");
+  ExprOperands operands = {};
+  for (uint32_t i = 0; i < program->operands; ++i) {
+    LLMOPT_REQUIRE(args.lengths[2 + i] >= (size_t)n * 2, "epilogue operand is shorter than n");
+    operands.pointer[i] = args.buffers[2 + i];
+  }
+  for (uint32_t pc = 0; pc < program->length;) {  // an fp32 operand must hold n floats
+    const uint8_t op = program->code[pc++];
+    if (op == kConst) pc += 4;
+    if (op == kRead) {
+      if (program->code[pc + 1]) LLMOPT_REQUIRE(args.lengths[2 + program->code[pc]] >= (size_t)n * 4, "fp32 epilogue operand is shorter than n");
+      pc += 2;
+    }
+  }
+  float* scratch = (float*)context_scratch(args.ctx, (size_t)m * n * sizeof(float), args.error);
+  if (scratch == nullptr) return 1;
+  if (int status = launch_q4_0_product_f32(args, (const __half*)args.buffers[0], (const uint8_t*)args.buffers[1], scratch, m, n, k))
+    return status;
+  const uint32_t total = m * n;
+  launch_kernel(args, expr_epilogue_kernel, dim3((total + 255) / 256), dim3(256), 0, (const float*)scratch,
+                (__half*)args.buffers[output], m, n, *program, operands);
+  return check_launch(args);
+}
+
 }  // namespace llmopt

@@ -158,7 +158,8 @@ template <int FORMAT>
 __global__ void __launch_bounds__(256) quant_linear_kernel(const __half* __restrict__ x,
                                                            const uint8_t* __restrict__ weight,
                                                            const __half* __restrict__ additive,
-                                                           __half* __restrict__ y, QuantLinearParams p) {
+                                                           __half* __restrict__ y, QuantLinearParams p,
+                                                           float* __restrict__ y_f32) {
   grid_chain_prologue();
   const uint32_t lane = threadIdx.x & 31u, col = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (col >= p.n) return;
@@ -173,6 +174,10 @@ __global__ void __launch_bounds__(256) quant_linear_kernel(const __half* __restr
       for (int r = 1; r < kRowTile; ++r)
         if (lane == (uint32_t)r) value = acc[r];
       const uint32_t row = row0 + lane;
+      if (y_f32 != nullptr) {  // the unrounded sums, for an epilogue that runs after this kernel
+        y_f32[(size_t)row * p.n + col] = value;
+        continue;
+      }
       if (p.mode == 1) value += __half2float(additive[col]);
       if (p.mode == 2) value += __half2float(additive[(size_t)row * p.n + col]);
       y[(size_t)row * p.n + col] = __float2half_rn(value);
@@ -295,6 +300,7 @@ struct MmaProblem {
   __half* out[3];
   uint32_t n[3], first_tile[3];  // columns and first CTA of every matrix
   const __half* additive;
+  float* out_f32;               // != null (one matrix, linear form): the unrounded sums [m, n] instead of the halves
   uint32_t chunk_buffers;       // 1 or 2
   uint32_t staged_rows;         // batch rows the activation staging is sized for (1..8)
   uint32_t tiles_total;         // 16-row tiles of all matrices
@@ -539,9 +545,13 @@ __global__ void __launch_bounds__(kMmaWarps * 32, NMAT == 1 ? 4 : 2) q4_0_mma_ke
         if (NMAT == 2) {
           p.out[0][(size_t)batch_row * n + column] = gated_product(value[0], value[NMAT - 1], p.mode);
         } else {
-          if (p.mode == 1) value[0] += __half2float(p.additive[column]);
-          if (p.mode == 2) value[0] += __half2float(p.additive[(size_t)batch_row * n + column]);
-          own_out[(size_t)batch_row * n + column] = __float2half_rn(value[0]);
+          if (p.out_f32 != nullptr) {
+            p.out_f32[(size_t)batch_row * n + column] = value[0];
+          } else {
+            if (p.mode == 1) value[0] += __half2float(p.additive[column]);
+            if (p.mode == 2) value[0] += __half2float(p.additive[(size_t)batch_row * n + column]);
+            own_out[(size_t)batch_row * n + column] = __float2half_rn(value[0]);
+          }
         }
       }
     }
@@ -686,9 +696,13 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) q4_0_mma_stream_kernel(cons
           p.out[0][(size_t)batch_row * n + column] = gated_product(value[0], value[NMAT - 1], p.mode);
         } else {
           __half* out = which == 0u ? p.out[0] : which == 1u ? p.out[1] : p.out[2];
-          if (p.mode == 1) value[0] += __half2float(p.additive[column]);
-          if (p.mode == 2) value[0] += __half2float(p.additive[(size_t)batch_row * n + column]);
-          out[(size_t)batch_row * n + column] = __float2half_rn(value[0]);
+          if (p.out_f32 != nullptr) {
+            p.out_f32[(size_t)batch_row * n + column] = value[0];
+          } else {
+            if (p.mode == 1) value[0] += __half2float(p.additive[column]);
+            if (p.mode == 2) value[0] += __half2float(p.additive[(size_t)batch_row * n + column]);
+            out[(size_t)batch_row * n + column] = __float2half_rn(value[0]);
+          }
         }
       }
     }
@@ -743,7 +757,8 @@ bool launch_mma_form(const KernelArgs& args, const __half* x, MmaProblem p, uint
     pass.m = min(m - row0, 8u * (uint32_t)kMaxRowTiles);
     for (uint32_t i = 0; i < 3; ++i)
       if (pass.out[i] != nullptr) pass.out[i] += (size_t)row0 * p.n[i];
-    if (NMAT == 1 && p.mode == 2) pass.additive += (size_t)row0 * p.n[0];
+    if (NMAT == 1 && p.mode == 2 && pass.additive != nullptr) pass.additive += (size_t)row0 * p.n[0];
+    if (pass.out_f32 != nullptr) pass.out_f32 += (size_t)row0 * p.n[0];
     launch_kernel(args, kernel, dim3(tiles), dim3(kMmaWarps * 32), shared, x + (size_t)row0 * p.k, pass);
   }
   return true;
@@ -776,7 +791,25 @@ static int launch_quant_linear(const KernelArgs& args) {
     if (launch_mma_form<1>(args, (const __half*)args.buffers[0], problem, (p.n + kMmaRows - 1) / kMmaRows)) return check_launch(args);
   }
   launch_kernel(args, quant_linear_kernel<FORMAT>, dim3((p.n + 7) / 8), dim3(256), 0, (const __half*)args.buffers[0],
-                (const uint8_t*)args.buffers[1], (const __half*)args.buffers[2], (__half*)args.buffers[3], p);
+                (const uint8_t*)args.buffers[1], (const __half*)args.buffers[2], (__half*)args.buffers[3], p, (float*)nullptr);
+  return check_launch(args);
+}
+
+// The unrounded Q4_0 product x W^T as fp32 [m, n], for an epilogue that runs as a kernel of its own
+// (the expression epilogues): the tensor-core form where the rows allow it, else the general kernel.
+int launch_q4_0_product_f32(const KernelArgs& args, const __half* x, const uint8_t* weight, float* out, uint32_t m, uint32_t n,
+                            uint32_t k) {
+  if (mma_form_ok(k, {weight})) {
+    MmaProblem problem = {};
+    problem.m = m, problem.k = k, problem.mode = 0, problem.matrices = 1;
+    problem.weight[0] = weight;
+    problem.n[0] = n;
+    problem.out_f32 = out;
+    if (launch_mma_form<1>(args, x, problem, (n + kMmaRows - 1) / kMmaRows)) return check_launch(args);
+  }
+  const QuantLinearParams p = {m, n, k, 0u};
+  launch_kernel(args, quant_linear_kernel<kQ4_0>, dim3((n + 7) / 8), dim3(256), 0, x, weight, (const __half*)nullptr,
+                (__half*)nullptr, p, out);
   return check_launch(args);
 }
 int launch_q4_0_linear(const KernelArgs& args) { return launch_quant_linear<kQ4_0>(args); }

@@ -85,6 +85,7 @@ struct ExprProgram {
 };
 const char* validate_expr_program(const uint8_t* code, size_t length, int operand_count);
 int launch_w4a16_linear_expr(const KernelArgs&);
+int launch_q4_0_linear_expr(const KernelArgs&);
 int launch_gated_delta_f32(const KernelArgs&);
 int launch_gated_delta_tm_f16(const KernelArgs&);
 int launch_triangular_recurrence(const KernelArgs&);
@@ -837,7 +838,9 @@ int llmopt_cuda_register_expr_epilogue(llmopt_cuda_library* library, const char*
   stored.length = (uint32_t)program_bytes;
   stored.operands = (uint32_t)operand_count;
   library->context->expr_programs[name] = stored;
-  library->launchers[name] = launch_w4a16_linear_expr;
+  // the base the digest name extends decides the product and the buffer order
+  const bool over_q4_0 = strncmp(name, "llmopt_q4_0_linear_f16", 22) == 0;
+  library->launchers[name] = over_q4_0 ? launch_q4_0_linear_expr : launch_w4a16_linear_expr;
   library->names.push_back(name);
   return LLMOPT_CUDA_OK;
 }

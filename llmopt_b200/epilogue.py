@@ -282,13 +282,14 @@ def compile_program(epilogue: Epilogue) -> tuple:
 
 
 def bind(runtime, base: str, epilogue: Epilogue) -> str:
-    """Makes the digest name of ``epilogue`` over the W4A16 linear ``base`` resolvable in
+    """Makes the digest name of ``epilogue`` over the W4A16 (or Q4_0-block) linear ``base`` resolvable in
     ``runtime``'s library and returns it: an alias of the matching built-in tagged kernel, or a
     registered expression program."""
     name = algebraic_kernel_name(base, epilogue)
     if runtime.has_function(name):
         return name
-    tag = matching_tag(epilogue)
+    # Q4_0-block bases (lib/metal_q4_0_epilogue_codegen.ml) have no built-in tagged kernels: always a program
+    tag = None if base.startswith("llmopt_q4_0_linear_f16") else matching_tag(epilogue)
     if tag is not None:
         runtime.register_alias(name, f"llmopt_w4a16_linear_f16_g64_epi_{tag}")
     else:

@@ -101,3 +101,47 @@ def test_gated_matches_oracle(runtime, oracle, activation, code):
                                          product=product, activation=activation)
     assert_close_f16(product.buffer.to_numpy(np.float16, (m, n)), oracle.q4_0_gated_linear(x, gate, up, code),
                      rel=3e-3, label=f"q4_0 gated {activation}")
+
+
+@pytest.mark.parametrize("m,k,n", [(3, 1024, 200), (2, 96, 40), (11, 512, 64)])
+def test_digest_named_epilogue_over_q4_0(runtime, oracle, m, k, n):
+    """A Q4_0 linear with an algebraic epilogue is named llmopt_q4_0_linear_f16<tactic>_<digest> and binds
+    [input, weight, epilogue inputs .., output] (Writeback.Epilogue, lib/metal_q4_0_epilogue_codegen.ml:7-31).
+    epilogue.bind registers the expression's program under that name; the result is the epilogue of the
+    unrounded Q4_0 sums, on the tensor-core form (K a multiple of 256) and on the general kernel."""
+    from llmopt_b200 import epilogue as ep, parameters
+    from llmopt_b200.cuda_native import Buffer
+
+    rng = np.random.default_rng(41 + k)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    blocks = _weights(rng, n, k)
+    up = rng.standard_normal(n).astype(np.float16)
+    ceiling = rng.uniform(0.2, 2.0, size=n).astype(np.float32)
+    # the unrounded sums from the raw blocks: w = d (q - 8), low nibbles first
+    raw = blocks.reshape(n, k // 32, 18)
+    d = raw[:, :, :2].copy().view(np.float16).astype(np.float64)  # [n, blocks, 1]
+    quants = raw[:, :, 2:].astype(np.int32)
+    q = np.concatenate([(quants & 15) - 8, (quants >> 4) - 8], axis=2).astype(np.float64)
+    acc = x.astype(np.float64) @ (d * q).reshape(n, k).T
+    base = "llmopt_q4_0_linear_f16_x8"
+    tree = ep.Triop("clamp", ep.Binop("add", ep.Binop("mul", ep.Unop("silu", ep.ACC), ep.Read(ep.Value(4))), ep.Const(0.5)),
+                    ep.Const(-1.0), ep.Read(ep.Value(9, "f32")))
+    name = ep.bind(runtime, base, ep.of_expr(tree))
+    assert name.startswith(base + "_") and runtime.has_function(name)
+    out = Buffer.of_array(runtime, np.full((m, n), np.nan, np.float16))
+    runtime.dispatch(name, buffers=[Buffer.of_array(runtime, x), Buffer.of_array(runtime, blocks), Buffer.of_array(runtime, up),
+                                    Buffer.of_array(runtime, ceiling), out],
+                     parameters=parameters.u32s([m, n, k, 0]), grid=(256, 1, 1))
+    want = np.clip((acc / (1 + np.exp(-acc))) * up.astype(np.float64) + 0.5, -1.0, ceiling.astype(np.float64))
+    assert_close_f16(out.to_numpy(np.float16, (m, n)), want, label=f"q4_0 expression epilogue m={m} k={k}")
+    # a tagged form has no built-in kernel over this base: it is a program as well
+    gated = ep.bind(runtime, base, ep.tagged("silu_mul", ep.Value(0)))
+    out = Buffer.of_array(runtime, np.full((m, n), np.nan, np.float16))
+    runtime.dispatch(gated, buffers=[Buffer.of_array(runtime, x), Buffer.of_array(runtime, blocks), Buffer.of_array(runtime, up), out],
+                     parameters=parameters.u32s([m, n, k, 0]), grid=(256, 1, 1))
+    assert_close_f16(out.to_numpy(np.float16, (m, n)), (acc / (1 + np.exp(-acc))) * up.astype(np.float64),
+                     label="q4_0 silu_mul epilogue")
+    from llmopt_b200.cuda_native import NativeError
+
+    with pytest.raises(NativeError, match="buffer count"):
+        runtime.dispatch(gated, buffers=[out] * 5, parameters=parameters.u32s([m, n, k, 0]), grid=(256, 1, 1))
